@@ -1,0 +1,322 @@
+#!/usr/bin/env python
+"""GPT-J-6B decode benchmark of the B200-native path (and its CPU reference arm).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl mtj|reference]
+
+One "step" is one decode step (one generated token per sequence) of the
+GPT-J-6B architecture at a full sliding window (2047 cached tokens), batch 1,
+greedy sampling, bf16 random-init N(0, 0.02) weights, after a prefill of a
+1 x 2048 synthetic prompt.  Prints ONE JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+PKG = os.path.join(ROOT, "mesh-transformer-jax_b200")
+for _p in (ROOT, PKG):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+METRIC = "gptj6b_decode_tokens_per_s"
+UNIT = "tokens/s"
+
+GPTJ_6B = {
+    "layers": 28, "d_model": 4096, "n_heads": 16, "n_vocab": 50400,
+    "norm": "layernorm", "pe": "rotary", "pe_rotary_dims": 64,
+    "seq": 2048, "cores_per_replica": 1, "per_replica_batch": 1,
+}
+
+
+def workload_config(args, n_gpus):
+    return {
+        "workload": "GPT-J-6B (L28 d4096 h16 dh256 rot64 ff16384 V50400) bf16 random-init; prefill 1x2048 "
+                    "uniform-random ids, then greedy decode at a full 2047-token sliding window",
+        "batch": args.batch, "window": GPTJ_6B["seq"] - 1, "parallelism": f"mp{n_gpus}",
+        "l2": "every step streams 11.7 GB of weights (>> 126 MB L2), no flush needed",
+    }
+
+
+# ------------------------------------------------------------------ clocks ----
+class ClockSampler:
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index=0):
+        self.samples, self.proc, self.index = [], None, index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append((time.time(), line.strip()))
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self, t0, t1):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ts, line in self.samples:
+            if ts < t0 or ts > t1 + 0.15:
+                continue
+            f = [x.strip() for x in line.split(",")]
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# --------------------------------------------------------------- reference ----
+def run_reference(args):
+    """The reference's algorithm on the host cores (CPU restatement: the
+    reference's own JAX code cannot be imported without jax/haiku)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import cpu_baseline
+    steps, warmup = max(1, min(args.steps, 3)), max(1, min(args.warmup, 1))
+    r = cpu_baseline.decode_tokens_per_s(GPTJ_6B, steps=steps, warmup=warmup, batch=args.batch)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": r["value"], "unit": UNIT, "n_gpus": args.gpus,
+        "steps": steps, "warmup": warmup, "ms_per_step": 1e3 * r["seconds"] / steps,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": workload_config(args, args.gpus),
+        "cpu_baseline": {"value": r["value"], "unit": UNIT, "cores": r["cores"], "kind": "port",
+                         "sample": r["sample"]},
+        "e2e": {"value": r["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------- mtj ----
+def decode_bytes_per_step(cfg, batch, ctx, mp=1):
+    """Algorithmic HBM bytes of one decode step, whole model (bf16)."""
+    L, d, V = cfg["layers"], cfg["d_model"], cfg["n_vocab"]
+    weights = 2 * (L * (12 * d * d + 5 * d + 2 * d) + d * V + V + 2 * d)
+    kv = batch * ctx * L * 2 * d * 2 + batch * L * 2 * d * 2 + batch * d * 2
+    return weights + kv
+
+
+def build_network(cfg, device, rank):
+    """Random-init N(0, 0.02) bf16 weights generated on the device leaf by leaf."""
+    import torch
+    from mesh_transformer._runtime import param_shapes
+    from mesh_transformer.transformer_shard import CausalTransformer
+    net = CausalTransformer(dict(cfg), device=device, init_weights=False)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(1234 + rank)
+    params = {}
+    for mod, leaves in param_shapes(cfg).items():
+        out = {}
+        for leaf, shape in leaves.items():
+            if leaf == "scale":
+                t = torch.ones((1,) + shape, dtype=torch.bfloat16, device=device)
+            elif leaf in ("offset", "b"):
+                t = torch.zeros((1,) + shape, dtype=torch.bfloat16, device=device)
+            else:
+                t = (torch.randn((1,) + shape, generator=gen, device=device, dtype=torch.float32) * 0.02
+                     ).to(torch.bfloat16)
+            out[leaf] = t
+        params[mod] = out
+    net.state = {"params": params, "step": 0}
+    return net
+
+
+def run_mtj(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    import __graft_entry__ as ge
+    if rank == 0:
+        ge.build()
+    if world > 1:
+        dist.barrier()
+
+    cfg = dict(GPTJ_6B, cores_per_replica=world)
+    seq, B = cfg["seq"], args.batch
+    net = build_network(cfg, device, rank)
+    rt = net._runtime(B, args.steps * 3 + args.warmup * 3 + 8)
+    net.state = None               # the packed copy in the arena is what runs
+    net._dirty = False
+    torch.cuda.empty_cache()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    rng = np.random.Generator(np.random.PCG64(0))
+    ctx = rng.integers(0, cfg["n_vocab"], size=(B, seq)).astype(np.uint32)
+    ctx_dev = torch.from_numpy(ctx.view(np.int32)).to(device)
+    lens = [seq] * B
+
+    # ---- prefill (reported beside the headline) ----
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    rt.prefill(ctx_dev, lens)
+    barrier()
+    e0.record()
+    rt.prefill(ctx_dev, lens)
+    e1.record()
+    barrier()
+    prefill_ms = e0.elapsed_time(e1)
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+
+    # ---- device-resident decode: the headline `value` ----
+    tok_out = torch.empty((B,), dtype=torch.int32, device=device)
+    for _ in range(args.warmup):
+        rt.decode_step(None, tok_out, None, greedy=True)
+    barrier()
+    launches0 = rt.launch_count()
+    t_wall0 = time.time()
+    e0.record()
+    for _ in range(args.steps):
+        rt.decode_step(None, tok_out, None, greedy=True)
+    e1.record()
+    barrier()
+    t_wall1 = time.time()
+    launches = rt.launch_count() - launches0
+    ms = torch.tensor([e0.elapsed_time(e1)], device=device)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_total = float(ms.item())
+
+    # ---- end to end: host token in, host token out, every step ----
+    pin_in = torch.empty((B,), dtype=torch.int32).pin_memory()
+    pin_out = torch.empty((B,), dtype=torch.int32).pin_memory()
+    tok_in = torch.empty((B,), dtype=torch.int32, device=device)
+    pin_in.copy_(tok_out.cpu())
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        tok_in.copy_(pin_in, non_blocking=True)
+        rt.decode_step(tok_in, tok_out, None, greedy=True)
+        pin_out.copy_(tok_out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        pin_in.copy_(pin_out)
+    e1.record()
+    barrier()
+    ms2 = torch.tensor([e0.elapsed_time(e1)], device=device)
+    if world > 1:
+        dist.all_reduce(ms2, op=dist.ReduceOp.MAX)
+    e2e_ms_total = float(ms2.item())
+
+    # ---- per-family kernel time for the roofline (separate pass, events between launches) ----
+    rt.profile_enable(True)
+    n_prof = min(args.steps, 32)
+    for _ in range(n_prof):
+        rt.decode_step(None, tok_out, None, greedy=True)
+    prof = rt.profile_read()
+    rt.profile_enable(False)
+    rt.check_device_status()
+    if rank == 0:
+        sampler.stop()
+
+    if rank != 0:
+        return
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
+    peak_kind = "measured" if "hbm_gbs" in peaks else "fallback"
+
+    d, dl, ffl = cfg["d_model"], cfg["d_model"] // world, 4 * cfg["d_model"] // world
+    inproj_bytes = (3 * dl + ffl) * d * 2 + ffl * 4 + 2 * d * 4 + B * (d * 4 + dl * 4 + ffl * 4 + 2 * dl * 2)
+    ip_ms, ip_n = prof["in_proj"]
+    ip_avg_ms = ip_ms / max(ip_n, 1)
+    achieved = inproj_bytes / (ip_avg_ms * 1e-3) / 1e9 if ip_n else None
+    fam = {k: {"ms_per_launch": v[0] / max(v[1], 1), "launches": v[1]} for k, v in prof.items()}
+
+    ms_step = ms_total / args.steps
+    value = B * args.steps / (ms_total * 1e-3)
+    step_bytes = decode_bytes_per_step(cfg, B, seq - 1)
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(args, world),
+        "e2e": {"value": B * args.steps / (e2e_ms_total * 1e-3), "unit": UNIT,
+                "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B},
+        "gpu_launches": launches,
+        "clocks": sampler.summary(t_wall0, t_wall1),
+        "roofline": {"bound": "hbm", "kernel": "gemv_kernel<in-proj> (LN + [Q|K|V|FF-in] GEMV, RoPE/GELU/KV epilogue)",
+                     "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
+                     "frac": (achieved / hbm_peak) if achieved else None, "traffic": None,
+                     "peak_source": f"of {peak_kind}", "algorithmic_bytes_per_launch": inproj_bytes,
+                     "ms_per_launch": ip_avg_ms},
+        "kernel_families": fam,
+        "step_hbm": {"algorithmic_bytes_per_step": step_bytes, "achieved_gbs": step_bytes / (ms_step * 1e-3) / 1e9,
+                     "frac_of_peak": step_bytes / (ms_step * 1e-3) / 1e9 / hbm_peak / world},
+        "prefill": {"tokens_per_s": B * (seq - 1) / (prefill_ms * 1e-3), "ms": prefill_ms, "tokens": B * (seq - 1)},
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        from oracle import cpu_baseline
+        r = cpu_baseline.decode_tokens_per_s(GPTJ_6B, steps=2, warmup=1, batch=1)
+        line["cpu_baseline"] = {"value": r["value"], "unit": UNIT, "cores": r["cores"], "kind": "port",
+                                "sample": r["sample"]}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="mtj", choices=["mtj", "reference"])
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_mtj(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,159 @@
+/*
+ * libmtj_b200 -- C ABI of the B200-native GPT-J forward / eval / decode path.
+ *
+ * The reference (kingoflolz/mesh-transformer-jax) has no FFI boundary: its hot
+ * path is Python traced by JAX.  This ABI sits underneath a Python host layer
+ * that mirrors the reference classes; each entry point cites the reference
+ * code whose work it performs (paths relative to the reference project).
+ *
+ * Conventions
+ *   - every function returns an int32 status (MTJ_OK == 0); nothing aborts,
+ *     traps or throws; mtj_last_error() gives a message for the last failure;
+ *   - all pointers named *_dev are device pointers owned by the caller; the
+ *     library allocates no device memory: weights and workspace are carved
+ *     from two caller-provided arenas;
+ *   - all kernels are launched on the caller's stream; no entry point
+ *     synchronises the device unless its comment says so;
+ *   - one handle per GPU / per rank; a handle is used from one thread at a time.
+ */
+#ifndef MTJ_B200_H_
+#define MTJ_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct mtj_handle mtj_handle;
+typedef void* mtj_stream;              /* a cudaStream_t */
+
+enum {
+  MTJ_OK = 0,
+  MTJ_ERR_INVALID = 1,        /* bad argument / unsupported shape            */
+  MTJ_ERR_STATE = 2,          /* call order (arena not bound, no prefill...) */
+  MTJ_ERR_CUDA = 3,           /* a CUDA runtime call failed                  */
+  MTJ_ERR_UNSUPPORTED = 4,    /* config outside the GPT-J path               */
+  MTJ_ERR_TIMEOUT = 5,        /* a bounded device-side wait ran out          */
+  MTJ_ERR_COMM = 6            /* collective / peer set-up failed             */
+};
+
+enum { MTJ_F32 = 0, MTJ_BF16 = 1 };
+
+/* Keys of the reference's config JSON that the path reads
+ * (configs/6B_roto_256.json:1-12; layers.py:168-170,232-245,548-549;
+ * transformer_shard.py:24-26,264-265).  norm must be "layernorm" and pe
+ * "rotary"; the host layer rejects anything else before calling in. */
+typedef struct mtj_config {
+  int32_t layers;
+  int32_t d_model;
+  int32_t n_heads;
+  int32_t n_vocab;
+  int32_t pe_rotary_dims;
+  int32_t seq;
+  int32_t cores_per_replica;   /* tensor-parallel degree (mp)                 */
+  int32_t rank;                /* this shard's index on the "shard" axis      */
+  int32_t max_batch;           /* sequences resident in the KV cache          */
+  int32_t max_gen;             /* generated tokens per generate() call        */
+  int32_t max_rows;            /* token rows processed per forward chunk      */
+  int32_t reserved;
+} mtj_config;
+
+const char* mtj_last_error(void);
+int32_t mtj_version(void);
+
+/* CausalTransformerShard.__init__ (transformer_shard.py:21-45): validates the
+ * same divisibility conditions the reference asserts (layers.py:172,238-239,552). */
+int32_t mtj_create(const mtj_config* cfg, mtj_handle** out);
+int32_t mtj_destroy(mtj_handle* h);
+
+/* Arena sizes for this handle's config, then binding of caller memory. */
+int64_t mtj_weights_bytes(const mtj_handle* h);
+int64_t mtj_workspace_bytes(const mtj_handle* h);
+int32_t mtj_bind_arenas(mtj_handle* h, void* weights_dev, int64_t weights_bytes,
+                        void* workspace_dev, int64_t workspace_bytes, mtj_stream s);
+
+/* Loads one per-shard leaf of CausalTransformer.state["params"]
+ * (transformer_shard.py:184-188; names and layouts as to_hf_weights.py:160-173:
+ * "<module>/<leaf>" with module in {embedding_shard, layer_<i>, projection_shard}
+ * and leaf in {linear[_k]/w, linear[_k]/b, replicated_layer_norm/scale|offset}).
+ * src_dev holds this shard's slice in the reference layout ([in, out] for w);
+ * it is repacked to bf16 into the weight arena (move_xmap's cast,
+ * transformer_shard.py:250-253) and may be freed after the stream has run. */
+int32_t mtj_load_param(mtj_handle* h, const char* name, const void* src_dev,
+                       int32_t dtype, int32_t ndim, const int64_t* shape, mtj_stream s);
+
+/* Tensor-parallel plumbing standing in for jax.lax.psum / all_gather on the
+ * "shard" axis (util.py:134-136; layers.py:193,313,565).  `nccl_comm` is an
+ * ncclComm_t created by the host for (rank, cores_per_replica). */
+int32_t mtj_set_nccl(mtj_handle* h, void* nccl_comm);
+
+/* generate_initial (transformer_shard.py:74-95) for `batch` left-padded
+ * contexts: prefills ctx[:, :-1] into the KV cache, keeps ctx[:, -1] as the
+ * first decode input.  ctx_dev: [batch, seq] uint32; ctx_length_host: [batch]
+ * (number of real tokens, >= 1).  Host-synchronous only in page set-up. */
+int32_t mtj_prefill(mtj_handle* h, const uint32_t* ctx_dev, const uint32_t* ctx_length_host,
+                    int32_t batch, mtj_stream s);
+
+/* One step of the generate scan (transformer_shard.py:198-210): generate_once
+ * then the sampler.  tokens_in_dev may be NULL (use the previous step's
+ * sample / the held-back last prompt token).  top_p/temp: [batch] f32 device;
+ * uniforms_dev: [batch, n_vocab] f32 or NULL when every top_p == 0 (greedy).
+ * Outputs: tokens_out_dev [batch] uint32 (may be NULL),
+ * logits_out_dev [batch, n_vocab] f32 (may be NULL). */
+int32_t mtj_decode_step(mtj_handle* h, const uint32_t* tokens_in_dev,
+                        const float* top_p_dev, const float* temp_dev,
+                        const float* uniforms_dev, int32_t greedy,
+                        uint32_t* tokens_out_dev, float* logits_out_dev, mtj_stream s);
+
+/* CausalTransformerShard.loss (transformer_shard.py:47-72, :123-132):
+ * obs/target [batch, T] uint32 device, ctx_length_host [batch];
+ * all_loss_out_dev [batch, T] f32, correct_out_dev [batch, T] uint8. */
+int32_t mtj_eval_loss(mtj_handle* h, const uint32_t* obs_dev, const uint32_t* target_dev,
+                      const uint32_t* ctx_length_host, int32_t batch, int32_t T,
+                      float* all_loss_out_dev, uint8_t* correct_out_dev, mtj_stream s);
+
+/* Full-sequence logits of the last `n_last` positions (proj(x),
+ * transformer_shard.py:95): logits_out_dev [batch, n_last, n_vocab/mp] f32. */
+int32_t mtj_forward_logits(mtj_handle* h, const uint32_t* obs_dev, const uint32_t* ctx_length_host,
+                           int32_t batch, int32_t T, int32_t n_last,
+                           float* logits_out_dev, mtj_stream s);
+
+/* nucleaus_sample (sampling.py:10-44): logits [rows, vocab] f32, uniforms
+ * [rows, vocab] f32 in (0,1), top_p/temp [rows]; scratch from
+ * mtj_sample_scratch_bytes(rows, vocab). */
+int64_t mtj_sample_scratch_bytes(int32_t rows, int32_t vocab);
+int32_t mtj_sample_top_p(const float* logits_dev, const float* uniforms_dev,
+                         const float* top_p_dev, const float* temp_dev,
+                         int32_t rows, int32_t vocab, void* scratch_dev, int64_t scratch_bytes,
+                         uint32_t* tokens_out_dev, mtj_stream s);
+
+/* Counters for the benchmark: kernels launched by this handle so far. */
+int64_t mtj_launch_count(const mtj_handle* h);
+
+/* Optional kernel-family timing for the benchmark's roofline figure: while
+ * enabled, every launch of the four dominant families is bracketed by CUDA
+ * events on the caller's stream (up to 64 steps' worth between reads).
+ * mtj_profile_read synchronises the stream, fills ms_sum[MTJ_FAMILY_COUNT] /
+ * count[MTJ_FAMILY_COUNT] and clears the record.  No reference counterpart. */
+enum { MTJ_FAMILY_INPROJ = 0, MTJ_FAMILY_ATTN = 1, MTJ_FAMILY_OUTPROJ = 2, MTJ_FAMILY_LOGITS = 3,
+       MTJ_FAMILY_COUNT = 4 };
+int32_t mtj_profile_enable(mtj_handle* h, int32_t on);
+int32_t mtj_profile_read(mtj_handle* h, double* ms_sum, int64_t* count, mtj_stream s);
+
+/* Reads (and clears) the device-side error word of this handle; synchronises
+ * the stream.  MTJ_ERR_TIMEOUT if a bounded wait in a kernel ran out. */
+int32_t mtj_check_device_status(mtj_handle* h, mtj_stream s);
+
+/* Unit entry points: one per kernel family, for parity tests ---------------- */
+
+/* EmbeddingShard.__call__ (layers.py:187-193), local part: rows of this
+ * shard's table for ids in its range (else 0) plus this shard's bias.
+ * Also returns LayerNorm statistics (mean, rstd) per row when mp == 1. */
+int32_t mtj_k_embed(mtj_handle* h, const uint32_t* ids_dev, int32_t rows,
+                    float* x_out_dev, float* stats_out_dev, mtj_stream s);
+
+#ifdef __cplusplus
+}
+#endif
+#endif  /* MTJ_B200_H_ */

@@ -1,0 +1,82 @@
+// Shared device helpers for the sm_100a kernels of libmtj_b200.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace mtj {
+
+constexpr int kPageTokens = 64;          // tokens per KV page
+constexpr int kWarp = 32;
+
+// Device-side error word bits (one word per handle, read by mtj_check_device_status).
+constexpr uint32_t kDevErrTimeout = 1u;
+constexpr uint32_t kDevErrBadIndex = 2u;
+
+// 16-byte streaming load of read-only data that is touched once per pass
+// (weights, KV pages): bypass L1 so the activations stay resident there.
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint32_t ld_stream4(const void* p) {
+  uint32_t v;
+  asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
+}
+
+// bf16 pair packed in a 32-bit word -> two floats (bf16 is the top half of fp32).
+__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+
+__device__ __forceinline__ void unpack8(const uint4& v, float* f) {
+  f[0] = bf16_lo(v.x); f[1] = bf16_hi(v.x);
+  f[2] = bf16_lo(v.y); f[3] = bf16_hi(v.y);
+  f[4] = bf16_lo(v.z); f[5] = bf16_hi(v.z);
+  f[6] = bf16_lo(v.w); f[7] = bf16_hi(v.w);
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&t);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// jax.nn.gelu's default tanh approximation.
+__device__ __forceinline__ float gelu_tanh(float x) {
+  const float c = 0.7978845608028654f;   // sqrt(2/pi)
+  return 0.5f * x * (1.0f + tanhf(c * (x + 0.044715f * x * x * x)));
+}
+
+// Programmatic dependent launch: a kernel launched with the programmatic
+// stream-serialisation attribute may start while its predecessor drains; it
+// must not touch the predecessor's outputs before pdl_wait().
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+// Physical location of (page-table row, absolute position) in a KV pool laid
+// out [page][head][kPageTokens][d_head].
+__device__ __forceinline__ size_t kv_offset(const int32_t* __restrict__ table_row, int ring_pages,
+                                            int heads, int d_head, int head, int pos) {
+  const int slot = (pos / kPageTokens) % ring_pages;
+  const int page = table_row[slot];
+  return ((static_cast<size_t>(page) * heads + head) * kPageTokens + (pos % kPageTokens)) *
+         static_cast<size_t>(d_head);
+}
+
+}  // namespace mtj

@@ -1,0 +1,119 @@
+// Host-side launcher interface of the sm_100a kernels (internal to libmtj_b200).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace mtj {
+
+// Rows of a forward chunk: row m belongs to sequence b0 + m / Tc and sits at
+// absolute position pos0 + m % Tc, where pos0 = *pos0_dev when that pointer is
+// set (decode: the step counter lives on the device so that a captured graph
+// can be replayed) and pos0_host otherwise (prefill / eval).
+struct RowMap {
+  int b0;
+  int Tc;
+  int pos0_host;
+  const int32_t* pos0_dev;
+};
+
+struct KvCache {
+  __nv_bfloat16* kpool;        // [pages][heads][kPageTokens][d_head], one layer
+  __nv_bfloat16* vpool;
+  const int32_t* page_table;   // [batch][ring_pages]
+  int ring_pages;
+  const int32_t* pad;          // [batch] first valid absolute position
+};
+
+enum GemvEpilogue { kEpiInProj = 0, kEpiOut = 1, kEpiLogits = 2 };
+
+struct GemvArgs {
+  // y[m, n] = sum_k W[n, k] * act(x[m, k]);  W is bf16 [N, K] (K contiguous).
+  const __nv_bfloat16* W;
+  int N, K, M;
+  const float* x;              // [M, ldx] fp32
+  int ldx;
+  // LayerNorm prologue (in-proj and logits): act(x) = scale*rstd*(x-mean)+offset
+  const float* ln_scale;
+  const float* ln_offset;
+  const float* stats;          // [M, 2] = (mean, rstd)
+  RowMap rows;
+  // in-proj epilogue: N = 3*dl + ffl laid out [Q | K | V | FF-in]
+  int dl, ffl, d_head, heads, rot;
+  const float2* sincos;        // [positions][rot/2] = (sin, cos)
+  const float* b_ff;           // [ffl]
+  float* q_out;                // [M, dl]
+  float* act2;                 // [M, dl + ffl]: attention vector | gelu(ff)
+  KvCache kv;
+  // out-proj epilogue: out = acc + bias (+ residual); stats of the finished rows
+  const float* bias;           // [N]
+  const float* residual;       // [M, N] or null
+  float* out;                  // [M, N]
+  float* stats_out;            // [M, 2] or null
+  uint32_t* counters;          // [ceil(M / tile)] zero-initialised, self-resetting
+  // logits epilogue: logits[m, n] = acc + bias[n]
+  float* logits;
+  int ld_logits;
+  const int32_t* row_select;   // optional [M]: source row of x / stats for output row m
+};
+
+cudaError_t launch_gemv(GemvEpilogue epi, const GemvArgs& a, cudaStream_t s, bool pdl);
+
+struct EmbedArgs {
+  // id of row m = ids[(rows.b0 + m / rows.Tc) * ids_ld + rows.pos0_host + m % rows.Tc]
+  const uint32_t* ids;
+  int ids_ld;
+  RowMap rows;
+  int M, d, vocab_local, vocab_start;
+  const __nv_bfloat16* table;  // [vocab_local, d]
+  const float* bias;           // [d]
+  float* x;                    // [M, d]
+  float* stats;                // [M, 2] or null
+};
+cudaError_t launch_embed(const EmbedArgs& a, cudaStream_t s, bool pdl);
+
+struct DecodeAttnArgs {
+  const float* q;              // [B, heads*d_head] rotated, unscaled
+  KvCache kv;
+  int B, heads, d_head, window;  // window = seq - 1 key slots
+  const int32_t* cur_dev;      // absolute position of the query token
+  int split_tokens;            // keys per split (multiple of 8)
+  int max_splits;              // stride of the partial buffers
+  int grid_splits;             // blocks launched per (sequence, head) >= ceil(window / split_tokens)
+  float* part_o;               // [B, heads, max_splits, d_head]
+  float* part_ml;              // [B, heads, max_splits, 2]
+  uint32_t* counters;          // [B*heads] zero-initialised, self-resetting
+  float* out;                  // act2 base: out[b*ld_out + head*d_head + j]
+  int ld_out;
+};
+cudaError_t launch_decode_attn(const DecodeAttnArgs& a, cudaStream_t s, bool pdl);
+
+struct PrefillAttnArgs {
+  const float* q;              // [M, heads*d_head] rotated, unscaled
+  KvCache kv;
+  RowMap rows;
+  int M, heads, d_head;
+  const int32_t* key_limit;    // optional [batch]: keys with pos > limit are masked (eval ctx mask)
+  float* out;
+  int ld_out;
+};
+cudaError_t launch_prefill_attn(const PrefillAttnArgs& a, cudaStream_t s);
+
+struct ArgmaxArgs {
+  const float* logits;         // [B, V]
+  int B, V;
+  uint32_t* tokens;            // [B]
+  uint32_t* tokens_copy;       // optional second destination
+  int32_t* cur_dev;            // incremented by one after the step (may be null)
+};
+cudaError_t launch_argmax(const ArgmaxArgs& a, cudaStream_t s, bool pdl);
+
+// [K, N] (reference layout, fp32 or bf16) -> bf16 [N, K] at dst + row offset.
+cudaError_t launch_pack_transpose(const void* src, int src_is_bf16, int K, int N,
+                                  __nv_bfloat16* dst, int ld_dst, int k_offset, cudaStream_t s);
+// elementwise copy to fp32 / bf16
+cudaError_t launch_to_f32(const void* src, int src_is_bf16, int64_t n, float* dst, cudaStream_t s);
+cudaError_t launch_to_bf16(const void* src, int src_is_bf16, int64_t n, __nv_bfloat16* dst,
+                           cudaStream_t s);
+
+}  // namespace mtj

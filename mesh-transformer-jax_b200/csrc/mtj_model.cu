@@ -1,0 +1,769 @@
+// Model runtime behind the C ABI: weight arena, workspace carving, paged KV
+// cache bookkeeping and the per-call kernel sequences (prefill, decode step,
+// full-sequence forward).  Host code only; kernels live in the other files.
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <algorithm>
+#include <string>
+#include <vector>
+
+#include "../../include/mtj_b200.h"
+#include "mtj_common.cuh"
+#include "mtj_kernels.h"
+
+namespace {
+
+thread_local std::string g_last_error;
+
+int32_t fail(int32_t code, const std::string& msg) {
+  g_last_error = msg;
+  return code;
+}
+
+#define MTJ_CUDA(expr)                                                              \
+  do {                                                                              \
+    cudaError_t _e = (expr);                                                        \
+    if (_e != cudaSuccess)                                                          \
+      return fail(MTJ_ERR_CUDA, std::string(#expr) + ": " + cudaGetErrorString(_e)); \
+  } while (0)
+
+struct LayerWeights {
+  __nv_bfloat16* w_in = nullptr;    // [3*dl + ffl, d]  rows: Q | K | V | FF-in
+  float* b_ff = nullptr;            // [ffl]
+  __nv_bfloat16* w_out = nullptr;   // [d, dl + ffl]    cols: attn vector | gelu(ff)
+  float* b_out = nullptr;           // [d]
+  float* ln_scale = nullptr;
+  float* ln_offset = nullptr;
+};
+
+int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
+
+// Bump allocator over a caller-provided arena; with base == nullptr it only sizes.
+struct Carver {
+  char* base;
+  int64_t off = 0;
+  explicit Carver(void* b) : base(static_cast<char*>(b)) {}
+  template <typename T>
+  T* take(int64_t count) {
+    off = align_up(off, 256);
+    T* p = base ? reinterpret_cast<T*>(base + off) : nullptr;
+    off += count * static_cast<int64_t>(sizeof(T));
+    return p;
+  }
+};
+
+}  // namespace
+
+struct mtj_handle {
+  mtj_config cfg;
+  int L, d, n_heads, heads, dh, rot, V, Vl, seq, W, mp, rank, dl, ffl;
+  int max_batch, max_gen, max_rows, ring_pages, n_pages, max_pos, max_splits;
+
+  // weight arena
+  __nv_bfloat16* emb_w = nullptr;
+  float* emb_b = nullptr;
+  std::vector<LayerWeights> layers;
+  float* lnf_scale = nullptr;
+  float* lnf_offset = nullptr;
+  __nv_bfloat16* proj_w = nullptr;
+  float* proj_b = nullptr;
+  float2* sincos = nullptr;
+  int64_t loaded = 0, expected = 0;
+
+  // workspace
+  float* x = nullptr;
+  float* stats = nullptr;
+  float* q = nullptr;
+  float* act2 = nullptr;
+  float* part_o = nullptr;
+  float* part_ml = nullptr;
+  uint32_t* counters = nullptr;     // attention + gemv tickets (zeroed at bind)
+  uint32_t* gemv_counters = nullptr;
+  float* logits = nullptr;          // [max_batch, Vl]
+  uint32_t* tokens = nullptr;       // [max_batch] next decode input
+  int32_t* cur = nullptr;           // absolute position of the next decode token
+  int32_t* pad = nullptr;           // [max_batch]
+  int32_t* key_limit = nullptr;     // [max_batch]
+  int32_t* page_table = nullptr;    // [max_batch, ring_pages]
+  int32_t* row_select = nullptr;    // [max_rows]
+  uint32_t* dev_err = nullptr;
+  __nv_bfloat16* kpool = nullptr;   // [L][n_pages][heads][kPageTokens][dh]
+  __nv_bfloat16* vpool = nullptr;
+  int64_t pool_layer_elems = 0;
+  bool bound = false;
+
+  // decode state
+  int batch = 0;
+  bool prefilled = false;
+  int steps_done = 0;
+  int64_t launches = 0;
+  bool use_pdl = true;
+
+  // optional per-family kernel timing (mtj_profile_*): events around launches
+  bool profile = false;
+  std::vector<cudaEvent_t> ev_pool;
+  size_t ev_used = 0;
+  std::vector<std::pair<int, std::pair<size_t, size_t>>> ev_spans;   // (family, (start, stop))
+
+  void prof_begin(int family, cudaStream_t s) {
+    if (!profile || ev_used + 2 > ev_pool.size()) return;
+    cudaEventRecord(ev_pool[ev_used], s);
+    ev_spans.push_back({family, {ev_used, ev_used + 1}});
+    ev_used += 2;
+  }
+  void prof_end(cudaStream_t s) {
+    if (!profile || ev_spans.empty()) return;
+    cudaEventRecord(ev_pool[ev_spans.back().second.second], s);
+  }
+
+  void carve_weights(Carver& c) {
+    emb_w = c.take<__nv_bfloat16>(static_cast<int64_t>(Vl) * d);
+    emb_b = c.take<float>(d);
+    layers.resize(L);
+    for (auto& lw : layers) {
+      lw.w_in = c.take<__nv_bfloat16>(static_cast<int64_t>(3 * dl + ffl) * d);
+      lw.b_ff = c.take<float>(ffl);
+      lw.w_out = c.take<__nv_bfloat16>(static_cast<int64_t>(d) * (dl + ffl));
+      lw.b_out = c.take<float>(d);
+      lw.ln_scale = c.take<float>(d);
+      lw.ln_offset = c.take<float>(d);
+    }
+    lnf_scale = c.take<float>(d);
+    lnf_offset = c.take<float>(d);
+    proj_w = c.take<__nv_bfloat16>(static_cast<int64_t>(Vl) * d);
+    proj_b = c.take<float>(Vl);
+    sincos = c.take<float2>(static_cast<int64_t>(max_pos) * (rot / 2));
+  }
+
+  void carve_workspace(Carver& c) {
+    const int64_t R = max_rows;
+    x = c.take<float>(R * d);
+    stats = c.take<float>(R * 2);
+    q = c.take<float>(R * dl);
+    act2 = c.take<float>(R * (dl + ffl));
+    part_o = c.take<float>(static_cast<int64_t>(max_batch) * heads * max_splits * dh);
+    part_ml = c.take<float>(static_cast<int64_t>(max_batch) * heads * max_splits * 2);
+    counters = c.take<uint32_t>(static_cast<int64_t>(max_batch) * heads);
+    gemv_counters = c.take<uint32_t>(R);
+    logits = c.take<float>(static_cast<int64_t>(std::max(max_batch, 1)) * Vl);
+    tokens = c.take<uint32_t>(max_batch);
+    cur = c.take<int32_t>(4);
+    pad = c.take<int32_t>(max_batch);
+    key_limit = c.take<int32_t>(max_batch);
+    page_table = c.take<int32_t>(static_cast<int64_t>(max_batch) * ring_pages);
+    row_select = c.take<int32_t>(R);
+    dev_err = c.take<uint32_t>(4);
+    pool_layer_elems = static_cast<int64_t>(n_pages) * heads * mtj::kPageTokens * dh;
+    kpool = c.take<__nv_bfloat16>(pool_layer_elems * L);
+    vpool = c.take<__nv_bfloat16>(pool_layer_elems * L);
+  }
+
+  mtj::KvCache kv(int layer) const {
+    mtj::KvCache k;
+    k.kpool = kpool + pool_layer_elems * layer;
+    k.vpool = vpool + pool_layer_elems * layer;
+    k.page_table = page_table;
+    k.ring_pages = ring_pages;
+    k.pad = pad;
+    return k;
+  }
+};
+
+namespace {
+
+using mtj::GemvArgs;
+
+// One transformer layer over a chunk of rows already in h->x (+ h->stats):
+// x <- x + attn(LN(x)) + ff(LN(x))  (layers.py:299-313 / :316-344 / :347-366).
+int32_t run_layer(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, bool decode,
+                  const int32_t* key_limit, cudaStream_t s) {
+  const LayerWeights& lw = h->layers[layer];
+  const bool pdl = h->use_pdl && decode;
+  GemvArgs a = {};
+  a.W = lw.w_in;
+  a.N = 3 * h->dl + h->ffl;
+  a.K = h->d;
+  a.M = M;
+  a.x = h->x;
+  a.ldx = h->d;
+  a.ln_scale = lw.ln_scale;
+  a.ln_offset = lw.ln_offset;
+  a.stats = h->stats;
+  a.rows = rows;
+  a.dl = h->dl;
+  a.ffl = h->ffl;
+  a.d_head = h->dh;
+  a.heads = h->heads;
+  a.rot = h->rot;
+  a.sincos = h->sincos;
+  a.b_ff = lw.b_ff;
+  a.q_out = h->q;
+  a.act2 = h->act2;
+  a.kv = h->kv(layer);
+  h->prof_begin(MTJ_FAMILY_INPROJ, s);
+  MTJ_CUDA(mtj::launch_gemv(mtj::kEpiInProj, a, s, pdl));
+  h->prof_end(s);
+  h->launches++;
+
+  if (decode) {
+    mtj::DecodeAttnArgs d = {};
+    d.q = h->q;
+    d.kv = h->kv(layer);
+    d.B = M;
+    d.heads = h->heads;
+    d.d_head = h->dh;
+    d.window = h->W;
+    d.cur_dev = h->cur;
+    // enough blocks to fill the GPU twice, at least 32 keys per split
+    int want = (2 * 148 + M * h->heads - 1) / (M * h->heads);
+    want = std::max(1, std::min(want, h->max_splits));
+    int st = (h->W + want - 1) / want;
+    st = std::max(st, (h->W + h->max_splits - 1) / h->max_splits);
+    st = std::max(32, (st + 7) / 8 * 8);
+    d.split_tokens = st;
+    d.max_splits = h->max_splits;
+    d.grid_splits = (h->W + st - 1) / st;
+    d.part_o = h->part_o;
+    d.part_ml = h->part_ml;
+    d.counters = h->counters;
+    d.out = h->act2;
+    d.ld_out = h->dl + h->ffl;
+    h->prof_begin(MTJ_FAMILY_ATTN, s);
+    MTJ_CUDA(mtj::launch_decode_attn(d, s, pdl));
+    h->prof_end(s);
+  } else {
+    mtj::PrefillAttnArgs p = {};
+    p.q = h->q;
+    p.kv = h->kv(layer);
+    p.rows = rows;
+    p.M = M;
+    p.heads = h->heads;
+    p.d_head = h->dh;
+    p.key_limit = key_limit;
+    p.out = h->act2;
+    p.ld_out = h->dl + h->ffl;
+    h->prof_begin(MTJ_FAMILY_ATTN, s);
+    MTJ_CUDA(mtj::launch_prefill_attn(p, s));
+    h->prof_end(s);
+  }
+  h->launches++;
+
+  GemvArgs o = {};
+  o.W = lw.w_out;
+  o.N = h->d;
+  o.K = h->dl + h->ffl;
+  o.M = M;
+  o.x = h->act2;
+  o.ldx = h->dl + h->ffl;
+  o.rows = rows;
+  o.bias = lw.b_out;
+  o.residual = h->x;
+  o.out = h->x;
+  o.stats_out = h->stats;
+  o.counters = h->gemv_counters;
+  h->prof_begin(MTJ_FAMILY_OUTPROJ, s);
+  MTJ_CUDA(mtj::launch_gemv(mtj::kEpiOut, o, s, pdl));
+  h->prof_end(s);
+  h->launches++;
+  return MTJ_OK;
+}
+
+int32_t run_embed(mtj_handle* h, const uint32_t* ids, int ids_ld, int M, const mtj::RowMap& rows,
+                  bool decode, cudaStream_t s) {
+  mtj::EmbedArgs e = {};
+  e.ids = ids;
+  e.ids_ld = ids_ld;
+  e.rows = rows;
+  e.M = M;
+  e.d = h->d;
+  e.vocab_local = h->Vl;
+  e.vocab_start = h->rank * h->Vl;
+  e.table = h->emb_w;
+  e.bias = h->emb_b;
+  e.x = h->x;
+  e.stats = h->stats;
+  MTJ_CUDA(mtj::launch_embed(e, s, h->use_pdl && decode));
+  h->launches++;
+  return MTJ_OK;
+}
+
+// final LayerNorm + vocab-sharded logits for M output rows (layers.py:561-564)
+int32_t run_logits(mtj_handle* h, int M, const int32_t* row_select, float* out, bool decode,
+                   cudaStream_t s) {
+  GemvArgs a = {};
+  a.W = h->proj_w;
+  a.N = h->Vl;
+  a.K = h->d;
+  a.M = M;
+  a.x = h->x;
+  a.ldx = h->d;
+  a.ln_scale = h->lnf_scale;
+  a.ln_offset = h->lnf_offset;
+  a.stats = h->stats;
+  a.bias = h->proj_b;
+  a.logits = out;
+  a.ld_logits = h->Vl;
+  a.row_select = row_select;
+  h->prof_begin(MTJ_FAMILY_LOGITS, s);
+  MTJ_CUDA(mtj::launch_gemv(mtj::kEpiLogits, a, s, h->use_pdl && decode));
+  h->prof_end(s);
+  h->launches++;
+  return MTJ_OK;
+}
+
+int32_t check_ready(const mtj_handle* h) {
+  if (!h) return fail(MTJ_ERR_INVALID, "null handle");
+  if (!h->bound) return fail(MTJ_ERR_STATE, "arenas not bound (mtj_bind_arenas)");
+  if (h->loaded != h->expected)
+    return fail(MTJ_ERR_STATE, "parameters missing: loaded " + std::to_string(h->loaded) + " of " +
+                                   std::to_string(h->expected));
+  return MTJ_OK;
+}
+
+// Sets per-sequence first valid position / key limit and the identity page map.
+int32_t setup_sequences(mtj_handle* h, const std::vector<int32_t>& pad,
+                        const std::vector<int32_t>& limit, int cur, cudaStream_t s) {
+  const int B = static_cast<int>(pad.size());
+  std::vector<int32_t> table(static_cast<size_t>(B) * h->ring_pages);
+  for (int b = 0; b < B; ++b)
+    for (int p = 0; p < h->ring_pages; ++p) table[static_cast<size_t>(b) * h->ring_pages + p] = b * h->ring_pages + p;
+  MTJ_CUDA(cudaMemcpyAsync(h->pad, pad.data(), B * sizeof(int32_t), cudaMemcpyHostToDevice, s));
+  MTJ_CUDA(cudaMemcpyAsync(h->key_limit, limit.data(), B * sizeof(int32_t), cudaMemcpyHostToDevice, s));
+  MTJ_CUDA(cudaMemcpyAsync(h->page_table, table.data(), table.size() * sizeof(int32_t),
+                           cudaMemcpyHostToDevice, s));
+  const int32_t c = cur;
+  MTJ_CUDA(cudaMemcpyAsync(h->cur, &c, sizeof(int32_t), cudaMemcpyHostToDevice, s));
+  // the host vectors above are pageable: the copies are staged before returning
+  return MTJ_OK;
+}
+
+// Runs embed + all layers over [batch, T] ids in chunks of at most max_rows rows.
+// After each chunk `after_chunk(b0, nseq, t0, Tc)` may read h->x / h->stats.
+template <typename F>
+int32_t forward_chunks(mtj_handle* h, const uint32_t* ids, int ids_ld, int batch, int T,
+                       const int32_t* key_limit, cudaStream_t s, F&& after_chunk) {
+  int Tc = std::min(T, h->max_rows);
+  int nseq = std::max(1, h->max_rows / Tc);
+  if (Tc < T) nseq = 1;
+  for (int b0 = 0; b0 < batch; b0 += nseq) {
+    const int ns = std::min(nseq, batch - b0);
+    for (int t0 = 0; t0 < T; t0 += Tc) {
+      const int tc = std::min(Tc, T - t0);
+      mtj::RowMap rows = {b0, tc, t0, nullptr};
+      const int M = ns * tc;
+      int32_t rc = run_embed(h, ids, ids_ld, M, rows, false, s);
+      if (rc) return rc;
+      for (int l = 0; l < h->L; ++l) {
+        rc = run_layer(h, l, M, rows, false, key_limit, s);
+        if (rc) return rc;
+      }
+      rc = after_chunk(b0, ns, t0, tc);
+      if (rc) return rc;
+    }
+  }
+  return MTJ_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* mtj_last_error(void) { return g_last_error.c_str(); }
+int32_t mtj_version(void) { return 1; }
+
+int32_t mtj_create(const mtj_config* c, mtj_handle** out) {
+  if (!c || !out) return fail(MTJ_ERR_INVALID, "null argument");
+  if (c->layers <= 0 || c->d_model <= 0 || c->n_heads <= 0 || c->n_vocab <= 0 || c->seq < 2)
+    return fail(MTJ_ERR_INVALID, "non-positive config value");
+  const int mp = c->cores_per_replica;
+  if (mp <= 0 || c->rank < 0 || c->rank >= mp) return fail(MTJ_ERR_INVALID, "bad rank / cores_per_replica");
+  if (c->n_vocab % mp) return fail(MTJ_ERR_INVALID, "n_vocab % cores_per_replica != 0");
+  if (c->d_model % c->n_heads) return fail(MTJ_ERR_INVALID, "d_model % n_heads != 0");
+  if (c->n_heads % mp) return fail(MTJ_ERR_INVALID, "n_heads % cores_per_replica != 0");
+  const int dh = c->d_model / c->n_heads;
+  if (dh != 64 && dh != 256) return fail(MTJ_ERR_UNSUPPORTED, "d_head must be 64 or 256");
+  const int rot = c->pe_rotary_dims > 0 ? c->pe_rotary_dims : dh;
+  if (rot > dh || (rot & 1)) return fail(MTJ_ERR_INVALID, "pe_rotary_dims must be even and <= d_head");
+  if (c->d_model % 256) return fail(MTJ_ERR_UNSUPPORTED, "d_model must be a multiple of 256");
+  if ((5 * c->d_model / mp) % 256) return fail(MTJ_ERR_UNSUPPORTED, "5*d_model/mp must be a multiple of 256");
+  if (c->max_batch <= 0 || c->max_gen < 0 || c->max_rows <= 0) return fail(MTJ_ERR_INVALID, "bad capacity");
+
+  mtj_handle* h = new mtj_handle();
+  h->cfg = *c;
+  h->L = c->layers;
+  h->d = c->d_model;
+  h->n_heads = c->n_heads;
+  h->heads = c->n_heads / mp;
+  h->dh = dh;
+  h->rot = rot;
+  h->V = c->n_vocab;
+  h->Vl = c->n_vocab / mp;
+  h->seq = c->seq;
+  h->W = c->seq - 1;
+  h->mp = mp;
+  h->rank = c->rank;
+  h->dl = c->d_model / mp;
+  h->ffl = 4 * c->d_model / mp;
+  h->max_batch = c->max_batch;
+  h->max_gen = c->max_gen;
+  h->max_rows = c->max_rows;
+  h->max_pos = c->seq + c->max_gen + 1;
+  const int need_all = (h->max_pos + mtj::kPageTokens - 1) / mtj::kPageTokens;
+  const int need_ring = (c->seq + mtj::kPageTokens - 1) / mtj::kPageTokens + 1;
+  h->ring_pages = std::min(need_all, need_ring);
+  h->n_pages = h->ring_pages * h->max_batch;
+  h->max_splits = 64;
+  h->expected = 2 + 10LL * h->L + 4;
+  const char* e = getenv("MTJ_NO_PDL");
+  h->use_pdl = !(e && e[0] == '1');
+  *out = h;
+  return MTJ_OK;
+}
+
+int32_t mtj_destroy(mtj_handle* h) {
+  if (h)
+    for (cudaEvent_t e : h->ev_pool) cudaEventDestroy(e);
+  delete h;
+  return MTJ_OK;
+}
+
+int64_t mtj_weights_bytes(const mtj_handle* h) {
+  if (!h) return -1;
+  mtj_handle tmp = *h;
+  Carver c(nullptr);
+  tmp.carve_weights(c);
+  return align_up(c.off, 256);
+}
+
+int64_t mtj_workspace_bytes(const mtj_handle* h) {
+  if (!h) return -1;
+  mtj_handle tmp = *h;
+  Carver c(nullptr);
+  tmp.carve_workspace(c);
+  return align_up(c.off, 256);
+}
+
+int32_t mtj_bind_arenas(mtj_handle* h, void* wdev, int64_t wbytes, void* sdev, int64_t sbytes,
+                        mtj_stream stream) {
+  if (!h || !wdev || !sdev) return fail(MTJ_ERR_INVALID, "null argument");
+  if ((reinterpret_cast<uintptr_t>(wdev) | reinterpret_cast<uintptr_t>(sdev)) & 255)
+    return fail(MTJ_ERR_INVALID, "arenas must be 256-byte aligned");
+  if (wbytes < mtj_weights_bytes(h) || sbytes < mtj_workspace_bytes(h))
+    return fail(MTJ_ERR_INVALID, "arena too small");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  Carver cw(wdev), cs(sdev);
+  h->carve_weights(cw);
+  h->carve_workspace(cs);
+  // RoPE angles in double precision like the reference's NumPy table (layers.py:128-134)
+  std::vector<float2> tab(static_cast<size_t>(h->max_pos) * (h->rot / 2));
+  for (int p = 0; p < h->max_pos; ++p)
+    for (int i = 0; i < h->rot / 2; ++i) {
+      const double inv_freq = 1.0 / pow(10000.0, (2.0 * i) / h->rot);
+      const double ang = static_cast<double>(p) * inv_freq;
+      tab[static_cast<size_t>(p) * (h->rot / 2) + i] = make_float2(static_cast<float>(sin(ang)),
+                                                                 static_cast<float>(cos(ang)));
+    }
+  MTJ_CUDA(cudaMemcpyAsync(h->sincos, tab.data(), tab.size() * sizeof(float2), cudaMemcpyHostToDevice, s));
+  MTJ_CUDA(cudaMemsetAsync(h->counters, 0, sizeof(uint32_t) * h->max_batch * h->heads, s));
+  MTJ_CUDA(cudaMemsetAsync(h->gemv_counters, 0, sizeof(uint32_t) * h->max_rows, s));
+  MTJ_CUDA(cudaMemsetAsync(h->dev_err, 0, sizeof(uint32_t) * 4, s));
+  MTJ_CUDA(cudaStreamSynchronize(s));   // `tab` is about to go out of scope
+  h->bound = true;
+  h->loaded = 0;
+  return MTJ_OK;
+}
+
+int32_t mtj_load_param(mtj_handle* h, const char* name, const void* src, int32_t dtype, int32_t ndim,
+                       const int64_t* shape, mtj_stream stream) {
+  if (!h || !name || !src || !shape) return fail(MTJ_ERR_INVALID, "null argument");
+  if (!h->bound) return fail(MTJ_ERR_STATE, "arenas not bound");
+  if (dtype != MTJ_F32 && dtype != MTJ_BF16) return fail(MTJ_ERR_INVALID, "dtype");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // tokens of the Haiku path, "~" and the top-level module name dropped
+  std::vector<std::string> tok;
+  {
+    std::string cur;
+    for (const char* p = name;; ++p) {
+      if (*p == '/' || *p == 0) {
+        if (!cur.empty() && cur != "~" && cur != "causal_transformer_shard") tok.push_back(cur);
+        cur.clear();
+        if (*p == 0) break;
+      } else {
+        cur.push_back(*p);
+      }
+    }
+  }
+  if (tok.size() != 3) return fail(MTJ_ERR_INVALID, std::string("unrecognised parameter name: ") + name);
+  const std::string &mod = tok[0], &lay = tok[1], &leaf = tok[2];
+  const int bf = dtype == MTJ_BF16;
+  auto want = [&](std::initializer_list<int64_t> dims) {
+    if (ndim != static_cast<int32_t>(dims.size())) return false;
+    int i = 0;
+    for (int64_t v : dims)
+      if (shape[i++] != v) return false;
+    return true;
+  };
+  auto bad_shape = [&]() { return fail(MTJ_ERR_INVALID, std::string("shape mismatch for ") + name); };
+  const int d = h->d, dl = h->dl, ffl = h->ffl, Vl = h->Vl;
+
+  if (mod == "embedding_shard" && lay == "linear") {
+    if (leaf == "w") {
+      if (!want({Vl, d})) return bad_shape();
+      MTJ_CUDA(mtj::launch_to_bf16(src, bf, static_cast<int64_t>(Vl) * d, h->emb_w, s));
+    } else if (leaf == "b") {
+      if (!want({d})) return bad_shape();
+      MTJ_CUDA(mtj::launch_to_f32(src, bf, d, h->emb_b, s));
+    } else {
+      return fail(MTJ_ERR_INVALID, std::string("unknown leaf: ") + name);
+    }
+  } else if (mod == "projection_shard") {
+    if (lay == "replicated_layer_norm" && (leaf == "scale" || leaf == "offset")) {
+      if (!want({d})) return bad_shape();
+      MTJ_CUDA(mtj::launch_to_f32(src, bf, d, leaf == "scale" ? h->lnf_scale : h->lnf_offset, s));
+    } else if (lay == "linear" && leaf == "w") {
+      if (!want({d, Vl})) return bad_shape();
+      MTJ_CUDA(mtj::launch_pack_transpose(src, bf, d, Vl, h->proj_w, d, 0, s));
+    } else if (lay == "linear" && leaf == "b") {
+      if (!want({Vl})) return bad_shape();
+      MTJ_CUDA(mtj::launch_to_f32(src, bf, Vl, h->proj_b, s));
+    } else {
+      return fail(MTJ_ERR_INVALID, std::string("unknown leaf: ") + name);
+    }
+  } else if (mod.rfind("layer_", 0) == 0) {
+    const int li = atoi(mod.c_str() + 6);
+    if (li < 0 || li >= h->L) return fail(MTJ_ERR_INVALID, std::string("layer out of range: ") + name);
+    LayerWeights& lw = h->layers[li];
+    const int kin = dl + ffl;
+    if (lay == "replicated_layer_norm" && (leaf == "scale" || leaf == "offset")) {
+      if (!want({d})) return bad_shape();
+      MTJ_CUDA(mtj::launch_to_f32(src, bf, d, leaf == "scale" ? lw.ln_scale : lw.ln_offset, s));
+    } else if (leaf == "w" && (lay == "linear" || lay == "linear_1" || lay == "linear_2")) {
+      // q -> rows [0, dl), k (linear_2) -> [dl, 2dl), v (linear_1) -> [2dl, 3dl)
+      if (!want({d, dl})) return bad_shape();
+      const int region = lay == "linear" ? 0 : (lay == "linear_2" ? 1 : 2);
+      MTJ_CUDA(mtj::launch_pack_transpose(src, bf, d, dl, lw.w_in + static_cast<size_t>(region) * dl * d, d, 0, s));
+    } else if (leaf == "w" && lay == "linear_3") {
+      if (!want({dl, d})) return bad_shape();
+      MTJ_CUDA(mtj::launch_pack_transpose(src, bf, dl, d, lw.w_out, kin, 0, s));
+    } else if (lay == "linear_4") {
+      if (leaf == "w") {
+        if (!want({d, ffl})) return bad_shape();
+        MTJ_CUDA(mtj::launch_pack_transpose(src, bf, d, ffl, lw.w_in + static_cast<size_t>(3) * dl * d, d, 0, s));
+      } else if (leaf == "b") {
+        if (!want({ffl})) return bad_shape();
+        MTJ_CUDA(mtj::launch_to_f32(src, bf, ffl, lw.b_ff, s));
+      } else {
+        return fail(MTJ_ERR_INVALID, std::string("unknown leaf: ") + name);
+      }
+    } else if (lay == "linear_5") {
+      if (leaf == "w") {
+        if (!want({ffl, d})) return bad_shape();
+        MTJ_CUDA(mtj::launch_pack_transpose(src, bf, ffl, d, lw.w_out, kin, dl, s));
+      } else if (leaf == "b") {
+        if (!want({d})) return bad_shape();
+        MTJ_CUDA(mtj::launch_to_f32(src, bf, d, lw.b_out, s));
+      } else {
+        return fail(MTJ_ERR_INVALID, std::string("unknown leaf: ") + name);
+      }
+    } else {
+      return fail(MTJ_ERR_INVALID, std::string("unknown leaf: ") + name);
+    }
+  } else {
+    return fail(MTJ_ERR_INVALID, std::string("unknown module: ") + name);
+  }
+  h->loaded++;
+  return MTJ_OK;
+}
+
+int32_t mtj_set_nccl(mtj_handle* h, void* comm) {
+  (void)comm;
+  if (!h) return fail(MTJ_ERR_INVALID, "null handle");
+  if (h->mp == 1) return MTJ_OK;
+  return fail(MTJ_ERR_UNSUPPORTED, "tensor-parallel execution is not wired yet");
+}
+
+int32_t mtj_prefill(mtj_handle* h, const uint32_t* ctx, const uint32_t* ctx_len, int32_t batch,
+                    mtj_stream stream) {
+  int32_t rc = check_ready(h);
+  if (rc) return rc;
+  if (h->mp != 1) return fail(MTJ_ERR_UNSUPPORTED, "tensor-parallel execution is not wired yet");
+  if (!ctx || !ctx_len || batch <= 0 || batch > h->max_batch) return fail(MTJ_ERR_INVALID, "bad batch");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  std::vector<int32_t> pad(batch), limit(batch, 0x7fffffff);
+  for (int b = 0; b < batch; ++b) {
+    if (ctx_len[b] < 1 || ctx_len[b] > static_cast<uint32_t>(h->seq))
+      return fail(MTJ_ERR_INVALID, "ctx_length must be in [1, seq]");
+    pad[b] = h->seq - static_cast<int>(ctx_len[b]);
+  }
+  rc = setup_sequences(h, pad, limit, h->W, s);
+  if (rc) return rc;
+  // held-back last token drives the first decode step (transformer_shard.py:76-77)
+  MTJ_CUDA(cudaMemcpy2DAsync(h->tokens, sizeof(uint32_t), ctx + (h->seq - 1), sizeof(uint32_t) * h->seq,
+                             sizeof(uint32_t), batch, cudaMemcpyDeviceToDevice, s));
+  rc = forward_chunks(h, ctx, h->seq, batch, h->W, nullptr, s,
+                      [](int, int, int, int) { return static_cast<int32_t>(MTJ_OK); });
+  if (rc) return rc;
+  h->batch = batch;
+  h->prefilled = true;
+  h->steps_done = 0;
+  return MTJ_OK;
+}
+
+int32_t mtj_decode_step(mtj_handle* h, const uint32_t* tokens_in, const float* top_p, const float* temp,
+                        const float* uniforms, int32_t greedy, uint32_t* tokens_out, float* logits_out,
+                        mtj_stream stream) {
+  int32_t rc = check_ready(h);
+  if (rc) return rc;
+  if (!h->prefilled) return fail(MTJ_ERR_STATE, "mtj_prefill has not run");
+  if (h->steps_done >= h->max_gen) return fail(MTJ_ERR_STATE, "max_gen steps already generated");
+  if (!greedy) {
+    (void)top_p; (void)temp; (void)uniforms;
+    return fail(MTJ_ERR_UNSUPPORTED, "sampled decoding is not wired yet");
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int B = h->batch;
+  if (tokens_in)
+    MTJ_CUDA(cudaMemcpyAsync(h->tokens, tokens_in, sizeof(uint32_t) * B, cudaMemcpyDeviceToDevice, s));
+  mtj::RowMap rows = {0, 1, 0, h->cur};
+  mtj::RowMap erows = {0, 1, 0, nullptr};
+  rc = run_embed(h, h->tokens, 1, B, erows, true, s);
+  if (rc) return rc;
+  for (int l = 0; l < h->L; ++l) {
+    rc = run_layer(h, l, B, rows, true, nullptr, s);
+    if (rc) return rc;
+  }
+  rc = run_logits(h, B, nullptr, h->logits, true, s);
+  if (rc) return rc;
+  mtj::ArgmaxArgs am = {};
+  am.logits = h->logits;
+  am.B = B;
+  am.V = h->Vl;
+  am.tokens = h->tokens;
+  am.tokens_copy = tokens_out;
+  am.cur_dev = h->cur;
+  MTJ_CUDA(mtj::launch_argmax(am, s, h->use_pdl));
+  h->launches++;
+  if (logits_out)
+    MTJ_CUDA(cudaMemcpyAsync(logits_out, h->logits, sizeof(float) * B * h->Vl, cudaMemcpyDeviceToDevice, s));
+  h->steps_done++;
+  return MTJ_OK;
+}
+
+int32_t mtj_forward_logits(mtj_handle* h, const uint32_t* obs, const uint32_t* ctx_len, int32_t batch,
+                           int32_t T, int32_t n_last, float* logits_out, mtj_stream stream) {
+  int32_t rc = check_ready(h);
+  if (rc) return rc;
+  if (h->mp != 1) return fail(MTJ_ERR_UNSUPPORTED, "tensor-parallel execution is not wired yet");
+  if (!obs || !logits_out || batch <= 0 || batch > h->max_batch) return fail(MTJ_ERR_INVALID, "bad batch");
+  if (T <= 0 || T > h->ring_pages * mtj::kPageTokens || T > h->max_pos)
+    return fail(MTJ_ERR_INVALID, "T exceeds the KV capacity");
+  if (n_last <= 0 || n_last > T) return fail(MTJ_ERR_INVALID, "bad n_last");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  std::vector<int32_t> pad(batch, 0), limit(batch);
+  for (int b = 0; b < batch; ++b) limit[b] = ctx_len ? static_cast<int32_t>(std::min<uint32_t>(ctx_len[b], 0x7fffffffu)) : T;
+  rc = setup_sequences(h, pad, limit, T, s);
+  if (rc) return rc;
+  h->prefilled = false;
+  const int first = T - n_last;
+  rc = forward_chunks(h, obs, T, batch, T, h->key_limit, s, [&](int b0, int ns, int t0, int tc) -> int32_t {
+    // rows of this chunk that fall into the last n_last positions
+    const int lo = std::max(first, t0), hi = t0 + tc;
+    if (lo >= hi) return MTJ_OK;
+    const int per = hi - lo;
+    std::vector<int32_t> sel(static_cast<size_t>(ns) * per);
+    for (int i = 0; i < ns; ++i)
+      for (int t = lo; t < hi; ++t) sel[static_cast<size_t>(i) * per + (t - lo)] = i * tc + (t - t0);
+    MTJ_CUDA(cudaMemcpyAsync(h->row_select, sel.data(), sel.size() * sizeof(int32_t), cudaMemcpyHostToDevice, s));
+    for (int i = 0; i < ns; ++i) {
+      float* dst = logits_out + (static_cast<size_t>(b0 + i) * n_last + (lo - first)) * h->Vl;
+      int32_t r2 = run_logits(h, per, h->row_select + static_cast<size_t>(i) * per, dst, false, s);
+      if (r2) return r2;
+    }
+    return MTJ_OK;
+  });
+  return rc;
+}
+
+int32_t mtj_eval_loss(mtj_handle*, const uint32_t*, const uint32_t*, const uint32_t*, int32_t, int32_t,
+                      float*, uint8_t*, mtj_stream) {
+  return fail(MTJ_ERR_UNSUPPORTED, "eval loss is not wired yet");
+}
+
+int64_t mtj_sample_scratch_bytes(int32_t, int32_t) { return 0; }
+int32_t mtj_sample_top_p(const float*, const float*, const float*, const float*, int32_t, int32_t, void*,
+                         int64_t, uint32_t*, mtj_stream) {
+  return fail(MTJ_ERR_UNSUPPORTED, "sampler is not wired yet");
+}
+
+int64_t mtj_launch_count(const mtj_handle* h) { return h ? h->launches : -1; }
+
+int32_t mtj_profile_enable(mtj_handle* h, int32_t on) {
+  if (!h) return fail(MTJ_ERR_INVALID, "null handle");
+  if (on && h->ev_pool.empty()) {
+    h->ev_pool.resize(2 * (3 * static_cast<size_t>(h->L) + 2) * 64);
+    for (auto& e : h->ev_pool) MTJ_CUDA(cudaEventCreate(&e));
+  }
+  h->profile = on != 0;
+  h->ev_used = 0;
+  h->ev_spans.clear();
+  return MTJ_OK;
+}
+
+int32_t mtj_profile_read(mtj_handle* h, double* ms_sum, int64_t* count, mtj_stream stream) {
+  if (!h || !ms_sum || !count) return fail(MTJ_ERR_INVALID, "null argument");
+  MTJ_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  for (int f = 0; f < MTJ_FAMILY_COUNT; ++f) {
+    ms_sum[f] = 0.0;
+    count[f] = 0;
+  }
+  for (const auto& sp : h->ev_spans) {
+    float ms = 0.f;
+    MTJ_CUDA(cudaEventElapsedTime(&ms, h->ev_pool[sp.second.first], h->ev_pool[sp.second.second]));
+    ms_sum[sp.first] += ms;
+    count[sp.first] += 1;
+  }
+  h->ev_used = 0;
+  h->ev_spans.clear();
+  return MTJ_OK;
+}
+
+int32_t mtj_check_device_status(mtj_handle* h, mtj_stream stream) {
+  if (!h || !h->bound) return fail(MTJ_ERR_STATE, "not bound");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  uint32_t w = 0;
+  MTJ_CUDA(cudaMemcpyAsync(&w, h->dev_err, sizeof(uint32_t), cudaMemcpyDeviceToHost, s));
+  MTJ_CUDA(cudaStreamSynchronize(s));
+  if (w) {
+    MTJ_CUDA(cudaMemsetAsync(h->dev_err, 0, sizeof(uint32_t), s));
+    if (w & mtj::kDevErrTimeout) return fail(MTJ_ERR_TIMEOUT, "a bounded device-side wait ran out");
+    return fail(MTJ_ERR_INVALID, "a kernel rejected an index");
+  }
+  return MTJ_OK;
+}
+
+int32_t mtj_k_embed(mtj_handle* h, const uint32_t* ids, int32_t rows, float* x_out, float* stats_out,
+                    mtj_stream stream) {
+  int32_t rc = check_ready(h);
+  if (rc) return rc;
+  if (!ids || !x_out || rows <= 0) return fail(MTJ_ERR_INVALID, "bad argument");
+  mtj::EmbedArgs e = {};
+  e.ids = ids;
+  e.ids_ld = 0;
+  e.rows = {0, rows, 0, nullptr};
+  e.M = rows;
+  e.d = h->d;
+  e.vocab_local = h->Vl;
+  e.vocab_start = h->rank * h->Vl;
+  e.table = h->emb_w;
+  e.bias = h->emb_b;
+  e.x = x_out;
+  e.stats = stats_out;
+  MTJ_CUDA(mtj::launch_embed(e, static_cast<cudaStream_t>(stream), false));
+  h->launches++;
+  return MTJ_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,163 @@
+"""Per-GPU runtime object: owns the device arenas (as torch tensors) and the
+libmtj_b200 handle.  torch is plumbing here (device memory, streams,
+torch.distributed); all model math runs in the library's CUDA kernels."""
+from __future__ import annotations
+
+import ctypes
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import MtjConfig, check, lib
+
+PREFIX = "causal_transformer_shard/~/"
+
+
+def validate_config(config: dict) -> None:
+    """The assertions / errors of the reference constructors
+    (layers.py:77,172,179,238-239,552; transformer_shard.py:42)."""
+    if config.get("norm", "layernorm") != "layernorm":
+        raise NotImplementedError("only norm == 'layernorm' is on the GPT-J path")
+    if config.get("pe", "rotary") != "rotary":
+        raise NotImplementedError("only pe == 'rotary' is on the GPT-J path")
+    mp = config["cores_per_replica"]
+    assert config["n_vocab"] % mp == 0
+    assert config["d_model"] % config["n_heads"] == 0
+    assert config["n_heads"] % mp == 0
+
+
+def param_shapes(config: dict) -> dict:
+    """Per-shard leaf shapes of the Haiku tree (layers.py:185,235-258,550-559)."""
+    mp = config["cores_per_replica"]
+    d, V, L = config["d_model"], config["n_vocab"], config["layers"]
+    dl, ffl, Vl = d // mp, 4 * d // mp, V // mp
+    s = {PREFIX + "embedding_shard/~/linear": {"w": (Vl, d), "b": (d,)}}
+    for i in range(L):
+        b = PREFIX + f"layer_{i}/~/"
+        s[b + "replicated_layer_norm"] = {"scale": (d,), "offset": (d,)}
+        s[b + "linear"] = {"w": (d, dl)}
+        s[b + "linear_1"] = {"w": (d, dl)}
+        s[b + "linear_2"] = {"w": (d, dl)}
+        s[b + "linear_3"] = {"w": (dl, d)}
+        s[b + "linear_4"] = {"w": (d, ffl), "b": (ffl,)}
+        s[b + "linear_5"] = {"w": (ffl, d), "b": (d,)}
+    s[PREFIX + "projection_shard/~/replicated_layer_norm"] = {"scale": (d,), "offset": (d,)}
+    s[PREFIX + "projection_shard/~/linear"] = {"w": (d, Vl), "b": (Vl,)}
+    return s
+
+
+class ShardRuntime:
+    """One shard (rank) of the model on one GPU."""
+
+    def __init__(self, config: dict, rank: int = 0, device=None, max_batch: int = 1,
+                 max_gen: int = 256, max_rows: int | None = None):
+        validate_config(config)
+        if not torch.cuda.is_available():
+            raise RuntimeError("libmtj_b200 needs a CUDA device; there is no CPU path")
+        self.config = config
+        self.device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
+        self.rank = rank
+        self.mp = config["cores_per_replica"]
+        seq = config["seq"]
+        d_head = config["d_model"] // config["n_heads"]
+        if max_rows is None:
+            max_rows = min(max(seq, max_batch), 4096)
+        cfg = MtjConfig(config["layers"], config["d_model"], config["n_heads"], config["n_vocab"],
+                        config.get("pe_rotary_dims", d_head), seq, self.mp, rank,
+                        max_batch, max_gen, max_rows, 0)
+        self.max_batch, self.max_gen, self.max_rows = max_batch, max_gen, max_rows
+        self._h = ctypes.c_void_p()
+        check(lib.mtj_create(ctypes.byref(cfg), ctypes.byref(self._h)))
+        with torch.cuda.device(self.device):
+            wb, sb = lib.mtj_weights_bytes(self._h), lib.mtj_workspace_bytes(self._h)
+            self.weights_arena = torch.empty(wb + 256, dtype=torch.uint8, device=self.device)
+            self.workspace = torch.empty(sb + 256, dtype=torch.uint8, device=self.device)
+            check(lib.mtj_bind_arenas(self._h, self._aligned(self.weights_arena), wb,
+                                      self._aligned(self.workspace), sb, self.stream))
+        self.vocab_local = config["n_vocab"] // self.mp
+
+    @staticmethod
+    def _aligned(t: torch.Tensor) -> int:
+        return (t.data_ptr() + 255) // 256 * 256
+
+    @property
+    def stream(self) -> int:
+        return torch.cuda.current_stream(self.device).cuda_stream
+
+    def close(self):
+        if getattr(self, "_h", None) is not None and self._h:
+            lib.mtj_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # -- parameters ---------------------------------------------------------
+    def load_param(self, name: str, value) -> None:
+        """`name` is '<haiku module path>/<leaf>', `value` this shard's slice."""
+        if isinstance(value, np.ndarray):
+            value = torch.from_numpy(np.ascontiguousarray(value))
+        t = value
+        if t.dtype not in (torch.float32, torch.bfloat16):
+            t = t.to(torch.float32)
+        t = t.to(self.device, non_blocking=False).contiguous()
+        shape = (ctypes.c_int64 * t.dim())(*t.shape)
+        dt = _lib.MTJ_BF16 if t.dtype == torch.bfloat16 else _lib.MTJ_F32
+        check(lib.mtj_load_param(self._h, name.encode(), t.data_ptr(), dt, t.dim(), shape, self.stream))
+        torch.cuda.current_stream(self.device).synchronize()   # `t` may be a temporary
+
+    def load_params(self, params: dict, shard_index: int | None = None) -> None:
+        """`params` is the reference's two-level dict; leaves carry a leading
+        shard axis (all shards, or only this one)."""
+        for mod, leaves in params.items():
+            for leaf, v in leaves.items():
+                n = v.shape[0]
+                idx = 0 if n == 1 else (self.rank if shard_index is None else shard_index)
+                self.load_param(f"{mod}/{leaf}", v[idx])
+
+    # -- path entry points --------------------------------------------------
+    def prefill(self, ctx_dev: torch.Tensor, ctx_length) -> None:
+        lens = _lib.u32_array(list(ctx_length))
+        check(lib.mtj_prefill(self._h, ctx_dev.data_ptr(), lens, ctx_dev.shape[0], self.stream))
+
+    def decode_step(self, tokens_in=None, tokens_out=None, logits_out=None, greedy=True,
+                    top_p=None, temp=None, uniforms=None) -> None:
+        p = lambda t: None if t is None else t.data_ptr()
+        check(lib.mtj_decode_step(self._h, p(tokens_in), p(top_p), p(temp), p(uniforms),
+                                  1 if greedy else 0, p(tokens_out), p(logits_out), self.stream))
+
+    def forward_logits(self, obs_dev: torch.Tensor, ctx_length, n_last: int) -> torch.Tensor:
+        B, T = obs_dev.shape
+        out = torch.empty((B, n_last, self.vocab_local), dtype=torch.float32, device=self.device)
+        lens = None if ctx_length is None else _lib.u32_array(list(ctx_length))
+        check(lib.mtj_forward_logits(self._h, obs_dev.data_ptr(), lens, B, T, n_last, out.data_ptr(),
+                                     self.stream))
+        return out
+
+    def embed(self, ids_dev: torch.Tensor):
+        rows = ids_dev.numel()
+        x = torch.empty((rows, self.config["d_model"]), dtype=torch.float32, device=self.device)
+        stats = torch.empty((rows, 2), dtype=torch.float32, device=self.device)
+        check(lib.mtj_k_embed(self._h, ids_dev.data_ptr(), rows, x.data_ptr(), stats.data_ptr(), self.stream))
+        return x, stats
+
+    FAMILIES = ("in_proj", "attention", "out_proj", "logits")
+
+    def profile_enable(self, on: bool) -> None:
+        check(lib.mtj_profile_enable(self._h, 1 if on else 0))
+
+    def profile_read(self) -> dict:
+        ms = (ctypes.c_double * 4)()
+        cnt = (ctypes.c_int64 * 4)()
+        check(lib.mtj_profile_read(self._h, ms, cnt, self.stream))
+        return {f: (ms[i], cnt[i]) for i, f in enumerate(self.FAMILIES)}
+
+    def launch_count(self) -> int:
+        return int(lib.mtj_launch_count(self._h))
+
+    def check_device_status(self) -> None:
+        check(lib.mtj_check_device_status(self._h, self.stream))

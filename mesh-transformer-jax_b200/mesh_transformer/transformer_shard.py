@@ -1,0 +1,190 @@
+"""Host-side mirror of the reference's model runtime API for the GPT-J path.
+
+``CausalTransformer`` keeps the constructor, ``state`` dict, ``eval``,
+``generate``, ``move_xmap``, ``write_ckpt``/``load_ckpt`` surface of
+mesh_transformer/transformer_shard.py:118-339 of the reference; the work runs
+in libmtj_b200's CUDA kernels on one GPU per shard (one process per GPU, the
+"shard" axis being the torch.distributed world).  Training (``train``) and the
+pjit "V2" model are outside this path.
+"""
+from __future__ import annotations
+
+import random
+
+import numpy as np
+import torch
+
+from ._runtime import PREFIX, ShardRuntime, param_shapes, validate_config
+from .util import head_print, to_bf16
+
+
+def _world():
+    import torch.distributed as dist
+    if dist.is_available() and dist.is_initialized():
+        return dist.get_rank(), dist.get_world_size()
+    return 0, 1
+
+
+class CausalTransformerShard:
+    """Per-shard program (transformer_shard.py:21-115) bound to one GPU."""
+
+    def __init__(self, config, runtime: ShardRuntime | None = None, **runtime_kw):
+        validate_config(config)
+        self.config = config
+        self.heads = config["n_heads"]
+        self.heads_per_shard = config["n_heads"] // config["cores_per_replica"]
+        self.runtime = runtime if runtime is not None else ShardRuntime(config, **runtime_kw)
+
+    def generate_initial(self, context_dev: torch.Tensor, length):
+        """Prefill context[:, :-1]; the last token is held back for the first
+        decode step (transformer_shard.py:74-95).  The reference also returns
+        the prefill logits, which its caller discards (:196); they are not
+        computed here."""
+        self.runtime.prefill(context_dev, length)
+
+    def generate_once(self, new_tok_dev=None, tokens_out=None, logits_out=None, **sampler):
+        """One decode step over all layers plus the sampler
+        (transformer_shard.py:97-115,198-210)."""
+        self.runtime.decode_step(new_tok_dev, tokens_out, logits_out, **sampler)
+
+
+class CausalTransformer:
+    def __init__(self, config, device=None, init_weights: bool = True):
+        self.config = config
+        validate_config(config)
+        rank, world = _world()
+        # transformer_shard.py:257 -- the mesh's mp size must match the config
+        assert world == config["cores_per_replica"], \
+            "run one process per shard: world size must equal cores_per_replica"
+        self.rank = rank
+        if device is None:
+            device = torch.device("cuda", torch.cuda.current_device())
+        self.device = torch.device(device)
+        self.gen_length = 1
+        self.return_logits = False
+        self._rt: ShardRuntime | None = None
+        self._rt_caps = (0, 0)
+        self._dirty = True
+        self._state = None
+        if init_weights:
+            self.state = self._init_state(seed=42)
+            n = sum(int(np.prod(v.shape)) for m in self._state["params"].values() for v in m.values())
+            head_print(f"Total parameters: {n * config['cores_per_replica'] // 1}")
+
+    # -- state ---------------------------------------------------------------
+    @property
+    def state(self):
+        return self._state
+
+    @state.setter
+    def state(self, value):
+        self._state = value
+        self._dirty = True
+
+    def _init_state(self, seed: int):
+        """Random initialisation with the reference's scales (layers.py:185,
+        253-258; transformer_shard.py:35): truncated normal, std 1/sqrt(fan_in)
+        for plain Linears, 1/sqrt(n_vocab) for the table, (2/layers)/sqrt(d)
+        for the two output projections; LN scale 1, everything else 0.  Leaves
+        carry a leading axis holding this process's shard."""
+        cfg = self.config
+        gen = torch.Generator(device=self.device)
+        gen.manual_seed(seed + 1000 * self.rank)
+        dtype = torch.bfloat16 if "early_cast" in cfg else torch.float32
+        d, L = cfg["d_model"], cfg["layers"]
+
+        def tn(shape, std):
+            t = torch.empty((1,) + tuple(shape), dtype=torch.float32, device=self.device)
+            torch.nn.init.trunc_normal_(t, mean=0.0, std=std, a=-2 * std, b=2 * std, generator=gen)
+            return t.to(dtype)
+
+        params = {}
+        for mod, leaves in param_shapes(cfg).items():
+            out = {}
+            for leaf, shape in leaves.items():
+                if leaf == "scale":
+                    out[leaf] = torch.ones((1,) + shape, dtype=dtype, device=self.device)
+                elif leaf in ("offset", "b"):
+                    out[leaf] = torch.zeros((1,) + shape, dtype=dtype, device=self.device)
+                elif "embedding_shard" in mod:
+                    out[leaf] = tn(shape, 1.0 / np.sqrt(cfg["n_vocab"]))
+                elif mod.endswith("linear_3") or mod.endswith("linear_5"):
+                    out[leaf] = tn(shape, (2.0 / L) / np.sqrt(d))
+                elif mod.endswith("linear_5") or mod.endswith("linear_4") or "projection_shard" in mod \
+                        or mod.endswith("linear") or mod.endswith("linear_1") or mod.endswith("linear_2"):
+                    fan_in = shape[0] if not mod.endswith("linear_5") else shape[0] * cfg["cores_per_replica"]
+                    out[leaf] = tn(shape, 1.0 / np.sqrt(fan_in))
+            params[mod] = out
+        return {"params": params, "step": np.array(0), "opt_state": None}
+
+    def move_xmap(self, state, _):
+        """to_bf16 over the state (transformer_shard.py:250-253)."""
+        return to_bf16(state)
+
+    def write_ckpt(self, path, shard):
+        raise NotImplementedError("checkpoint I/O is outside the forward/decode path")
+
+    def load_ckpt(self, path):
+        raise NotImplementedError("checkpoint I/O is outside the forward/decode path")
+
+    def train(self, sample):
+        raise NotImplementedError("training is outside the forward/decode path")
+
+    # -- runtime -------------------------------------------------------------
+    def _runtime(self, batch: int, gen_length: int) -> ShardRuntime:
+        cap_b, cap_g = self._rt_caps
+        if self._rt is None or batch > cap_b or gen_length > cap_g:
+            if self._rt is not None:
+                self._rt.close()
+            cap_b, cap_g = max(batch, cap_b), max(gen_length, cap_g, 1)
+            self._rt = ShardRuntime(self.config, rank=self.rank, device=self.device,
+                                    max_batch=cap_b, max_gen=cap_g)
+            self._rt_caps = (cap_b, cap_g)
+            self._dirty = True
+        if self._dirty:
+            if self._state is None:
+                raise RuntimeError("network.state has not been set")
+            self._rt.load_params(self._state["params"])
+            self._dirty = False
+        return self._rt
+
+    # -- eval ----------------------------------------------------------------
+    def eval(self, sample):
+        """transformer_shard.py:308-324."""
+        raise NotImplementedError("eval loss is not wired yet")
+
+    # -- generate ------------------------------------------------------------
+    def generate(self, ctx, ctx_length, gen_length, sampler_options=None, return_logits=False):
+        """transformer_shard.py:326-339.  ``ctx`` is [batch, seq] left-padded
+        token ids, ``ctx_length`` the number of real tokens per row.  Returns
+        ``(final_state, (tokens[batch, gen, 1] uint32, None[, logits]))`` like
+        the reference's scan output."""
+        sampler_options = sampler_options or {}
+        ctx = np.ascontiguousarray(np.asarray(ctx), dtype=np.uint32)
+        batch = ctx.shape[0]
+        assert ctx.shape[1] == self.config["seq"], "context must be padded to config['seq']"
+        lengths = np.asarray(ctx_length, dtype=np.uint32).reshape(batch)
+        self.gen_length = gen_length
+        self.return_logits = return_logits
+        key = random.randint(0, 2 ** 60)   # the reference seeds its PRNG the same way (:327)
+        rt = self._runtime(batch, gen_length)
+        top_p = np.asarray(sampler_options.get("top_p", np.zeros(batch)), dtype=np.float32).reshape(batch)
+        greedy = bool(np.all(top_p == 0.0)) or not sampler_options
+        if not greedy:
+            raise NotImplementedError("sampled decoding is not wired yet")
+        del key
+        with torch.cuda.device(self.device):
+            ctx_dev = torch.from_numpy(ctx.view(np.int32)).to(self.device)
+            toks = torch.empty((gen_length, batch), dtype=torch.int32, device=self.device)
+            logits = None
+            if return_logits:
+                logits = torch.empty((gen_length, batch, rt.vocab_local), dtype=torch.float32, device=self.device)
+            shard = CausalTransformerShard(self.config, runtime=rt)
+            shard.generate_initial(ctx_dev, lengths)
+            for t in range(gen_length):
+                shard.generate_once(None, toks[t], None if logits is None else logits[t], greedy=True)
+            out_tokens = toks.cpu().numpy().view(np.uint32).T[:, :, None]
+            output = (out_tokens, None)
+            if return_logits:
+                output = output + (logits.permute(1, 0, 2)[:, :, None, :].cpu().numpy(),)
+        return None, output

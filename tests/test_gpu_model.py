@@ -1,0 +1,138 @@
+"""GPU parity: the CUDA path through the C ABI against the CPU oracle.
+
+Tolerances (the path's stated bf16 bar): logits max|delta| / max|ref| <= 2e-2 on
+valid positions, greedy ids identical for >= 32 steps.
+"""
+import numpy as np
+import pytest
+
+from oracle import gptj_oracle as go
+from oracle import spec
+
+pytestmark = pytest.mark.gpu
+
+LOGIT_TOL = 2e-2
+
+
+def _net(cfg, params, cuda_device):
+    import torch
+    torch.cuda.set_device(cuda_device)
+    from mesh_transformer.transformer_shard import CausalTransformer
+    net = CausalTransformer(dict(cfg), init_weights=False)
+    net.state = {"params": params, "step": np.array(0)}
+    return net
+
+
+def _rel(a, b):
+    return float(np.abs(a - b).max() / np.abs(b).max())
+
+
+@pytest.mark.parametrize("stress", [False, True])
+def test_embedding_rows_and_ln_stats(cuda_device, stress):
+    import torch
+    cfg = spec.tiny_config(1)
+    params = spec.make_params(cfg, seed=0, stress=stress)
+    net = _net(cfg, params, cuda_device)
+    rt = net._runtime(1, 1)
+    ids = spec.token_ids(7, 1, 40, 512)[0]
+    x, stats = rt.embed(torch.from_numpy(ids.view(np.int32)).to(cuda_device))
+    ref = go.EmbeddingShard(cfg, params)(ids)[0]
+    assert np.array_equal(x.cpu().numpy(), ref)          # a gather of bf16-exact values plus bias
+    mean = ref.mean(-1)
+    rstd = 1.0 / np.sqrt(ref.var(-1) + 1e-5)
+    assert np.allclose(stats.cpu().numpy()[:, 0], mean, atol=1e-6)
+    assert np.allclose(stats.cpu().numpy()[:, 1], rstd, rtol=1e-5)
+
+
+@pytest.mark.parametrize("stress", [False, True])
+def test_full_forward_logits_tiny(cuda_device, stress):
+    import torch
+    cfg = spec.tiny_config(1)
+    params = spec.make_params(cfg, seed=0, stress=stress)
+    net = _net(cfg, params, cuda_device)
+    ids = spec.token_ids(0, 2, 128, 512)
+    rt = net._runtime(2, 1)
+    out = rt.forward_logits(torch.from_numpy(ids.view(np.int32)).to(cuda_device), None, 128).cpu().numpy()
+    ref = np.stack([go.CausalTransformerShard(cfg, params).logits(ids[b]) for b in range(2)])
+    assert _rel(out, ref) <= LOGIT_TOL
+    # and the n_last slicing returns the same rows
+    out8 = rt.forward_logits(torch.from_numpy(ids.view(np.int32)).to(cuda_device), None, 8).cpu().numpy()
+    assert np.array_equal(out8, out[:, -8:])
+
+
+def test_forward_with_eval_key_mask(cuda_device):
+    import torch
+    cfg = spec.tiny_config(1, seq=64)
+    params = spec.make_params(cfg, seed=3)
+    net = _net(cfg, params, cuda_device)
+    ids = spec.token_ids(4, 2, 64, 512)
+    lens = np.array([64, 20], np.uint32)
+    rt = net._runtime(2, 1)
+    out = rt.forward_logits(torch.from_numpy(ids.view(np.int32)).to(cuda_device), lens, 64).cpu().numpy()
+    shard = go.CausalTransformerShard(cfg, params)
+    for b in range(2):
+        mask = (np.arange(64) > int(lens[b])) * -1e10      # transformer_shard.py:130
+        assert _rel(out[b], shard.logits(ids[b], mask=mask)) <= LOGIT_TOL
+
+
+def test_forward_in_row_chunks_matches_single_chunk(cuda_device):
+    """max_rows smaller than the sequence: later chunks read earlier keys from the cache."""
+    import torch
+    from mesh_transformer._runtime import ShardRuntime
+    cfg = spec.tiny_config(1)
+    params = spec.make_params(cfg, seed=0)
+    ids = torch.from_numpy(spec.token_ids(0, 2, 128, 512).view(np.int32)).to(cuda_device)
+    outs = []
+    for rows in (256, 48):
+        rt = ShardRuntime(cfg, max_batch=2, max_gen=1, max_rows=rows)
+        rt.load_params(params)
+        outs.append(rt.forward_logits(ids, None, 128).cpu().numpy())
+        rt.close()
+    assert np.abs(outs[0] - outs[1]).max() < 1e-5
+
+
+@pytest.mark.parametrize("case", ["left_pad", "full_window_eviction", "short_prompt", "stress"])
+def test_greedy_generate_matches_oracle(cuda_device, case):
+    seq = 128 if case != "full_window_eviction" else 64
+    cfg = spec.tiny_config(1, seq=seq)
+    params = spec.make_params(cfg, seed=5, stress=(case == "stress"))
+    if case == "left_pad" or case == "stress":
+        lens = np.array([90, 37], np.uint32)
+    elif case == "short_prompt":
+        lens = np.array([1, 2], np.uint32)
+    else:
+        lens = np.array([64, 64], np.uint32)                 # prompt fills seq: a key is evicted every step
+    ctx = np.zeros((2, seq), np.uint32)
+    for b in range(2):
+        ctx[b, seq - lens[b]:] = spec.token_ids(10 + b, 1, int(lens[b]), 512)[0]
+    net = _net(cfg, params, cuda_device)
+    steps = 32
+    _, out = net.generate(ctx, lens, steps, {"top_p": np.zeros(2), "temp": np.ones(2)}, return_logits=True)
+    _, ref = go.CausalTransformer(cfg, params).generate(ctx, lens, steps, return_logits=True)
+    assert out[0].shape == (2, steps, 1) and out[0].dtype == np.uint32
+    assert _rel(out[2][:, 0], ref[2][:, 0]) <= LOGIT_TOL
+    assert np.array_equal(out[0], ref[0]), "greedy ids differ within 32 steps"
+    assert _rel(out[2], ref[2]) <= LOGIT_TOL
+
+
+def test_generate_twice_reuses_the_runtime(cuda_device):
+    cfg = spec.tiny_config(1, seq=64)
+    params = spec.make_params(cfg, seed=6)
+    net = _net(cfg, params, cuda_device)
+    ctx = spec.left_pad(spec.token_ids(1, 1, 30, 512), 64)
+    a = net.generate(ctx, [30], 6, {"top_p": np.zeros(1), "temp": np.ones(1)})[1][0]
+    b = net.generate(ctx, [30], 6, {"top_p": np.zeros(1), "temp": np.ones(1)})[1][0]
+    assert np.array_equal(a, b)
+
+
+def test_errors_are_status_codes_not_faults(cuda_device):
+    from mesh_transformer._lib import MtjError
+    cfg = spec.tiny_config(1, seq=64)
+    net = _net(cfg, spec.make_params(cfg, seed=6), cuda_device)
+    ctx = spec.left_pad(spec.token_ids(1, 1, 30, 512), 64)
+    with pytest.raises(MtjError):
+        net.generate(ctx, [0], 2, {"top_p": np.zeros(1)})      # ctx_length must be >= 1
+    with pytest.raises(MtjError):
+        net.generate(ctx, [65], 2, {"top_p": np.zeros(1)})
+    net.generate(ctx, [30], 2, {"top_p": np.zeros(1)})
+    net._rt.check_device_status()
