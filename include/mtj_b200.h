@@ -153,6 +153,35 @@ int32_t mtj_check_device_status(mtj_handle* h, mtj_stream s);
 int32_t mtj_k_embed(mtj_handle* h, const uint32_t* ids_dev, int32_t rows,
                     float* x_out_dev, float* stats_out_dev, mtj_stream s);
 
+/* Single-query attention of decode_once over the paged bf16 KV cache
+ * (layers.py:316-338 with self_attn :260-283, before the output projection):
+ * q_dev [batch, heads*d_head] f32 (rotated, unscaled); kpool/vpool
+ * [pages][heads][64][d_head] bf16; page_table_dev [batch, ring_pages];
+ * pad_dev [batch] first valid position; cur_dev[0] the query position; keys
+ * [max(pad, cur-window+1), cur] are visible.  out_dev[b*ld_out + head*d_head + j].
+ * scratch_dev (mtj_k_decode_attn_scratch_bytes) holds the per-split partial
+ * results; the call clears the part of it that must start at zero. */
+int64_t mtj_k_decode_attn_scratch_bytes(int32_t batch, int32_t heads, int32_t d_head, int32_t window,
+                                        int32_t split_tokens);
+int32_t mtj_k_decode_attn(const float* q_dev, const void* kpool_dev, const void* vpool_dev,
+                          const int32_t* page_table_dev, const int32_t* pad_dev, const int32_t* cur_dev,
+                          int32_t batch, int32_t heads, int32_t d_head, int32_t window,
+                          int32_t ring_pages, int32_t split_tokens,
+                          void* scratch_dev, int64_t scratch_bytes,
+                          float* out_dev, int32_t ld_out, mtj_stream s);
+
+/* ProjectionShard.__call__ before the all-gather (layers.py:561-564), also the
+ * shape of every LayerNorm + Linear pair on the decode path: out[m, n] =
+ * sum_k w[n, k] * (scale[k]*rstd[m]*(x[m, k]-mean[m]) + offset[k]) + bias[n].
+ * w_dev bf16 [N, K] (the library's packed layout), x_dev f32 [M, K], stats_dev
+ * [M, 2] = (mean, rstd).  k_split in {0 (auto),1,2,4,8} and rows_per_group in
+ * {0 (default),8} select the launch shape (tuning knobs; results do not depend
+ * on them beyond fp32 summation order). */
+int32_t mtj_k_ln_gemv(const void* w_dev, const float* x_dev, const float* stats_dev,
+                      const float* ln_scale_dev, const float* ln_offset_dev, const float* bias_dev,
+                      int32_t M, int32_t N, int32_t K, int32_t k_split, int32_t rows_per_group,
+                      float* out_dev, mtj_stream s);
+
 #ifdef __cplusplus
 }
 #endif

@@ -54,16 +54,29 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attn_kernel(const DecodeA
   __shared__ float sm_o[kAttnWarps][DH];
   __shared__ bool is_last;
 
-  pdl_wait();
-  pdl_launch_dependents();
-
+  // The step counter, the page table and every cached token except the newest
+  // were written before the predecessor kernel started, so they may be read
+  // (and the old keys/values pulled into L2) before waiting for it.
   const int cur = *a.cur_dev;
   const int start = max(a.kv.pad[b], cur - a.window + 1);
   const int end = cur + 1;
   const int nsplit = (end - start + a.split_tokens - 1) / a.split_tokens;
-  if (split >= nsplit) return;
   const int t0 = start + split * a.split_tokens;
   const int t1 = min(end, t0 + a.split_tokens);
+  const int32_t* table = a.kv.page_table + static_cast<size_t>(b) * a.kv.ring_pages;
+  if (split < nsplit) {
+    constexpr int kLines = DH * 2 / 128;                    // 128-byte lines per token row
+    for (int i = threadIdx.x; i < (t1 - t0) * kLines; i += kAttnThreads) {
+      const int tt = t0 + i / kLines;
+      if (tt == cur) continue;                              // written by the predecessor
+      const size_t off = kv_offset(table, a.kv.ring_pages, a.heads, DH, head, tt) + (i % kLines) * 64;
+      prefetch_l2(a.kv.kpool + off);
+      prefetch_l2(a.kv.vpool + off);
+    }
+  }
+  pdl_wait();
+  pdl_launch_dependents();
+  if (split >= nsplit) return;
 
   constexpr float scale = DH == 256 ? 0.0625f : 0.125f;   // 1 / sqrt(d_head), exact
   float q[EPL];
@@ -72,7 +85,6 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attn_kernel(const DecodeA
 #pragma unroll
     for (int e = 0; e < EPL; ++e) q[e] = qp[e] * scale;
   }
-  const int32_t* table = a.kv.page_table + static_cast<size_t>(b) * a.kv.ring_pages;
 
   float m = -INFINITY, l = 0.f, o[EPL];
 #pragma unroll

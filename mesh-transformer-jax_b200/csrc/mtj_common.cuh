@@ -28,6 +28,10 @@ __device__ __forceinline__ uint32_t ld_stream4(const void* p) {
   return v;
 }
 
+__device__ __forceinline__ void prefetch_l2(const void* p) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
+
 // bf16 pair packed in a 32-bit word -> two floats (bf16 is the top half of fp32).
 __device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }

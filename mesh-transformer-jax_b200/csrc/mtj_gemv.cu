@@ -1,9 +1,10 @@
 // Weight-streaming GEMV family for small token counts (decode): HBM-bound.
 //
-// One warp owns RW consecutive output rows and walks the whole K extent with
-// 16-byte streaming loads (32 lanes x 8 bf16 = 256 elements per step); the
-// activations are fp32 and shared by all warps through L1.  There is no
-// block-level synchronisation on the streaming path, so warps overlap freely.
+// A group of KS warps owns RW consecutive output rows; each warp walks its
+// share of the K extent with 16-byte streaming loads (32 lanes x 8 bf16 = 256
+// elements per step), the activations are fp32 and shared by all warps through
+// L1.  There is no block-level synchronisation on the streaming path; the KS
+// partial sums meet once in shared memory and are added in a fixed order.
 // Three epilogues share the loop:
 //   in-proj : LayerNorm prologue, [Q|K|V|FF-in] rows, interleaved RoPE on Q/K,
 //             bf16 K/V written straight into the paged cache, bias + GELU on FF
@@ -33,20 +34,21 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
   return t;
 }
 
-template <int BT, int RW, int EPI>
-__global__ void __launch_bounds__(kGemvThreads) gemv_kernel(const GemvArgs a) {
+template <int BT, int RW, int EPI, int KS>
+__global__ void __launch_bounds__(kGemvThreads, BT == 1 ? (EPI == kEpiOut ? 4 : 3) : 2) gemv_kernel(const GemvArgs a) {
   constexpr bool kLN = (EPI != kEpiOut);
+  constexpr int kGroups = kGemvWarps / KS;      // row groups per block; KS warps share one group's K extent
+  static_assert(RW * BT <= 32 && (RW & 1) == 0, "one lane finishes one (row, token) pair");
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
-  const int row0 = (blockIdx.x * kGemvWarps + warp) * RW;
+  const int grp = warp / KS, kpart = warp % KS;
+  const int row0 = (blockIdx.x * kGroups + grp) * RW;
   const bool active = row0 < a.N;
   const int m0 = blockIdx.y * BT;
   const int nb = min(BT, a.M - m0);
 
-  const __nv_bfloat16* wp[RW];
-#pragma unroll
-  for (int r = 0; r < RW; ++r)
-    wp[r] = a.W + static_cast<size_t>(min(row0 + r, a.N - 1)) * a.K + lane * 8;
+  // N is a multiple of RW (checked at launch), so an active group has RW valid rows
+  const __nv_bfloat16* wbase = a.W + static_cast<size_t>(active ? row0 : 0) * a.K + lane * 8;
 
   float acc[RW][BT];
 #pragma unroll
@@ -56,9 +58,13 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_kernel(const GemvArgs a) {
 
   const int nch = a.K >> 8;
   uint4 wnext[RW];
-  if (active) {
+  if (active && kpart < nch) {
+    // weights do not depend on the predecessor kernel: start streaming before the wait
 #pragma unroll
-    for (int r = 0; r < RW; ++r) wnext[r] = ld_stream16(wp[r]);   // weights do not depend on the predecessor
+    for (int r = 0; r < RW; ++r) wnext[r] = ld_stream16(wbase + static_cast<size_t>(r) * a.K + kpart * 256);
+#pragma unroll
+    for (int r = 0; r < RW; ++r)
+      if (kpart + KS < nch) prefetch_l2(wbase + static_cast<size_t>(r) * a.K + (kpart + KS) * 256);
   }
   pdl_wait();
   pdl_launch_dependents();
@@ -77,13 +83,13 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_kernel(const GemvArgs a) {
   }
 
   if (active) {
-    for (int c = 0; c < nch; ++c) {
+    for (int c = kpart; c < nch; c += KS) {
       uint4 wcur[RW];
 #pragma unroll
       for (int r = 0; r < RW; ++r) wcur[r] = wnext[r];
-      if (c + 1 < nch) {
+      if (c + KS < nch) {
 #pragma unroll
-        for (int r = 0; r < RW; ++r) wnext[r] = ld_stream16(wp[r] + (c + 1) * 256);
+        for (int r = 0; r < RW; ++r) wnext[r] = ld_stream16(wbase + static_cast<size_t>(r) * a.K + (c + KS) * 256);
       }
       const int k = c * 256;
       float sc[8], of[8];
@@ -124,17 +130,27 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_kernel(const GemvArgs a) {
     for (int r = 0; r < RW; ++r)
 #pragma unroll
       for (int bt = 0; bt < BT; ++bt) acc[r][bt] = warp_sum(acc[r][bt]);
-
-    // lane (bt*RW + r) finishes output (row0 + r, m0 + bt)
-    float val = 0.f, partner = 0.f;
+  }
+  // lane (bt*RW + r) finishes output (row0 + r, m0 + bt)
+  float val = 0.f;
 #pragma unroll
-    for (int r = 0; r < RW; ++r)
+  for (int r = 0; r < RW; ++r)
 #pragma unroll
-      for (int bt = 0; bt < BT; ++bt)
-        if (lane == bt * RW + r) {
-          val = acc[r][bt];
-          partner = acc[r ^ 1][bt];
-        }
+    for (int bt = 0; bt < BT; ++bt)
+      if (lane == bt * RW + r) val = acc[r][bt];
+  if (KS > 1) {
+    // fixed-order sum of the KS partial results of this row group
+    __shared__ float part[kGroups][KS][32];
+    part[grp][kpart][lane] = val;
+    __syncthreads();
+    if (kpart == 0) {
+      val = 0.f;
+#pragma unroll
+      for (int kp = 0; kp < KS; ++kp) val += part[grp][kp][lane];
+    }
+  }
+  if (active && kpart == 0) {
+    const float partner = __shfl_xor_sync(0xffffffffu, val, 1);   // the other row of the RoPE pair
     const int r = lane % RW, bt = lane / RW;
     const int n = row0 + r;
     if (lane < RW * BT && bt < nb && n < a.N) {
@@ -208,10 +224,11 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_kernel(const GemvArgs a) {
   }
 }
 
-template <int BT, int RW, int EPI>
+template <int BT, int RW, int EPI, int KS>
 cudaError_t launch_one(const GemvArgs& a, cudaStream_t s, bool pdl) {
+  constexpr int rows_per_block = RW * (kGemvWarps / KS);
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((a.N + RW * kGemvWarps - 1) / (RW * kGemvWarps), (a.M + BT - 1) / BT, 1);
+  cfg.gridDim = dim3((a.N + rows_per_block - 1) / rows_per_block, (a.M + BT - 1) / BT, 1);
   cfg.blockDim = dim3(kGemvThreads, 1, 1);
   cfg.dynamicSmemBytes = 0;
   cfg.stream = s;
@@ -220,20 +237,48 @@ cudaError_t launch_one(const GemvArgs& a, cudaStream_t s, bool pdl) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl ? 1 : 0;
-  return cudaLaunchKernelEx(&cfg, gemv_kernel<BT, RW, EPI>, a);
+  return cudaLaunchKernelEx(&cfg, gemv_kernel<BT, RW, EPI, KS>, a);
+}
+
+template <int BT, int EPI>
+cudaError_t launch_ks(const GemvArgs& a, cudaStream_t s, bool pdl) {
+  // Split K over the warps of a block until there are enough blocks to fill
+  // the GPU several times over (148 SMs x ~4 resident blocks).
+  const int nch = a.K >> 8;
+  const long long tiles = (a.M + BT - 1) / BT;
+  int ks = 1;
+  while (ks < 8 && ks * 2 <= nch && tiles * ((a.N + 4 * (8 / ks) - 1) / (4 * (8 / ks))) < 4 * 148 * 3) ks *= 2;
+  if (a.ks_override > 0) ks = a.ks_override;
+  if (BT == 1 && a.rw_override == 8 && (a.N & 7) == 0) {
+    switch (ks) {
+      case 1: return launch_one<1, 8, EPI, 1>(a, s, pdl);
+      case 2: return launch_one<1, 8, EPI, 2>(a, s, pdl);
+      case 4: return launch_one<1, 8, EPI, 4>(a, s, pdl);
+      default: return launch_one<1, 8, EPI, 8>(a, s, pdl);
+    }
+  }
+  switch (ks) {
+    case 1: return launch_one<BT, 4, EPI, 1>(a, s, pdl);
+    case 2: return launch_one<BT, 4, EPI, 2>(a, s, pdl);
+    case 4: return launch_one<BT, 4, EPI, 4>(a, s, pdl);
+    default: return launch_one<BT, 4, EPI, 8>(a, s, pdl);
+  }
 }
 
 template <int EPI>
 cudaError_t launch_epi(const GemvArgs& a, cudaStream_t s, bool pdl) {
-  if (a.M == 1) return launch_one<1, 4, EPI>(a, s, pdl);
-  if (a.M == 2) return launch_one<2, 4, EPI>(a, s, pdl);
-  return launch_one<4, 4, EPI>(a, s, pdl);
+  if (a.M == 1) return launch_ks<1, EPI>(a, s, pdl);
+  if (a.M == 2) return launch_ks<2, EPI>(a, s, pdl);
+  return launch_ks<4, EPI>(a, s, pdl);
 }
 
 }  // namespace
 
 cudaError_t launch_gemv(GemvEpilogue epi, const GemvArgs& a, cudaStream_t s, bool pdl) {
-  if (a.M <= 0 || a.N <= 0 || a.K <= 0 || (a.K & 255) != 0) return cudaErrorInvalidValue;
+  if (a.M <= 0 || a.N <= 0 || a.K <= 0 || (a.K & 255) != 0 || (a.N & 3) != 0) return cudaErrorInvalidValue;
+  if (a.ks_override != 0 && a.ks_override != 1 && a.ks_override != 2 && a.ks_override != 4 &&
+      a.ks_override != 8)
+    return cudaErrorInvalidValue;
   switch (epi) {
     case kEpiInProj: return launch_epi<kEpiInProj>(a, s, pdl);
     case kEpiOut: return launch_epi<kEpiOut>(a, s, pdl);

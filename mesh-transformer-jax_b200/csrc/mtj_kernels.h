@@ -55,6 +55,8 @@ struct GemvArgs {
   float* logits;
   int ld_logits;
   const int32_t* row_select;   // optional [M]: source row of x / stats for output row m
+  int ks_override;             // 0 = pick the K split from the shape; 1/2/4/8 = force it
+  int rw_override;             // 0 = default rows per warp group; 8 = eight rows (single-token launches)
 };
 
 cudaError_t launch_gemv(GemvEpilogue epi, const GemvArgs& a, cudaStream_t s, bool pdl);

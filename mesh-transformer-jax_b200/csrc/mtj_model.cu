@@ -102,6 +102,14 @@ struct mtj_handle {
   int64_t launches = 0;
   bool use_pdl = true;
 
+  // decode step captured once per batch size and replayed (the step counter,
+  // tokens and page table live on the device, so the graph never changes)
+  bool use_graph = true;
+  cudaStream_t capture_stream = nullptr;
+  cudaGraphExec_t graph_exec = nullptr;
+  int graph_batch = 0;
+  int64_t graph_kernels = 0;
+
   // optional per-family kernel timing (mtj_profile_*): events around launches
   bool profile = false;
   std::vector<cudaEvent_t> ev_pool;
@@ -372,6 +380,7 @@ int32_t forward_chunks(mtj_handle* h, const uint32_t* ids, int ids_ld, int batch
 extern "C" {
 
 const char* mtj_last_error(void) { return g_last_error.c_str(); }
+int32_t mtj_set_error(int32_t code, const char* msg) { return fail(code, msg ? msg : ""); }
 int32_t mtj_version(void) { return 1; }
 
 int32_t mtj_create(const mtj_config* c, mtj_handle** out) {
@@ -419,13 +428,18 @@ int32_t mtj_create(const mtj_config* c, mtj_handle** out) {
   h->expected = 2 + 10LL * h->L + 4;
   const char* e = getenv("MTJ_NO_PDL");
   h->use_pdl = !(e && e[0] == '1');
+  e = getenv("MTJ_NO_GRAPH");
+  h->use_graph = !(e && e[0] == '1');
   *out = h;
   return MTJ_OK;
 }
 
 int32_t mtj_destroy(mtj_handle* h) {
-  if (h)
+  if (h) {
     for (cudaEvent_t e : h->ev_pool) cudaEventDestroy(e);
+    if (h->graph_exec) cudaGraphExecDestroy(h->graph_exec);
+    if (h->capture_stream) cudaStreamDestroy(h->capture_stream);
+  }
   delete h;
   return MTJ_OK;
 }
@@ -627,25 +641,60 @@ int32_t mtj_decode_step(mtj_handle* h, const uint32_t* tokens_in, const float* t
   const int B = h->batch;
   if (tokens_in)
     MTJ_CUDA(cudaMemcpyAsync(h->tokens, tokens_in, sizeof(uint32_t) * B, cudaMemcpyDeviceToDevice, s));
-  mtj::RowMap rows = {0, 1, 0, h->cur};
-  mtj::RowMap erows = {0, 1, 0, nullptr};
-  rc = run_embed(h, h->tokens, 1, B, erows, true, s);
-  if (rc) return rc;
-  for (int l = 0; l < h->L; ++l) {
-    rc = run_layer(h, l, B, rows, true, nullptr, s);
+  auto enqueue = [&](cudaStream_t st) -> int32_t {
+    mtj::RowMap rows = {0, 1, 0, h->cur};
+    mtj::RowMap erows = {0, 1, 0, nullptr};
+    int32_t r = run_embed(h, h->tokens, 1, B, erows, true, st);
+    if (r) return r;
+    for (int l = 0; l < h->L; ++l) {
+      r = run_layer(h, l, B, rows, true, nullptr, st);
+      if (r) return r;
+    }
+    r = run_logits(h, B, nullptr, h->logits, true, st);
+    if (r) return r;
+    mtj::ArgmaxArgs am = {};
+    am.logits = h->logits;
+    am.B = B;
+    am.V = h->Vl;
+    am.tokens = h->tokens;
+    am.tokens_copy = nullptr;
+    am.cur_dev = h->cur;
+    MTJ_CUDA(mtj::launch_argmax(am, st, h->use_pdl));
+    h->launches++;
+    return MTJ_OK;
+  };
+  if (h->use_graph && !h->profile) {
+    if (h->graph_exec == nullptr || h->graph_batch != B) {
+      if (h->graph_exec) {
+        cudaGraphExecDestroy(h->graph_exec);
+        h->graph_exec = nullptr;
+      }
+      if (!h->capture_stream) MTJ_CUDA(cudaStreamCreateWithFlags(&h->capture_stream, cudaStreamNonBlocking));
+      const int64_t before = h->launches;
+      MTJ_CUDA(cudaStreamBeginCapture(h->capture_stream, cudaStreamCaptureModeThreadLocal));
+      rc = enqueue(h->capture_stream);
+      cudaGraph_t graph = nullptr;
+      cudaError_t ce = cudaStreamEndCapture(h->capture_stream, &graph);
+      h->graph_kernels = h->launches - before;
+      h->launches = before;
+      if (rc) {
+        if (graph) cudaGraphDestroy(graph);
+        return rc;
+      }
+      if (ce != cudaSuccess) return fail(MTJ_ERR_CUDA, std::string("graph capture: ") + cudaGetErrorString(ce));
+      ce = cudaGraphInstantiate(&h->graph_exec, graph, 0);
+      cudaGraphDestroy(graph);
+      if (ce != cudaSuccess) return fail(MTJ_ERR_CUDA, std::string("graph instantiate: ") + cudaGetErrorString(ce));
+      h->graph_batch = B;
+    }
+    MTJ_CUDA(cudaGraphLaunch(h->graph_exec, s));
+    h->launches += h->graph_kernels;
+  } else {
+    rc = enqueue(s);
     if (rc) return rc;
   }
-  rc = run_logits(h, B, nullptr, h->logits, true, s);
-  if (rc) return rc;
-  mtj::ArgmaxArgs am = {};
-  am.logits = h->logits;
-  am.B = B;
-  am.V = h->Vl;
-  am.tokens = h->tokens;
-  am.tokens_copy = tokens_out;
-  am.cur_dev = h->cur;
-  MTJ_CUDA(mtj::launch_argmax(am, s, h->use_pdl));
-  h->launches++;
+  if (tokens_out)
+    MTJ_CUDA(cudaMemcpyAsync(tokens_out, h->tokens, sizeof(uint32_t) * B, cudaMemcpyDeviceToDevice, s));
   if (logits_out)
     MTJ_CUDA(cudaMemcpyAsync(logits_out, h->logits, sizeof(float) * B * h->Vl, cudaMemcpyDeviceToDevice, s));
   h->steps_done++;
