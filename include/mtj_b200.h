@@ -182,6 +182,27 @@ int32_t mtj_k_ln_gemv(const void* w_dev, const float* x_dev, const float* stats_
                       int32_t M, int32_t N, int32_t K, int32_t k_split, int32_t rows_per_group,
                       float* out_dev, mtj_stream s);
 
+/* No counterpart in the reference.  The same attention as mtj_k_decode_attn
+ * for callers that can neither pass scratch memory nor tolerate an allocation
+ * inside the library (custom-call handlers with framework-planned buffers,
+ * processes whose GPU memory is already reserved by another runtime, loops
+ * that cannot afford the device synchronisation an allocation implies).  The
+ * scratch is a fixed MTJ_NOALLOC_SCRATCH_BYTES array inside the library image,
+ * resident on every GPU that loads the library until the process exits; the
+ * call allocates nothing.  Shapes whose scratch need
+ * (mtj_k_decode_attn_scratch_bytes) exceeds that size are rejected with
+ * MTJ_ERR_INVALID.  The first call on each device looks the array's device
+ * address up (with that device current) and should therefore be made before
+ * any stream capture begins.  All calls on a device share the one array: two
+ * calls whose kernels can overlap on the GPU (different streams) race; calls
+ * on one stream are safe, each call re-initialising what it needs. */
+#define MTJ_NOALLOC_SCRATCH_BYTES (4 * 1024 * 1024)
+int32_t mtj_k_decode_attn_noalloc(const float* q_dev, const void* kpool_dev, const void* vpool_dev,
+                                  const int32_t* page_table_dev, const int32_t* pad_dev,
+                                  const int32_t* cur_dev, int32_t batch, int32_t heads, int32_t d_head,
+                                  int32_t window, int32_t ring_pages, int32_t split_tokens,
+                                  float* out_dev, int32_t ld_out, mtj_stream s);
+
 #ifdef __cplusplus
 }
 #endif
