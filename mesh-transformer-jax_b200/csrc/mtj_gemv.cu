@@ -247,7 +247,7 @@ cudaError_t launch_ks(const GemvArgs& a, cudaStream_t s, bool pdl) {
   const int nch = a.K >> 8;
   const long long tiles = (a.M + BT - 1) / BT;
   int ks = 1;
-  while (ks < 8 && ks * 2 <= nch && tiles * ((a.N + 4 * (8 / ks) - 1) / (4 * (8 / ks))) < 4 * 148 * 3) ks *= 2;
+  while (ks < 8 && ks * 2 <= nch && tiles * ((a.N + 4 * (8 / ks) - 1) / (4 * (8 / ks))) < 148 * 6) ks *= 2;
   if (a.ks_override > 0) ks = a.ks_override;
   if (BT == 1 && a.rw_override == 8 && (a.N & 7) == 0) {
     switch (ks) {

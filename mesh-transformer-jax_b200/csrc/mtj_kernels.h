@@ -56,6 +56,7 @@ struct GemvArgs {
   int ld_logits;
   const int32_t* row_select;   // optional [M]: source row of x / stats for output row m
   int ks_override;             // 0 = pick the K split from the shape; 1/2/4/8 = force it
+  uint32_t* dev_err;           // device error word (bounded waits that ran out), may be null
   int rw_override;             // 0 = default rows per warp group; 8 = eight rows (single-token launches)
 };
 

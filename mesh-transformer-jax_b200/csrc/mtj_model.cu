@@ -211,6 +211,7 @@ int32_t run_layer(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, bool
   a.q_out = h->q;
   a.act2 = h->act2;
   a.kv = h->kv(layer);
+  a.dev_err = h->dev_err;
   h->prof_begin(MTJ_FAMILY_INPROJ, s);
   MTJ_CUDA(mtj::launch_gemv(mtj::kEpiInProj, a, s, pdl));
   h->prof_end(s);
@@ -272,6 +273,7 @@ int32_t run_layer(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, bool
   o.out = h->x;
   o.stats_out = h->stats;
   o.counters = h->gemv_counters;
+  o.dev_err = h->dev_err;
   h->prof_begin(MTJ_FAMILY_OUTPROJ, s);
   MTJ_CUDA(mtj::launch_gemv(mtj::kEpiOut, o, s, pdl));
   h->prof_end(s);
@@ -315,6 +317,7 @@ int32_t run_logits(mtj_handle* h, int M, const int32_t* row_select, float* out, 
   a.logits = out;
   a.ld_logits = h->Vl;
   a.row_select = row_select;
+  a.dev_err = h->dev_err;
   h->prof_begin(MTJ_FAMILY_LOGITS, s);
   MTJ_CUDA(mtj::launch_gemv(mtj::kEpiLogits, a, s, h->use_pdl && decode));
   h->prof_end(s);
