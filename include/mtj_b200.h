@@ -83,10 +83,14 @@ int32_t mtj_bind_arenas(mtj_handle* h, void* weights_dev, int64_t weights_bytes,
 int32_t mtj_load_param(mtj_handle* h, const char* name, const void* src_dev,
                        int32_t dtype, int32_t ndim, const int64_t* shape, mtj_stream s);
 
-/* Tensor-parallel plumbing standing in for jax.lax.psum / all_gather on the
- * "shard" axis (util.py:134-136; layers.py:193,313,565).  `nccl_comm` is an
- * ncclComm_t created by the host for (rank, cores_per_replica). */
-int32_t mtj_set_nccl(mtj_handle* h, void* nccl_comm);
+/* Tensor-parallel plumbing standing in for jax.lax.psum / pmax / all_gather on
+ * the "shard" axis (util.py:134-136; layers.py:193,313,565,575-585): one NCCL
+ * communicator over the cores_per_replica ranks.  Rank 0 obtains a 128-byte id
+ * with mtj_comm_unique_id, the host distributes it, every rank calls
+ * mtj_comm_init (collective; blocks until all ranks have joined).  NCCL is
+ * looked up in the process at run time (libnccl.so.2).  Not needed for mp == 1. */
+int32_t mtj_comm_unique_id(uint8_t* out128);
+int32_t mtj_comm_init(mtj_handle* h, const uint8_t* id128);
 
 /* generate_initial (transformer_shard.py:74-95) for `batch` left-padded
  * contexts: prefills ctx[:, :-1] into the KV cache, keeps ctx[:, -1] as the

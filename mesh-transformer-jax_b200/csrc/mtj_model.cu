@@ -11,6 +11,7 @@
 #include <vector>
 
 #include "../../include/mtj_b200.h"
+#include "mtj_comm.h"
 #include "mtj_common.cuh"
 #include "mtj_kernels.h"
 
@@ -82,7 +83,11 @@ struct mtj_handle {
   float* part_ml = nullptr;
   uint32_t* counters = nullptr;     // attention + gemv tickets (zeroed at bind)
   uint32_t* gemv_counters = nullptr;
-  float* logits = nullptr;          // [max_batch, Vl]
+  float* logits = nullptr;          // [max_batch, Vl] this shard's logits
+  float* logits_all = nullptr;      // [max_batch, V]  (== logits when mp == 1)
+  float* logits_gather = nullptr;   // [mp, max_batch, Vl] all-gather landing zone (mp > 1)
+  float* part = nullptr;            // [max_rows, d] this shard's partial sums before the all-reduce (mp > 1)
+  void* comm = nullptr;             // ncclComm_t over the "shard" axis
   uint32_t* tokens = nullptr;       // [max_batch] next decode input
   int32_t* cur = nullptr;           // absolute position of the next decode token
   int32_t* pad = nullptr;           // [max_batch]
@@ -157,6 +162,12 @@ struct mtj_handle {
     counters = c.take<uint32_t>(static_cast<int64_t>(max_batch) * heads);
     gemv_counters = c.take<uint32_t>(R);
     logits = c.take<float>(static_cast<int64_t>(std::max(max_batch, 1)) * Vl);
+    logits_all = logits;
+    if (mp > 1) {
+      logits_all = c.take<float>(static_cast<int64_t>(max_batch) * V);
+      logits_gather = c.take<float>(static_cast<int64_t>(max_batch) * V);
+      part = c.take<float>(R * d);
+    }
     tokens = c.take<uint32_t>(max_batch);
     cur = c.take<int32_t>(4);
     pad = c.take<int32_t>(max_batch);
@@ -183,6 +194,17 @@ struct mtj_handle {
 namespace {
 
 using mtj::GemvArgs;
+
+// g_psum of the [M, d] partial sums in h->part, then x (+)= sum and the LN statistics.
+int32_t reduce_into_x(mtj_handle* h, int M, bool accumulate, bool pdl, cudaStream_t s) {
+  if (!h->comm) return fail(MTJ_ERR_STATE, "cores_per_replica > 1 needs mtj_comm_init first");
+  std::string err;
+  if (mtj::comm_all_reduce(h->comm, h->part, static_cast<size_t>(M) * h->d, false, s, &err))
+    return fail(MTJ_ERR_COMM, err);
+  MTJ_CUDA(mtj::launch_residual_stats(h->x, h->part, h->stats, M, h->d, accumulate, s, pdl));
+  h->launches += 2;
+  return MTJ_OK;
+}
 
 // One transformer layer over a chunk of rows already in h->x (+ h->stats):
 // x <- x + attn(LN(x)) + ff(LN(x))  (layers.py:299-313 / :316-344 / :347-366).
@@ -269,15 +291,16 @@ int32_t run_layer(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, bool
   o.ldx = h->dl + h->ffl;
   o.rows = rows;
   o.bias = lw.b_out;
-  o.residual = h->x;
-  o.out = h->x;
-  o.stats_out = h->stats;
+  o.residual = h->mp == 1 ? h->x : nullptr;
+  o.out = h->mp == 1 ? h->x : h->part;
+  o.stats_out = h->mp == 1 ? h->stats : nullptr;
   o.counters = h->gemv_counters;
   o.dev_err = h->dev_err;
   h->prof_begin(MTJ_FAMILY_OUTPROJ, s);
   MTJ_CUDA(mtj::launch_gemv(mtj::kEpiOut, o, s, pdl));
   h->prof_end(s);
   h->launches++;
+  if (h->mp > 1) return reduce_into_x(h, M, true, pdl, s);
   return MTJ_OK;
 }
 
@@ -293,10 +316,11 @@ int32_t run_embed(mtj_handle* h, const uint32_t* ids, int ids_ld, int M, const m
   e.vocab_start = h->rank * h->Vl;
   e.table = h->emb_w;
   e.bias = h->emb_b;
-  e.x = h->x;
-  e.stats = h->stats;
+  e.x = h->mp == 1 ? h->x : h->part;
+  e.stats = h->mp == 1 ? h->stats : nullptr;
   MTJ_CUDA(mtj::launch_embed(e, s, h->use_pdl && decode));
   h->launches++;
+  if (h->mp > 1) return reduce_into_x(h, M, false, h->use_pdl && decode, s);
   return MTJ_OK;
 }
 
@@ -441,6 +465,7 @@ int32_t mtj_destroy(mtj_handle* h) {
   if (h) {
     for (cudaEvent_t e : h->ev_pool) cudaEventDestroy(e);
     if (h->graph_exec) cudaGraphExecDestroy(h->graph_exec);
+    if (h->comm) mtj::comm_destroy(h->comm);
     if (h->capture_stream) cudaStreamDestroy(h->capture_stream);
   }
   delete h;
@@ -595,18 +620,27 @@ int32_t mtj_load_param(mtj_handle* h, const char* name, const void* src, int32_t
   return MTJ_OK;
 }
 
-int32_t mtj_set_nccl(mtj_handle* h, void* comm) {
-  (void)comm;
-  if (!h) return fail(MTJ_ERR_INVALID, "null handle");
+int32_t mtj_comm_unique_id(uint8_t* out128) {
+  if (!out128) return fail(MTJ_ERR_INVALID, "null argument");
+  std::string err;
+  if (mtj::comm_unique_id(out128, &err)) return fail(MTJ_ERR_COMM, err);
+  return MTJ_OK;
+}
+
+int32_t mtj_comm_init(mtj_handle* h, const uint8_t* id128) {
+  if (!h || !id128) return fail(MTJ_ERR_INVALID, "null argument");
   if (h->mp == 1) return MTJ_OK;
-  return fail(MTJ_ERR_UNSUPPORTED, "tensor-parallel execution is not wired yet");
+  if (h->comm) return fail(MTJ_ERR_STATE, "communicator already initialised");
+  std::string err;
+  if (mtj::comm_init(id128, h->rank, h->mp, &h->comm, &err)) return fail(MTJ_ERR_COMM, err);
+  return MTJ_OK;
 }
 
 int32_t mtj_prefill(mtj_handle* h, const uint32_t* ctx, const uint32_t* ctx_len, int32_t batch,
                     mtj_stream stream) {
   int32_t rc = check_ready(h);
   if (rc) return rc;
-  if (h->mp != 1) return fail(MTJ_ERR_UNSUPPORTED, "tensor-parallel execution is not wired yet");
+  if (h->mp > 1 && !h->comm) return fail(MTJ_ERR_STATE, "cores_per_replica > 1 needs mtj_comm_init first");
   if (!ctx || !ctx_len || batch <= 0 || batch > h->max_batch) return fail(MTJ_ERR_INVALID, "bad batch");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   std::vector<int32_t> pad(batch), limit(batch, 0x7fffffff);
@@ -655,10 +689,18 @@ int32_t mtj_decode_step(mtj_handle* h, const uint32_t* tokens_in, const float* t
     }
     r = run_logits(h, B, nullptr, h->logits, true, st);
     if (r) return r;
+    if (h->mp > 1) {
+      // all_gather + transpose + flatten of ProjectionShard.__call__ (layers.py:565-567)
+      std::string err;
+      if (mtj::comm_all_gather(h->comm, h->logits, h->logits_gather, static_cast<size_t>(B) * h->Vl, st, &err))
+        return fail(MTJ_ERR_COMM, err);
+      MTJ_CUDA(mtj::launch_gather_rows(h->logits_gather, h->logits_all, h->mp, B, h->Vl, st));
+      h->launches += 2;
+    }
     mtj::ArgmaxArgs am = {};
-    am.logits = h->logits;
+    am.logits = h->logits_all;
     am.B = B;
-    am.V = h->Vl;
+    am.V = h->V;
     am.tokens = h->tokens;
     am.tokens_copy = nullptr;
     am.cur_dev = h->cur;
@@ -699,7 +741,7 @@ int32_t mtj_decode_step(mtj_handle* h, const uint32_t* tokens_in, const float* t
   if (tokens_out)
     MTJ_CUDA(cudaMemcpyAsync(tokens_out, h->tokens, sizeof(uint32_t) * B, cudaMemcpyDeviceToDevice, s));
   if (logits_out)
-    MTJ_CUDA(cudaMemcpyAsync(logits_out, h->logits, sizeof(float) * B * h->Vl, cudaMemcpyDeviceToDevice, s));
+    MTJ_CUDA(cudaMemcpyAsync(logits_out, h->logits_all, sizeof(float) * B * h->V, cudaMemcpyDeviceToDevice, s));
   h->steps_done++;
   return MTJ_OK;
 }
@@ -708,7 +750,7 @@ int32_t mtj_forward_logits(mtj_handle* h, const uint32_t* obs, const uint32_t* c
                            int32_t T, int32_t n_last, float* logits_out, mtj_stream stream) {
   int32_t rc = check_ready(h);
   if (rc) return rc;
-  if (h->mp != 1) return fail(MTJ_ERR_UNSUPPORTED, "tensor-parallel execution is not wired yet");
+  if (h->mp > 1 && !h->comm) return fail(MTJ_ERR_STATE, "cores_per_replica > 1 needs mtj_comm_init first");
   if (!obs || !logits_out || batch <= 0 || batch > h->max_batch) return fail(MTJ_ERR_INVALID, "bad batch");
   if (T <= 0 || T > h->ring_pages * mtj::kPageTokens || T > h->max_pos)
     return fail(MTJ_ERR_INVALID, "T exceeds the KV capacity");

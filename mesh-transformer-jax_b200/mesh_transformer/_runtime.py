@@ -47,6 +47,15 @@ def param_shapes(config: dict) -> dict:
     return s
 
 
+def gather_vocab_shards(local: torch.Tensor) -> torch.Tensor:
+    """all_gather + transpose + flatten of ProjectionShard.__call__
+    (layers.py:565-567): [..., V/mp] per rank -> [..., V], shard-major."""
+    import torch.distributed as dist
+    parts = [torch.empty_like(local) for _ in range(dist.get_world_size())]
+    dist.all_gather(parts, local.contiguous())
+    return torch.cat(parts, dim=-1)
+
+
 class ShardRuntime:
     """One shard (rank) of the model on one GPU."""
 
@@ -76,6 +85,24 @@ class ShardRuntime:
             check(lib.mtj_bind_arenas(self._h, self._aligned(self.weights_arena), wb,
                                       self._aligned(self.workspace), sb, self.stream))
         self.vocab_local = config["n_vocab"] // self.mp
+        if self.mp > 1:
+            self._init_comm()
+
+    def _init_comm(self) -> None:
+        """One NCCL communicator over the shard axis; the id travels through
+        the torch.distributed world the processes were launched in."""
+        import torch.distributed as dist
+        assert dist.is_initialized() and dist.get_world_size() == self.mp, \
+            "cores_per_replica > 1 needs one torch.distributed process per shard"
+        uid = (ctypes.c_uint8 * 128)()
+        if self.rank == 0:
+            check(lib.mtj_comm_unique_id(uid))
+        on_gpu = dist.get_backend() == "nccl"
+        t = torch.tensor(list(uid), dtype=torch.uint8, device=self.device if on_gpu else "cpu")
+        dist.broadcast(t, src=0)
+        uid = (ctypes.c_uint8 * 128)(*t.cpu().tolist())
+        with torch.cuda.device(self.device):
+            check(lib.mtj_comm_init(self._h, uid))
 
     @staticmethod
     def _aligned(t: torch.Tensor) -> int:
@@ -136,6 +163,8 @@ class ShardRuntime:
         lens = None if ctx_length is None else _lib.u32_array(list(ctx_length))
         check(lib.mtj_forward_logits(self._h, obs_dev.data_ptr(), lens, B, T, n_last, out.data_ptr(),
                                      self.stream))
+        if self.mp > 1:
+            out = gather_vocab_shards(out)
         return out
 
     def embed(self, ids_dev: torch.Tensor):

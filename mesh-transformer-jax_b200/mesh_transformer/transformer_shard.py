@@ -178,7 +178,8 @@ class CausalTransformer:
             toks = torch.empty((gen_length, batch), dtype=torch.int32, device=self.device)
             logits = None
             if return_logits:
-                logits = torch.empty((gen_length, batch, rt.vocab_local), dtype=torch.float32, device=self.device)
+                logits = torch.empty((gen_length, batch, self.config["n_vocab"]), dtype=torch.float32,
+                                     device=self.device)
             shard = CausalTransformerShard(self.config, runtime=rt)
             shard.generate_initial(ctx_dev, lengths)
             for t in range(gen_length):

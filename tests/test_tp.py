@@ -1,0 +1,38 @@
+"""The shard axis: host helpers as gloo ranks on CPU, the model on 2 GPUs."""
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _run(nproc, env_extra, timeout):
+    env = dict(os.environ, **env_extra)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), os.path.join(HERE, "tp_worker.py")]
+    p = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
+    assert p.returncode == 0 and "TP_OK" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
+
+
+def test_shard_axis_host_helpers_on_two_cpu_ranks():
+    import __graft_entry__ as ge
+    ge.build()
+    _run(2, {"MTJ_TP_CPU": "1"}, 300)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("mp", [2, 4])
+def test_tensor_parallel_generate_matches_oracle(mp):
+    import torch
+    if torch.cuda.device_count() < mp:
+        pytest.skip(f"needs {mp} GPUs")
+    _run(mp, {}, 600)

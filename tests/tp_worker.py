@@ -1,0 +1,78 @@
+"""Tensor-parallel parity worker: run under torch.distributed.run with one
+process per GPU (or, with MTJ_TP_CPU=1, as gloo ranks on CPU for the host-side
+helpers only).  Rank 0 prints TP_OK when everything matched the oracle."""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+for p in (ROOT, os.path.join(ROOT, "mesh-transformer-jax_b200")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+from oracle import gptj_oracle as go  # noqa: E402
+from oracle import spec  # noqa: E402
+
+
+def cpu_checks(rank, world):
+    from mesh_transformer._runtime import gather_vocab_shards
+    from mesh_transformer.util import g_psum
+    x = torch.full((3,), float(rank + 1))
+    assert torch.equal(g_psum(x), torch.full((3,), float(sum(range(1, world + 1)))))
+    assert torch.equal(x, torch.full((3,), float(rank + 1)))          # input untouched
+    local = torch.arange(4, dtype=torch.float32).reshape(1, 4) + 10 * rank
+    full = gather_vocab_shards(local)
+    assert full.shape == (1, 4 * world) and full[0, 4 * (world - 1)].item() == 10 * (world - 1)
+    from mesh_transformer.transformer_shard import _world
+    assert _world() == (rank, world)
+
+
+def gpu_checks(rank, world):
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+    from mesh_transformer.transformer_shard import CausalTransformer
+    cfg = spec.tiny_config(world, seq=64)
+    full = spec.full_weights(cfg, seed=5, stress=True)
+    params = spec.shard_params(cfg, full)
+    lens = np.array([64, 30], np.uint32)
+    ctx = np.zeros((2, 64), np.uint32)
+    for b in range(2):
+        ctx[b, 64 - lens[b]:] = spec.token_ids(10 + b, 1, int(lens[b]), 512)[0]
+    net = CausalTransformer(dict(cfg), init_weights=False)
+    net.state = {"params": params, "step": np.array(0)}
+    _, out = net.generate(ctx, lens, 32, {"top_p": np.zeros(2), "temp": np.ones(2)}, return_logits=True)
+    ids = spec.token_ids(0, 2, 64, 512)
+    rt = net._runtime(2, 32)
+    fl = rt.forward_logits(torch.from_numpy(ids.view(np.int32)).cuda(), None, 64).cpu().numpy()
+    net._rt.check_device_status()
+    if rank == 0:
+        ref_net = go.CausalTransformer(cfg, params)
+        _, ref = ref_net.generate(ctx, lens, 32, return_logits=True)
+        rel = lambda a, b: float(np.abs(a - b).max() / np.abs(b).max())
+        assert rel(out[2], ref[2]) <= 2e-2, rel(out[2], ref[2])
+        assert np.array_equal(out[0], ref[0]), "greedy ids differ"
+        shard = go.CausalTransformerShard(cfg, params)
+        for b in range(2):
+            assert rel(fl[b], shard.logits(ids[b])) <= 2e-2
+    # every rank must have produced the same tokens (replicated sampler)
+    t = torch.from_numpy(out[0].astype(np.int64)).cuda()
+    ts = [torch.empty_like(t) for _ in range(world)]
+    dist.all_gather(ts, t)
+    assert all(torch.equal(ts[0], x) for x in ts)
+
+
+def main():
+    cpu = os.environ.get("MTJ_TP_CPU") == "1"
+    dist.init_process_group("gloo" if cpu else "nccl")
+    rank, world = dist.get_rank(), dist.get_world_size()
+    (cpu_checks if cpu else gpu_checks)(rank, world)
+    dist.barrier()
+    if rank == 0:
+        print("TP_OK", flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
