@@ -256,6 +256,11 @@ def run_mtj(args):
     rt.check_device_status()
     if rank == 0:
         sampler.stop()
+    # orderly, collective shutdown on every rank before rank 0 goes on to report
+    barrier()
+    rt.close()
+    if world > 1:
+        dist.destroy_process_group()
 
     if rank != 0:
         return
@@ -303,8 +308,6 @@ def run_mtj(args):
         line["cpu_baseline"] = {"value": r["value"], "unit": UNIT, "cores": r["cores"], "kind": "port",
                                 "sample": r["sample"]}
     print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
 
 
 def main():

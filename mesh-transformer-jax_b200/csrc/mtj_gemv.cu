@@ -56,15 +56,17 @@ __global__ void __launch_bounds__(kGemvThreads, BT == 1 ? (EPI == kEpiOut ? 4 : 
 #pragma unroll
     for (int bt = 0; bt < BT; ++bt) acc[r][bt] = 0.f;
 
-  const int nch = a.K >> 8;
+  const int nch = (a.K + 255) >> 8;             // the last chunk may be partial (K is a multiple of 8)
+  const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
   uint4 wnext[RW];
   if (active && kpart < nch) {
     // weights do not depend on the predecessor kernel: start streaming before the wait
 #pragma unroll
-    for (int r = 0; r < RW; ++r) wnext[r] = ld_stream16(wbase + static_cast<size_t>(r) * a.K + kpart * 256);
+    for (int r = 0; r < RW; ++r)
+      wnext[r] = (kpart * 256 + lane * 8 < a.K) ? ld_stream16(wbase + static_cast<size_t>(r) * a.K + kpart * 256) : zero4;
 #pragma unroll
     for (int r = 0; r < RW; ++r)
-      if (kpart + KS < nch) prefetch_l2(wbase + static_cast<size_t>(r) * a.K + (kpart + KS) * 256);
+      if ((kpart + KS) * 256 + lane * 8 < a.K) prefetch_l2(wbase + static_cast<size_t>(r) * a.K + (kpart + KS) * 256);
   }
   pdl_wait();
   pdl_launch_dependents();
@@ -89,11 +91,19 @@ __global__ void __launch_bounds__(kGemvThreads, BT == 1 ? (EPI == kEpiOut ? 4 : 
       for (int r = 0; r < RW; ++r) wcur[r] = wnext[r];
       if (c + KS < nch) {
 #pragma unroll
-        for (int r = 0; r < RW; ++r) wnext[r] = ld_stream16(wbase + static_cast<size_t>(r) * a.K + (c + KS) * 256);
+        for (int r = 0; r < RW; ++r)
+          wnext[r] = ((c + KS) * 256 + lane * 8 < a.K)
+                         ? ld_stream16(wbase + static_cast<size_t>(r) * a.K + (c + KS) * 256)
+                         : zero4;
       }
       const int k = c * 256;
+      const bool in_k = k + lane * 8 < a.K;       // lanes past the end of a partial chunk contribute zeros
       float sc[8], of[8];
-      if (kLN) {
+      if (kLN && !in_k) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sc[e] = of[e] = 0.f;
+      }
+      if (kLN && in_k) {
         const float4 s0 = *reinterpret_cast<const float4*>(a.ln_scale + k + lane * 8);
         const float4 s1 = *reinterpret_cast<const float4*>(a.ln_scale + k + lane * 8 + 4);
         const float4 o0 = *reinterpret_cast<const float4*>(a.ln_offset + k + lane * 8);
@@ -106,8 +116,9 @@ __global__ void __launch_bounds__(kGemvThreads, BT == 1 ? (EPI == kEpiOut ? 4 : 
       float xv[BT][8];
 #pragma unroll
       for (int bt = 0; bt < BT; ++bt) {
-        const float4 x0 = *reinterpret_cast<const float4*>(xr[bt] + k);
-        const float4 x1 = *reinterpret_cast<const float4*>(xr[bt] + k + 4);
+        const float4 zf = make_float4(0.f, 0.f, 0.f, 0.f);
+        const float4 x0 = in_k ? *reinterpret_cast<const float4*>(xr[bt] + k) : zf;
+        const float4 x1 = in_k ? *reinterpret_cast<const float4*>(xr[bt] + k + 4) : zf;
         xv[bt][0] = x0.x; xv[bt][1] = x0.y; xv[bt][2] = x0.z; xv[bt][3] = x0.w;
         xv[bt][4] = x1.x; xv[bt][5] = x1.y; xv[bt][6] = x1.z; xv[bt][7] = x1.w;
         if (kLN) {
@@ -244,7 +255,7 @@ template <int BT, int EPI>
 cudaError_t launch_ks(const GemvArgs& a, cudaStream_t s, bool pdl) {
   // Split K over the warps of a block until there are enough blocks to fill
   // the GPU several times over (148 SMs x ~4 resident blocks).
-  const int nch = a.K >> 8;
+  const int nch = (a.K + 255) >> 8;
   const long long tiles = (a.M + BT - 1) / BT;
   int ks = 1;
   while (ks < 8 && ks * 2 <= nch && tiles * ((a.N + 4 * (8 / ks) - 1) / (4 * (8 / ks))) < 148 * 6) ks *= 2;
@@ -275,7 +286,7 @@ cudaError_t launch_epi(const GemvArgs& a, cudaStream_t s, bool pdl) {
 }  // namespace
 
 cudaError_t launch_gemv(GemvEpilogue epi, const GemvArgs& a, cudaStream_t s, bool pdl) {
-  if (a.M <= 0 || a.N <= 0 || a.K <= 0 || (a.K & 255) != 0 || (a.N & 3) != 0) return cudaErrorInvalidValue;
+  if (a.M <= 0 || a.N <= 0 || a.K <= 0 || (a.K & 7) != 0 || (a.N & 3) != 0) return cudaErrorInvalidValue;
   if (a.ks_override != 0 && a.ks_override != 1 && a.ks_override != 2 && a.ks_override != 4 &&
       a.ks_override != 8)
     return cudaErrorInvalidValue;

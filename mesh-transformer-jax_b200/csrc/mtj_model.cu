@@ -423,8 +423,8 @@ int32_t mtj_create(const mtj_config* c, mtj_handle** out) {
   if (dh != 64 && dh != 256) return fail(MTJ_ERR_UNSUPPORTED, "d_head must be 64 or 256");
   const int rot = c->pe_rotary_dims > 0 ? c->pe_rotary_dims : dh;
   if (rot > dh || (rot & 1)) return fail(MTJ_ERR_INVALID, "pe_rotary_dims must be even and <= d_head");
-  if (c->d_model % 256) return fail(MTJ_ERR_UNSUPPORTED, "d_model must be a multiple of 256");
-  if ((5 * c->d_model / mp) % 256) return fail(MTJ_ERR_UNSUPPORTED, "5*d_model/mp must be a multiple of 256");
+  if (c->d_model % 8 || (c->d_model / mp) % 8) return fail(MTJ_ERR_UNSUPPORTED, "d_model / mp must be a multiple of 8");
+  if ((c->n_vocab / mp) % 4) return fail(MTJ_ERR_UNSUPPORTED, "n_vocab / mp must be a multiple of 4");
   if (c->max_batch <= 0 || c->max_gen < 0 || c->max_rows <= 0) return fail(MTJ_ERR_INVALID, "bad capacity");
 
   mtj_handle* h = new mtj_handle();
@@ -457,6 +457,7 @@ int32_t mtj_create(const mtj_config* c, mtj_handle** out) {
   h->use_pdl = !(e && e[0] == '1');
   e = getenv("MTJ_NO_GRAPH");
   h->use_graph = !(e && e[0] == '1');
+
   *out = h;
   return MTJ_OK;
 }
@@ -633,6 +634,18 @@ int32_t mtj_comm_init(mtj_handle* h, const uint8_t* id128) {
   if (h->comm) return fail(MTJ_ERR_STATE, "communicator already initialised");
   std::string err;
   if (mtj::comm_init(id128, h->rank, h->mp, &h->comm, &err)) return fail(MTJ_ERR_COMM, err);
+  if (h->bound) {
+    // first use of each collective sets connections up; do that here, outside any graph capture
+    cudaStream_t s = nullptr;
+    MTJ_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+    MTJ_CUDA(cudaMemsetAsync(h->part, 0, sizeof(float) * h->d, s));
+    int32_t rc = mtj::comm_all_reduce(h->comm, h->part, h->d, false, s, &err);
+    if (!rc) rc = mtj::comm_all_gather(h->comm, h->logits, h->logits_gather, h->Vl, s, &err);
+    cudaError_t ce = cudaStreamSynchronize(s);
+    cudaStreamDestroy(s);
+    if (rc) return fail(MTJ_ERR_COMM, err);
+    if (ce != cudaSuccess) return fail(MTJ_ERR_CUDA, std::string("collective warm-up: ") + cudaGetErrorString(ce));
+  }
   return MTJ_OK;
 }
 
@@ -708,7 +721,7 @@ int32_t mtj_decode_step(mtj_handle* h, const uint32_t* tokens_in, const float* t
     h->launches++;
     return MTJ_OK;
   };
-  if (h->use_graph && !h->profile) {
+  if (h->use_graph && !h->profile && (h->mp == 1 || h->steps_done > 0)) {
     if (h->graph_exec == nullptr || h->graph_batch != B) {
       if (h->graph_exec) {
         cudaGraphExecDestroy(h->graph_exec);

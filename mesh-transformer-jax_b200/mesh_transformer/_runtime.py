@@ -113,11 +113,20 @@ class ShardRuntime:
         return torch.cuda.current_stream(self.device).cuda_stream
 
     def close(self):
+        """Releases the handle.  With cores_per_replica > 1 this is collective:
+        every rank must call it (it tears the NCCL communicator down)."""
         if getattr(self, "_h", None) is not None and self._h:
+            torch.cuda.synchronize(self.device)
             lib.mtj_destroy(self._h)
             self._h = None
 
     def __del__(self):
+        # At interpreter shutdown the CUDA context and the peers of a collective
+        # communicator may already be gone: tearing the handle down then can
+        # block, so it is only done while the interpreter is alive.
+        import sys
+        if sys.is_finalizing():
+            return
         try:
             self.close()
         except Exception:

@@ -130,6 +130,13 @@ class CausalTransformer:
     def train(self, sample):
         raise NotImplementedError("training is outside the forward/decode path")
 
+    def close(self):
+        """Frees the device runtime (collective across shards when mp > 1)."""
+        if self._rt is not None:
+            self._rt.close()
+            self._rt = None
+            self._rt_caps = (0, 0)
+
     # -- runtime -------------------------------------------------------------
     def _runtime(self, batch: int, gen_length: int) -> ShardRuntime:
         cap_b, cap_g = self._rt_caps

@@ -35,4 +35,4 @@ def test_tensor_parallel_generate_matches_oracle(mp):
     import torch
     if torch.cuda.device_count() < mp:
         pytest.skip(f"needs {mp} GPUs")
-    _run(mp, {}, 600)
+    _run(mp, {"NCCL_DEBUG": "WARN"}, 240)

@@ -57,10 +57,12 @@ def gpu_checks(rank, world):
         for b in range(2):
             assert rel(fl[b], shard.logits(ids[b])) <= 2e-2
     # every rank must have produced the same tokens (replicated sampler)
-    t = torch.from_numpy(out[0].astype(np.int64)).cuda()
+    t = torch.from_numpy(np.ascontiguousarray(out[0]).astype(np.int64)).cuda()
     ts = [torch.empty_like(t) for _ in range(world)]
     dist.all_gather(ts, t)
     assert all(torch.equal(ts[0], x) for x in ts)
+    dist.barrier()
+    net.close()
 
 
 def main():
