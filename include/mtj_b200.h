@@ -157,6 +157,28 @@ int32_t mtj_check_device_status(mtj_handle* h, mtj_stream s);
 int32_t mtj_k_embed(mtj_handle* h, const uint32_t* ids_dev, int32_t rows,
                     float* x_out_dev, float* stats_out_dev, mtj_stream s);
 
+/* TransformerLayerShard.__call__ (layers.py:299-313), get_init_decode_state
+ * (:347-366) and decode_once (:316-344) of layer `layer`: x_dev [batch*T, d] f32
+ * is the layer input, out_dev receives g_psum(attn_out + dense_out) -- the
+ * residual is NOT added, as in the reference.  Row (b, t) sits at absolute
+ * position pos0 + t.  pad_host[b] (or NULL = 0) is the first visible key
+ * position (left padding, :353-360); key_limit_host[b] (or NULL) masks keys
+ * with position > limit (the eval mask, transformer_shard.py:130).  The
+ * layer's K/V for these rows are written to the cache; with decode != 0
+ * (T must be 1, :320) attention runs over the sliding window ending at pos0. */
+int32_t mtj_k_layer(mtj_handle* h, int32_t layer, const float* x_dev, int32_t batch, int32_t T, int32_t pos0,
+                    const int32_t* pad_host, const int32_t* key_limit_host, int32_t decode,
+                    float* out_dev, mtj_stream s);
+
+/* ProjectionShard.__call__ before the all-gather (layers.py:561-564):
+ * logits_out_dev [rows, n_vocab/mp] of this shard. */
+int32_t mtj_k_projection(mtj_handle* h, const float* x_dev, int32_t rows, float* logits_out_dev, mtj_stream s);
+
+/* ProjectionShard.loss with z_loss = 0 (layers.py:569-593): targets_dev [rows]
+ * uint32 -> loss_out_dev [rows] f32, correct_out_dev [rows] uint8. */
+int32_t mtj_k_projection_loss(mtj_handle* h, const float* x_dev, const uint32_t* targets_dev, int32_t rows,
+                              float* loss_out_dev, uint8_t* correct_out_dev, mtj_stream s);
+
 /* Single-query attention of decode_once over the paged bf16 KV cache
  * (layers.py:316-338 with self_attn :260-283, before the output projection):
  * q_dev [batch, heads*d_head] f32 (rotated, unscaled); kpool/vpool

@@ -111,6 +111,37 @@ struct ArgmaxArgs {
 };
 cudaError_t launch_argmax(const ArgmaxArgs& a, cudaStream_t s, bool pdl);
 
+struct SampleArgs {
+  const float* logits;         // [rows, V]
+  const float* uniforms;       // [rows, V] in [tiny, 1)
+  const float* top_p;          // [rows]
+  const float* temp;           // [rows]
+  int rows, V;                 // V <= 65535
+  void* scratch;               // sample_scratch_bytes(rows, V)
+  uint32_t* tokens;            // [rows]
+  uint32_t* tokens_copy;       // optional second destination
+  int32_t* cur_dev;            // incremented by one after the step (may be null)
+};
+int64_t sample_scratch_bytes(int rows, int vocab);
+cudaError_t launch_sample_top_p(const SampleArgs& a, cudaStream_t s, bool pdl);
+
+struct CeArgs {
+  const float* logits;         // [rows of this launch, vl] this shard's logits
+  int vl, vocab_start;
+  RowMap rows;                 // chunk geometry: row m -> (sequence, position)
+  int row0;                    // first chunk row covered by `logits`
+  int T;                       // targets / outputs are [batch, T]
+  const uint32_t* targets;
+  float* pmax;                 // [chunk rows] local (then global) max
+  float* psum;                 // [chunk rows, 2] sum of exp, target logit
+  uint8_t* hit;                // [chunk rows] target id lies in this shard's range
+  float* loss_out;             // [batch, T]
+  uint8_t* correct_out;        // [batch, T]
+};
+cudaError_t launch_ce_partial(const CeArgs& a, int rows, cudaStream_t s);
+cudaError_t launch_ce_rescale(const CeArgs& a, const float* lmax, int n, cudaStream_t s);
+cudaError_t launch_ce_finalize(const CeArgs& a, int n, cudaStream_t s);
+
 // [K, N] (reference layout, fp32 or bf16) -> bf16 [N, K] at dst + row offset.
 cudaError_t launch_pack_transpose(const void* src, int src_is_bf16, int K, int N,
                                   __nv_bfloat16* dst, int ld_dst, int k_offset, cudaStream_t s);

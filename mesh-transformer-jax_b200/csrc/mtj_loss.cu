@@ -1,0 +1,87 @@
+// Vocab-sharded softmax cross-entropy of ProjectionShard.loss (layers.py:569-593).
+//
+// ce_partial : per row of this shard's logits: local max, sum of exp(l - local
+//              max) and the target's logit if the target id falls into this
+//              shard's vocabulary range (the one-hot product of :578-579).
+// ce_rescale : after the cross-shard max (pmax, :575): sums rescaled to the
+//              global max, target logit shifted by it.
+// ce_finalize: after the cross-shard sums (:580,:585): loss = log(sum_exp) -
+//              target logit; correct = (shifted target logit == 0), i.e. the
+//              target holds the global maximum (:591).  z_loss is 0 in eval.
+#include <math.h>
+
+#include "mtj_common.cuh"
+#include "mtj_kernels.h"
+
+namespace mtj {
+namespace {
+
+constexpr int kThreads = 256;
+
+__device__ __forceinline__ float block_reduce(float v, float* red, bool is_max) {
+  v = is_max ? warp_max(v) : warp_sum(v);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = red[0];
+#pragma unroll
+  for (int i = 1; i < kThreads / 32; ++i) t = is_max ? fmaxf(t, red[i]) : t + red[i];
+  __syncthreads();
+  return t;
+}
+
+__global__ void __launch_bounds__(kThreads) ce_partial_kernel(const CeArgs a) {
+  __shared__ float red[kThreads / 32];
+  const int r = blockIdx.x;
+  const float* row = a.logits + static_cast<size_t>(r) * a.vl;
+  float m = -INFINITY;
+  for (int i = threadIdx.x; i < a.vl; i += kThreads) m = fmaxf(m, row[i]);
+  m = block_reduce(m, red, true);
+  float s = 0.f;
+  for (int i = threadIdx.x; i < a.vl; i += kThreads) s += expf(row[i] - m);
+  s = block_reduce(s, red, false);
+  if (threadIdx.x == 0) {
+    const int mrow = a.row0 + r;
+    const int b = a.rows.b0 + mrow / a.rows.Tc, t = a.rows.pos0_host + mrow % a.rows.Tc;
+    const int64_t local = static_cast<int64_t>(a.targets[static_cast<size_t>(b) * a.T + t]) - a.vocab_start;
+    const bool hit = local >= 0 && local < a.vl;
+    a.pmax[mrow] = m;
+    a.psum[2 * mrow] = s;
+    a.psum[2 * mrow + 1] = hit ? row[local] : 0.f;
+    a.hit[mrow] = hit ? 1 : 0;
+  }
+}
+
+__global__ void ce_rescale_kernel(const CeArgs a, const float* __restrict__ lmax, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float g = a.pmax[i];                 // global max after the all-reduce
+  a.psum[2 * i] = a.psum[2 * i] * expf(lmax[i] - g);
+  a.psum[2 * i + 1] = a.hit[i] ? a.psum[2 * i + 1] - g : 0.f;
+}
+
+__global__ void ce_finalize_kernel(const CeArgs a, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int b = a.rows.b0 + i / a.rows.Tc, t = a.rows.pos0_host + i % a.rows.Tc;
+  const float predicted = a.psum[2 * i + 1];
+  a.loss_out[static_cast<size_t>(b) * a.T + t] = logf(a.psum[2 * i]) - predicted;
+  a.correct_out[static_cast<size_t>(b) * a.T + t] = (predicted == 0.0f) ? 1 : 0;
+}
+
+}  // namespace
+
+cudaError_t launch_ce_partial(const CeArgs& a, int rows, cudaStream_t s) {
+  ce_partial_kernel<<<rows, kThreads, 0, s>>>(a);
+  return cudaGetLastError();
+}
+cudaError_t launch_ce_rescale(const CeArgs& a, const float* lmax, int n, cudaStream_t s) {
+  ce_rescale_kernel<<<(n + 255) / 256, 256, 0, s>>>(a, lmax, n);
+  return cudaGetLastError();
+}
+cudaError_t launch_ce_finalize(const CeArgs& a, int n, cudaStream_t s) {
+  ce_finalize_kernel<<<(n + 255) / 256, 256, 0, s>>>(a, n);
+  return cudaGetLastError();
+}
+
+}  // namespace mtj

@@ -88,6 +88,16 @@ struct mtj_handle {
   float* logits_gather = nullptr;   // [mp, max_batch, Vl] all-gather landing zone (mp > 1)
   float* part = nullptr;            // [max_rows, d] this shard's partial sums before the all-reduce (mp > 1)
   void* comm = nullptr;             // ncclComm_t over the "shard" axis
+  float* uniforms = nullptr;        // [max_batch, V] sampler inputs of the current step
+  float* top_p = nullptr;           // [max_batch]
+  float* temp = nullptr;            // [max_batch]
+  void* sample_scratch = nullptr;
+  int eval_rows = 0;                // rows of logits materialised at a time by the loss path
+  float* eval_logits = nullptr;     // [eval_rows, Vl]
+  float* ce_max = nullptr;          // [max_rows] local max, then global max
+  float* ce_lmax = nullptr;         // [max_rows] copy of the local max (mp > 1)
+  float* ce_sum = nullptr;          // [max_rows, 2]
+  uint8_t* ce_hit = nullptr;        // [max_rows]
   uint32_t* tokens = nullptr;       // [max_batch] next decode input
   int32_t* cur = nullptr;           // absolute position of the next decode token
   int32_t* pad = nullptr;           // [max_batch]
@@ -113,6 +123,7 @@ struct mtj_handle {
   cudaStream_t capture_stream = nullptr;
   cudaGraphExec_t graph_exec = nullptr;
   int graph_batch = 0;
+  int graph_greedy = -1;
   int64_t graph_kernels = 0;
 
   // optional per-family kernel timing (mtj_profile_*): events around launches
@@ -168,6 +179,16 @@ struct mtj_handle {
       logits_gather = c.take<float>(static_cast<int64_t>(max_batch) * V);
       part = c.take<float>(R * d);
     }
+    uniforms = c.take<float>(static_cast<int64_t>(max_batch) * V);
+    top_p = c.take<float>(max_batch);
+    temp = c.take<float>(max_batch);
+    sample_scratch = c.take<char>(mtj::sample_scratch_bytes(max_batch, V));
+    eval_rows = static_cast<int>(std::min<int64_t>(R, 256));
+    eval_logits = c.take<float>(static_cast<int64_t>(eval_rows) * Vl);
+    ce_max = c.take<float>(R);
+    ce_lmax = c.take<float>(R);
+    ce_sum = c.take<float>(R * 2);
+    ce_hit = c.take<uint8_t>(R);
     tokens = c.take<uint32_t>(max_batch);
     cur = c.take<int32_t>(4);
     pad = c.take<int32_t>(max_batch);
@@ -209,7 +230,7 @@ int32_t reduce_into_x(mtj_handle* h, int M, bool accumulate, bool pdl, cudaStrea
 // One transformer layer over a chunk of rows already in h->x (+ h->stats):
 // x <- x + attn(LN(x)) + ff(LN(x))  (layers.py:299-313 / :316-344 / :347-366).
 int32_t run_layer(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, bool decode,
-                  const int32_t* key_limit, cudaStream_t s) {
+                  const int32_t* key_limit, cudaStream_t s, float* detached_out = nullptr) {
   const LayerWeights& lw = h->layers[layer];
   const bool pdl = h->use_pdl && decode;
   GemvArgs a = {};
@@ -291,15 +312,23 @@ int32_t run_layer(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, bool
   o.ldx = h->dl + h->ffl;
   o.rows = rows;
   o.bias = lw.b_out;
-  o.residual = h->mp == 1 ? h->x : nullptr;
-  o.out = h->mp == 1 ? h->x : h->part;
-  o.stats_out = h->mp == 1 ? h->stats : nullptr;
+  // detached_out: return g_psum(attn + ff) on its own instead of adding it to the residual stream
+  o.residual = (h->mp == 1 && !detached_out) ? h->x : nullptr;
+  o.out = h->mp == 1 ? (detached_out ? detached_out : h->x) : h->part;
+  o.stats_out = (h->mp == 1 && !detached_out) ? h->stats : nullptr;
   o.counters = h->gemv_counters;
   o.dev_err = h->dev_err;
   h->prof_begin(MTJ_FAMILY_OUTPROJ, s);
   MTJ_CUDA(mtj::launch_gemv(mtj::kEpiOut, o, s, pdl));
   h->prof_end(s);
   h->launches++;
+  if (h->mp > 1 && detached_out) {
+    std::string err;
+    if (mtj::comm_all_reduce(h->comm, h->part, static_cast<size_t>(M) * h->d, false, s, &err))
+      return fail(MTJ_ERR_COMM, err);
+    MTJ_CUDA(cudaMemcpyAsync(detached_out, h->part, sizeof(float) * M * h->d, cudaMemcpyDeviceToDevice, s));
+    return MTJ_OK;
+  }
   if (h->mp > 1) return reduce_into_x(h, M, true, pdl, s);
   return MTJ_OK;
 }
@@ -326,17 +355,17 @@ int32_t run_embed(mtj_handle* h, const uint32_t* ids, int ids_ld, int M, const m
 
 // final LayerNorm + vocab-sharded logits for M output rows (layers.py:561-564)
 int32_t run_logits(mtj_handle* h, int M, const int32_t* row_select, float* out, bool decode,
-                   cudaStream_t s) {
+                   cudaStream_t s, int row0 = 0) {
   GemvArgs a = {};
   a.W = h->proj_w;
   a.N = h->Vl;
   a.K = h->d;
   a.M = M;
-  a.x = h->x;
+  a.x = h->x + static_cast<size_t>(row0) * h->d;
   a.ldx = h->d;
   a.ln_scale = h->lnf_scale;
   a.ln_offset = h->lnf_offset;
-  a.stats = h->stats;
+  a.stats = h->stats + 2 * static_cast<size_t>(row0);
   a.bias = h->proj_b;
   a.logits = out;
   a.ld_logits = h->Vl;
@@ -683,12 +712,15 @@ int32_t mtj_decode_step(mtj_handle* h, const uint32_t* tokens_in, const float* t
   if (rc) return rc;
   if (!h->prefilled) return fail(MTJ_ERR_STATE, "mtj_prefill has not run");
   if (h->steps_done >= h->max_gen) return fail(MTJ_ERR_STATE, "max_gen steps already generated");
-  if (!greedy) {
-    (void)top_p; (void)temp; (void)uniforms;
-    return fail(MTJ_ERR_UNSUPPORTED, "sampled decoding is not wired yet");
-  }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int B = h->batch;
+  if (!greedy) {
+    if (!top_p || !temp || !uniforms) return fail(MTJ_ERR_INVALID, "sampling needs top_p, temp and uniforms");
+    if (h->V > 65535) return fail(MTJ_ERR_UNSUPPORTED, "the sampler handles n_vocab <= 65535");
+    MTJ_CUDA(cudaMemcpyAsync(h->top_p, top_p, sizeof(float) * B, cudaMemcpyDeviceToDevice, s));
+    MTJ_CUDA(cudaMemcpyAsync(h->temp, temp, sizeof(float) * B, cudaMemcpyDeviceToDevice, s));
+    MTJ_CUDA(cudaMemcpyAsync(h->uniforms, uniforms, sizeof(float) * B * h->V, cudaMemcpyDeviceToDevice, s));
+  }
   if (tokens_in)
     MTJ_CUDA(cudaMemcpyAsync(h->tokens, tokens_in, sizeof(uint32_t) * B, cudaMemcpyDeviceToDevice, s));
   auto enqueue = [&](cudaStream_t st) -> int32_t {
@@ -710,19 +742,33 @@ int32_t mtj_decode_step(mtj_handle* h, const uint32_t* tokens_in, const float* t
       MTJ_CUDA(mtj::launch_gather_rows(h->logits_gather, h->logits_all, h->mp, B, h->Vl, st));
       h->launches += 2;
     }
-    mtj::ArgmaxArgs am = {};
-    am.logits = h->logits_all;
-    am.B = B;
-    am.V = h->V;
-    am.tokens = h->tokens;
-    am.tokens_copy = nullptr;
-    am.cur_dev = h->cur;
-    MTJ_CUDA(mtj::launch_argmax(am, st, h->use_pdl));
+    if (greedy) {
+      mtj::ArgmaxArgs am = {};
+      am.logits = h->logits_all;
+      am.B = B;
+      am.V = h->V;
+      am.tokens = h->tokens;
+      am.tokens_copy = nullptr;
+      am.cur_dev = h->cur;
+      MTJ_CUDA(mtj::launch_argmax(am, st, h->use_pdl));
+    } else {
+      mtj::SampleArgs sa = {};
+      sa.logits = h->logits_all;
+      sa.uniforms = h->uniforms;
+      sa.top_p = h->top_p;
+      sa.temp = h->temp;
+      sa.rows = B;
+      sa.V = h->V;
+      sa.scratch = h->sample_scratch;
+      sa.tokens = h->tokens;
+      sa.cur_dev = h->cur;
+      MTJ_CUDA(mtj::launch_sample_top_p(sa, st, h->use_pdl));
+    }
     h->launches++;
     return MTJ_OK;
   };
   if (h->use_graph && !h->profile && (h->mp == 1 || h->steps_done > 0)) {
-    if (h->graph_exec == nullptr || h->graph_batch != B) {
+    if (h->graph_exec == nullptr || h->graph_batch != B || h->graph_greedy != (greedy ? 1 : 0)) {
       if (h->graph_exec) {
         cudaGraphExecDestroy(h->graph_exec);
         h->graph_exec = nullptr;
@@ -744,6 +790,7 @@ int32_t mtj_decode_step(mtj_handle* h, const uint32_t* tokens_in, const float* t
       cudaGraphDestroy(graph);
       if (ce != cudaSuccess) return fail(MTJ_ERR_CUDA, std::string("graph instantiate: ") + cudaGetErrorString(ce));
       h->graph_batch = B;
+      h->graph_greedy = greedy ? 1 : 0;
     }
     MTJ_CUDA(cudaGraphLaunch(h->graph_exec, s));
     h->launches += h->graph_kernels;
@@ -794,15 +841,86 @@ int32_t mtj_forward_logits(mtj_handle* h, const uint32_t* obs, const uint32_t* c
   return rc;
 }
 
-int32_t mtj_eval_loss(mtj_handle*, const uint32_t*, const uint32_t*, const uint32_t*, int32_t, int32_t,
-                      float*, uint8_t*, mtj_stream) {
-  return fail(MTJ_ERR_UNSUPPORTED, "eval loss is not wired yet");
+int32_t mtj_eval_loss(mtj_handle* h, const uint32_t* obs, const uint32_t* target, const uint32_t* ctx_len,
+                      int32_t batch, int32_t T, float* all_loss, uint8_t* correct, mtj_stream stream) {
+  int32_t rc = check_ready(h);
+  if (rc) return rc;
+  if (h->mp > 1 && !h->comm) return fail(MTJ_ERR_STATE, "cores_per_replica > 1 needs mtj_comm_init first");
+  if (!obs || !target || !all_loss || !correct || batch <= 0 || batch > h->max_batch)
+    return fail(MTJ_ERR_INVALID, "bad argument");
+  if (T <= 0 || T > h->ring_pages * mtj::kPageTokens || T > h->max_pos)
+    return fail(MTJ_ERR_INVALID, "T exceeds the KV capacity");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  std::vector<int32_t> pad(batch, 0), limit(batch);
+  // mask = (arange(T) > ctx_length) * -1e10 on the keys (transformer_shard.py:130)
+  for (int b = 0; b < batch; ++b) limit[b] = ctx_len ? static_cast<int32_t>(std::min<uint32_t>(ctx_len[b], 0x7fffffffu)) : T;
+  rc = setup_sequences(h, pad, limit, T, s);
+  if (rc) return rc;
+  h->prefilled = false;
+  rc = forward_chunks(h, obs, T, batch, T, h->key_limit, s, [&](int b0, int ns, int t0, int tc) -> int32_t {
+    const int M = ns * tc;
+    mtj::CeArgs ce = {};
+    ce.vl = h->Vl;
+    ce.vocab_start = h->rank * h->Vl;
+    ce.rows = {b0, tc, t0, nullptr};
+    ce.T = T;
+    ce.targets = target;
+    ce.pmax = h->ce_max;
+    ce.psum = h->ce_sum;
+    ce.hit = h->ce_hit;
+    ce.loss_out = all_loss;
+    ce.correct_out = correct;
+    for (int m0 = 0; m0 < M; m0 += h->eval_rows) {
+      const int n = std::min(h->eval_rows, M - m0);
+      int32_t r2 = run_logits(h, n, nullptr, h->eval_logits, false, s, m0);
+      if (r2) return r2;
+      ce.logits = h->eval_logits;
+      ce.row0 = m0;
+      MTJ_CUDA(mtj::launch_ce_partial(ce, n, s));
+      h->launches++;
+    }
+    if (h->mp > 1) {
+      std::string err;
+      MTJ_CUDA(cudaMemcpyAsync(h->ce_lmax, h->ce_max, sizeof(float) * M, cudaMemcpyDeviceToDevice, s));
+      if (mtj::comm_all_reduce(h->comm, h->ce_max, M, true, s, &err)) return fail(MTJ_ERR_COMM, err);
+    }
+    MTJ_CUDA(mtj::launch_ce_rescale(ce, h->mp > 1 ? h->ce_lmax : h->ce_max, M, s));
+    if (h->mp > 1) {
+      std::string err;
+      if (mtj::comm_all_reduce(h->comm, h->ce_sum, 2 * static_cast<size_t>(M), false, s, &err))
+        return fail(MTJ_ERR_COMM, err);
+    }
+    MTJ_CUDA(mtj::launch_ce_finalize(ce, M, s));
+    h->launches += 2;
+    return MTJ_OK;
+  });
+  return rc;
 }
 
-int64_t mtj_sample_scratch_bytes(int32_t, int32_t) { return 0; }
-int32_t mtj_sample_top_p(const float*, const float*, const float*, const float*, int32_t, int32_t, void*,
-                         int64_t, uint32_t*, mtj_stream) {
-  return fail(MTJ_ERR_UNSUPPORTED, "sampler is not wired yet");
+int64_t mtj_sample_scratch_bytes(int32_t rows, int32_t vocab) {
+  if (rows <= 0 || vocab <= 0) return -1;
+  return mtj::sample_scratch_bytes(rows, vocab);
+}
+
+int32_t mtj_sample_top_p(const float* logits, const float* uniforms, const float* top_p, const float* temp,
+                         int32_t rows, int32_t vocab, void* scratch, int64_t scratch_bytes,
+                         uint32_t* tokens_out, mtj_stream stream) {
+  if (!logits || !uniforms || !top_p || !temp || !scratch || !tokens_out)
+    return fail(MTJ_ERR_INVALID, "null argument");
+  if (rows <= 0 || vocab <= 0) return fail(MTJ_ERR_INVALID, "rows and vocab must be positive");
+  if (vocab > 65535) return fail(MTJ_ERR_UNSUPPORTED, "the sampler handles vocab <= 65535");
+  if (scratch_bytes < mtj::sample_scratch_bytes(rows, vocab)) return fail(MTJ_ERR_INVALID, "scratch too small");
+  mtj::SampleArgs sa = {};
+  sa.logits = logits;
+  sa.uniforms = uniforms;
+  sa.top_p = top_p;
+  sa.temp = temp;
+  sa.rows = rows;
+  sa.V = vocab;
+  sa.scratch = scratch;
+  sa.tokens = tokens_out;
+  MTJ_CUDA(mtj::launch_sample_top_p(sa, static_cast<cudaStream_t>(stream), false));
+  return MTJ_OK;
 }
 
 int64_t mtj_launch_count(const mtj_handle* h) { return h ? h->launches : -1; }
@@ -848,6 +966,86 @@ int32_t mtj_check_device_status(mtj_handle* h, mtj_stream stream) {
     if (w & mtj::kDevErrTimeout) return fail(MTJ_ERR_TIMEOUT, "a bounded device-side wait ran out");
     return fail(MTJ_ERR_INVALID, "a kernel rejected an index");
   }
+  return MTJ_OK;
+}
+
+int32_t mtj_k_layer(mtj_handle* h, int32_t layer, const float* x_in, int32_t batch, int32_t T, int32_t pos0,
+                    const int32_t* pad_host, const int32_t* key_limit_host, int32_t decode, float* out,
+                    mtj_stream stream) {
+  int32_t rc = check_ready(h);
+  if (rc) return rc;
+  if (h->mp > 1 && !h->comm) return fail(MTJ_ERR_STATE, "cores_per_replica > 1 needs mtj_comm_init first");
+  if (!x_in || !out || layer < 0 || layer >= h->L || batch <= 0 || batch > h->max_batch || T <= 0)
+    return fail(MTJ_ERR_INVALID, "bad argument");
+  const int64_t M = static_cast<int64_t>(batch) * T;
+  if (M > h->max_rows) return fail(MTJ_ERR_INVALID, "batch * T exceeds max_rows");
+  if (decode && T != 1) return fail(MTJ_ERR_INVALID, "decode_once takes exactly one token per sequence");   // layers.py:320
+  if (pos0 < 0 || pos0 + T > h->max_pos) return fail(MTJ_ERR_INVALID, "position outside the RoPE table");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  std::vector<int32_t> pad(batch, 0), limit(batch, 0x7fffffff);
+  for (int b = 0; b < batch; ++b) {
+    if (pad_host) pad[b] = pad_host[b];
+    if (key_limit_host) limit[b] = key_limit_host[b];
+  }
+  rc = setup_sequences(h, pad, limit, pos0, s);
+  if (rc) return rc;
+  h->prefilled = false;
+  // x <- x_in with its LayerNorm statistics
+  MTJ_CUDA(mtj::launch_residual_stats(h->x, x_in, h->stats, static_cast<int>(M), h->d, false, s, false));
+  h->launches++;
+  mtj::RowMap rows = {0, T, pos0, nullptr};
+  if (decode) rows = {0, 1, 0, h->cur};
+  return run_layer(h, layer, static_cast<int>(M), rows, decode != 0, key_limit_host ? h->key_limit : nullptr, s, out);
+}
+
+int32_t mtj_k_projection(mtj_handle* h, const float* x_in, int32_t rows, float* logits_out, mtj_stream stream) {
+  int32_t rc = check_ready(h);
+  if (rc) return rc;
+  if (!x_in || !logits_out || rows <= 0 || rows > h->max_rows) return fail(MTJ_ERR_INVALID, "bad argument");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  MTJ_CUDA(mtj::launch_residual_stats(h->x, x_in, h->stats, rows, h->d, false, s, false));
+  h->launches++;
+  return run_logits(h, rows, nullptr, logits_out, false, s);
+}
+
+int32_t mtj_k_projection_loss(mtj_handle* h, const float* x_in, const uint32_t* targets, int32_t rows,
+                              float* loss_out, uint8_t* correct_out, mtj_stream stream) {
+  int32_t rc = check_ready(h);
+  if (rc) return rc;
+  if (h->mp > 1 && !h->comm) return fail(MTJ_ERR_STATE, "cores_per_replica > 1 needs mtj_comm_init first");
+  if (!x_in || !targets || !loss_out || !correct_out || rows <= 0 || rows > h->max_rows)
+    return fail(MTJ_ERR_INVALID, "bad argument");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  MTJ_CUDA(mtj::launch_residual_stats(h->x, x_in, h->stats, rows, h->d, false, s, false));
+  h->launches++;
+  mtj::CeArgs ce = {};
+  ce.vl = h->Vl;
+  ce.vocab_start = h->rank * h->Vl;
+  ce.rows = {0, rows, 0, nullptr};
+  ce.T = rows;
+  ce.targets = targets;
+  ce.pmax = h->ce_max;
+  ce.psum = h->ce_sum;
+  ce.hit = h->ce_hit;
+  ce.loss_out = loss_out;
+  ce.correct_out = correct_out;
+  for (int m0 = 0; m0 < rows; m0 += h->eval_rows) {
+    const int n = std::min(h->eval_rows, rows - m0);
+    rc = run_logits(h, n, nullptr, h->eval_logits, false, s, m0);
+    if (rc) return rc;
+    ce.logits = h->eval_logits;
+    ce.row0 = m0;
+    MTJ_CUDA(mtj::launch_ce_partial(ce, n, s));
+  }
+  std::string err;
+  if (h->mp > 1) {
+    MTJ_CUDA(cudaMemcpyAsync(h->ce_lmax, h->ce_max, sizeof(float) * rows, cudaMemcpyDeviceToDevice, s));
+    if (mtj::comm_all_reduce(h->comm, h->ce_max, rows, true, s, &err)) return fail(MTJ_ERR_COMM, err);
+  }
+  MTJ_CUDA(mtj::launch_ce_rescale(ce, h->mp > 1 ? h->ce_lmax : h->ce_max, rows, s));
+  if (h->mp > 1 && mtj::comm_all_reduce(h->comm, h->ce_sum, 2 * static_cast<size_t>(rows), false, s, &err))
+    return fail(MTJ_ERR_COMM, err);
+  MTJ_CUDA(mtj::launch_ce_finalize(ce, rows, s));
   return MTJ_OK;
 }
 

@@ -55,6 +55,9 @@ def _load():
         "mtj_profile_enable": (i32, [vp, i32]),
         "mtj_profile_read": (i32, [vp, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(i64), vp]),
         "mtj_k_embed": (i32, [vp, vp, i32, vp, vp, vp]),
+        "mtj_k_layer": (i32, [vp, i32, vp, i32, i32, i32, ctypes.POINTER(i32), ctypes.POINTER(i32), i32, vp, vp]),
+        "mtj_k_projection": (i32, [vp, vp, i32, vp, vp]),
+        "mtj_k_projection_loss": (i32, [vp, vp, vp, i32, vp, vp, vp]),
         "mtj_k_decode_attn_scratch_bytes": (i64, [i32, i32, i32, i32, i32]),
         "mtj_k_ln_gemv": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp]),
         "mtj_k_decode_attn_noalloc": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, i32, vp]),

@@ -176,6 +176,40 @@ class ShardRuntime:
             out = gather_vocab_shards(out)
         return out
 
+    def eval_loss(self, obs_dev: torch.Tensor, target_dev: torch.Tensor, ctx_length):
+        B, T = obs_dev.shape
+        loss = torch.empty((B, T), dtype=torch.float32, device=self.device)
+        correct = torch.empty((B, T), dtype=torch.uint8, device=self.device)
+        lens = None if ctx_length is None else _lib.u32_array(list(ctx_length))
+        check(lib.mtj_eval_loss(self._h, obs_dev.data_ptr(), target_dev.data_ptr(), lens, B, T,
+                                loss.data_ptr(), correct.data_ptr(), self.stream))
+        return loss, correct
+
+    def layer(self, index: int, x: torch.Tensor, batch: int, T: int, pos0: int = 0, pad=None, key_limit=None,
+              decode: bool = False) -> torch.Tensor:
+        i32 = lambda v: None if v is None else (ctypes.c_int32 * len(v))(*[int(a) for a in v])
+        x = x.to(self.device, torch.float32).contiguous()
+        out = torch.empty_like(x)
+        check(lib.mtj_k_layer(self._h, index, x.data_ptr(), batch, T, pos0, i32(pad), i32(key_limit),
+                              1 if decode else 0, out.data_ptr(), self.stream))
+        return out
+
+    def projection(self, x: torch.Tensor) -> torch.Tensor:
+        x = x.to(self.device, torch.float32).contiguous()
+        rows = x.shape[0]
+        out = torch.empty((rows, self.vocab_local), dtype=torch.float32, device=self.device)
+        check(lib.mtj_k_projection(self._h, x.data_ptr(), rows, out.data_ptr(), self.stream))
+        return gather_vocab_shards(out) if self.mp > 1 else out
+
+    def projection_loss(self, x: torch.Tensor, targets: torch.Tensor):
+        x = x.to(self.device, torch.float32).contiguous()
+        rows = x.shape[0]
+        loss = torch.empty((rows,), dtype=torch.float32, device=self.device)
+        correct = torch.empty((rows,), dtype=torch.uint8, device=self.device)
+        check(lib.mtj_k_projection_loss(self._h, x.data_ptr(), targets.data_ptr(), rows, loss.data_ptr(),
+                                        correct.data_ptr(), self.stream))
+        return loss, correct.bool()
+
     def embed(self, ids_dev: torch.Tensor):
         rows = ids_dev.numel()
         x = torch.empty((rows, self.config["d_model"]), dtype=torch.float32, device=self.device)

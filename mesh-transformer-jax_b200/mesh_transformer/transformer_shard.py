@@ -15,6 +15,7 @@ import numpy as np
 import torch
 
 from ._runtime import PREFIX, ShardRuntime, param_shapes, validate_config
+from .sampling import draw_uniforms
 from .util import head_print, to_bf16
 
 
@@ -157,15 +158,32 @@ class CausalTransformer:
 
     # -- eval ----------------------------------------------------------------
     def eval(self, sample):
-        """transformer_shard.py:308-324."""
-        raise NotImplementedError("eval loss is not wired yet")
+        """transformer_shard.py:308-324: ``sample`` holds ``obs`` and ``target``
+        [batch, T] and optionally ``ctx_length`` [batch]; returns the dict of
+        transformer_shard.py:67-72 with a leading batch axis."""
+        obs = np.ascontiguousarray(np.asarray(sample["obs"]), dtype=np.uint32)
+        tgt = np.ascontiguousarray(np.asarray(sample["target"]), dtype=np.uint32)
+        if "ctx_length" in sample:
+            ctx_length = np.asarray(sample["ctx_length"]).reshape(-1)
+        else:
+            ctx_length = np.array([len(obs[0])] * len(obs))
+        rt = self._runtime(obs.shape[0], max(self._rt_caps[1], 1))
+        with torch.cuda.device(self.device):
+            loss, correct = rt.eval_loss(torch.from_numpy(obs.view(np.int32)).to(self.device),
+                                         torch.from_numpy(tgt.view(np.int32)).to(self.device), ctx_length)
+            all_loss = loss.cpu().numpy()
+            return {"loss": all_loss.mean(-1), "last_loss": all_loss[:, -1], "all_loss": all_loss,
+                    "correct": correct.cpu().numpy().astype(bool)}
 
     # -- generate ------------------------------------------------------------
-    def generate(self, ctx, ctx_length, gen_length, sampler_options=None, return_logits=False):
+    def generate(self, ctx, ctx_length, gen_length, sampler_options=None, return_logits=False, uniforms=None):
         """transformer_shard.py:326-339.  ``ctx`` is [batch, seq] left-padded
         token ids, ``ctx_length`` the number of real tokens per row.  Returns
         ``(final_state, (tokens[batch, gen, 1] uint32, None[, logits]))`` like
-        the reference's scan output."""
+        the reference's scan output.  ``uniforms`` ([gen, batch, n_vocab] in
+        [tiny, 1)) replaces the PRNG key stream for reproducible sampling; when
+        omitted they are drawn on the device from a seed taken from Python's
+        ``random`` like the reference's key (:327)."""
         sampler_options = sampler_options or {}
         ctx = np.ascontiguousarray(np.asarray(ctx), dtype=np.uint32)
         batch = ctx.shape[0]
@@ -174,12 +192,25 @@ class CausalTransformer:
         self.gen_length = gen_length
         self.return_logits = return_logits
         key = random.randint(0, 2 ** 60)   # the reference seeds its PRNG the same way (:327)
+        if self.config["cores_per_replica"] > 1:
+            # every shard samples the same token: all of them need the same key
+            import torch.distributed as dist
+            kt = torch.tensor([key], dtype=torch.int64,
+                              device=self.device if dist.get_backend() == "nccl" else "cpu")
+            dist.broadcast(kt, src=0)
+            key = int(kt.item())
+        sampler = self.config.get("sampler")
+        name = getattr(sampler, "__name__", None)
+        if sampler is not None and name not in ("nucleaus_sample", "softmax_sample"):
+            raise NotImplementedError("only nucleaus_sample / softmax_sample run on the device path")
         rt = self._runtime(batch, gen_length)
         top_p = np.asarray(sampler_options.get("top_p", np.zeros(batch)), dtype=np.float32).reshape(batch)
-        greedy = bool(np.all(top_p == 0.0)) or not sampler_options
-        if not greedy:
-            raise NotImplementedError("sampled decoding is not wired yet")
-        del key
+        temp = np.asarray(sampler_options.get("temp", np.ones(batch)), dtype=np.float32).reshape(batch)
+        if "top_k" in sampler_options and sampler_options["top_k"] is not None:
+            raise NotImplementedError("the reference's top_k branch is outside this path")
+        if name == "softmax_sample":
+            top_p = np.full(batch, np.inf, np.float32)
+        greedy = bool(np.all(top_p == 0.0))
         with torch.cuda.device(self.device):
             ctx_dev = torch.from_numpy(ctx.view(np.int32)).to(self.device)
             toks = torch.empty((gen_length, batch), dtype=torch.int32, device=self.device)
@@ -187,10 +218,25 @@ class CausalTransformer:
             if return_logits:
                 logits = torch.empty((gen_length, batch, self.config["n_vocab"]), dtype=torch.float32,
                                      device=self.device)
+            samp = {"greedy": True}
+            gen = None
+            if not greedy:
+                samp = {"greedy": False,
+                        "top_p": torch.from_numpy(top_p).to(self.device),
+                        "temp": torch.from_numpy(temp).to(self.device)}
+                if uniforms is not None:
+                    uniforms = torch.as_tensor(np.asarray(uniforms, dtype=np.float32)).to(self.device)
+                    assert tuple(uniforms.shape) == (gen_length, batch, self.config["n_vocab"])
+                else:
+                    gen = torch.Generator(device=self.device)
+                    gen.manual_seed(key)
             shard = CausalTransformerShard(self.config, runtime=rt)
             shard.generate_initial(ctx_dev, lengths)
             for t in range(gen_length):
-                shard.generate_once(None, toks[t], None if logits is None else logits[t], greedy=True)
+                if not greedy:
+                    samp["uniforms"] = uniforms[t].contiguous() if uniforms is not None else \
+                        draw_uniforms(gen, (batch, self.config["n_vocab"]), self.device)
+                shard.generate_once(None, toks[t], None if logits is None else logits[t], **samp)
             out_tokens = toks.cpu().numpy().view(np.uint32).T[:, :, None]
             output = (out_tokens, None)
             if return_logits:

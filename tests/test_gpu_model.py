@@ -136,3 +136,83 @@ def test_errors_are_status_codes_not_faults(cuda_device):
         net.generate(ctx, [65], 2, {"top_p": np.zeros(1)})
     net.generate(ctx, [30], 2, {"top_p": np.zeros(1)})
     net._rt.check_device_status()
+
+
+@pytest.mark.parametrize("stress", [False, True])
+def test_eval_loss_dict_matches_oracle(cuda_device, stress):
+    cfg = spec.tiny_config(1, seq=64)
+    params = spec.make_params(cfg, seed=12, stress=stress)
+    net = _net(cfg, params, cuda_device)
+    ids = spec.token_ids(13, 3, 65, 512)
+    sample = {"obs": ids[:, :-1], "target": ids[:, 1:], "ctx_length": np.array([64, 20, 5])}
+    out = net.eval(sample)
+    ref = go.CausalTransformer(cfg, params).eval(sample)
+    assert set(out) == {"loss", "last_loss", "all_loss", "correct"}
+    assert out["all_loss"].shape == (3, 64) and out["correct"].dtype == bool
+    assert np.abs(out["all_loss"] - ref["all_loss"]).max() <= 2e-2
+    assert np.abs(out["loss"] - ref["loss"]).max() <= 1e-3              # mean loss bar
+    assert np.abs(out["last_loss"] - ref["last_loss"]).max() <= 2e-2
+    # `correct` is an exact float equality in the reference; it may only differ where the
+    # oracle's top-2 logits are closer than the logit tolerance
+    assert (out["correct"] != ref["correct"]).mean() <= 0.02
+    # default ctx_length = T (transformer_shard.py:314-317)
+    out2 = net.eval({"obs": ids[:, :-1], "target": ids[:, 1:]})
+    ref2 = go.CausalTransformer(cfg, params).eval({"obs": ids[:, :-1], "target": ids[:, 1:]})
+    assert np.abs(out2["loss"] - ref2["loss"]).max() <= 1e-3
+
+
+def test_module_classes_follow_the_reference_modules(cuda_device):
+    """EmbeddingShard / TransformerLayerShard / ProjectionShard called one by one
+    the way CausalTransformerShard composes them (transformer_shard.py:47-115)."""
+    import torch
+    from mesh_transformer.layers import EmbeddingShard, ProjectionShard, TransformerLayerShard, getnorm
+    cfg = spec.tiny_config(1, seq=64)
+    params = spec.make_params(cfg, seed=14, stress=True)
+    net = _net(cfg, params, cuda_device)
+    rt = net._runtime(1, 8)
+    embed = EmbeddingShard(cfg, runtime=rt)
+    layers = [TransformerLayerShard(cfg, name=f"layer_{i}", runtime=rt) for i in range(cfg["layers"])]
+    proj = ProjectionShard(cfg, runtime=rt)
+    oracle = go.CausalTransformerShard(cfg, params)
+    ids = spec.token_ids(15, 1, 40, 512)[0]
+    tgt = spec.token_ids(16, 1, 40, 512)[0]
+    # eval composition: embed, x = x + layer(x, bias), proj.loss
+    mask = (np.arange(40) > 25) * -1e10
+    x = embed(ids)
+    xo = oracle.embed(ids)
+    assert np.array_equal(x.cpu().numpy(), xo[0])
+    for l, lo in zip(layers, oracle.transformer_layers):
+        res = l(x, mask)
+        reso = lo(xo, mask.astype(np.float32))
+        assert np.abs(res.cpu().numpy() - reso[0]).max() <= 2e-2 * max(1.0, np.abs(reso[0]).max())
+        x = x + res
+        xo = [xo[0] + reso[0]]
+    logits = proj(x).cpu().numpy()
+    assert np.abs(logits - oracle.proj(xo)).max() / np.abs(oracle.proj(xo)).max() <= 2e-2
+    loss, correct = proj.loss(x, tgt, z_loss=0.)
+    lo_loss, lo_correct = oracle.proj.loss(xo, tgt, 0.)
+    assert np.abs(loss.cpu().numpy() - lo_loss).max() <= 2e-2
+    # generate composition: get_init_decode_state then decode_once
+    ctx = spec.left_pad(spec.token_ids(17, 1, 30, 512), 41)[0]
+    x = embed(ctx[:-1])
+    xo = oracle.embed(ctx[:-1])
+    states, states_o = [], []
+    for l, lo in zip(layers, oracle.transformer_layers):
+        res, st = l.get_init_decode_state(x, 29, 0)
+        reso, sto = lo.get_init_decode_state(xo, 29, 0)
+        x, xo = x + res, [xo[0] + reso[0]]
+        states.append(st)
+        states_o.append(sto)
+    for step in range(3):
+        tok = np.array([7 + step], np.uint32)
+        x, xo = embed(tok), oracle.embed(tok)
+        for i, (l, lo) in enumerate(zip(layers, oracle.transformer_layers)):
+            res, states[i] = l.decode_once(states[i], x, 0)
+            reso, states_o[i] = lo.decode_once(states_o[i], xo, 0)
+            assert np.abs(res.cpu().numpy() - reso[0]).max() <= 2e-2 * max(1.0, np.abs(reso[0]).max())
+            x, xo = x + res, [xo[0] + reso[0]]
+        assert states[0]["tokens_decoded"] == states_o[0][0]["tokens_decoded"]
+    with pytest.raises(Exception):
+        getnorm("rmsnorm")
+    with pytest.raises(NotImplementedError):
+        proj.loss(x, tgt[:1], z_loss=1)

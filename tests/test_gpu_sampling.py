@@ -1,0 +1,100 @@
+"""GPU parity of the sampling kernel: token ids bit-exact against the oracle
+given identical logits and uniforms."""
+import numpy as np
+import pytest
+
+from oracle import gptj_oracle as go
+from oracle import sampling_oracle as so
+from oracle import spec
+
+pytestmark = pytest.mark.gpu
+
+
+def _sample_gpu(cuda_device, logits, uniforms, top_p, temp):
+    import torch
+    torch.cuda.set_device(cuda_device)
+    from mesh_transformer.sampling import nucleaus_sample
+    toks, info = nucleaus_sample(torch.from_numpy(uniforms).to(cuda_device), torch.from_numpy(logits).to(cuda_device),
+                                 None, top_p=top_p, temp=temp)
+    assert info is None and toks.dtype == np.uint32
+    return toks
+
+
+@pytest.mark.parametrize("vocab,scale", [(50400, 0.5), (50400, 3.0), (50400, 8.0), (512, 1.0), (12, 1.0), (65535, 2.0)])
+def test_sampler_bit_exact_against_oracle(cuda_device, vocab, scale):
+    rng = np.random.default_rng(vocab + int(scale * 10))
+    rows = 6
+    lg = (rng.standard_normal((rows, vocab)) * scale).astype(np.float32)
+    un = rng.random((rows, vocab), dtype=np.float32).clip(so.TINY, None)
+    top_p = np.array([0.9, 0.5, 0.0, 1.0, 0.999, 0.05], np.float32)
+    temp = np.array([1.0, 0.75, 1.0, 1.3, 0.2, 2.0], np.float32)
+    got = _sample_gpu(cuda_device, lg, un, top_p, temp)
+    want = so.nucleaus_sample(un, lg, top_p, temp)
+    assert np.array_equal(got, want)
+
+
+def test_sampler_tie_order_and_signed_zero(cuda_device):
+    vocab = 2048
+    rng = np.random.default_rng(9)
+    lg = rng.integers(-3, 4, size=(4, vocab)).astype(np.float32)        # heavy ties
+    lg[0, ::7] = -0.0
+    un = rng.random((4, vocab), dtype=np.float32).clip(so.TINY, None)
+    for top_p in (0.0, 0.3, 0.9):
+        got = _sample_gpu(cuda_device, lg, un, np.full(4, top_p, np.float32), np.ones(4, np.float32))
+        assert np.array_equal(got, so.nucleaus_sample(un, lg, top_p, 1.0))
+    # top_p -> 0 is the arg-max with the highest index among equal logits
+    top = _sample_gpu(cuda_device, lg, un, np.zeros(4, np.float32), np.ones(4, np.float32))
+    for r in range(4):
+        assert top[r] == np.flatnonzero(lg[r] == lg[r].max())[-1]
+
+
+def test_softmax_sample_is_unfiltered(cuda_device):
+    import torch
+    from mesh_transformer.sampling import softmax_sample
+    rng = np.random.default_rng(10)
+    lg = rng.standard_normal((3, 512)).astype(np.float32)
+    un = rng.random((3, 512), dtype=np.float32).clip(so.TINY, None)
+    got, _ = softmax_sample(torch.from_numpy(un).to(cuda_device), torch.from_numpy(lg).to(cuda_device), None, temp=0.9)
+    score = (lg / np.float32(0.9)).astype(np.float32) + so.gumbel(un)
+    assert np.array_equal(got, np.argmax(score, -1).astype(np.uint32))
+
+
+def test_sampled_generate_follows_the_oracle_sampler(cuda_device):
+    """End to end: at every step the token the device sampled equals the oracle
+    sampler applied to the logits the device produced and the same uniforms."""
+    import torch
+    torch.cuda.set_device(cuda_device)
+    from mesh_transformer.sampling import nucleaus_sample
+    from mesh_transformer.transformer_shard import CausalTransformer
+    cfg = spec.tiny_config(1, seq=64)
+    params = spec.make_params(cfg, seed=8, stress=True)
+    net = CausalTransformer(dict(cfg, sampler=nucleaus_sample), init_weights=False)
+    net.state = {"params": params, "step": np.array(0)}
+    lens = np.array([40, 17], np.uint32)
+    ctx = np.zeros((2, 64), np.uint32)
+    for b in range(2):
+        ctx[b, 64 - lens[b]:] = spec.token_ids(20 + b, 1, int(lens[b]), 512)[0]
+    steps = 24
+    un = np.random.default_rng(11).random((steps, 2, 512), dtype=np.float32).clip(so.TINY, None)
+    opts = {"top_p": np.array([0.9, 0.6]), "temp": np.array([1.0, 0.8])}
+    _, out = net.generate(ctx, lens, steps, opts, return_logits=True, uniforms=un)
+    toks, logits = out[0], out[2]
+    for t in range(steps):
+        want = so.nucleaus_sample(un[t], logits[:, t, 0], opts["top_p"].astype(np.float32),
+                                  opts["temp"].astype(np.float32))
+        assert np.array_equal(toks[:, t, 0], want)
+    # and the logits themselves track the oracle model driven by the same tokens
+    ref = go.CausalTransformerShard(cfg, params)
+    for b in range(2):
+        _, (nxt, state) = ref.generate_initial(ctx[b], lens[b])
+        for t in range(steps):
+            lg, state = ref.generate_once(nxt, state)
+            assert np.abs(lg[0] - logits[b, t, 0]).max() / np.abs(lg).max() <= 2e-2
+            nxt = toks[b, t]
+    # a seeded run without explicit uniforms is reproducible
+    import random
+    random.seed(5)
+    a = net.generate(ctx, lens, 6, opts)[1][0]
+    random.seed(5)
+    b2 = net.generate(ctx, lens, 6, opts)[1][0]
+    assert np.array_equal(a, b2)
