@@ -208,6 +208,13 @@ int32_t mtj_k_ln_gemv(const void* w_dev, const float* x_dev, const float* stats_
                       int32_t M, int32_t N, int32_t K, int32_t k_split, int32_t rows_per_group,
                       float* out_dev, mtj_stream s);
 
+/* The tensor-core form of the same Linear for many token rows (prefill / eval;
+ * hk.Linear of layers.py:249-258,559 on [T, d] inputs): out[m, n] =
+ * sum_k w[n, k] * x[m, k] + bias[n] with w_dev bf16 [N, K], x_dev bf16 [M, K],
+ * fp32 accumulation in tensor memory, out_dev f32 [M, N].  K % 64 == 0. */
+int32_t mtj_k_gemm_tc(const void* w_dev, const void* x_dev, const float* bias_dev, int32_t M, int32_t N,
+                      int32_t K, float* out_dev, mtj_stream s);
+
 /* No counterpart in the reference.  The same attention as mtj_k_decode_attn
  * for callers that can neither pass scratch memory nor tolerate an allocation
  * inside the library (custom-call handlers with framework-planned buffers,

@@ -256,9 +256,14 @@ __global__ void __launch_bounds__(kAttnThreads) prefill_attn_kernel(const Prefil
     if (i >= nq) break;
     const int row = bi * a.rows.Tc + tl0 + i;
     const float inv = l[i] > 0.f ? 1.0f / l[i] : 0.f;   // rows with no visible key (left pad) give 0
-    float* op = a.out + static_cast<size_t>(row) * a.ld_out + head * DH + lane * EPL;
+    const size_t o_off = static_cast<size_t>(row) * a.ld_out + head * DH + lane * EPL;
+    if (a.out_bf16) {
 #pragma unroll
-    for (int e = 0; e < EPL; ++e) op[e] = o[i][e] * inv;
+      for (int e = 0; e < EPL; ++e) a.out_bf16[o_off + e] = __float2bfloat16_rn(o[i][e] * inv);
+    } else {
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) a.out[o_off + e] = o[i][e] * inv;
+    }
   }
 }
 

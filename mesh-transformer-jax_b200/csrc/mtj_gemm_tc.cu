@@ -1,0 +1,334 @@
+// Tensor-core GEMM for many token rows (prefill / eval): tcgen05.mma with the
+// accumulator in tensor memory, operands staged in shared memory by TMA.
+//
+//   Y^T[n, m] = sum_k W[n, k] * X[m, k]      W: bf16 [N, K] (packed weights)
+//                                            X: bf16 [M, K] (activations)
+//
+// The WEIGHT rows are the MMA's M dimension (128 per tile) and the token rows
+// its N dimension (BN per tile), so an epilogue thread owns one output feature
+// (one TMEM lane) for BN tokens: the RoPE partner feature sits in the
+// neighbouring lane, and for a fixed token the 32 lanes of a warp write 32
+// consecutive features (coalesced).  The epilogues are those of the GEMV
+// family (in-proj: RoPE / KV-cache write / bias + GELU; out-proj: bias +
+// residual; logits: bias) -- reference lines are cited there.
+//
+// One tile per block; 6 warps: warp 0 = TMA producer, warp 1 = TMEM allocator
+// and MMA issuer (one elected thread), warps 2-5 = epilogue (one TMEM lane
+// quadrant each).  Two blocks fit on an SM, so one block's epilogue overlaps
+// the other's main loop.  Every mbarrier wait is bounded; a wait that runs out
+// sets the device error word and the block drains and frees its TMEM.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include <math.h>
+
+#include "mtj_common.cuh"
+#include "mtj_kernels.h"
+
+namespace mtj {
+namespace {
+
+constexpr int kBM = 128;          // weight rows per tile (UMMA M)
+constexpr int kBK = 64;           // bf16 per 128-byte swizzled row
+constexpr int kTcThreads = 192;
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// K-major operand tile, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr >> 4) & 0x3FFF);
+  d |= static_cast<uint64_t>(1) << 16;                 // leading byte offset (unused with swizzle) = 16 B
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;         // stride between 8-row groups
+  d |= static_cast<uint64_t>(1) << 46;                 // descriptor version (sm_100)
+  d |= static_cast<uint64_t>(2) << 61;                 // SWIZZLE_128B
+  return d;
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+template <int BN, int STAGES, int EPI>
+__global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
+                                                             const __grid_constant__ CUtensorMap map_x,
+                                                             const GemmTcArgs a) {
+  constexpr uint32_t kABytes = kBM * kBK * 2, kBBytes = BN * kBK * 2, kStageBytes = kABytes + kBBytes;
+  constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
+                              (static_cast<uint32_t>(kBM >> 4) << 24);
+  extern __shared__ unsigned char tc_smem_raw[];
+  const uint32_t smem_base = (smem_u32(tc_smem_raw) + 1023u) & ~1023u;   // swizzled tiles need 1024-byte alignment
+  __shared__ __align__(8) uint64_t bars[2 * STAGES + 1];
+  __shared__ uint32_t tmem_slot;
+  __shared__ uint32_t failed;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t bar0 = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
+  const uint32_t acc_bar = bar0 + 8u * (2 * STAGES);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < 2 * STAGES + 1; ++s) mbar_init(bar0 + 8u * s, 1);
+    mbar_fence_init();
+    failed = 0;
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
+                 "r"(static_cast<uint32_t>(BN))
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_acc = tmem_slot;
+
+  pdl_wait();                      // the activations come from the predecessor kernel
+  pdl_launch_dependents();
+
+  const int n0 = blockIdx.x * kBM;           // first weight row of the tile
+  const int m0 = blockIdx.y * BN;            // first token row of the tile
+  const int nk = a.K / kBK;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kb = 0; kb < nk; ++kb) {
+        const int s = kb % STAGES;
+        if (kb >= STAGES && !mbar_wait(empty_bar(s), ((kb / STAGES) - 1) & 1)) {
+          atomicOr(&failed, 1u);
+          break;
+        }
+        mbar_expect_tx(full_bar(s), kStageBytes);
+        const uint32_t dst = smem_base + s * kStageBytes;
+        tma_load_2d(dst, &map_w, kb * kBK, n0, full_bar(s));
+        tma_load_2d(dst + kABytes, &map_x, kb * kBK, a.x_row0 + m0, full_bar(s));
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      for (int kb = 0; kb < nk; ++kb) {
+        const int s = kb % STAGES;
+        if (!mbar_wait(full_bar(s), (kb / STAGES) & 1)) {
+          atomicOr(&failed, 1u);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t sa = smem_base + s * kStageBytes;
+        const uint64_t adesc = smem_desc_sw128(sa), bdesc = smem_desc_sw128(sa + kABytes);
+#pragma unroll
+        for (int k4 = 0; k4 < kBK / 16; ++k4)      // UMMA K = 16 bf16 = 32 bytes = 2 descriptor units
+          tc_mma_bf16(tmem_acc, adesc + 2 * k4, bdesc + 2 * k4, kIdesc, (kb > 0 || k4 > 0) ? 1u : 0u);
+        tc_commit(empty_bar(s));                   // frees the stage once these MMAs have read it
+      }
+      tc_commit(acc_bar);                          // accumulator complete
+    }
+  } else {
+    const bool ok = mbar_wait(acc_bar, 0);
+    if (!ok) atomicOr(&failed, 1u);
+    tc_fence_after();
+    const int quad = warp & 3;                     // TMEM lanes this warp may read
+    const int n = n0 + quad * 32 + lane;
+    const bool n_ok = n < a.N;
+    // per-feature constants of the epilogue
+    int region = 0, nn = 0, head = 0, j = 0;
+    float bias = 0.f;
+    if (EPI == kEpiInProj) {
+      if (n_ok) {
+        if (n < 3 * a.dl) {
+          region = n / a.dl;
+          nn = n - region * a.dl;
+          head = nn / a.d_head;
+          j = nn % a.d_head;
+        } else {
+          region = 3;
+          nn = n - 3 * a.dl;
+          bias = a.b_ff[nn];
+        }
+      }
+    } else if (n_ok) {
+      bias = a.bias[n];
+    }
+    if (ok) {
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld32(tmem_acc + (static_cast<uint32_t>(quad * 32) << 16) + c0, r);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int m = m0 + c0 + i;
+          const float v = __uint_as_float(r[i]);
+          const float partner = __shfl_xor_sync(0xffffffffu, v, 1);
+          if (m >= a.M || !n_ok) continue;
+          if (EPI == kEpiInProj) {
+            const int seq = a.rows.b0 + m / a.rows.Tc;
+            const int pos = a.rows.pos0_host + m % a.rows.Tc;
+            if (region < 3) {
+              float y = v;
+              if (region < 2 && j < a.rot) {
+                const float2 sc = a.sincos[static_cast<size_t>(pos) * (a.rot >> 1) + (j >> 1)];
+                y = (j & 1) ? (v * sc.y + partner * sc.x) : (v * sc.y - partner * sc.x);
+              }
+              if (region == 0) {
+                a.q_out[static_cast<size_t>(m) * a.dl + nn] = y;
+              } else if (pos >= a.kv.pad[seq]) {
+                __nv_bfloat16* pool = region == 1 ? a.kv.kpool : a.kv.vpool;
+                const size_t off = kv_offset(a.kv.page_table + static_cast<size_t>(seq) * a.kv.ring_pages,
+                                             a.kv.ring_pages, a.heads, a.d_head, head, pos);
+                pool[off + j] = __float2bfloat16_rn(y);
+              }
+            } else {
+              a.act_out[static_cast<size_t>(m) * (a.dl + a.ffl) + a.dl + nn] =
+                  __float2bfloat16_rn(gelu_tanh(v + bias));
+            }
+          } else if (EPI == kEpiOut) {
+            float y = v + bias;
+            if (a.residual) y += a.residual[static_cast<size_t>(m) * a.N + n];
+            a.out[static_cast<size_t>(m) * a.N + n] = y;
+          } else {
+            a.out[static_cast<size_t>(m) * a.ld_out + n] = v + bias;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc),
+                 "r"(static_cast<uint32_t>(BN))
+                 : "memory");
+  }
+  if (threadIdx.x == 0 && failed && a.dev_err) atomicOr(a.dev_err, kDevErrTimeout);
+}
+
+// LayerNorm of fp32 rows into bf16 (the GEMM's activation operand), layers.py:17-36.
+__global__ void __launch_bounds__(256) ln_rows_kernel(const float* __restrict__ x, const float* __restrict__ scale,
+                                                      const float* __restrict__ offset,
+                                                      __nv_bfloat16* __restrict__ out, int d) {
+  __shared__ float red[8];
+  pdl_wait();
+  pdl_launch_dependents();
+  const float* xr = x + static_cast<size_t>(blockIdx.x) * d;
+  __nv_bfloat16* o = out + static_cast<size_t>(blockIdx.x) * d;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  auto block_sum = [&](float v) {
+    v = warp_sum(v);
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t += red[i];
+    __syncthreads();
+    return t;
+  };
+  float s = 0.f;
+  for (int i = threadIdx.x; i < d; i += 256) s += xr[i];
+  const float mu = block_sum(s) / static_cast<float>(d);
+  float v = 0.f;
+  for (int i = threadIdx.x; i < d; i += 256) {
+    const float t = xr[i] - mu;
+    v = fmaf(t, t, v);
+  }
+  const float rstd = 1.0f / sqrtf(block_sum(v) / static_cast<float>(d) + 1e-5f);
+  for (int i = threadIdx.x; i < d; i += 256)
+    o[i] = __float2bfloat16_rn(fmaf(scale[i] * rstd, xr[i] - mu, offset[i]));
+}
+
+PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  if (fn) return fn;
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+      q != cudaDriverEntryPointSuccess)
+    return nullptr;
+  fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+  return fn;
+}
+
+template <int BN, int STAGES, int EPI>
+cudaError_t launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const GemmTcArgs& a, cudaStream_t s, bool pdl) {
+  constexpr int smem = STAGES * (kBM * kBK * 2 + BN * kBK * 2) + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, EPI>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((a.N + kBM - 1) / kBM, (a.M + BN - 1) / BN, 1);
+  cfg.blockDim = dim3(kTcThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, STAGES, EPI>, mw, mx, a);
+}
+
+}  // namespace
+
+int gemm_tc_token_tile() { return 128; }
+
+cudaError_t make_tensor_map_bf16(void* map_out, const void* base, int64_t rows, int64_t K, int box_rows) {
+  PFN_cuTensorMapEncodeTiled_v12000 fn = encode_fn();
+  if (!fn) return cudaErrorNotSupported;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (K * 2) % 16 || box_rows > 256) return cudaErrorInvalidValue;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(K) * 2};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(kBK), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(static_cast<CUtensorMap*>(map_out), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base),
+                  dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+cudaError_t launch_gemm_tc(GemvEpilogue epi, const void* map_w, const void* map_x, const GemmTcArgs& a,
+                           cudaStream_t s, bool pdl) {
+  if (a.M <= 0 || a.N <= 0 || a.K <= 0 || a.K % kBK) return cudaErrorInvalidValue;
+  const CUtensorMap& mw = *static_cast<const CUtensorMap*>(map_w);
+  const CUtensorMap& mx = *static_cast<const CUtensorMap*>(map_x);
+  switch (epi) {
+    case kEpiInProj: return launch_tc<128, 3, kEpiInProj>(mw, mx, a, s, pdl);
+    case kEpiOut: return launch_tc<128, 3, kEpiOut>(mw, mx, a, s, pdl);
+    default: return launch_tc<128, 3, kEpiLogits>(mw, mx, a, s, pdl);
+  }
+}
+
+cudaError_t launch_ln_rows(const float* x, const float* scale, const float* offset, __nv_bfloat16* out, int rows,
+                           int d, cudaStream_t s) {
+  ln_rows_kernel<<<rows, 256, 0, s>>>(x, scale, offset, out, d);
+  return cudaGetLastError();
+}
+
+}  // namespace mtj

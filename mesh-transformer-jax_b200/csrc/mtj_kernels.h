@@ -97,7 +97,8 @@ struct PrefillAttnArgs {
   RowMap rows;
   int M, heads, d_head;
   const int32_t* key_limit;    // optional [batch]: keys with pos > limit are masked (eval ctx mask)
-  float* out;
+  float* out;                  // fp32 destination, or
+  __nv_bfloat16* out_bf16;     // bf16 destination (operand of the tensor-core out-proj); exactly one is set
   int ld_out;
 };
 cudaError_t launch_prefill_attn(const PrefillAttnArgs& a, cudaStream_t s);
@@ -110,6 +111,31 @@ struct ArgmaxArgs {
   int32_t* cur_dev;            // incremented by one after the step (may be null)
 };
 cudaError_t launch_argmax(const ArgmaxArgs& a, cudaStream_t s, bool pdl);
+
+// Tensor-core GEMM (many token rows): weights bf16 [N, K], activations bf16 [*, K]
+// reached through TMA tensor maps; epilogues as in GemvArgs.
+struct GemmTcArgs {
+  int M, N, K;                 // token rows, weight rows, reduction length (multiple of 64)
+  int x_row0;                  // first activation row (TMA row coordinate offset)
+  RowMap rows;
+  int dl, ffl, d_head, heads, rot;
+  const float2* sincos;
+  const float* b_ff;
+  float* q_out;                // [M, dl] fp32
+  __nv_bfloat16* act_out;      // [M, dl + ffl] bf16: gelu(ff) goes to columns [dl, dl + ffl)
+  KvCache kv;
+  const float* bias;           // [N] (out-proj, logits)
+  const float* residual;       // [M, N] or null
+  float* out;                  // out-proj: [M, N]; logits: [M, ld_out]
+  int ld_out;
+  uint32_t* dev_err;
+};
+int gemm_tc_token_tile();
+cudaError_t make_tensor_map_bf16(void* map_out_128B, const void* base, int64_t rows, int64_t K, int box_rows);
+cudaError_t launch_gemm_tc(GemvEpilogue epi, const void* map_w, const void* map_x, const GemmTcArgs& a,
+                           cudaStream_t s, bool pdl);
+cudaError_t launch_ln_rows(const float* x, const float* scale, const float* offset, __nv_bfloat16* out, int rows,
+                           int d, cudaStream_t s);
 
 struct SampleArgs {
   const float* logits;         // [rows, V]

@@ -31,6 +31,8 @@ int32_t fail(int32_t code, const std::string& msg) {
       return fail(MTJ_ERR_CUDA, std::string(#expr) + ": " + cudaGetErrorString(_e)); \
   } while (0)
 
+struct alignas(64) TensorMap { unsigned char bytes[128]; };   // a CUtensorMap
+
 struct LayerWeights {
   __nv_bfloat16* w_in = nullptr;    // [3*dl + ffl, d]  rows: Q | K | V | FF-in
   float* b_ff = nullptr;            // [ffl]
@@ -38,6 +40,7 @@ struct LayerWeights {
   float* b_out = nullptr;           // [d]
   float* ln_scale = nullptr;
   float* ln_offset = nullptr;
+  TensorMap map_in, map_out;        // TMA views of w_in / w_out for the tensor-core path
 };
 
 int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
@@ -92,6 +95,11 @@ struct mtj_handle {
   float* top_p = nullptr;           // [max_batch]
   float* temp = nullptr;            // [max_batch]
   void* sample_scratch = nullptr;
+  // tensor-core path (many token rows): bf16 activation operands and their TMA views
+  bool tc_ok = false;
+  __nv_bfloat16* xn_bf16 = nullptr;   // [max_rows, d] LayerNorm output
+  __nv_bfloat16* act_bf16 = nullptr;  // [max_rows, dl + ffl] attention vector | gelu(ff)
+  TensorMap map_xn, map_act, map_proj;
   int eval_rows = 0;                // rows of logits materialised at a time by the loss path
   float* eval_logits = nullptr;     // [eval_rows, Vl]
   float* ce_max = nullptr;          // [max_rows] local max, then global max
@@ -183,6 +191,8 @@ struct mtj_handle {
     top_p = c.take<float>(max_batch);
     temp = c.take<float>(max_batch);
     sample_scratch = c.take<char>(mtj::sample_scratch_bytes(max_batch, V));
+    xn_bf16 = c.take<__nv_bfloat16>(R * d);
+    act_bf16 = c.take<__nv_bfloat16>(R * (dl + ffl));
     eval_rows = static_cast<int>(std::min<int64_t>(R, 256));
     eval_logits = c.take<float>(static_cast<int64_t>(eval_rows) * Vl);
     ce_max = c.take<float>(R);
@@ -333,6 +343,92 @@ int32_t run_layer(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, bool
   return MTJ_OK;
 }
 
+// The same layer for many token rows on the tensor cores: LayerNorm to bf16, in-proj GEMM
+// (RoPE / KV / GELU epilogue), causal attention, out-proj GEMM (+ bias + residual).
+int32_t run_layer_tc(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, const int32_t* key_limit,
+                     cudaStream_t s, float* detached_out = nullptr) {
+  LayerWeights& lw = h->layers[layer];
+  MTJ_CUDA(mtj::launch_ln_rows(h->x, lw.ln_scale, lw.ln_offset, h->xn_bf16, M, h->d, s));
+  mtj::GemmTcArgs a = {};
+  a.M = M;
+  a.N = 3 * h->dl + h->ffl;
+  a.K = h->d;
+  a.rows = rows;
+  a.dl = h->dl;
+  a.ffl = h->ffl;
+  a.d_head = h->dh;
+  a.heads = h->heads;
+  a.rot = h->rot;
+  a.sincos = h->sincos;
+  a.b_ff = lw.b_ff;
+  a.q_out = h->q;
+  a.act_out = h->act_bf16;
+  a.kv = h->kv(layer);
+  a.dev_err = h->dev_err;
+  h->prof_begin(MTJ_FAMILY_INPROJ, s);
+  MTJ_CUDA(mtj::launch_gemm_tc(mtj::kEpiInProj, &lw.map_in, &h->map_xn, a, s, false));
+  h->prof_end(s);
+
+  mtj::PrefillAttnArgs p = {};
+  p.q = h->q;
+  p.kv = h->kv(layer);
+  p.rows = rows;
+  p.M = M;
+  p.heads = h->heads;
+  p.d_head = h->dh;
+  p.key_limit = key_limit;
+  p.out_bf16 = h->act_bf16;
+  p.ld_out = h->dl + h->ffl;
+  h->prof_begin(MTJ_FAMILY_ATTN, s);
+  MTJ_CUDA(mtj::launch_prefill_attn(p, s));
+  h->prof_end(s);
+
+  mtj::GemmTcArgs o = {};
+  o.M = M;
+  o.N = h->d;
+  o.K = h->dl + h->ffl;
+  o.bias = lw.b_out;
+  o.residual = (h->mp == 1 && !detached_out) ? h->x : nullptr;
+  o.out = h->mp == 1 ? (detached_out ? detached_out : h->x) : h->part;
+  o.ld_out = h->d;
+  o.dev_err = h->dev_err;
+  h->prof_begin(MTJ_FAMILY_OUTPROJ, s);
+  MTJ_CUDA(mtj::launch_gemm_tc(mtj::kEpiOut, &lw.map_out, &h->map_act, o, s, false));
+  h->prof_end(s);
+  h->launches += 4;
+  if (h->mp > 1 && detached_out) {
+    std::string err;
+    if (mtj::comm_all_reduce(h->comm, h->part, static_cast<size_t>(M) * h->d, false, s, &err))
+      return fail(MTJ_ERR_COMM, err);
+    MTJ_CUDA(cudaMemcpyAsync(detached_out, h->part, sizeof(float) * M * h->d, cudaMemcpyDeviceToDevice, s));
+    return MTJ_OK;
+  }
+  if (h->mp > 1) return reduce_into_x(h, M, true, false, s);
+  return MTJ_OK;
+}
+
+// final LayerNorm + vocab-sharded logits for rows [row0, row0 + M) of h->x on the tensor cores
+int32_t run_logits_tc(mtj_handle* h, int M, int row0, float* out, cudaStream_t s) {
+  MTJ_CUDA(mtj::launch_ln_rows(h->x + static_cast<size_t>(row0) * h->d, h->lnf_scale, h->lnf_offset,
+                               h->xn_bf16 + static_cast<size_t>(row0) * h->d, M, h->d, s));
+  mtj::GemmTcArgs a = {};
+  a.M = M;
+  a.N = h->Vl;
+  a.K = h->d;
+  a.x_row0 = row0;
+  a.bias = h->proj_b;
+  a.out = out;
+  a.ld_out = h->Vl;
+  a.dev_err = h->dev_err;
+  h->prof_begin(MTJ_FAMILY_LOGITS, s);
+  MTJ_CUDA(mtj::launch_gemm_tc(mtj::kEpiLogits, &h->map_proj, &h->map_xn, a, s, false));
+  h->prof_end(s);
+  h->launches += 2;
+  return MTJ_OK;
+}
+
+bool use_tc(const mtj_handle* h, int M) { return h->tc_ok && M >= 32; }
+
 int32_t run_embed(mtj_handle* h, const uint32_t* ids, int ids_ld, int M, const mtj::RowMap& rows,
                   bool decode, cudaStream_t s) {
   mtj::EmbedArgs e = {};
@@ -421,7 +517,8 @@ int32_t forward_chunks(mtj_handle* h, const uint32_t* ids, int ids_ld, int batch
       int32_t rc = run_embed(h, ids, ids_ld, M, rows, false, s);
       if (rc) return rc;
       for (int l = 0; l < h->L; ++l) {
-        rc = run_layer(h, l, M, rows, false, key_limit, s);
+        rc = use_tc(h, M) ? run_layer_tc(h, l, M, rows, key_limit, s)
+                          : run_layer(h, l, M, rows, false, key_limit, s);
         if (rc) return rc;
       }
       rc = after_chunk(b0, ns, t0, tc);
@@ -543,6 +640,22 @@ int32_t mtj_bind_arenas(mtj_handle* h, void* wdev, int64_t wbytes, void* sdev, i
   MTJ_CUDA(cudaMemsetAsync(h->gemv_counters, 0, sizeof(uint32_t) * h->max_rows, s));
   MTJ_CUDA(cudaMemsetAsync(h->dev_err, 0, sizeof(uint32_t) * 4, s));
   MTJ_CUDA(cudaStreamSynchronize(s));   // `tab` is about to go out of scope
+  // TMA views for the tensor-core GEMM (needs K % 64 == 0 on both projections)
+  h->tc_ok = false;
+  const char* no_tc = getenv("MTJ_NO_TC");
+  if (h->d % 64 == 0 && (h->dl + h->ffl) % 64 == 0 && !(no_tc && no_tc[0] == '1')) {
+    const int bn = mtj::gemm_tc_token_tile();
+    bool ok = true;
+    for (auto& lw : h->layers) {
+      ok = ok && mtj::make_tensor_map_bf16(&lw.map_in, lw.w_in, 3 * h->dl + h->ffl, h->d, 128) == cudaSuccess;
+      ok = ok && mtj::make_tensor_map_bf16(&lw.map_out, lw.w_out, h->d, h->dl + h->ffl, 128) == cudaSuccess;
+    }
+    ok = ok && mtj::make_tensor_map_bf16(&h->map_proj, h->proj_w, h->Vl, h->d, 128) == cudaSuccess;
+    ok = ok && mtj::make_tensor_map_bf16(&h->map_xn, h->xn_bf16, h->max_rows, h->d, bn) == cudaSuccess;
+    ok = ok && mtj::make_tensor_map_bf16(&h->map_act, h->act_bf16, h->max_rows, h->dl + h->ffl, bn) == cudaSuccess;
+    if (!ok) return fail(MTJ_ERR_CUDA, "cuTensorMapEncodeTiled failed");
+    h->tc_ok = true;
+  }
   h->bound = true;
   h->loaded = 0;
   return MTJ_OK;
@@ -827,6 +940,14 @@ int32_t mtj_forward_logits(mtj_handle* h, const uint32_t* obs, const uint32_t* c
     const int lo = std::max(first, t0), hi = t0 + tc;
     if (lo >= hi) return MTJ_OK;
     const int per = hi - lo;
+    if (use_tc(h, ns * tc)) {
+      for (int i = 0; i < ns; ++i) {
+        float* dst = logits_out + (static_cast<size_t>(b0 + i) * n_last + (lo - first)) * h->Vl;
+        int32_t r2 = run_logits_tc(h, per, i * tc + (lo - t0), dst, s);
+        if (r2) return r2;
+      }
+      return MTJ_OK;
+    }
     std::vector<int32_t> sel(static_cast<size_t>(ns) * per);
     for (int i = 0; i < ns; ++i)
       for (int t = lo; t < hi; ++t) sel[static_cast<size_t>(i) * per + (t - lo)] = i * tc + (t - t0);
@@ -872,7 +993,8 @@ int32_t mtj_eval_loss(mtj_handle* h, const uint32_t* obs, const uint32_t* target
     ce.correct_out = correct;
     for (int m0 = 0; m0 < M; m0 += h->eval_rows) {
       const int n = std::min(h->eval_rows, M - m0);
-      int32_t r2 = run_logits(h, n, nullptr, h->eval_logits, false, s, m0);
+      int32_t r2 = use_tc(h, M) ? run_logits_tc(h, n, m0, h->eval_logits, s)
+                                : run_logits(h, n, nullptr, h->eval_logits, false, s, m0);
       if (r2) return r2;
       ce.logits = h->eval_logits;
       ce.row0 = m0;
@@ -995,6 +1117,8 @@ int32_t mtj_k_layer(mtj_handle* h, int32_t layer, const float* x_in, int32_t bat
   h->launches++;
   mtj::RowMap rows = {0, T, pos0, nullptr};
   if (decode) rows = {0, 1, 0, h->cur};
+  if (!decode && use_tc(h, static_cast<int>(M)))
+    return run_layer_tc(h, layer, static_cast<int>(M), rows, key_limit_host ? h->key_limit : nullptr, s, out);
   return run_layer(h, layer, static_cast<int>(M), rows, decode != 0, key_limit_host ? h->key_limit : nullptr, s, out);
 }
 
@@ -1005,6 +1129,7 @@ int32_t mtj_k_projection(mtj_handle* h, const float* x_in, int32_t rows, float* 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   MTJ_CUDA(mtj::launch_residual_stats(h->x, x_in, h->stats, rows, h->d, false, s, false));
   h->launches++;
+  if (use_tc(h, rows)) return run_logits_tc(h, rows, 0, logits_out, s);
   return run_logits(h, rows, nullptr, logits_out, false, s);
 }
 
@@ -1031,7 +1156,8 @@ int32_t mtj_k_projection_loss(mtj_handle* h, const float* x_in, const uint32_t* 
   ce.correct_out = correct_out;
   for (int m0 = 0; m0 < rows; m0 += h->eval_rows) {
     const int n = std::min(h->eval_rows, rows - m0);
-    rc = run_logits(h, n, nullptr, h->eval_logits, false, s, m0);
+    rc = use_tc(h, rows) ? run_logits_tc(h, n, m0, h->eval_logits, s)
+                         : run_logits(h, n, nullptr, h->eval_logits, false, s, m0);
     if (rc) return rc;
     ce.logits = h->eval_logits;
     ce.row0 = m0;

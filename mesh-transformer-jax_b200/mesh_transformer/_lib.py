@@ -60,6 +60,7 @@ def _load():
         "mtj_k_projection_loss": (i32, [vp, vp, vp, i32, vp, vp, vp]),
         "mtj_k_decode_attn_scratch_bytes": (i64, [i32, i32, i32, i32, i32]),
         "mtj_k_ln_gemv": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp]),
+        "mtj_k_gemm_tc": (i32, [vp, vp, vp, i32, i32, i32, vp, vp]),
         "mtj_k_decode_attn_noalloc": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, i32, vp]),
         "mtj_k_decode_attn": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, i64, vp, i32, vp]),
     }

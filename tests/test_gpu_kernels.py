@@ -41,3 +41,22 @@ def test_decode_attention_matches_reference(cuda_device, d_head, heads, batch, w
         ref = attention_reference(q[b], keys[b], vals[b], d_head)
         assert np.abs(got[b] - ref).max() <= 2e-3 * max(1.0, np.abs(ref).max())
     assert float(out[:, heads * d_head:].abs().max()) == 0.0     # nothing written past the row
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (128, 256, 256), (256, 1792, 256), (254, 512, 1280),
+                                   (2047, 4096, 4096), (100, 6300, 4096), (33, 384, 128)])
+def test_tensor_core_gemm_matches_fp32_matmul(cuda_device, M, N, K):
+    """tcgen05 GEMM against a plain fp32 matmul of the same bf16 values."""
+    import torch
+    from mesh_transformer._lib import check, lib
+    g = torch.Generator(device=cuda_device)
+    g.manual_seed(M * 7 + N)
+    w = (torch.randn((N, K), generator=g, device=cuda_device) * 0.05).to(torch.bfloat16)
+    x = torch.randn((M, K), generator=g, device=cuda_device).to(torch.bfloat16)
+    bias = torch.randn((N,), generator=g, device=cuda_device)
+    out = torch.full((M, N), float("nan"), device=cuda_device)
+    check(lib.mtj_k_gemm_tc(ptr(w), ptr(x), ptr(bias), M, N, K, ptr(out), torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    ref = x.float() @ w.float().T + bias
+    err = (out - ref).abs().max().item()
+    assert err <= 2e-3 * max(1.0, ref.abs().max().item()), err
