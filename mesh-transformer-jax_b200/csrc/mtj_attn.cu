@@ -1,10 +1,12 @@
 // Attention over the paged bf16 KV cache.
 //
 // decode_attn_kernel : one query per (sequence, head); the visible key range
-//   [max(pad, cur-window+1), cur] is cut into splits, one block per split;
-//   partial (max, sum, weighted V) triples are merged by the last block of each
-//   (sequence, head) to finish.  HBM-bound: every K/V byte is read once with
-//   coalesced 16-byte loads.  (reference: layers.py:316-338 -- the sliding
+//   [max(pad, cur-window+1), cur] is cut into one split per 64-token page, one
+//   block per split: the page's K and V slabs of that head are contiguous and
+//   arrive in shared memory by one bulk copy (TMA) each, issued before the wait
+//   on the predecessor kernel for every page but the newest.  Partial (max,
+//   sum, weighted V) triples are merged by the last block of each (sequence,
+//   head) to finish.  HBM-bound: every K/V byte is read once.  (reference: layers.py:316-338 -- the sliding
 //   window of seq-1 slots, left slots masked by tokens_decoded.)
 // prefill_attn_kernel: causal multi-query attention used to build the decode
 //   state and for eval (layers.py:275-283,299-313,347-366); CUDA-core version.
@@ -31,12 +33,14 @@ template <>
 struct KvVec<8> {
   uint4 v;
   __device__ __forceinline__ void load(const __nv_bfloat16* p) { v = ld_stream16(p); }
+  __device__ __forceinline__ void load_shared(const __nv_bfloat16* p) { v = *reinterpret_cast<const uint4*>(p); }
   __device__ __forceinline__ void get(float* f) const { unpack8(v, f); }
 };
 template <>
 struct KvVec<2> {
   uint32_t v;
   __device__ __forceinline__ void load(const __nv_bfloat16* p) { v = ld_stream4(p); }
+  __device__ __forceinline__ void load_shared(const __nv_bfloat16* p) { v = *reinterpret_cast<const uint32_t*>(p); }
   __device__ __forceinline__ void get(float* f) const {
     f[0] = bf16_lo(v);
     f[1] = bf16_hi(v);
@@ -46,37 +50,52 @@ struct KvVec<2> {
 template <int DH>
 __global__ void __launch_bounds__(kAttnThreads) decode_attn_kernel(const DecodeAttnArgs a) {
   constexpr int EPL = DH / 32;
-  constexpr int U = 4;
+  constexpr int TPW = kPageTokens / kAttnWarps;            // tokens per warp: 8
+  constexpr uint32_t kSlab = kPageTokens * DH * 2;         // one (page, head) slab of K or V in bytes
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int split = blockIdx.x, head = blockIdx.y, b = blockIdx.z;
 
+  extern __shared__ __align__(128) unsigned char attn_smem[];
+  __nv_bfloat16* sk = reinterpret_cast<__nv_bfloat16*>(attn_smem);
+  __nv_bfloat16* sv = reinterpret_cast<__nv_bfloat16*>(attn_smem + kSlab);
+  __shared__ __align__(8) uint64_t bar;
   __shared__ float sm_m[kAttnWarps], sm_l[kAttnWarps];
   __shared__ float sm_o[kAttnWarps][DH];
   __shared__ bool is_last;
 
   // The step counter, the page table and every cached token except the newest
-  // were written before the predecessor kernel started, so they may be read
-  // (and the old keys/values pulled into L2) before waiting for it.
+  // were written before the predecessor kernel started: the split geometry can
+  // be worked out, and all pages but the one holding the newest token fetched,
+  // before waiting for it.  One split = one 64-token page of one head, whose K
+  // (and V) slab is contiguous: a single bulk copy each.
   const int cur = *a.cur_dev;
   const int start = max(a.kv.pad[b], cur - a.window + 1);
   const int end = cur + 1;
-  const int nsplit = (end - start + a.split_tokens - 1) / a.split_tokens;
-  const int t0 = start + split * a.split_tokens;
-  const int t1 = min(end, t0 + a.split_tokens);
-  const int32_t* table = a.kv.page_table + static_cast<size_t>(b) * a.kv.ring_pages;
-  if (split < nsplit) {
-    constexpr int kLines = DH * 2 / 128;                    // 128-byte lines per token row
-    for (int i = threadIdx.x; i < (t1 - t0) * kLines; i += kAttnThreads) {
-      const int tt = t0 + i / kLines;
-      if (tt == cur) continue;                              // written by the predecessor
-      const size_t off = kv_offset(table, a.kv.ring_pages, a.heads, DH, head, tt) + (i % kLines) * 64;
-      prefetch_l2(a.kv.kpool + off);
-      prefetch_l2(a.kv.vpool + off);
-    }
+  const int first_page = start / kPageTokens;
+  const int nsplit = cur / kPageTokens - first_page + 1;
+  const int page_pos0 = (first_page + split) * kPageTokens;
+  const bool active = split < nsplit;
+  const bool newest_page = page_pos0 + kPageTokens > cur;
+  const int t0 = max(start, page_pos0), t1 = min(end, page_pos0 + kPageTokens);
+  const uint32_t bar_u32 = smem_u32(&bar);
+  auto fetch = [&]() {
+    const int32_t* table = a.kv.page_table + static_cast<size_t>(b) * a.kv.ring_pages;
+    const int page = table[(first_page + split) % a.kv.ring_pages];
+    const size_t off = (static_cast<size_t>(page) * a.heads + head) * kPageTokens * DH;
+    const uint64_t pol = l2_evict_first_policy();
+    mbar_expect_tx(bar_u32, 2 * kSlab);
+    bulk_load(smem_u32(sk), a.kv.kpool + off, kSlab, bar_u32, pol);
+    bulk_load(smem_u32(sv), a.kv.vpool + off, kSlab, bar_u32, pol);
+  };
+  if (threadIdx.x == 0) {
+    mbar_init(bar_u32, 1);
+    mbar_fence_init();
+    if (active && !newest_page) fetch();
   }
   pdl_wait();
   pdl_launch_dependents();
-  if (split >= nsplit) return;
+  if (!active) return;
+  if (threadIdx.x == 0 && newest_page) fetch();
 
   constexpr float scale = DH == 256 ? 0.0625f : 0.125f;   // 1 / sqrt(d_head), exact
   float q[EPL];
@@ -85,27 +104,24 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attn_kernel(const DecodeA
 #pragma unroll
     for (int e = 0; e < EPL; ++e) q[e] = qp[e] * scale;
   }
+  __syncthreads();                                         // the barrier's init is visible to every waiter
+  const bool arrived = mbar_wait(bar_u32, 0);
+  if (!arrived && threadIdx.x == 0 && a.dev_err) atomicOr(a.dev_err, kDevErrTimeout);
 
   float m = -INFINITY, l = 0.f, o[EPL];
 #pragma unroll
   for (int e = 0; e < EPL; ++e) o[e] = 0.f;
-
-  for (int t = t0 + warp; t < t1; t += kAttnWarps * U) {
-    KvVec<EPL> kv[U], vv[U];
-    bool ok[U];
+  {
+    float s[TPW];
+    bool ok[TPW];
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int tt = t + u * kAttnWarps;
-      ok[u] = tt < t1;
-      const size_t off = kv_offset(table, a.kv.ring_pages, a.heads, DH, head, ok[u] ? tt : t) + lane * EPL;
-      kv[u].load(a.kv.kpool + off);
-      vv[u].load(a.kv.vpool + off);
-    }
-    float s[U];
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
+    for (int u = 0; u < TPW; ++u) {
+      const int tt = page_pos0 + warp * TPW + u;
+      ok[u] = arrived && tt >= t0 && tt < t1;
+      KvVec<EPL> kv;
+      kv.load_shared(sk + static_cast<size_t>(warp * TPW + u) * DH + lane * EPL);
       float kf[EPL];
-      kv[u].get(kf);
+      kv.get(kf);
       float d = 0.f;
 #pragma unroll
       for (int e = 0; e < EPL; ++e) d = fmaf(q[e], kf[e], d);
@@ -114,26 +130,22 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attn_kernel(const DecodeA
 #pragma unroll
     for (int o2 = 16; o2 > 0; o2 >>= 1)
 #pragma unroll
-      for (int u = 0; u < U; ++u) s[u] += __shfl_xor_sync(0xffffffffu, s[u], o2);
-    float mn = m;
+      for (int u = 0; u < TPW; ++u) s[u] += __shfl_xor_sync(0xffffffffu, s[u], o2);
 #pragma unroll
-    for (int u = 0; u < U; ++u)
-      if (ok[u]) mn = fmaxf(mn, s[u]);
-    const float corr = __expf(m - mn);
-    l *= corr;
+    for (int u = 0; u < TPW; ++u)
+      if (ok[u]) m = fmaxf(m, s[u]);
 #pragma unroll
-    for (int e = 0; e < EPL; ++e) o[e] *= corr;
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
+    for (int u = 0; u < TPW; ++u) {
       if (!ok[u]) continue;
-      const float p = __expf(s[u] - mn);
+      const float p = __expf(s[u] - m);
+      KvVec<EPL> vv;
+      vv.load_shared(sv + static_cast<size_t>(warp * TPW + u) * DH + lane * EPL);
       float vf[EPL];
-      vv[u].get(vf);
+      vv.get(vf);
       l += p;
 #pragma unroll
       for (int e = 0; e < EPL; ++e) o[e] = fmaf(p, vf[e], o[e]);
     }
-    m = mn;
   }
 
   // merge the warps of this split
@@ -152,7 +164,7 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attn_kernel(const DecodeA
     float L = 0.f, O = 0.f;
 #pragma unroll
     for (int w = 0; w < kAttnWarps; ++w) {
-      const float f = __expf(sm_m[w] - M);     // exp(-inf) = 0 for idle warps
+      const float f = sm_m[w] == -INFINITY ? 0.f : __expf(sm_m[w] - M);   // warps without a visible key
       L = fmaf(sm_l[w], f, L);
       O = fmaf(sm_o[w][threadIdx.x], f, O);
     }
@@ -173,17 +185,47 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attn_kernel(const DecodeA
   __syncthreads();
   if (!is_last) return;
   __threadfence();
-  if (threadIdx.x < DH) {
+  {
+    // Merge of the splits: the per-split weights are worked out by one warp with all its
+    // loads in flight at once, then every output dimension sums its column with
+    // independent loads (a serial walk over the splits would cost one L2 round trip each).
+    __shared__ float wgt[64];
+    __shared__ float inv_l;
     const size_t base = (static_cast<size_t>(b) * a.heads + head) * a.max_splits;
-    float M = -INFINITY;
-    for (int sidx = 0; sidx < nsplit; ++sidx) M = fmaxf(M, __ldcg(a.part_ml + (base + sidx) * 2));
-    float L = 0.f, O = 0.f;
-    for (int sidx = 0; sidx < nsplit; ++sidx) {
-      const float f = __expf(__ldcg(a.part_ml + (base + sidx) * 2) - M);
-      L = fmaf(__ldcg(a.part_ml + (base + sidx) * 2 + 1), f, L);
-      O = fmaf(__ldcg(a.part_o + (base + sidx) * DH + threadIdx.x), f, O);
+    if (warp == 0) {
+      float ms[2], ls[2];
+#pragma unroll
+      for (int h2 = 0; h2 < 2; ++h2) {
+        const int sidx = lane + 32 * h2;
+        ms[h2] = sidx < nsplit ? __ldcg(a.part_ml + (base + sidx) * 2) : -INFINITY;
+        ls[h2] = sidx < nsplit ? __ldcg(a.part_ml + (base + sidx) * 2 + 1) : 0.f;
+      }
+      const float M = warp_max(fmaxf(ms[0], ms[1]));
+      float lsum = 0.f;
+#pragma unroll
+      for (int h2 = 0; h2 < 2; ++h2) {
+        const float f = ms[h2] == -INFINITY ? 0.f : __expf(ms[h2] - M);
+        wgt[lane + 32 * h2] = f;
+        lsum = fmaf(ls[h2], f, lsum);
+      }
+      lsum = warp_sum(lsum);
+      if (lane == 0) inv_l = 1.0f / lsum;
     }
-    a.out[static_cast<size_t>(b) * a.ld_out + head * DH + threadIdx.x] = O / L;
+    __syncthreads();
+    if (threadIdx.x < DH) {
+      const float* po = a.part_o + base * DH + threadIdx.x;
+      float O = 0.f;
+      int sidx = 0;
+      for (; sidx + 8 <= nsplit; sidx += 8) {
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = __ldcg(po + static_cast<size_t>(sidx + u) * DH);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) O = fmaf(v[u], wgt[sidx + u], O);
+      }
+      for (; sidx < nsplit; ++sidx) O = fmaf(__ldcg(po + static_cast<size_t>(sidx) * DH), wgt[sidx], O);
+      a.out[static_cast<size_t>(b) * a.ld_out + head * DH + threadIdx.x] = O * inv_l;
+    }
   }
   if (threadIdx.x == 0) a.counters[b * a.heads + head] = 0u;
 }
@@ -283,13 +325,37 @@ cudaError_t launch_cfg(K kernel, dim3 grid, dim3 block, cudaStream_t s, bool pdl
 
 }  // namespace
 
+template <int DH>
+cudaError_t launch_decode_dh(const DecodeAttnArgs& a, cudaStream_t s, bool pdl) {
+  constexpr int smem = 2 * kPageTokens * DH * 2;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(decode_attn_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(a.grid_splits, a.heads, a.B);
+  cfg.blockDim = dim3(kAttnThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, decode_attn_kernel<DH>, a);
+}
+
+// Splits of the visible window: one per 64-token page it can touch.
+int decode_attn_splits(int window) { return (window + kPageTokens - 1) / kPageTokens + 1; }
+
 cudaError_t launch_decode_attn(const DecodeAttnArgs& a, cudaStream_t s, bool pdl) {
-  if (a.B <= 0 || a.split_tokens <= 0 || a.grid_splits <= 0 || a.grid_splits > a.max_splits ||
-      static_cast<long long>(a.grid_splits) * a.split_tokens < a.window)
+  if (a.B <= 0 || a.grid_splits <= 0 || a.grid_splits > a.max_splits || a.kv.ring_pages < a.grid_splits ||
+      (a.grid_splits < decode_attn_splits(a.window) && a.grid_splits < a.kv.ring_pages))
     return cudaErrorInvalidValue;
-  const dim3 grid(a.grid_splits, a.heads, a.B), block(kAttnThreads);
-  if (a.d_head == 256) return launch_cfg(decode_attn_kernel<256>, grid, block, s, pdl, a);
-  if (a.d_head == 64) return launch_cfg(decode_attn_kernel<64>, grid, block, s, pdl, a);
+  if (a.d_head == 256) return launch_decode_dh<256>(a, s, pdl);
+  if (a.d_head == 64) return launch_decode_dh<64>(a, s, pdl);
   return cudaErrorInvalidValue;
 }
 

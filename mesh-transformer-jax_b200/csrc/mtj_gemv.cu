@@ -163,8 +163,8 @@ __global__ void __launch_bounds__(kGemvThreads, BT == 1 ? (EPI == kEpiOut ? 4 : 
   if (active && kpart == 0) {
     const float partner = __shfl_xor_sync(0xffffffffu, val, 1);   // the other row of the RoPE pair
     const int r = lane % RW, bt = lane / RW;
-    const int n = row0 + r;
-    if (lane < RW * BT && bt < nb && n < a.N) {
+    const int n = a.n0 + row0 + r;                 // row index within the full projection
+    if (lane < RW * BT && bt < nb && row0 + r < a.N) {
       const int m = m0 + bt;
       if (EPI == kEpiInProj) {
         const int seq = a.rows.b0 + m / a.rows.Tc;
@@ -218,9 +218,11 @@ __global__ void __launch_bounds__(kGemvThreads, BT == 1 ? (EPI == kEpiOut ? 4 : 
     for (int bt = 0; bt < nb; ++bt) {
       const float* row = a.out + static_cast<size_t>(m0 + bt) * a.N;
       float s = 0.f;
+#pragma unroll 8
       for (int i = threadIdx.x; i < a.N; i += kGemvThreads) s += __ldcg(row + i);
       const float mu = block_sum(s, red) / static_cast<float>(a.N);
       float v = 0.f;
+#pragma unroll 8
       for (int i = threadIdx.x; i < a.N; i += kGemvThreads) {
         const float dlt = __ldcg(row + i) - mu;
         v = fmaf(dlt, dlt, v);

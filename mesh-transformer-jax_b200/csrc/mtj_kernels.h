@@ -29,8 +29,9 @@ enum GemvEpilogue { kEpiInProj = 0, kEpiOut = 1, kEpiLogits = 2 };
 
 struct GemvArgs {
   // y[m, n] = sum_k W[n, k] * act(x[m, k]);  W is bf16 [N, K] (K contiguous).
-  const __nv_bfloat16* W;
-  int N, K, M;
+  const __nv_bfloat16* W;      // first row of this launch
+  int N, K, M;                 // N = rows covered by this launch
+  int n0;                      // index of W's first row within the full projection (epilogue indexing)
   const float* x;              // [M, ldx] fp32
   int ldx;
   // LayerNorm prologue (in-proj and logits): act(x) = scale*rstd*(x-mean)+offset
@@ -80,15 +81,16 @@ struct DecodeAttnArgs {
   KvCache kv;
   int B, heads, d_head, window;  // window = seq - 1 key slots
   const int32_t* cur_dev;      // absolute position of the query token
-  int split_tokens;            // keys per split (multiple of 8)
   int max_splits;              // stride of the partial buffers
-  int grid_splits;             // blocks launched per (sequence, head) >= ceil(window / split_tokens)
+  int grid_splits;             // blocks per (sequence, head) = decode_attn_splits(window)
   float* part_o;               // [B, heads, max_splits, d_head]
   float* part_ml;              // [B, heads, max_splits, 2]
   uint32_t* counters;          // [B*heads] zero-initialised, self-resetting
   float* out;                  // act2 base: out[b*ld_out + head*d_head + j]
   int ld_out;
+  uint32_t* dev_err;           // may be null
 };
+int decode_attn_splits(int window);
 cudaError_t launch_decode_attn(const DecodeAttnArgs& a, cudaStream_t s, bool pdl);
 
 struct PrefillAttnArgs {

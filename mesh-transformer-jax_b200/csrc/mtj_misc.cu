@@ -68,11 +68,20 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const ArgmaxArgs a) {
   const float* row = a.logits + static_cast<size_t>(b) * a.V;
   float best = -INFINITY;
   int bi = -1;
-  for (int i = threadIdx.x; i < a.V; i += blockDim.x) {
-    const float v = row[i];
-    if (v > best || (v == best && i > bi) || bi < 0) {
-      best = v;
-      bi = i;
+  for (int i0 = threadIdx.x; i0 < a.V; i0 += 8 * blockDim.x) {
+    float v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {            // eight independent loads in flight
+      const int i = i0 + u * blockDim.x;
+      v[u] = i < a.V ? row[i] : -INFINITY;
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int i = i0 + u * blockDim.x;
+      if (i < a.V && (v[u] > best || (v[u] == best && i > bi) || bi < 0)) {
+        best = v[u];
+        bi = i;
+      }
     }
   }
 #pragma unroll

@@ -124,6 +124,12 @@ struct mtj_handle {
   int steps_done = 0;
   int64_t launches = 0;
   bool use_pdl = true;
+  int ks_inproj = 0, ks_out = 0, ks_logits = 0;   // K-split overrides (tuning; 0 = automatic)
+  // decode: attention runs on a side stream next to the FF half of the in-projection
+  bool fork_attn = true;
+  bool fork_pdl = false;            // let the out-projection start early although it also waits on the side stream
+  cudaStream_t side_stream = nullptr;
+  cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
 
   // decode step captured once per batch size and replayed (the step counter,
   // tokens and page table live on the device, so the graph never changes)
@@ -265,8 +271,32 @@ int32_t run_layer(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, bool
   a.act2 = h->act2;
   a.kv = h->kv(layer);
   a.dev_err = h->dev_err;
+  a.ks_override = decode ? h->ks_inproj : 0;
+  // Decode: only the Q/K/V rows have to be finished before attention can start, so the
+  // projection is launched in two parts and attention runs beside the FF-in part.
+  const bool fork = decode && h->fork_attn;
+  if (fork && !h->side_stream) {
+    MTJ_CUDA(cudaStreamCreateWithFlags(&h->side_stream, cudaStreamNonBlocking));
+    MTJ_CUDA(cudaEventCreateWithFlags(&h->ev_fork, cudaEventDisableTiming));
+    MTJ_CUDA(cudaEventCreateWithFlags(&h->ev_join, cudaEventDisableTiming));
+  }
+  cudaStream_t sa = fork ? h->side_stream : s;      // stream of the attention kernel
   h->prof_begin(MTJ_FAMILY_INPROJ, s);
-  MTJ_CUDA(mtj::launch_gemv(mtj::kEpiInProj, a, s, pdl));
+  if (fork) {
+    GemvArgs qkv = a;
+    qkv.N = 3 * h->dl;
+    MTJ_CUDA(mtj::launch_gemv(mtj::kEpiInProj, qkv, s, pdl));
+    MTJ_CUDA(cudaEventRecord(h->ev_fork, s));
+    MTJ_CUDA(cudaStreamWaitEvent(sa, h->ev_fork, 0));
+    GemvArgs ffp = a;
+    ffp.W = lw.w_in + static_cast<size_t>(3) * h->dl * h->d;
+    ffp.N = h->ffl;
+    ffp.n0 = 3 * h->dl;
+    MTJ_CUDA(mtj::launch_gemv(mtj::kEpiInProj, ffp, s, pdl));
+    h->launches++;
+  } else {
+    MTJ_CUDA(mtj::launch_gemv(mtj::kEpiInProj, a, s, pdl));
+  }
   h->prof_end(s);
   h->launches++;
 
@@ -279,23 +309,21 @@ int32_t run_layer(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, bool
     d.d_head = h->dh;
     d.window = h->W;
     d.cur_dev = h->cur;
-    // enough blocks to fill the GPU twice, at least 32 keys per split
-    int want = (2 * 148 + M * h->heads - 1) / (M * h->heads);
-    want = std::max(1, std::min(want, h->max_splits));
-    int st = (h->W + want - 1) / want;
-    st = std::max(st, (h->W + h->max_splits - 1) / h->max_splits);
-    st = std::max(32, (st + 7) / 8 * 8);
-    d.split_tokens = st;
     d.max_splits = h->max_splits;
-    d.grid_splits = (h->W + st - 1) / st;
+    d.grid_splits = std::min(mtj::decode_attn_splits(h->W), h->ring_pages);
+    d.dev_err = h->dev_err;
     d.part_o = h->part_o;
     d.part_ml = h->part_ml;
     d.counters = h->counters;
     d.out = h->act2;
     d.ld_out = h->dl + h->ffl;
-    h->prof_begin(MTJ_FAMILY_ATTN, s);
-    MTJ_CUDA(mtj::launch_decode_attn(d, s, pdl));
-    h->prof_end(s);
+    if (!fork) h->prof_begin(MTJ_FAMILY_ATTN, s);
+    MTJ_CUDA(mtj::launch_decode_attn(d, sa, pdl && !fork));
+    if (!fork) h->prof_end(s);
+    if (fork) {
+      MTJ_CUDA(cudaEventRecord(h->ev_join, sa));
+      MTJ_CUDA(cudaStreamWaitEvent(s, h->ev_join, 0));
+    }
   } else {
     mtj::PrefillAttnArgs p = {};
     p.q = h->q;
@@ -328,8 +356,9 @@ int32_t run_layer(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, bool
   o.stats_out = (h->mp == 1 && !detached_out) ? h->stats : nullptr;
   o.counters = h->gemv_counters;
   o.dev_err = h->dev_err;
+  o.ks_override = decode ? h->ks_out : 0;
   h->prof_begin(MTJ_FAMILY_OUTPROJ, s);
-  MTJ_CUDA(mtj::launch_gemv(mtj::kEpiOut, o, s, pdl));
+  MTJ_CUDA(mtj::launch_gemv(mtj::kEpiOut, o, s, pdl && (!fork || h->fork_pdl)));
   h->prof_end(s);
   h->launches++;
   if (h->mp > 1 && detached_out) {
@@ -467,6 +496,7 @@ int32_t run_logits(mtj_handle* h, int M, const int32_t* row_select, float* out, 
   a.ld_logits = h->Vl;
   a.row_select = row_select;
   a.dev_err = h->dev_err;
+  a.ks_override = decode ? h->ks_logits : 0;
   h->prof_begin(MTJ_FAMILY_LOGITS, s);
   MTJ_CUDA(mtj::launch_gemv(mtj::kEpiLogits, a, s, h->use_pdl && decode));
   h->prof_end(s);
@@ -552,6 +582,8 @@ int32_t mtj_create(const mtj_config* c, mtj_handle** out) {
   if (c->d_model % 8 || (c->d_model / mp) % 8) return fail(MTJ_ERR_UNSUPPORTED, "d_model / mp must be a multiple of 8");
   if ((c->n_vocab / mp) % 4) return fail(MTJ_ERR_UNSUPPORTED, "n_vocab / mp must be a multiple of 4");
   if (c->max_batch <= 0 || c->max_gen < 0 || c->max_rows <= 0) return fail(MTJ_ERR_INVALID, "bad capacity");
+  if (mtj::decode_attn_splits(c->seq - 1) > 64)
+    return fail(MTJ_ERR_UNSUPPORTED, "seq up to 4032 is supported (64 pages of 64 tokens per sliding window)");
 
   mtj_handle* h = new mtj_handle();
   h->cfg = *c;
@@ -577,10 +609,20 @@ int32_t mtj_create(const mtj_config* c, mtj_handle** out) {
   const int need_ring = (c->seq + mtj::kPageTokens - 1) / mtj::kPageTokens + 1;
   h->ring_pages = std::min(need_all, need_ring);
   h->n_pages = h->ring_pages * h->max_batch;
-  h->max_splits = 64;
+  h->max_splits = mtj::decode_attn_splits(h->W);
   h->expected = 2 + 10LL * h->L + 4;
   const char* e = getenv("MTJ_NO_PDL");
   h->use_pdl = !(e && e[0] == '1');
+  e = getenv("MTJ_NO_FORK");
+  h->fork_attn = !(e && e[0] == '1');
+  e = getenv("MTJ_FORK_PDL");
+  h->fork_pdl = e && e[0] == '1';
+  e = getenv("MTJ_KS_INPROJ");
+  if (e) h->ks_inproj = atoi(e);
+  e = getenv("MTJ_KS_OUT");
+  if (e) h->ks_out = atoi(e);
+  e = getenv("MTJ_KS_LOGITS");
+  if (e) h->ks_logits = atoi(e);
   e = getenv("MTJ_NO_GRAPH");
   h->use_graph = !(e && e[0] == '1');
 
@@ -592,6 +634,9 @@ int32_t mtj_destroy(mtj_handle* h) {
   if (h) {
     for (cudaEvent_t e : h->ev_pool) cudaEventDestroy(e);
     if (h->graph_exec) cudaGraphExecDestroy(h->graph_exec);
+    if (h->ev_fork) cudaEventDestroy(h->ev_fork);
+    if (h->ev_join) cudaEventDestroy(h->ev_join);
+    if (h->side_stream) cudaStreamDestroy(h->side_stream);
     if (h->comm) mtj::comm_destroy(h->comm);
     if (h->capture_stream) cudaStreamDestroy(h->capture_stream);
   }

@@ -23,7 +23,7 @@ int32_t plan_decode_attn(int32_t batch, int32_t heads, int32_t d_head, int32_t w
     *err = "d_head must be 64 or 256";
     return MTJ_ERR_UNSUPPORTED;
   }
-  p->splits = (window + split_tokens - 1) / split_tokens;
+  p->splits = decode_attn_splits(window);      // one split per 64-token page; split_tokens is only validated
   const int64_t rows = static_cast<int64_t>(batch) * heads;
   p->counters_bytes = align256(rows * 4);
   p->ml_off = p->counters_bytes;
@@ -52,7 +52,6 @@ int32_t run_decode_attn(const DecodeAttnPlan& p, char* scratch, const float* q, 
     a.d_head = d_head;
     a.window = window;
     a.cur_dev = cur;
-    a.split_tokens = split_tokens;
     a.max_splits = p.splits;
     a.grid_splits = p.splits;
     a.counters = reinterpret_cast<uint32_t*>(scratch);
