@@ -224,7 +224,9 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attn_kernel(const DecodeA
         for (int u = 0; u < 8; ++u) O = fmaf(v[u], wgt[sidx + u], O);
       }
       for (; sidx < nsplit; ++sidx) O = fmaf(__ldcg(po + static_cast<size_t>(sidx) * DH), wgt[sidx], O);
-      a.out[static_cast<size_t>(b) * a.ld_out + head * DH + threadIdx.x] = O * inv_l;
+      const size_t oi = static_cast<size_t>(b) * a.ld_out + head * DH + threadIdx.x;
+      if (a.out_bf16) a.out_bf16[oi] = __float2bfloat16_rn(O * inv_l);
+      else a.out[oi] = O * inv_l;
     }
   }
   if (threadIdx.x == 0) a.counters[b * a.heads + head] = 0u;

@@ -21,6 +21,8 @@
 #include <cudaTypedefs.h>
 #include <math.h>
 
+#include <algorithm>
+
 #include "mtj_common.cuh"
 #include "mtj_kernels.h"
 
@@ -114,7 +116,11 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
 
   const int n0 = blockIdx.x * kBM;           // first weight row of the tile
   const int m0 = blockIdx.y * BN;            // first token row of the tile
-  const int nk = a.K / kBK;
+  // split-K: block z covers k-blocks [kb0, kb0 + nk) and leaves a partial sum
+  const int nk_total = a.K / kBK;
+  const int per_z = (nk_total + gridDim.z - 1) / gridDim.z;
+  const int kb0 = blockIdx.z * per_z;
+  const int nk = max(0, min(per_z, nk_total - kb0));
 
   if (warp == 0) {
     if (lane == 0) {
@@ -126,8 +132,8 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
         }
         mbar_expect_tx(full_bar(s), kStageBytes);
         const uint32_t dst = smem_base + s * kStageBytes;
-        tma_load_2d(dst, &map_w, kb * kBK, n0, full_bar(s));
-        tma_load_2d(dst + kABytes, &map_x, kb * kBK, a.x_row0 + m0, full_bar(s));
+        tma_load_2d(dst, &map_w, (kb0 + kb) * kBK, n0, full_bar(s));
+        tma_load_2d(dst + kABytes, &map_x, (kb0 + kb) * kBK, a.x_row0 + m0, full_bar(s));
       }
     }
   } else if (warp == 1) {
@@ -149,8 +155,8 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
       tc_commit(acc_bar);                          // accumulator complete
     }
   } else {
-    const bool ok = mbar_wait(acc_bar, 0);
-    if (!ok) atomicOr(&failed, 1u);
+    const bool ok = nk > 0 && mbar_wait(acc_bar, 0);
+    if (!ok && nk > 0) atomicOr(&failed, 1u);
     tc_fence_after();
     const int quad = warp & 3;                     // TMEM lanes this warp may read
     const int n = n0 + quad * 32 + lane;
@@ -174,10 +180,15 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
     } else if (n_ok) {
       bias = a.bias[n];
     }
-    if (ok) {
+    if (ok || (nk == 0 && a.partial)) {
       for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t r[32];
-        tmem_ld32(tmem_acc + (static_cast<uint32_t>(quad * 32) << 16) + c0, r);
+        if (ok) {
+          tmem_ld32(tmem_acc + (static_cast<uint32_t>(quad * 32) << 16) + c0, r);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = 0u;      // an empty K range contributes zeros
+        }
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           const int m = m0 + c0 + i;
@@ -186,7 +197,7 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
           if (m >= a.M || !n_ok) continue;
           if (EPI == kEpiInProj) {
             const int seq = a.rows.b0 + m / a.rows.Tc;
-            const int pos = a.rows.pos0_host + m % a.rows.Tc;
+            const int pos = (a.rows.pos0_dev ? *a.rows.pos0_dev : a.rows.pos0_host) + m % a.rows.Tc;
             if (region < 3) {
               float y = v;
               if (region < 2 && j < a.rot) {
@@ -205,6 +216,9 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
               a.act_out[static_cast<size_t>(m) * (a.dl + a.ffl) + a.dl + nn] =
                   __float2bfloat16_rn(gelu_tanh(v + bias));
             }
+          } else if (a.partial) {
+            // split-K: raw partial sum; bias / residual are added by the reduction kernel
+            a.partial[(static_cast<size_t>(blockIdx.z) * a.M + m) * a.N + n] = v;
           } else if (EPI == kEpiOut) {
             float y = v + bias;
             if (a.residual) y += a.residual[static_cast<size_t>(m) * a.N + n];
@@ -283,7 +297,7 @@ cudaError_t launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const GemmTc
     configured = true;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((a.N + kBM - 1) / kBM, (a.M + BN - 1) / BN, 1);
+  cfg.gridDim = dim3((a.N + kBM - 1) / kBM, (a.M + BN - 1) / BN, a.partial ? a.ksplit : 1);
   cfg.blockDim = dim3(kTcThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = s;
@@ -323,6 +337,32 @@ cudaError_t launch_gemm_tc(GemvEpilogue epi, const void* map_w, const void* map_
     case kEpiOut: return launch_tc<128, 3, kEpiOut>(mw, mx, a, s, pdl);
     default: return launch_tc<128, 3, kEpiLogits>(mw, mx, a, s, pdl);
   }
+}
+
+namespace {
+// out[m, n] = sum_z partial[z, m, n] + bias[n] (+ residual[m, n]); fixed summation order
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, int ksplit, int M, int N,
+                                     const float* __restrict__ bias, const float* residual, float* out, int ld_out) {
+  const size_t total = static_cast<size_t>(M) * N;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const int n = static_cast<int>(i % N);
+    const size_t m = i / N;
+    float acc = 0.f;
+    for (int z = 0; z < ksplit; ++z) acc += partial[static_cast<size_t>(z) * total + i];
+    acc += bias[n];
+    if (residual) acc += residual[i];
+    out[m * ld_out + n] = acc;
+  }
+}
+}  // namespace
+
+cudaError_t launch_splitk_reduce(const float* partial, int ksplit, int M, int N, const float* bias,
+                                 const float* residual, float* out, int ld_out, cudaStream_t s) {
+  const size_t total = static_cast<size_t>(M) * N;
+  const int grid = static_cast<int>(std::min<size_t>((total + 255) / 256, 148 * 8));
+  splitk_reduce_kernel<<<grid, 256, 0, s>>>(partial, ksplit, M, N, bias, residual, out, ld_out);
+  return cudaGetLastError();
 }
 
 cudaError_t launch_ln_rows(const float* x, const float* scale, const float* offset, __nv_bfloat16* out, int rows,

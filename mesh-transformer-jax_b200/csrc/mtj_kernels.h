@@ -86,7 +86,8 @@ struct DecodeAttnArgs {
   float* part_o;               // [B, heads, max_splits, d_head]
   float* part_ml;              // [B, heads, max_splits, 2]
   uint32_t* counters;          // [B*heads] zero-initialised, self-resetting
-  float* out;                  // act2 base: out[b*ld_out + head*d_head + j]
+  float* out;                  // act2 base: out[b*ld_out + head*d_head + j] (fp32), or
+  __nv_bfloat16* out_bf16;     // the same element in bf16 (operand of the tensor-core out-proj)
   int ld_out;
   uint32_t* dev_err;           // may be null
 };
@@ -130,9 +131,13 @@ struct GemmTcArgs {
   const float* residual;       // [M, N] or null
   float* out;                  // out-proj: [M, N]; logits: [M, ld_out]
   int ld_out;
+  float* partial;              // split-K: [ksplit, M, N] raw partial sums (out-proj / logits epilogues), or null
+  int ksplit;
   uint32_t* dev_err;
 };
 int gemm_tc_token_tile();
+cudaError_t launch_splitk_reduce(const float* partial, int ksplit, int M, int N, const float* bias,
+                                 const float* residual, float* out, int ld_out, cudaStream_t s);
 cudaError_t make_tensor_map_bf16(void* map_out_128B, const void* base, int64_t rows, int64_t K, int box_rows);
 cudaError_t launch_gemm_tc(GemvEpilogue epi, const void* map_w, const void* map_x, const GemmTcArgs& a,
                            cudaStream_t s, bool pdl);

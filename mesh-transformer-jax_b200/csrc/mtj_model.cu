@@ -31,6 +31,9 @@ int32_t fail(int32_t code, const std::string& msg) {
       return fail(MTJ_ERR_CUDA, std::string(#expr) + ": " + cudaGetErrorString(_e)); \
   } while (0)
 
+constexpr int kTcSplitMax = 8;      // split-K factor limit of the small-M out-projection
+constexpr int kTcSplitRows = 128;   // it is used up to this many token rows
+
 struct alignas(64) TensorMap { unsigned char bytes[128]; };   // a CUtensorMap
 
 struct LayerWeights {
@@ -100,6 +103,7 @@ struct mtj_handle {
   __nv_bfloat16* xn_bf16 = nullptr;   // [max_rows, d] LayerNorm output
   __nv_bfloat16* act_bf16 = nullptr;  // [max_rows, dl + ffl] attention vector | gelu(ff)
   TensorMap map_xn, map_act, map_proj;
+  float* tc_partial = nullptr;        // [kTcSplitMax, kTcSplitRows, d] split-K partial sums of small-M out-projections
   int eval_rows = 0;                // rows of logits materialised at a time by the loss path
   float* eval_logits = nullptr;     // [eval_rows, Vl]
   float* ce_max = nullptr;          // [max_rows] local max, then global max
@@ -197,6 +201,7 @@ struct mtj_handle {
     top_p = c.take<float>(max_batch);
     temp = c.take<float>(max_batch);
     sample_scratch = c.take<char>(mtj::sample_scratch_bytes(max_batch, V));
+    tc_partial = c.take<float>(static_cast<int64_t>(kTcSplitMax) * std::min<int64_t>(R, kTcSplitRows) * d);
     xn_bf16 = c.take<__nv_bfloat16>(R * d);
     act_bf16 = c.take<__nv_bfloat16>(R * (dl + ffl));
     eval_rows = static_cast<int>(std::min<int64_t>(R, 256));
@@ -375,7 +380,7 @@ int32_t run_layer(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, bool
 // The same layer for many token rows on the tensor cores: LayerNorm to bf16, in-proj GEMM
 // (RoPE / KV / GELU epilogue), causal attention, out-proj GEMM (+ bias + residual).
 int32_t run_layer_tc(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, const int32_t* key_limit,
-                     cudaStream_t s, float* detached_out = nullptr) {
+                     cudaStream_t s, float* detached_out = nullptr, bool decode = false) {
   LayerWeights& lw = h->layers[layer];
   MTJ_CUDA(mtj::launch_ln_rows(h->x, lw.ln_scale, lw.ln_offset, h->xn_bf16, M, h->d, s));
   mtj::GemmTcArgs a = {};
@@ -398,18 +403,38 @@ int32_t run_layer_tc(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, c
   MTJ_CUDA(mtj::launch_gemm_tc(mtj::kEpiInProj, &lw.map_in, &h->map_xn, a, s, false));
   h->prof_end(s);
 
-  mtj::PrefillAttnArgs p = {};
-  p.q = h->q;
-  p.kv = h->kv(layer);
-  p.rows = rows;
-  p.M = M;
-  p.heads = h->heads;
-  p.d_head = h->dh;
-  p.key_limit = key_limit;
-  p.out_bf16 = h->act_bf16;
-  p.ld_out = h->dl + h->ffl;
   h->prof_begin(MTJ_FAMILY_ATTN, s);
-  MTJ_CUDA(mtj::launch_prefill_attn(p, s));
+  if (decode) {
+    mtj::DecodeAttnArgs d = {};
+    d.q = h->q;
+    d.kv = h->kv(layer);
+    d.B = M;
+    d.heads = h->heads;
+    d.d_head = h->dh;
+    d.window = h->W;
+    d.cur_dev = h->cur;
+    d.max_splits = h->max_splits;
+    d.grid_splits = std::min(mtj::decode_attn_splits(h->W), h->ring_pages);
+    d.dev_err = h->dev_err;
+    d.part_o = h->part_o;
+    d.part_ml = h->part_ml;
+    d.counters = h->counters;
+    d.out_bf16 = h->act_bf16;
+    d.ld_out = h->dl + h->ffl;
+    MTJ_CUDA(mtj::launch_decode_attn(d, s, false));
+  } else {
+    mtj::PrefillAttnArgs p = {};
+    p.q = h->q;
+    p.kv = h->kv(layer);
+    p.rows = rows;
+    p.M = M;
+    p.heads = h->heads;
+    p.d_head = h->dh;
+    p.key_limit = key_limit;
+    p.out_bf16 = h->act_bf16;
+    p.ld_out = h->dl + h->ffl;
+    MTJ_CUDA(mtj::launch_prefill_attn(p, s));
+  }
   h->prof_end(s);
 
   mtj::GemmTcArgs o = {};
@@ -421,8 +446,22 @@ int32_t run_layer_tc(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, c
   o.out = h->mp == 1 ? (detached_out ? detached_out : h->x) : h->part;
   o.ld_out = h->d;
   o.dev_err = h->dev_err;
+  // Few token rows give only d/128 tiles: split K over blocks so the whole GPU streams the weights.
+  const int tiles = ((h->d + 127) / 128) * ((M + mtj::gemm_tc_token_tile() - 1) / mtj::gemm_tc_token_tile());
+  int ksplit = 1;
+  if (M <= kTcSplitRows && tiles < 148) ksplit = std::max(1, std::min({kTcSplitMax, 296 / tiles, o.K / 64}));
   h->prof_begin(MTJ_FAMILY_OUTPROJ, s);
-  MTJ_CUDA(mtj::launch_gemm_tc(mtj::kEpiOut, &lw.map_out, &h->map_act, o, s, false));
+  if (ksplit > 1) {
+    float* dst = o.out;
+    const float* res = o.residual;
+    o.partial = h->tc_partial;
+    o.ksplit = ksplit;
+    MTJ_CUDA(mtj::launch_gemm_tc(mtj::kEpiOut, &lw.map_out, &h->map_act, o, s, false));
+    MTJ_CUDA(mtj::launch_splitk_reduce(h->tc_partial, ksplit, M, h->d, lw.b_out, res, dst, h->d, s));
+    h->launches++;
+  } else {
+    MTJ_CUDA(mtj::launch_gemm_tc(mtj::kEpiOut, &lw.map_out, &h->map_act, o, s, false));
+  }
   h->prof_end(s);
   h->launches += 4;
   if (h->mp > 1 && detached_out) {
@@ -457,6 +496,8 @@ int32_t run_logits_tc(mtj_handle* h, int M, int row0, float* out, cudaStream_t s
 }
 
 bool use_tc(const mtj_handle* h, int M) { return h->tc_ok && M >= 32; }
+// decode: from this many sequences on, one tensor-core pass over the weights beats ceil(B/4) GEMV passes
+bool use_tc_decode(const mtj_handle* h, int B) { return h->tc_ok && B >= 8; }
 
 int32_t run_embed(mtj_handle* h, const uint32_t* ids, int ids_ld, int M, const mtj::RowMap& rows,
                   bool decode, cudaStream_t s) {
@@ -886,11 +927,12 @@ int32_t mtj_decode_step(mtj_handle* h, const uint32_t* tokens_in, const float* t
     mtj::RowMap erows = {0, 1, 0, nullptr};
     int32_t r = run_embed(h, h->tokens, 1, B, erows, true, st);
     if (r) return r;
+    const bool tc = use_tc_decode(h, B);
     for (int l = 0; l < h->L; ++l) {
-      r = run_layer(h, l, B, rows, true, nullptr, st);
+      r = tc ? run_layer_tc(h, l, B, rows, nullptr, st, nullptr, true) : run_layer(h, l, B, rows, true, nullptr, st);
       if (r) return r;
     }
-    r = run_logits(h, B, nullptr, h->logits, true, st);
+    r = tc ? run_logits_tc(h, B, 0, h->logits, st) : run_logits(h, B, nullptr, h->logits, true, st);
     if (r) return r;
     if (h->mp > 1) {
       // all_gather + transpose + flatten of ProjectionShard.__call__ (layers.py:565-567)

@@ -4,6 +4,7 @@ torch.distributed); all model math runs in the library's CUDA kernels."""
 from __future__ import annotations
 
 import ctypes
+import sys
 
 import numpy as np
 import torch
@@ -124,8 +125,7 @@ class ShardRuntime:
         # At interpreter shutdown the CUDA context and the peers of a collective
         # communicator may already be gone: tearing the handle down then can
         # block, so it is only done while the interpreter is alive.
-        import sys
-        if sys.is_finalizing():
+        if sys is None or sys.is_finalizing():
             return
         try:
             self.close()
