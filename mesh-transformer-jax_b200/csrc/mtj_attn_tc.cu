@@ -1,0 +1,342 @@
+// Causal flash-style attention for prefill / eval on the tensor cores
+// (d_head = 256): tcgen05.mma with S and O in tensor memory, Q / K / V tiles
+// staged by TMA, fp32 online softmax in registers.  Reference semantics:
+// layers.py:275-283 (logits / sqrt(d_head), additive masks, softmax, weighted
+// V) with the causal mask of :305-308, the left-pad mask of :353-360 and the
+// eval key mask of transformer_shard.py:130.
+//
+// One block = one (sequence, head, 128-query tile).  Keys are walked in blocks
+// of 64 (= one page of the KV cache, whose (page, head) slab is a dense
+// [64, 256] matrix):
+//     S[128, 64]   = Q[128, 256] . K^T          16 MMAs (K-major operands)
+//     P            = exp2(S*c - m)              4 softmax warps, one row per thread
+//     O[128, 256] += P[128, 64] . V[64, 256]    4 MMAs (V is MN-major: no transpose)
+// Warp 0 feeds TMA, warp 1 issues the MMAs, warps 2-5 do the softmax and the
+// epilogue.  O is only rescaled when a row's running maximum grows by more
+// than 2^8 (the stale maximum stays the reference, which is exact because the
+// final normalisation uses the same reference).  Masked keys are excluded,
+// which equals the reference's -1e10 whenever a row sees at least one key;
+// rows that see none (left padding) give zeros.  Every wait is bounded.
+#include <cuda.h>
+#include <math.h>
+
+#include "mtj_common.cuh"
+#include "mtj_kernels.h"
+
+namespace mtj {
+namespace {
+
+constexpr int kQT = 128;                 // queries per block
+constexpr int kKB = 64;                  // keys per block (one cache page)
+constexpr int kDH = 256;
+constexpr int kThreadsTc = 192;
+constexpr uint32_t kQBytes = kQT * kDH * 2;          // 64 KB
+constexpr uint32_t kKBytes = kKB * kDH * 2;          // 32 KB
+constexpr uint32_t kStage = 2 * kKBytes;             // K + V of one key block
+constexpr uint32_t kPBytes = kQT * kKB * 2;          // 16 KB
+constexpr uint32_t kSmemTc = kQBytes + 2 * kStage + kPBytes + 1024;
+constexpr uint32_t kColS = 0, kColO = 64, kTmemCols = 512;
+
+__device__ __forceinline__ void tma2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mma_bf16(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(acc)
+      : "memory");
+}
+// shared-memory matrix descriptor, 128-byte swizzle; lbo / sbo in bytes
+__device__ __forceinline__ uint64_t sdesc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((addr >> 4) & 0x3FFF);
+  d |= static_cast<uint64_t>((lbo >> 4) & 0x3FFF) << 16;
+  d |= static_cast<uint64_t>((sbo >> 4) & 0x3FFF) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+__device__ __forceinline__ void tm_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tm_st32(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+
+__global__ void __launch_bounds__(kThreadsTc) prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q,
+                                                                     const __grid_constant__ CUtensorMap map_k,
+                                                                     const __grid_constant__ CUtensorMap map_v,
+                                                                     const PrefillAttnTcArgs a) {
+  extern __shared__ unsigned char att_smem_raw[];
+  const uint32_t base = (smem_u32(att_smem_raw) + 1023u) & ~1023u;
+  unsigned char* base_ptr = att_smem_raw + (base - smem_u32(att_smem_raw));
+  const uint32_t sQ = base, sKV = base + kQBytes, sP = base + kQBytes + 2 * kStage;
+  __shared__ __align__(8) uint64_t bars[8];
+  __shared__ uint32_t tmem_slot;
+  __shared__ uint32_t failed;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t bar0 = smem_u32(bars);
+  const uint32_t q_full = bar0, kv_full0 = bar0 + 8, kv_empty0 = bar0 + 24, s_full = bar0 + 40,
+                 p_full = bar0 + 48, o_done = bar0 + 56;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    mbar_init(kv_full0, 1);
+    mbar_init(kv_full0 + 8, 1);
+    mbar_init(kv_empty0, 1);
+    mbar_init(kv_empty0 + 8, 1);
+    mbar_init(s_full, 1);
+    mbar_init(p_full, 128);
+    mbar_init(o_done, 1);
+    mbar_fence_init();
+    failed = 0;
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  fence_before();
+  __syncthreads();
+  fence_after();
+  const uint32_t tmem = tmem_slot;
+
+  const int tile = blockIdx.x, head = blockIdx.y, bi = blockIdx.z;
+  const int b = a.rows.b0 + bi;
+  const int pos0 = a.rows.pos0_host;
+  const int Tc = a.rows.Tc;
+  const int row0 = bi * Tc + tile * kQT;                  // first chunk row of this tile
+  const int q_rows = min(kQT, Tc - tile * kQT);
+  const int pad = a.kv.pad[b];
+  const int limit = a.key_limit ? a.key_limit[b] : 0x7fffffff;
+  const int last_key = min(pos0 + tile * kQT + q_rows - 1, limit);
+  const int first_blk = pad / kKB;
+  const int nb = last_key >= pad ? last_key / kKB - first_blk + 1 : 0;
+
+  if (warp == 0) {
+    if (lane == 0 && nb > 0) {
+      mbar_expect_tx(q_full, kQBytes);
+#pragma unroll
+      for (int kb = 0; kb < 4; ++kb) tma2d(sQ + kb * (kQT * 128), &map_q, head * kDH + kb * 64, row0, q_full);
+      const int32_t* table = a.kv.page_table + static_cast<size_t>(b) * a.kv.ring_pages;
+      for (int j = 0; j < nb; ++j) {
+        const int st = j & 1;
+        if (j >= 2 && !mbar_wait(kv_empty0 + 8 * st, ((j >> 1) - 1) & 1)) {
+          atomicOr(&failed, 1u);
+          break;
+        }
+        const int page = table[(first_blk + j) % a.kv.ring_pages];
+        const int row = (page * a.heads + head) * kKB;
+        const uint32_t dk = sKV + st * kStage, dv = dk + kKBytes;
+        mbar_expect_tx(kv_full0 + 8 * st, kStage);
+#pragma unroll
+        for (int kb = 0; kb < 4; ++kb) {
+          tma2d(dk + kb * (kKB * 128), &map_k, kb * 64, row, kv_full0 + 8 * st);
+          tma2d(dv + kb * (kKB * 128), &map_v, kb * 64, row, kv_full0 + 8 * st);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && nb > 0) {
+      // instruction descriptors: fp32 accumulate, bf16 operands
+      constexpr uint32_t kIdS = (1u << 4) | (1u << 7) | (1u << 10) | ((kKB >> 3) << 17) | ((kQT >> 4) << 24);
+      constexpr uint32_t kIdO = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((kDH >> 3) << 17) | ((kQT >> 4) << 24);
+      auto issue_s = [&](int j) {
+        const uint32_t dk = sKV + (j & 1) * kStage;
+#pragma unroll
+        for (int kb = 0; kb < 4; ++kb) {
+          const uint64_t ad = sdesc(sQ + kb * (kQT * 128), 16, 1024), bd = sdesc(dk + kb * (kKB * 128), 16, 1024);
+#pragma unroll
+          for (int k4 = 0; k4 < 4; ++k4) mma_bf16(tmem + kColS, ad + 2 * k4, bd + 2 * k4, kIdS, (kb | k4) ? 1u : 0u);
+        }
+        commit(s_full);
+      };
+      bool ok = mbar_wait(q_full, 0) && mbar_wait(kv_full0, 0);
+      if (ok) {
+        fence_after();
+        issue_s(0);
+      }
+      for (int j = 0; ok && j < nb; ++j) {
+        ok = mbar_wait(p_full, j & 1);                         // P_j written, S_j consumed
+        if (!ok) break;
+        fence_after();
+        if (j + 1 < nb) {
+          ok = mbar_wait(kv_full0 + 8 * ((j + 1) & 1), ((j + 1) >> 1) & 1);
+          if (!ok) break;
+          fence_after();
+          issue_s(j + 1);
+        }
+        // O += P . V : V tile is [64 keys][256 dh] -> MN-major B operand, 64-column blocks 8 KB apart
+        const uint32_t dv = sKV + (j & 1) * kStage + kKBytes;
+#pragma unroll
+        for (int k4 = 0; k4 < 4; ++k4) {
+          const uint64_t ad = sdesc(sP, 16, 1024) + 2 * k4;
+          const uint64_t bd = sdesc(dv + k4 * 2048, kKB * 128, 1024);
+          mma_bf16(tmem + kColO, ad, bd, kIdO, (j | k4) ? 1u : 0u);
+        }
+        commit(kv_empty0 + 8 * (j & 1));
+        commit(o_done);
+      }
+      if (!ok) atomicOr(&failed, 1u);
+    }
+  } else {
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;                            // query row within the tile = TMEM lane
+    const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    const bool row_ok = r < q_rows;
+    const int qpos = pos0 + tile * kQT + r;
+    const float c2 = 0.0625f * 1.4426950408889634f;            // 1/sqrt(256) * log2(e)
+    float m_ref = -INFINITY, l = 0.f;
+    bool ok = nb > 0;
+    for (int j = 0; ok && j < nb; ++j) {
+      ok = mbar_wait(s_full, j & 1);
+      if (!ok) break;
+      fence_after();
+      uint32_t sr[64];
+      tm_ld32(tmem + lane_addr + kColS, sr);
+      tm_ld32(tmem + lane_addr + kColS + 32, sr + 32);
+      const int kbase = (first_blk + j) * kKB;
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 64; ++c) {
+        const int key = kbase + c;
+        const bool vis = row_ok && key >= pad && key <= qpos && key <= limit;
+        const float v = vis ? __uint_as_float(sr[c]) * c2 : -INFINITY;
+        sr[c] = __float_as_uint(v);
+        mx = fmaxf(mx, v);
+      }
+      float m_new = m_ref;
+      if (mx > m_ref + 8.0f || (m_ref == -INFINITY && mx > -INFINITY)) m_new = mx;
+      const float corr = (m_new == m_ref || m_ref == -INFINITY) ? 1.0f : exp2f(m_ref - m_new);
+      float psum = 0.f;
+      uint32_t pk[32];
+#pragma unroll
+      for (int c = 0; c < 64; c += 2) {
+        const float v0 = __uint_as_float(sr[c]), v1 = __uint_as_float(sr[c + 1]);
+        const float p0 = v0 == -INFINITY ? 0.f : exp2f(v0 - m_new);
+        const float p1 = v1 == -INFINITY ? 0.f : exp2f(v1 - m_new);
+        // the row sum uses the values the tensor core will see
+        const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
+        psum += __bfloat162float(pb.x) + __bfloat162float(pb.y);
+        pk[c >> 1] = *reinterpret_cast<const uint32_t*>(&pb);
+      }
+      l = l * corr + psum;
+      if (j > 0) {
+        ok = mbar_wait(o_done, (j - 1) & 1);                   // P buffer and O are free again
+        if (!ok) break;
+        fence_after();
+        if (__any_sync(0xffffffffu, corr != 1.0f)) {
+#pragma unroll 1
+          for (int c0 = 0; c0 < kDH; c0 += 32) {
+            uint32_t o[32];
+            tm_ld32(tmem + lane_addr + kColO + c0, o);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
+            tm_st32(tmem + lane_addr + kColO + c0, o);
+          }
+          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        }
+      }
+      // P row -> shared memory in the 128-byte-swizzled K-major layout the MMA reads
+      unsigned char* prow = base_ptr + (sP - base) + r * 128;
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch)
+        *reinterpret_cast<uint4*>(prow + ((ch ^ (r & 7)) << 4)) =
+            make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      fence_before();
+      mbar_arrive(p_full);
+      m_ref = m_new;
+    }
+    if (nb > 0 && ok) ok = mbar_wait(o_done, (nb - 1) & 1);
+    if (nb > 0 && !ok) atomicOr(&failed, 1u);
+    fence_after();
+    {
+      // the TMEM loads are warp-wide: every lane takes part, only the stores are per row
+      __nv_bfloat16* dst = a.out_bf16 + static_cast<size_t>(row0 + (row_ok ? r : 0)) * a.ld_out + head * kDH;
+      const bool have = nb > 0 && ok;
+      const float inv = (have && l > 0.f) ? 1.0f / l : 0.f;
+#pragma unroll 1
+      for (int c0 = 0; c0 < kDH; c0 += 32) {
+        uint32_t o[32];
+        if (have) {
+          tm_ld32(tmem + lane_addr + kColO + c0, o);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = 0u;
+        }
+        if (row_ok) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 w;
+            w.x = pack_bf16x2(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
+            w.y = pack_bf16x2(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+            w.z = pack_bf16x2(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
+            w.w = pack_bf16x2(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + c0 + i) = w;
+          }
+        }
+      }
+    }
+  }
+  fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+  }
+  if (threadIdx.x == 0 && failed && a.dev_err) atomicOr(a.dev_err, kDevErrTimeout);
+}
+
+}  // namespace
+
+cudaError_t launch_prefill_attn_tc(const void* map_q, const void* map_k, const void* map_v,
+                                   const PrefillAttnTcArgs& a, cudaStream_t s) {
+  if (a.M <= 0 || a.rows.Tc <= 0 || a.M % a.rows.Tc != 0 || a.d_head != kDH) return cudaErrorInvalidValue;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(prefill_attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(kSmemTc));
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  const dim3 grid((a.rows.Tc + kQT - 1) / kQT, a.heads, a.M / a.rows.Tc);
+  prefill_attn_tc_kernel<<<grid, kThreadsTc, kSmemTc, s>>>(*static_cast<const CUtensorMap*>(map_q),
+                                                           *static_cast<const CUtensorMap*>(map_k),
+                                                           *static_cast<const CUtensorMap*>(map_v), a);
+  return cudaGetLastError();
+}
+
+}  // namespace mtj

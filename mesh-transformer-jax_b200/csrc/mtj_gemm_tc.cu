@@ -206,6 +206,7 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
               }
               if (region == 0) {
                 a.q_out[static_cast<size_t>(m) * a.dl + nn] = y;
+                if (a.q_bf16) a.q_bf16[static_cast<size_t>(m) * a.dl + nn] = __float2bfloat16_rn(y);
               } else if (pos >= a.kv.pad[seq]) {
                 __nv_bfloat16* pool = region == 1 ? a.kv.kpool : a.kv.vpool;
                 const size_t off = kv_offset(a.kv.page_table + static_cast<size_t>(seq) * a.kv.ring_pages,

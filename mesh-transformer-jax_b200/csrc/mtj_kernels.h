@@ -106,6 +106,19 @@ struct PrefillAttnArgs {
 };
 cudaError_t launch_prefill_attn(const PrefillAttnArgs& a, cudaStream_t s);
 
+// Tensor-core causal attention for prefill / eval, d_head = 256 (see mtj_attn_tc.cu).
+struct PrefillAttnTcArgs {
+  KvCache kv;
+  RowMap rows;
+  int M, heads, d_head;
+  const int32_t* key_limit;    // optional [batch]
+  __nv_bfloat16* out_bf16;     // [M, ld_out]
+  int ld_out;
+  uint32_t* dev_err;
+};
+cudaError_t launch_prefill_attn_tc(const void* map_q, const void* map_k, const void* map_v,
+                                   const PrefillAttnTcArgs& a, cudaStream_t s);
+
 struct ArgmaxArgs {
   const float* logits;         // [B, V]
   int B, V;
@@ -125,6 +138,7 @@ struct GemmTcArgs {
   const float2* sincos;
   const float* b_ff;
   float* q_out;                // [M, dl] fp32
+  __nv_bfloat16* q_bf16;       // optional [M, dl] bf16 copy (operand of the tensor-core attention)
   __nv_bfloat16* act_out;      // [M, dl + ffl] bf16: gelu(ff) goes to columns [dl, dl + ffl)
   KvCache kv;
   const float* bias;           // [N] (out-proj, logits)

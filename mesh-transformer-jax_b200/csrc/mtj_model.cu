@@ -44,6 +44,7 @@ struct LayerWeights {
   float* ln_scale = nullptr;
   float* ln_offset = nullptr;
   TensorMap map_in, map_out;        // TMA views of w_in / w_out for the tensor-core path
+  TensorMap map_k, map_v;           // TMA views of this layer's K / V pools as [pages*heads*64, d_head]
 };
 
 int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
@@ -102,7 +103,9 @@ struct mtj_handle {
   bool tc_ok = false;
   __nv_bfloat16* xn_bf16 = nullptr;   // [max_rows, d] LayerNorm output
   __nv_bfloat16* act_bf16 = nullptr;  // [max_rows, dl + ffl] attention vector | gelu(ff)
-  TensorMap map_xn, map_act, map_proj;
+  TensorMap map_xn, map_act, map_proj, map_q;
+  __nv_bfloat16* q_bf16 = nullptr;    // [max_rows, dl] rotated queries for the tensor-core attention
+  bool attn_tc_ok = false;
   float* tc_partial = nullptr;        // [kTcSplitMax, kTcSplitRows, d] split-K partial sums of small-M out-projections
   int eval_rows = 0;                // rows of logits materialised at a time by the loss path
   float* eval_logits = nullptr;     // [eval_rows, Vl]
@@ -202,6 +205,7 @@ struct mtj_handle {
     temp = c.take<float>(max_batch);
     sample_scratch = c.take<char>(mtj::sample_scratch_bytes(max_batch, V));
     tc_partial = c.take<float>(static_cast<int64_t>(kTcSplitMax) * std::min<int64_t>(R, kTcSplitRows) * d);
+    q_bf16 = c.take<__nv_bfloat16>(R * dl);
     xn_bf16 = c.take<__nv_bfloat16>(R * d);
     act_bf16 = c.take<__nv_bfloat16>(R * (dl + ffl));
     eval_rows = static_cast<int>(std::min<int64_t>(R, 256));
@@ -396,6 +400,7 @@ int32_t run_layer_tc(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, c
   a.sincos = h->sincos;
   a.b_ff = lw.b_ff;
   a.q_out = h->q;
+  a.q_bf16 = (h->attn_tc_ok && !decode) ? h->q_bf16 : nullptr;
   a.act_out = h->act_bf16;
   a.kv = h->kv(layer);
   a.dev_err = h->dev_err;
@@ -422,6 +427,18 @@ int32_t run_layer_tc(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, c
     d.out_bf16 = h->act_bf16;
     d.ld_out = h->dl + h->ffl;
     MTJ_CUDA(mtj::launch_decode_attn(d, s, false));
+  } else if (h->attn_tc_ok) {
+    mtj::PrefillAttnTcArgs p = {};
+    p.kv = h->kv(layer);
+    p.rows = rows;
+    p.M = M;
+    p.heads = h->heads;
+    p.d_head = h->dh;
+    p.key_limit = key_limit;
+    p.out_bf16 = h->act_bf16;
+    p.ld_out = h->dl + h->ffl;
+    p.dev_err = h->dev_err;
+    MTJ_CUDA(mtj::launch_prefill_attn_tc(&h->map_q, &lw.map_k, &lw.map_v, p, s));
   } else {
     mtj::PrefillAttnArgs p = {};
     p.q = h->q;
@@ -741,6 +758,18 @@ int32_t mtj_bind_arenas(mtj_handle* h, void* wdev, int64_t wbytes, void* sdev, i
     ok = ok && mtj::make_tensor_map_bf16(&h->map_act, h->act_bf16, h->max_rows, h->dl + h->ffl, bn) == cudaSuccess;
     if (!ok) return fail(MTJ_ERR_CUDA, "cuTensorMapEncodeTiled failed");
     h->tc_ok = true;
+    const char* no_atc = getenv("MTJ_NO_ATTN_TC");
+    if (h->dh == 256 && !(no_atc && no_atc[0] == '1')) {
+      const int64_t pool_rows = static_cast<int64_t>(h->n_pages) * h->heads * mtj::kPageTokens;
+      for (int l = 0; l < h->L; ++l) {
+        mtj::KvCache kv = h->kv(l);
+        ok = ok && mtj::make_tensor_map_bf16(&h->layers[l].map_k, kv.kpool, pool_rows, h->dh, 64) == cudaSuccess;
+        ok = ok && mtj::make_tensor_map_bf16(&h->layers[l].map_v, kv.vpool, pool_rows, h->dh, 64) == cudaSuccess;
+      }
+      ok = ok && mtj::make_tensor_map_bf16(&h->map_q, h->q_bf16, h->max_rows, h->dl, 128) == cudaSuccess;
+      if (!ok) return fail(MTJ_ERR_CUDA, "cuTensorMapEncodeTiled failed (attention)");
+      h->attn_tc_ok = true;
+    }
   }
   h->bound = true;
   h->loaded = 0;

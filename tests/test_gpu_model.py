@@ -241,3 +241,38 @@ def test_batched_decode_on_tensor_cores_matches_oracle(cuda_device):
     upto = int(np.min(first_diff))
     assert _rel(out[2][:, :max(upto, 1)], ref[2][:, :max(upto, 1)]) <= LOGIT_TOL
     assert same.mean() >= 0.95, "greedy ids diverge beyond what bf16 activations explain"
+
+
+def _wide_head_config(seq):
+    """d_head = 256 like GPT-J-6B (2 heads of 256, rotary 64), small enough for the CPU oracle."""
+    return {"layers": 2, "d_model": 512, "n_heads": 2, "n_vocab": 512, "norm": "layernorm", "pe": "rotary",
+            "pe_rotary_dims": 64, "seq": seq, "cores_per_replica": 1, "per_replica_batch": 1}
+
+
+@pytest.mark.parametrize("seq", [320, 200])
+def test_tensor_core_prefill_attention_d_head_256(cuda_device, seq):
+    """Full forward, masked eval and left-padded generate with d_head = 256: prefill attention runs on
+    the tensor cores (several 128-query tiles, 64-key blocks, partial tiles, pad and key-limit masks)."""
+    import torch
+    cfg = _wide_head_config(seq)
+    params = spec.make_params(cfg, seed=31, stress=True)
+    net = _net(cfg, params, cuda_device)
+    ids = spec.token_ids(32, 2, seq, 512)
+    rt = net._runtime(2, 8)
+    out = rt.forward_logits(torch.from_numpy(ids.view(np.int32)).to(cuda_device), None, seq).cpu().numpy()
+    shard = go.CausalTransformerShard(cfg, params)
+    for b in range(2):
+        assert _rel(out[b], shard.logits(ids[b])) <= LOGIT_TOL
+    lens = np.array([seq, 77], np.uint32)
+    outm = rt.forward_logits(torch.from_numpy(ids.view(np.int32)).to(cuda_device), lens, seq).cpu().numpy()
+    mask = (np.arange(seq) > 77) * -1e10
+    assert _rel(outm[1], shard.logits(ids[1], mask=mask)) <= LOGIT_TOL
+    glens = np.array([seq - 3, 70], np.uint32)
+    ctx = np.zeros((2, seq), np.uint32)
+    for b in range(2):
+        ctx[b, seq - glens[b]:] = ids[b, :glens[b]]
+    _, gen = net.generate(ctx, glens, 8, {"top_p": np.zeros(2), "temp": np.ones(2)}, return_logits=True)
+    _, ref = go.CausalTransformer(cfg, params).generate(ctx, glens, 8, return_logits=True)
+    assert _rel(gen[2], ref[2]) <= LOGIT_TOL
+    assert np.array_equal(gen[0], ref[0])
+    net._rt.check_device_status()
