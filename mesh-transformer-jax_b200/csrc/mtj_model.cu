@@ -742,6 +742,13 @@ int32_t mtj_bind_arenas(mtj_handle* h, void* wdev, int64_t wbytes, void* sdev, i
   MTJ_CUDA(cudaMemsetAsync(h->counters, 0, sizeof(uint32_t) * h->max_batch * h->heads, s));
   MTJ_CUDA(cudaMemsetAsync(h->gemv_counters, 0, sizeof(uint32_t) * h->max_rows, s));
   MTJ_CUDA(cudaMemsetAsync(h->dev_err, 0, sizeof(uint32_t) * 4, s));
+  // The tensor-core attention multiplies masked keys' V rows by exactly zero: slots that were
+  // never written must hold finite values, so the pools (and the bf16 operand buffers) start at zero.
+  MTJ_CUDA(cudaMemsetAsync(h->kpool, 0, sizeof(__nv_bfloat16) * h->pool_layer_elems * h->L, s));
+  MTJ_CUDA(cudaMemsetAsync(h->vpool, 0, sizeof(__nv_bfloat16) * h->pool_layer_elems * h->L, s));
+  MTJ_CUDA(cudaMemsetAsync(h->q_bf16, 0, sizeof(__nv_bfloat16) * h->max_rows * h->dl, s));
+  MTJ_CUDA(cudaMemsetAsync(h->xn_bf16, 0, sizeof(__nv_bfloat16) * static_cast<size_t>(h->max_rows) * h->d, s));
+  MTJ_CUDA(cudaMemsetAsync(h->act_bf16, 0, sizeof(__nv_bfloat16) * static_cast<size_t>(h->max_rows) * (h->dl + h->ffl), s));
   MTJ_CUDA(cudaStreamSynchronize(s));   // `tab` is about to go out of scope
   // TMA views for the tensor-core GEMM (needs K % 64 == 0 on both projections)
   h->tc_ok = false;
