@@ -25,6 +25,9 @@ for _p in (ROOT, PKG):
         sys.path.insert(0, _p)
 
 METRIC = "gptj6b_decode_tokens_per_s"
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under profiles/
+# (GPT-J-6B layer shapes, batch 1, window 2047); the kernels read every weight byte exactly once.
+NCU_TRAFFIC = {"in_proj": None, "ff_in_proj": None, "attention": 33.6e6, "out_proj": 171.4e6, "logits": 416.4e6}
 UNIT = "tokens/s"
 
 GPTJ_6B = {
@@ -202,6 +205,11 @@ def run_mtj(args):
     e1.record()
     barrier()
     prefill_ms = e0.elapsed_time(e1)
+    # kernel-family times of one more prefill (events between launches)
+    rt.profile_enable(True)
+    rt.prefill(ctx_dev, lens)
+    prefill_prof = rt.profile_read()
+    rt.profile_enable(False)
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -273,11 +281,38 @@ def run_mtj(args):
     peak_kind = "measured" if "hbm_gbs" in peaks else "fallback"
 
     d, dl, ffl = cfg["d_model"], cfg["d_model"] // world, 4 * cfg["d_model"] // world
-    inproj_bytes = (3 * dl + ffl) * d * 2 + ffl * 4 + 2 * d * 4 + B * (d * 4 + dl * 4 + ffl * 4 + 2 * dl * 2)
-    ip_ms, ip_n = prof["in_proj"]
-    ip_avg_ms = ip_ms / max(ip_n, 1)
-    achieved = inproj_bytes / (ip_avg_ms * 1e-3) / 1e9 if ip_n else None
-    fam = {k: {"ms_per_launch": v[0] / max(v[1], 1), "launches": v[1]} for k, v in prof.items()}
+    Vl, L = cfg["n_vocab"] // world, cfg["layers"]
+    # algorithmic bytes per launch of each decode kernel family (weights dominate)
+    fam_bytes = {
+        "in_proj": ((3 * dl + (0 if prof["ff_in_proj"][1] else ffl)) * d * 2 + 2 * d * 4
+                    + B * (d * 4 + dl * 4 + 2 * dl * 2)),
+        "ff_in_proj": ffl * d * 2 + ffl * 4 + 2 * d * 4 + B * (d * 4 + ffl * 4),
+        "attention": B * (seq - 1) * 2 * dl * 2 + B * 2 * dl * 4,
+        "out_proj": d * (dl + ffl) * 2 + d * 4 + B * ((dl + ffl) * 4 + 2 * d * 4),
+        "logits": Vl * d * 2 + Vl * 4 + 2 * d * 4 + B * (d * 4 + Vl * 4),
+    }
+    fam_kernel = {
+        "in_proj": "gemv_kernel<in-proj> (LN + Q/K/V rows, RoPE, KV-cache write)",
+        "ff_in_proj": "gemv_kernel<in-proj> (LN + FF-in rows, bias + GELU)",
+        "attention": "decode_attn_kernel",
+        "out_proj": "gemv_kernel<out-proj> ([attn | gelu(ff)] x [W_o ; W_ff_out] + bias + residual + LN stats)",
+        "logits": "gemv_kernel<logits>",
+    }
+    per_step = {"in_proj": L, "ff_in_proj": L, "attention": L, "out_proj": L, "logits": 1}
+    fam = {}
+    for k, (ms_sum, n) in prof.items():
+        if not n:
+            continue
+        ms_l = ms_sum / n
+        fam[k] = {"ms_per_launch": ms_l, "launches": n, "bytes_per_launch": fam_bytes[k],
+                  "gbs": fam_bytes[k] / (ms_l * 1e-3) / 1e9, "ms_per_step": ms_l * per_step[k]}
+    top = max(fam, key=lambda k: fam[k]["ms_per_step"]) if fam else None
+    achieved = fam[top]["gbs"] if top else None
+    pf = {k: v[0] for k, v in prefill_prof.items() if v[1]}
+    gemm_flops = 2.0 * (L * 12 * d * d // world) * B * (seq - 1)
+    attn_flops = L * 2.0 * (d // world) * (seq - 1) * seq * B
+    tc_peak = float(peaks.get("bf16_tflops_sustained", 1400.0))
+    gemm_ms = pf.get("in_proj", 0.0) + pf.get("out_proj", 0.0)
 
     ms_step = ms_total / args.steps
     value = B * args.steps / (ms_total * 1e-3)
@@ -290,15 +325,24 @@ def run_mtj(args):
                 "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B},
         "gpu_launches": launches,
         "clocks": sampler.summary(t_wall0, t_wall1),
-        "roofline": {"bound": "hbm", "kernel": "gemv_kernel<in-proj> (LN + [Q|K|V|FF-in] GEMV, RoPE/GELU/KV epilogue)",
-                     "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
-                     "frac": (achieved / hbm_peak) if achieved else None, "traffic": None,
-                     "peak_source": f"of {peak_kind}", "algorithmic_bytes_per_launch": inproj_bytes,
-                     "ms_per_launch": ip_avg_ms},
+        "roofline": {"bound": "hbm", "kernel": fam_kernel.get(top), "achieved": achieved, "peak": hbm_peak,
+                     "unit": "GB/s", "frac": (achieved / hbm_peak) if achieved else None,
+                     "traffic": NCU_TRAFFIC.get(top) if world == 1 and B == 1 else None,
+                     "peak_source": f"of {peak_kind}",
+                     "algorithmic_bytes_per_launch": fam[top]["bytes_per_launch"] if top else None,
+                     "ms_per_launch": fam[top]["ms_per_launch"] if top else None,
+                     "note": "kernel with the largest share of the decode step; time from CUDA events around "
+                             "each launch in a separate pass (no graph replay, so launch gaps are included)"},
         "kernel_families": fam,
         "step_hbm": {"algorithmic_bytes_per_step": step_bytes, "achieved_gbs": step_bytes / (ms_step * 1e-3) / 1e9,
                      "frac_of_peak": step_bytes / (ms_step * 1e-3) / 1e9 / hbm_peak / world},
-        "prefill": {"tokens_per_s": B * (seq - 1) / (prefill_ms * 1e-3), "ms": prefill_ms, "tokens": B * (seq - 1)},
+        "prefill": {"tokens_per_s": B * (seq - 1) / (prefill_ms * 1e-3), "ms": prefill_ms, "tokens": B * (seq - 1),
+                    "family_ms": pf,
+                    "gemm_tflops": (gemm_flops / (gemm_ms * 1e-3) / 1e12) if gemm_ms else None,
+                    "gemm_frac_of_sustained_peak": (gemm_flops / (gemm_ms * 1e-3) / 1e12 / tc_peak) if gemm_ms else None,
+                    "attention_tflops": (attn_flops / (pf["attention"] * 1e-3) / 1e12) if pf.get("attention") else None,
+                    "whole_prefill_frac_of_sustained_peak":
+                        (gemm_flops + attn_flops + 0.0) / (prefill_ms * 1e-3) / 1e12 / tc_peak},
     }
     if args.layers > 0:
         line["profile_only"] = f"reduced depth: {args.layers} layers"

@@ -92,6 +92,17 @@ int32_t mtj_load_param(mtj_handle* h, const char* name, const void* src_dev,
 int32_t mtj_comm_unique_id(uint8_t* out128);
 int32_t mtj_comm_init(mtj_handle* h, const uint8_t* id128);
 
+/* Optional low-latency form of the same psum for decode-size messages
+ * ([batch, d_model] fp32): the ranks read each other's partial sums directly
+ * over NVLink peer memory and fuse the residual add and LayerNorm statistics
+ * into the same kernel.  mtj_p2p_export allocates this rank's exchange buffer
+ * (the one device allocation the library makes itself: it has to be exportable
+ * to the other ranks' processes) and returns its 64-byte CUDA IPC handle; the
+ * host gathers the handles of all ranks in rank order and passes them to
+ * mtj_p2p_import on every rank.  Without these calls all reductions use NCCL. */
+int32_t mtj_p2p_export(mtj_handle* h, uint8_t* ipc_handle_out64);
+int32_t mtj_p2p_import(mtj_handle* h, const uint8_t* ipc_handles_all_ranks);
+
 /* generate_initial (transformer_shard.py:74-95) for `batch` left-padded
  * contexts: prefills ctx[:, :-1] into the KV cache, keeps ctx[:, -1] as the
  * first decode input.  ctx_dev: [batch, seq] uint32; ctx_length_host: [batch]
@@ -136,12 +147,14 @@ int32_t mtj_sample_top_p(const float* logits_dev, const float* uniforms_dev,
 int64_t mtj_launch_count(const mtj_handle* h);
 
 /* Optional kernel-family timing for the benchmark's roofline figure: while
- * enabled, every launch of the four dominant families is bracketed by CUDA
+ * enabled, every launch of the dominant kernel families is bracketed by CUDA
  * events on the caller's stream (up to 64 steps' worth between reads).
  * mtj_profile_read synchronises the stream, fills ms_sum[MTJ_FAMILY_COUNT] /
  * count[MTJ_FAMILY_COUNT] and clears the record.  No reference counterpart. */
-enum { MTJ_FAMILY_INPROJ = 0, MTJ_FAMILY_ATTN = 1, MTJ_FAMILY_OUTPROJ = 2, MTJ_FAMILY_LOGITS = 3,
-       MTJ_FAMILY_COUNT = 4 };
+enum { MTJ_FAMILY_INPROJ = 0,    /* LN + Q/K/V (+ FF-in when launched as one kernel) projection */
+       MTJ_FAMILY_ATTN = 1, MTJ_FAMILY_OUTPROJ = 2, MTJ_FAMILY_LOGITS = 3,
+       MTJ_FAMILY_FFIN = 4,      /* the FF-in half of the in-projection when it is launched on its own */
+       MTJ_FAMILY_COUNT = 5 };
 int32_t mtj_profile_enable(mtj_handle* h, int32_t on);
 int32_t mtj_profile_read(mtj_handle* h, double* ms_sum, int64_t* count, mtj_stream s);
 

@@ -343,8 +343,10 @@ cudaError_t launch_gemm_tc(GemvEpilogue epi, const void* map_w, const void* map_
 namespace {
 // out[m, n] = sum_z partial[z, m, n] + bias[n] (+ residual[m, n]); fixed summation order
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int ksplit, int M, int N,
-                                     const float* __restrict__ bias, const float* residual, float* out, int ld_out) {
+                                     const float* __restrict__ bias, const float* residual, float* out, int ld_out,
+                                     const uint32_t* slot_sel, size_t slot_stride) {
   const size_t total = static_cast<size_t>(M) * N;
+  if (slot_sel) out += static_cast<size_t>(*slot_sel & 1u) * slot_stride;
   for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
        i += static_cast<size_t>(gridDim.x) * blockDim.x) {
     const int n = static_cast<int>(i % N);
@@ -359,10 +361,11 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int kspl
 }  // namespace
 
 cudaError_t launch_splitk_reduce(const float* partial, int ksplit, int M, int N, const float* bias,
-                                 const float* residual, float* out, int ld_out, cudaStream_t s) {
+                                 const float* residual, float* out, int ld_out, const uint32_t* slot_sel,
+                                 size_t slot_stride, cudaStream_t s) {
   const size_t total = static_cast<size_t>(M) * N;
   const int grid = static_cast<int>(std::min<size_t>((total + 255) / 256, 148 * 8));
-  splitk_reduce_kernel<<<grid, 256, 0, s>>>(partial, ksplit, M, N, bias, residual, out, ld_out);
+  splitk_reduce_kernel<<<grid, 256, 0, s>>>(partial, ksplit, M, N, bias, residual, out, ld_out, slot_sel, slot_stride);
   return cudaGetLastError();
 }
 

@@ -193,7 +193,8 @@ __global__ void __launch_bounds__(kGemvThreads, BT == 1 ? (EPI == kEpiOut ? 4 : 
       } else if (EPI == kEpiOut) {
         float y = val + a.bias[n];
         if (a.residual) y += a.residual[static_cast<size_t>(m) * a.N + n];
-        a.out[static_cast<size_t>(m) * a.N + n] = y;
+        float* outp = a.out + (a.slot_sel ? static_cast<size_t>(*a.slot_sel & 1u) * a.slot_stride : 0);
+        outp[static_cast<size_t>(m) * a.N + n] = y;
       } else {
         a.logits[static_cast<size_t>(m) * a.ld_logits + n] = val + a.bias[n];
       }

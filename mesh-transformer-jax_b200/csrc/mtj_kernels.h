@@ -58,6 +58,8 @@ struct GemvArgs {
   const int32_t* row_select;   // optional [M]: source row of x / stats for output row m
   int ks_override;             // 0 = pick the K split from the shape; 1/2/4/8 = force it
   uint32_t* dev_err;           // device error word (bounded waits that ran out), may be null
+  const uint32_t* slot_sel;    // optional: out += (*slot_sel & 1) * slot_stride (peer all-reduce slots)
+  size_t slot_stride;
   int rw_override;             // 0 = default rows per warp group; 8 = eight rows (single-token launches)
 };
 
@@ -73,6 +75,8 @@ struct EmbedArgs {
   const float* bias;           // [d]
   float* x;                    // [M, d]
   float* stats;                // [M, 2] or null
+  const uint32_t* slot_sel;    // optional: x += (*slot_sel & 1) * slot_stride (peer all-reduce slots)
+  size_t slot_stride;
 };
 cudaError_t launch_embed(const EmbedArgs& a, cudaStream_t s, bool pdl);
 
@@ -151,7 +155,8 @@ struct GemmTcArgs {
 };
 int gemm_tc_token_tile();
 cudaError_t launch_splitk_reduce(const float* partial, int ksplit, int M, int N, const float* bias,
-                                 const float* residual, float* out, int ld_out, cudaStream_t s);
+                                 const float* residual, float* out, int ld_out, const uint32_t* slot_sel,
+                                 size_t slot_stride, cudaStream_t s);
 cudaError_t make_tensor_map_bf16(void* map_out_128B, const void* base, int64_t rows, int64_t K, int box_rows);
 cudaError_t launch_gemm_tc(GemvEpilogue epi, const void* map_w, const void* map_x, const GemmTcArgs& a,
                            cudaStream_t s, bool pdl);

@@ -36,7 +36,8 @@ __global__ void __launch_bounds__(kThreads) embed_kernel(const EmbedArgs a) {
   const int64_t local = static_cast<int64_t>(id) - a.vocab_start;
   const bool hit = local >= 0 && local < a.vocab_local;
   const __nv_bfloat16* row = a.table + static_cast<size_t>(hit ? local : 0) * a.d;
-  float* xo = a.x + static_cast<size_t>(m) * a.d;
+  float* xo = a.x + (a.slot_sel ? static_cast<size_t>(*a.slot_sel & 1u) * a.slot_stride : 0) +
+              static_cast<size_t>(m) * a.d;
   float s = 0.f;
   for (int i = threadIdx.x; i < a.d; i += kThreads) {
     const float v = (hit ? __bfloat162float(row[i]) : 0.f) + a.bias[i];

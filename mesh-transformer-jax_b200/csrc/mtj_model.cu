@@ -95,6 +95,13 @@ struct mtj_handle {
   float* logits_gather = nullptr;   // [mp, max_batch, Vl] all-gather landing zone (mp > 1)
   float* part = nullptr;            // [max_rows, d] this shard's partial sums before the all-reduce (mp > 1)
   void* comm = nullptr;             // ncclComm_t over the "shard" axis
+  // peer-memory all-reduce for small messages (decode); buffers are cudaMalloc'ed once at set-up
+  // because they have to be exportable to the other ranks' processes
+  bool p2p_ready = false;
+  int p2p_rows = 0;                 // rows a data slot holds
+  char* p2p_local = nullptr;        // [2 slots][p2p_rows * d] floats | flags | seq | ticket
+  char* p2p_peer[mtj::kP2pMaxWorld] = {};
+  size_t p2p_flag_off = 0;
   float* uniforms = nullptr;        // [max_batch, V] sampler inputs of the current step
   float* top_p = nullptr;           // [max_batch]
   float* temp = nullptr;            // [max_batch]
@@ -242,8 +249,39 @@ namespace {
 using mtj::GemvArgs;
 
 // g_psum of the [M, d] partial sums in h->part, then x (+)= sum and the LN statistics.
+bool use_p2p(const mtj_handle* h, int M) { return h->p2p_ready && M <= h->p2p_rows; }
+// where the producer of the partial sums writes them: the peer-visible slot or the plain buffer
+float* partial_dst(const mtj_handle* h, int M) {
+  return use_p2p(h, M) ? reinterpret_cast<float*>(h->p2p_local) : h->part;
+}
+const uint32_t* partial_slot_sel(const mtj_handle* h, int M) {
+  return use_p2p(h, M) ? reinterpret_cast<const uint32_t*>(h->p2p_local + h->p2p_flag_off + 256) : nullptr;
+}
+size_t partial_slot_stride(const mtj_handle* h) { return static_cast<size_t>(h->p2p_rows) * h->d; }
+
 int32_t reduce_into_x(mtj_handle* h, int M, bool accumulate, bool pdl, cudaStream_t s) {
   if (!h->comm) return fail(MTJ_ERR_STATE, "cores_per_replica > 1 needs mtj_comm_init first");
+  if (use_p2p(h, M)) {
+    mtj::P2pArgs a = {};
+    a.rank = h->rank;
+    a.world = h->mp;
+    a.d = h->d;
+    a.slot_elems = partial_slot_stride(h);
+    for (int r = 0; r < h->mp; ++r) {
+      a.peer_data[r] = reinterpret_cast<const float*>(h->p2p_peer[r]);
+      a.peer_flags[r] = reinterpret_cast<uint32_t*>(h->p2p_peer[r] + h->p2p_flag_off);
+    }
+    a.local_flags = reinterpret_cast<const uint32_t*>(h->p2p_local + h->p2p_flag_off);
+    a.seq = reinterpret_cast<uint32_t*>(h->p2p_local + h->p2p_flag_off + 256);
+    a.ticket = a.seq + 1;
+    a.x = h->x;
+    a.stats = h->stats;
+    a.accumulate = accumulate ? 1 : 0;
+    a.dev_err = h->dev_err;
+    MTJ_CUDA(mtj::launch_p2p_allreduce(a, M, s, pdl));
+    h->launches++;
+    return MTJ_OK;
+  }
   std::string err;
   if (mtj::comm_all_reduce(h->comm, h->part, static_cast<size_t>(M) * h->d, false, s, &err))
     return fail(MTJ_ERR_COMM, err);
@@ -295,18 +333,21 @@ int32_t run_layer(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, bool
     GemvArgs qkv = a;
     qkv.N = 3 * h->dl;
     MTJ_CUDA(mtj::launch_gemv(mtj::kEpiInProj, qkv, s, pdl));
+    h->prof_end(s);
     MTJ_CUDA(cudaEventRecord(h->ev_fork, s));
     MTJ_CUDA(cudaStreamWaitEvent(sa, h->ev_fork, 0));
     GemvArgs ffp = a;
     ffp.W = lw.w_in + static_cast<size_t>(3) * h->dl * h->d;
     ffp.N = h->ffl;
     ffp.n0 = 3 * h->dl;
+    h->prof_begin(MTJ_FAMILY_FFIN, s);
     MTJ_CUDA(mtj::launch_gemv(mtj::kEpiInProj, ffp, s, pdl));
+    h->prof_end(s);
     h->launches++;
   } else {
     MTJ_CUDA(mtj::launch_gemv(mtj::kEpiInProj, a, s, pdl));
+    h->prof_end(s);
   }
-  h->prof_end(s);
   h->launches++;
 
   if (decode) {
@@ -326,9 +367,9 @@ int32_t run_layer(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, bool
     d.counters = h->counters;
     d.out = h->act2;
     d.ld_out = h->dl + h->ffl;
-    if (!fork) h->prof_begin(MTJ_FAMILY_ATTN, s);
+    h->prof_begin(MTJ_FAMILY_ATTN, sa);
     MTJ_CUDA(mtj::launch_decode_attn(d, sa, pdl && !fork));
-    if (!fork) h->prof_end(s);
+    h->prof_end(sa);
     if (fork) {
       MTJ_CUDA(cudaEventRecord(h->ev_join, sa));
       MTJ_CUDA(cudaStreamWaitEvent(s, h->ev_join, 0));
@@ -361,7 +402,11 @@ int32_t run_layer(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, bool
   o.bias = lw.b_out;
   // detached_out: return g_psum(attn + ff) on its own instead of adding it to the residual stream
   o.residual = (h->mp == 1 && !detached_out) ? h->x : nullptr;
-  o.out = h->mp == 1 ? (detached_out ? detached_out : h->x) : h->part;
+  o.out = h->mp == 1 ? (detached_out ? detached_out : h->x) : (detached_out ? h->part : partial_dst(h, M));
+  if (h->mp > 1 && !detached_out) {
+    o.slot_sel = partial_slot_sel(h, M);
+    o.slot_stride = partial_slot_stride(h);
+  }
   o.stats_out = (h->mp == 1 && !detached_out) ? h->stats : nullptr;
   o.counters = h->gemv_counters;
   o.dev_err = h->dev_err;
@@ -460,13 +505,15 @@ int32_t run_layer_tc(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, c
   o.K = h->dl + h->ffl;
   o.bias = lw.b_out;
   o.residual = (h->mp == 1 && !detached_out) ? h->x : nullptr;
-  o.out = h->mp == 1 ? (detached_out ? detached_out : h->x) : h->part;
+  const bool to_slot = h->mp > 1 && !detached_out && use_p2p(h, M);
+  o.out = h->mp == 1 ? (detached_out ? detached_out : h->x) : (to_slot ? partial_dst(h, M) : h->part);
   o.ld_out = h->d;
   o.dev_err = h->dev_err;
   // Few token rows give only d/128 tiles: split K over blocks so the whole GPU streams the weights.
   const int tiles = ((h->d + 127) / 128) * ((M + mtj::gemm_tc_token_tile() - 1) / mtj::gemm_tc_token_tile());
   int ksplit = 1;
   if (M <= kTcSplitRows && tiles < 148) ksplit = std::max(1, std::min({kTcSplitMax, 296 / tiles, o.K / 64}));
+  if (to_slot && ksplit == 1) ksplit = 2;          // the slot is selected by the reduction kernel
   h->prof_begin(MTJ_FAMILY_OUTPROJ, s);
   if (ksplit > 1) {
     float* dst = o.out;
@@ -474,7 +521,8 @@ int32_t run_layer_tc(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, c
     o.partial = h->tc_partial;
     o.ksplit = ksplit;
     MTJ_CUDA(mtj::launch_gemm_tc(mtj::kEpiOut, &lw.map_out, &h->map_act, o, s, false));
-    MTJ_CUDA(mtj::launch_splitk_reduce(h->tc_partial, ksplit, M, h->d, lw.b_out, res, dst, h->d, s));
+    MTJ_CUDA(mtj::launch_splitk_reduce(h->tc_partial, ksplit, M, h->d, lw.b_out, res, dst, h->d,
+                                       to_slot ? partial_slot_sel(h, M) : nullptr, partial_slot_stride(h), s));
     h->launches++;
   } else {
     MTJ_CUDA(mtj::launch_gemm_tc(mtj::kEpiOut, &lw.map_out, &h->map_act, o, s, false));
@@ -528,7 +576,11 @@ int32_t run_embed(mtj_handle* h, const uint32_t* ids, int ids_ld, int M, const m
   e.vocab_start = h->rank * h->Vl;
   e.table = h->emb_w;
   e.bias = h->emb_b;
-  e.x = h->mp == 1 ? h->x : h->part;
+  e.x = h->mp == 1 ? h->x : partial_dst(h, M);
+  if (h->mp > 1) {
+    e.slot_sel = partial_slot_sel(h, M);
+    e.slot_stride = partial_slot_stride(h);
+  }
   e.stats = h->mp == 1 ? h->stats : nullptr;
   MTJ_CUDA(mtj::launch_embed(e, s, h->use_pdl && decode));
   h->launches++;
@@ -696,6 +748,9 @@ int32_t mtj_destroy(mtj_handle* h) {
     if (h->ev_join) cudaEventDestroy(h->ev_join);
     if (h->side_stream) cudaStreamDestroy(h->side_stream);
     if (h->comm) mtj::comm_destroy(h->comm);
+    for (int r = 0; r < mtj::kP2pMaxWorld; ++r)
+      if (h->p2p_peer[r] && h->p2p_peer[r] != h->p2p_local) cudaIpcCloseMemHandle(h->p2p_peer[r]);
+    if (h->p2p_local) cudaFree(h->p2p_local);
     if (h->capture_stream) cudaStreamDestroy(h->capture_stream);
   }
   delete h;
@@ -910,6 +965,41 @@ int32_t mtj_comm_init(mtj_handle* h, const uint8_t* id128) {
     if (rc) return fail(MTJ_ERR_COMM, err);
     if (ce != cudaSuccess) return fail(MTJ_ERR_CUDA, std::string("collective warm-up: ") + cudaGetErrorString(ce));
   }
+  return MTJ_OK;
+}
+
+int32_t mtj_p2p_export(mtj_handle* h, uint8_t* handle64) {
+  if (!h || !handle64) return fail(MTJ_ERR_INVALID, "null argument");
+  if (h->mp < 2 || h->mp > mtj::kP2pMaxWorld) return fail(MTJ_ERR_UNSUPPORTED, "peer all-reduce needs 2..8 ranks");
+  if (h->p2p_local) return fail(MTJ_ERR_STATE, "already exported");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  h->p2p_rows = std::min(h->max_rows, std::max(h->max_batch, 1));
+  const size_t data = 2 * static_cast<size_t>(h->p2p_rows) * h->d * sizeof(float);
+  h->p2p_flag_off = (data + 255) / 256 * 256;
+  const size_t total = h->p2p_flag_off + 512;
+  MTJ_CUDA(cudaMalloc(reinterpret_cast<void**>(&h->p2p_local), total));
+  MTJ_CUDA(cudaMemset(h->p2p_local, 0, total));
+  cudaIpcMemHandle_t ih;
+  MTJ_CUDA(cudaIpcGetMemHandle(&ih, h->p2p_local));
+  memcpy(handle64, &ih, 64);
+  return MTJ_OK;
+}
+
+int32_t mtj_p2p_import(mtj_handle* h, const uint8_t* handles) {
+  if (!h || !handles) return fail(MTJ_ERR_INVALID, "null argument");
+  if (!h->p2p_local) return fail(MTJ_ERR_STATE, "mtj_p2p_export has not run");
+  for (int r = 0; r < h->mp; ++r) {
+    if (r == h->rank) {
+      h->p2p_peer[r] = h->p2p_local;
+      continue;
+    }
+    cudaIpcMemHandle_t ih;
+    memcpy(&ih, handles + 64 * r, 64);
+    void* p = nullptr;
+    MTJ_CUDA(cudaIpcOpenMemHandle(&p, ih, cudaIpcMemLazyEnablePeerAccess));
+    h->p2p_peer[r] = static_cast<char*>(p);
+  }
+  h->p2p_ready = true;
   return MTJ_OK;
 }
 
@@ -1173,7 +1263,7 @@ int64_t mtj_launch_count(const mtj_handle* h) { return h ? h->launches : -1; }
 int32_t mtj_profile_enable(mtj_handle* h, int32_t on) {
   if (!h) return fail(MTJ_ERR_INVALID, "null handle");
   if (on && h->ev_pool.empty()) {
-    h->ev_pool.resize(2 * (3 * static_cast<size_t>(h->L) + 2) * 64);
+    h->ev_pool.resize(2 * (4 * static_cast<size_t>(h->L) + 2) * 64);
     for (auto& e : h->ev_pool) MTJ_CUDA(cudaEventCreate(&e));
   }
   h->profile = on != 0;

@@ -44,6 +44,8 @@ def _load():
         "mtj_load_param": (i32, [vp, ctypes.c_char_p, vp, i32, i32, ctypes.POINTER(i64), vp]),
         "mtj_comm_unique_id": (i32, [vp]),
         "mtj_comm_init": (i32, [vp, vp]),
+        "mtj_p2p_export": (i32, [vp, vp]),
+        "mtj_p2p_import": (i32, [vp, vp]),
         "mtj_prefill": (i32, [vp, vp, ctypes.POINTER(ctypes.c_uint32), i32, vp]),
         "mtj_decode_step": (i32, [vp, vp, vp, vp, vp, i32, vp, vp, vp]),
         "mtj_eval_loss": (i32, [vp, vp, vp, ctypes.POINTER(ctypes.c_uint32), i32, i32, vp, vp, vp]),

@@ -4,6 +4,7 @@ torch.distributed); all model math runs in the library's CUDA kernels."""
 from __future__ import annotations
 
 import ctypes
+import os
 import sys
 
 import numpy as np
@@ -104,6 +105,15 @@ class ShardRuntime:
         uid = (ctypes.c_uint8 * 128)(*t.cpu().tolist())
         with torch.cuda.device(self.device):
             check(lib.mtj_comm_init(self._h, uid))
+            if os.environ.get("MTJ_NO_P2P") != "1" and self.mp <= 8:
+                # exchange buffers for the peer-memory all-reduce of decode-size messages
+                mine = (ctypes.c_uint8 * 64)()
+                check(lib.mtj_p2p_export(self._h, mine))
+                t = torch.tensor(list(mine), dtype=torch.uint8, device=self.device if on_gpu else "cpu")
+                parts = [torch.empty_like(t) for _ in range(self.mp)]
+                dist.all_gather(parts, t)
+                allh = (ctypes.c_uint8 * (64 * self.mp))(*torch.cat(parts).cpu().tolist())
+                check(lib.mtj_p2p_import(self._h, allh))
 
     @staticmethod
     def _aligned(t: torch.Tensor) -> int:
@@ -217,14 +227,14 @@ class ShardRuntime:
         check(lib.mtj_k_embed(self._h, ids_dev.data_ptr(), rows, x.data_ptr(), stats.data_ptr(), self.stream))
         return x, stats
 
-    FAMILIES = ("in_proj", "attention", "out_proj", "logits")
+    FAMILIES = ("in_proj", "attention", "out_proj", "logits", "ff_in_proj")
 
     def profile_enable(self, on: bool) -> None:
         check(lib.mtj_profile_enable(self._h, 1 if on else 0))
 
     def profile_read(self) -> dict:
-        ms = (ctypes.c_double * 4)()
-        cnt = (ctypes.c_int64 * 4)()
+        ms = (ctypes.c_double * len(self.FAMILIES))()
+        cnt = (ctypes.c_int64 * len(self.FAMILIES))()
         check(lib.mtj_profile_read(self._h, ms, cnt, self.stream))
         return {f: (ms[i], cnt[i]) for i, f in enumerate(self.FAMILIES)}
 
