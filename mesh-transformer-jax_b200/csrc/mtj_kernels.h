@@ -123,6 +123,43 @@ struct PrefillAttnTcArgs {
 cudaError_t launch_prefill_attn_tc(const void* map_q, const void* map_k, const void* map_v,
                                    const PrefillAttnTcArgs& a, cudaStream_t s);
 
+// Persistent whole-step decode kernel (mtj_decode_mega.cu), one GPU, 1-4 sequences.
+struct MegaLayer {
+  const __nv_bfloat16* w_in;
+  const float* b_ff;
+  const __nv_bfloat16* w_out;
+  const float* b_out;
+  const float* ln_scale;
+  const float* ln_offset;
+  __nv_bfloat16* kpool;
+  __nv_bfloat16* vpool;
+};
+struct MegaArgs {
+  int L, d, dl, ffl, heads, dh, rot, V, B, window, ring_pages, grid_splits, max_splits;
+  const MegaLayer* layers;     // device array [L]
+  const __nv_bfloat16* emb_w;
+  const float* emb_b;
+  const float* lnf_scale;
+  const float* lnf_offset;
+  const __nv_bfloat16* proj_w;
+  const float* proj_b;
+  const float2* sincos;
+  const uint32_t* tokens;      // [B]
+  const int32_t* cur;
+  const int32_t* pad;
+  const int32_t* page_table;
+  float* x;                    // [B, d]
+  float* q;                    // [B, dl]
+  float* act2;                 // [B, dl + ffl]
+  float* part_o;
+  float* part_ml;
+  uint32_t* head_counters;     // [B * heads], zero between launches
+  float* logits;               // [B, V]
+  uint32_t* sync;              // [3 L + 2] phase arrival counters, zero between launches
+  uint32_t* dev_err;
+};
+cudaError_t launch_decode_mega(const MegaArgs& a, cudaStream_t s, int* grid_out);
+
 struct ArgmaxArgs {
   const float* logits;         // [B, V]
   int B, V;

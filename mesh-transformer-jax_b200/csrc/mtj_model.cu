@@ -139,6 +139,10 @@ struct mtj_handle {
   int64_t launches = 0;
   bool use_pdl = true;
   int ks_inproj = 0, ks_out = 0, ks_logits = 0;   // K-split overrides (tuning; 0 = automatic)
+  // decode of 1-4 sequences on one GPU: the whole step as one persistent kernel
+  bool use_mega = true;
+  mtj::MegaLayer* mega_layers = nullptr;   // device copy of the per-layer pointers
+  uint32_t* mega_sync = nullptr;           // [3 L + 2] phase counters
   // decode: attention runs on a side stream next to the FF half of the in-projection
   bool fork_attn = true;
   bool fork_pdl = false;            // let the out-projection start early although it also waits on the side stream
@@ -221,6 +225,8 @@ struct mtj_handle {
     ce_lmax = c.take<float>(R);
     ce_sum = c.take<float>(R * 2);
     ce_hit = c.take<uint8_t>(R);
+    mega_layers = c.take<mtj::MegaLayer>(L);
+    mega_sync = c.take<uint32_t>(3 * L + 2);
     tokens = c.take<uint32_t>(max_batch);
     cur = c.take<int32_t>(4);
     pad = c.take<int32_t>(max_batch);
@@ -723,6 +729,8 @@ int32_t mtj_create(const mtj_config* c, mtj_handle** out) {
   h->expected = 2 + 10LL * h->L + 4;
   const char* e = getenv("MTJ_NO_PDL");
   h->use_pdl = !(e && e[0] == '1');
+  e = getenv("MTJ_NO_MEGA");
+  h->use_mega = !(e && e[0] == '1');
   e = getenv("MTJ_NO_FORK");
   h->fork_attn = !(e && e[0] == '1');
   e = getenv("MTJ_FORK_PDL");
@@ -804,6 +812,17 @@ int32_t mtj_bind_arenas(mtj_handle* h, void* wdev, int64_t wbytes, void* sdev, i
   MTJ_CUDA(cudaMemsetAsync(h->q_bf16, 0, sizeof(__nv_bfloat16) * h->max_rows * h->dl, s));
   MTJ_CUDA(cudaMemsetAsync(h->xn_bf16, 0, sizeof(__nv_bfloat16) * static_cast<size_t>(h->max_rows) * h->d, s));
   MTJ_CUDA(cudaMemsetAsync(h->act_bf16, 0, sizeof(__nv_bfloat16) * static_cast<size_t>(h->max_rows) * (h->dl + h->ffl), s));
+  {
+    std::vector<mtj::MegaLayer> ml(h->L);
+    for (int l = 0; l < h->L; ++l) {
+      const LayerWeights& lw = h->layers[l];
+      mtj::KvCache kv = h->kv(l);
+      ml[l] = {lw.w_in, lw.b_ff, lw.w_out, lw.b_out, lw.ln_scale, lw.ln_offset, kv.kpool, kv.vpool};
+    }
+    MTJ_CUDA(cudaMemcpyAsync(h->mega_layers, ml.data(), sizeof(mtj::MegaLayer) * h->L, cudaMemcpyHostToDevice, s));
+    MTJ_CUDA(cudaMemsetAsync(h->mega_sync, 0, sizeof(uint32_t) * (3 * h->L + 2), s));
+    MTJ_CUDA(cudaStreamSynchronize(s));   // `ml` goes out of scope
+  }
   MTJ_CUDA(cudaStreamSynchronize(s));   // `tab` is about to go out of scope
   // TMA views for the tensor-core GEMM (needs K % 64 == 0 on both projections)
   h->tc_ok = false;
@@ -1051,15 +1070,33 @@ int32_t mtj_decode_step(mtj_handle* h, const uint32_t* tokens_in, const float* t
   auto enqueue = [&](cudaStream_t st) -> int32_t {
     mtj::RowMap rows = {0, 1, 0, h->cur};
     mtj::RowMap erows = {0, 1, 0, nullptr};
-    int32_t r = run_embed(h, h->tokens, 1, B, erows, true, st);
+    const bool mega = h->use_mega && h->mp == 1 && B <= 4 && !h->profile && (h->d % 256) == 0;
+    int32_t r = mega ? MTJ_OK : run_embed(h, h->tokens, 1, B, erows, true, st);
     if (r) return r;
+    if (mega) {
+      mtj::MegaArgs ma = {};
+      ma.L = h->L; ma.d = h->d; ma.dl = h->dl; ma.ffl = h->ffl; ma.heads = h->heads; ma.dh = h->dh;
+      ma.rot = h->rot; ma.V = h->Vl; ma.B = B; ma.window = h->W; ma.ring_pages = h->ring_pages;
+      ma.grid_splits = std::min(mtj::decode_attn_splits(h->W), h->ring_pages);
+      ma.max_splits = h->max_splits;
+      ma.layers = h->mega_layers;
+      ma.emb_w = h->emb_w; ma.emb_b = h->emb_b; ma.lnf_scale = h->lnf_scale; ma.lnf_offset = h->lnf_offset;
+      ma.proj_w = h->proj_w; ma.proj_b = h->proj_b; ma.sincos = h->sincos;
+      ma.tokens = h->tokens; ma.cur = h->cur; ma.pad = h->pad; ma.page_table = h->page_table;
+      ma.x = h->x; ma.q = h->q; ma.act2 = h->act2; ma.part_o = h->part_o; ma.part_ml = h->part_ml;
+      ma.head_counters = h->counters; ma.logits = h->logits; ma.sync = h->mega_sync; ma.dev_err = h->dev_err;
+      MTJ_CUDA(mtj::launch_decode_mega(ma, st, nullptr));
+      h->launches++;
+    }
     const bool tc = use_tc_decode(h, B);
-    for (int l = 0; l < h->L; ++l) {
+    for (int l = 0; !mega && l < h->L; ++l) {
       r = tc ? run_layer_tc(h, l, B, rows, nullptr, st, nullptr, true) : run_layer(h, l, B, rows, true, nullptr, st);
       if (r) return r;
     }
-    r = tc ? run_logits_tc(h, B, 0, h->logits, st) : run_logits(h, B, nullptr, h->logits, true, st);
-    if (r) return r;
+    if (!mega) {
+      r = tc ? run_logits_tc(h, B, 0, h->logits, st) : run_logits(h, B, nullptr, h->logits, true, st);
+      if (r) return r;
+    }
     if (h->mp > 1) {
       // all_gather + transpose + flatten of ProjectionShard.__call__ (layers.py:565-567)
       std::string err;
