@@ -158,6 +158,14 @@ enum { MTJ_FAMILY_INPROJ = 0,    /* LN + Q/K/V (+ FF-in when launched as one ker
 int32_t mtj_profile_enable(mtj_handle* h, int32_t on);
 int32_t mtj_profile_read(mtj_handle* h, double* ms_sum, int64_t* count, mtj_stream s);
 
+/* Phase time stamps of the persistent decode kernel (profiling aid, no reference
+ * counterpart): enable != 0 makes later steps record, for block 0, the
+ * %globaltimer value (ns) at 6 points per layer (before / after the wait for
+ * the residual stream, after its in-projection rows, after its attention units,
+ * after the wait for all attention + FF-in, after its out-projection rows) and 3
+ * at the end; out (host, n entries, may be NULL) receives the last step's record. */
+int32_t mtj_mega_trace(mtj_handle* h, int32_t enable, uint64_t* out_host, int32_t n, mtj_stream s);
+
 /* Reads (and clears) the device-side error word of this handle; synchronises
  * the stream.  MTJ_ERR_TIMEOUT if a bounded wait in a kernel ran out. */
 int32_t mtj_check_device_status(mtj_handle* h, mtj_stream s);

@@ -29,11 +29,23 @@ namespace {
 constexpr int kMT = 256;                 // threads per block
 constexpr int kMW = kMT / 32;            // warps per block
 constexpr int kWaitLimit = 1 << 22;
+#ifndef MTJ_MEGA_NC
+#define MTJ_MEGA_NC 4
+#endif
 
 __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
   uint32_t v;
   asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
+}
+
+__device__ __forceinline__ void trace(unsigned long long* t, int slot) {
+  // phase time stamps of block 0 (nanoseconds), for the profiling read-out
+  if (t && blockIdx.x == 0 && threadIdx.x == 0) {
+    unsigned long long v;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(v));
+    t[slot] = v;
+  }
 }
 
 // All threads of the block call these.
@@ -127,42 +139,127 @@ __device__ __forceinline__ void layer_norm_to_smem(const float* __restrict__ x, 
   __syncthreads();
 }
 
-// Two weight rows x BT activation rows over chunks c = c0, c0 + cs, ... (< nch) of 256 elements.
-// XS: activations come from the shared-memory layout above; otherwise from global fp32 rows.
+template <int BT>
+__device__ __forceinline__ float pick_lane_value(const float (&acc)[2][BT], int lane) {
+  float val = 0.f;
+#pragma unroll
+  for (int r = 0; r < 2; ++r)
+#pragma unroll
+    for (int bt = 0; bt < BT; ++bt)
+      if (lane == bt * 2 + r) val = acc[r][bt];
+  return val;
+}
+
+// acc += rows (w, w + K) x activations over chunks [c_begin, c_end) of 256 elements, two stages of
+// NC chunks in flight.  XS: activations in the shared-memory layout, otherwise global fp32 rows.
 template <int BT, bool XS>
-__device__ __forceinline__ void warp_gemv2(const __nv_bfloat16* __restrict__ w, int K, int nch, int c0, int cs,
+__device__ __forceinline__ void warp_rows2(const __nv_bfloat16* __restrict__ w, int K, int c_begin, int c_end,
                                            const float4* xn, const float* xg, int ldx, int lane,
                                            float (&acc)[2][BT]) {
+  constexpr int NC = MTJ_MEGA_NC;
   const uint4 z4 = make_uint4(0u, 0u, 0u, 0u);
   const __nv_bfloat16* wl = w + lane * 8;
-  constexpr int NC = 4;                      // chunks per pipeline stage (two stages in flight)
-  auto load2 = [&](uint4 (&buf)[NC][2], int c) {
+  auto load = [&](uint4 (&buf)[NC][2], int c) {
 #pragma unroll
-    for (int u = 0; u < NC; ++u) {
-      const int cc = c + u * cs;
-      const bool ok = cc < nch && cc * 256 + lane * 8 < K;
-      buf[u][0] = ok ? ld_stream16(wl + static_cast<size_t>(cc) * 256) : z4;
-      buf[u][1] = ok ? ld_stream16(wl + K + static_cast<size_t>(cc) * 256) : z4;
+    for (int i = 0; i < NC; ++i) {
+      const int cc = c + i;
+      const bool ok = cc < c_end && cc * 256 + lane * 8 < K;
+      buf[i][0] = ok ? ld_stream16(wl + static_cast<size_t>(cc) * 256) : z4;
+      buf[i][1] = ok ? ld_stream16(wl + K + static_cast<size_t>(cc) * 256) : z4;
     }
   };
+  if (c_begin >= c_end) return;
   uint4 nxt[NC][2];
-  load2(nxt, c0);
-  for (int c = c0; c < nch; c += NC * cs) {
+  load(nxt, c_begin);
+  for (int c = c_begin; c < c_end; c += NC) {
     uint4 cur[NC][2];
 #pragma unroll
-    for (int u = 0; u < NC; ++u) {
-      cur[u][0] = nxt[u][0];
-      cur[u][1] = nxt[u][1];
+    for (int i = 0; i < NC; ++i) {
+      cur[i][0] = nxt[i][0];
+      cur[i][1] = nxt[i][1];
     }
-    if (c + NC * cs < nch) load2(nxt, c + NC * cs);
+    if (c + NC < c_end) load(nxt, c + NC);
 #pragma unroll
-    for (int u = 0; u < NC; ++u) {
-      const int cc = c + u * cs;
+    for (int i = 0; i < NC; ++i) {
+      const int cc = c + i;
+      if (cc >= c_end) break;
+      const bool in_k = cc * 256 + lane * 8 < K;
+      float w0[8], w1[8];
+      unpack8(cur[i][0], w0);
+      unpack8(cur[i][1], w1);
+#pragma unroll
+      for (int bt = 0; bt < BT; ++bt) {
+        float4 a, b;
+        if (XS) {
+          const float4* lo = xn + static_cast<size_t>(bt) * 2 * (K >> 3);
+          a = lo[cc * 32 + lane];
+          b = lo[(K >> 3) + cc * 32 + lane];
+        } else {
+          const float* xr = xg + static_cast<size_t>(bt) * ldx + cc * 256 + lane * 8;
+          a = in_k ? __ldcg(reinterpret_cast<const float4*>(xr)) : make_float4(0.f, 0.f, 0.f, 0.f);
+          b = in_k ? __ldcg(reinterpret_cast<const float4*>(xr + 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        const float xv[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          acc[0][bt] = fmaf(w0[e], xv[e], acc[0][bt]);
+          acc[1][bt] = fmaf(w1[e], xv[e], acc[1][bt]);
+        }
+      }
+    }
+  }
+}
+
+// The same two-row product for a whole list of units u = u_first, u_first + u_step, ... (< u_end),
+// rows 2u and 2u + 1 of W, as ONE software pipeline: the loads of the next unit's first chunks are
+// already in flight while the current unit is reduced and finished by epi(u, value-of-this-lane).
+template <int BT, bool XS, typename Epi>
+__device__ __forceinline__ void warp_stream(const __nv_bfloat16* __restrict__ W, int K, int nch, int u_first,
+                                            int u_step, int u_end, const float4* xn, const float* xg, int ldx,
+                                            int lane, Epi epi) {
+  constexpr int NC = MTJ_MEGA_NC;            // chunks per pipeline stage (two stages in flight)
+  if (u_first >= u_end) return;
+  const int spu = (nch + NC - 1) / NC;       // stages per unit
+  const uint4 z4 = make_uint4(0u, 0u, 0u, 0u);
+  auto load = [&](uint4 (&buf)[NC][2], int u, int st) {
+    const __nv_bfloat16* wl = W + static_cast<size_t>(2 * u) * K + lane * 8;
+#pragma unroll
+    for (int i = 0; i < NC; ++i) {
+      const int cc = st * NC + i;
+      const bool ok = cc < nch && cc * 256 + lane * 8 < K;
+      buf[i][0] = ok ? ld_stream16(wl + static_cast<size_t>(cc) * 256) : z4;
+      buf[i][1] = ok ? ld_stream16(wl + K + static_cast<size_t>(cc) * 256) : z4;
+    }
+  };
+  float acc[2][BT];
+#pragma unroll
+  for (int r = 0; r < 2; ++r)
+#pragma unroll
+    for (int bt = 0; bt < BT; ++bt) acc[r][bt] = 0.f;
+  uint4 nxt[NC][2];
+  int u = u_first, st = 0;
+  load(nxt, u, st);
+  while (u < u_end) {
+    uint4 cur[NC][2];
+#pragma unroll
+    for (int i = 0; i < NC; ++i) {
+      cur[i][0] = nxt[i][0];
+      cur[i][1] = nxt[i][1];
+    }
+    int un = u, sn = st + 1;                 // the stage after this one
+    if (sn == spu) {
+      sn = 0;
+      un = u + u_step;
+    }
+    if (un < u_end) load(nxt, un, sn);
+#pragma unroll
+    for (int i = 0; i < NC; ++i) {
+      const int cc = st * NC + i;
       if (cc >= nch) break;
       const bool in_k = cc * 256 + lane * 8 < K;
       float w0[8], w1[8];
-      unpack8(cur[u][0], w0);
-      unpack8(cur[u][1], w1);
+      unpack8(cur[i][0], w0);
+      unpack8(cur[i][1], w1);
 #pragma unroll
       for (int bt = 0; bt < BT; ++bt) {
         float4 a, b;
@@ -183,18 +280,20 @@ __device__ __forceinline__ void warp_gemv2(const __nv_bfloat16* __restrict__ w, 
         }
       }
     }
+    if (st == spu - 1) {
+#pragma unroll
+      for (int r = 0; r < 2; ++r)
+#pragma unroll
+        for (int bt = 0; bt < BT; ++bt) acc[r][bt] = warp_sum(acc[r][bt]);
+      epi(u, pick_lane_value<BT>(acc, lane));
+#pragma unroll
+      for (int r = 0; r < 2; ++r)
+#pragma unroll
+        for (int bt = 0; bt < BT; ++bt) acc[r][bt] = 0.f;
+    }
+    u = un;
+    st = sn;
   }
-}
-
-template <int BT>
-__device__ __forceinline__ float pick_lane_value(const float (&acc)[2][BT], int lane) {
-  float val = 0.f;
-#pragma unroll
-  for (int r = 0; r < 2; ++r)
-#pragma unroll
-    for (int bt = 0; bt < BT; ++bt)
-      if (lane == bt * 2 + r) val = acc[r][bt];
-  return val;
 }
 
 template <int BT, int DH>
@@ -202,7 +301,6 @@ __global__ void __launch_bounds__(kMT, BT == 1 ? 2 : 1) decode_mega_kernel(const
   extern __shared__ __align__(128) unsigned char mega_smem[];
   __shared__ float red[kMW];
 
-  __shared__ __align__(8) uint64_t bar;
   __shared__ float sm_m[kMW], sm_l[kMW];
   __shared__ float sm_o[kMW][DH];
   __shared__ float wgt[64];
@@ -217,16 +315,10 @@ __global__ void __launch_bounds__(kMT, BT == 1 ? 2 : 1) decode_mega_kernel(const
   float4* xn = reinterpret_cast<float4*>(mega_smem);
   uint32_t* c_x = a.sync;                            // [L + 1]
   uint32_t* c_qkv = a.sync + (L + 1);                // [L]
-  uint32_t* c_af = a.sync + (2 * L + 1);             // [L]
-  uint32_t* c_end = a.sync + (3 * L + 1);
+  uint32_t* c_af = a.sync + (2 * L + 1);             // [L] attention (incl. merges) done
+  uint32_t* c_ff = a.sync + (3 * L + 1);             // [L] FF-in rows done
+  uint32_t* c_end = a.sync + (4 * L + 1);
   const uint32_t target = static_cast<uint32_t>(G);
-  const uint32_t bar_u32 = smem_u32(&bar);
-  uint32_t bar_phase = 0;
-  if (threadIdx.x == 0) {
-    mbar_init(bar_u32, 1);
-    mbar_fence_init();
-  }
-  __syncthreads();
 
   const int cur = *a.cur;                            // absolute position of this step's token
 
@@ -246,140 +338,159 @@ __global__ void __launch_bounds__(kMT, BT == 1 ? 2 : 1) decode_mega_kernel(const
     const int nq = (3 * dl) >> 1, n1 = N1 >> 1;      // warp units (2 rows each): Q/K/V first, then FF-in
     // ask for the first weights of this block's first unit before waiting for x
     if (gw < n1) {
-      prefetch_l2(lw.w_in + static_cast<size_t>(2 * gw) * d + lane * 8);
-      prefetch_l2(lw.w_in + static_cast<size_t>(2 * gw + 1) * d + lane * 8);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        if (c * 256 + lane * 8 < d) {
+          prefetch_l2(lw.w_in + static_cast<size_t>(2 * gw) * d + c * 256 + lane * 8);
+          prefetch_l2(lw.w_in + static_cast<size_t>(2 * gw + 1) * d + c * 256 + lane * 8);
+        }
+      }
     }
+    trace(a.trace, 6 * l + 0);
     phase_wait(c_x + l, target, a.dev_err);
+    trace(a.trace, 6 * l + 1);
     layer_norm_to_smem<BT>(a.x, B, d, lw.ln_scale, lw.ln_offset, xn, red);
+
+    // this block's attention unit is known already: pull its keys / values (all but the newest token)
+    // towards L2 while the projections stream
+    {
+      const int splits = a.grid_splits;
+      const int unit = blockIdx.x;
+      if (unit < B * a.heads * splits) {
+        const int split = unit % splits, head = (unit / splits) % a.heads, b = unit / (splits * a.heads);
+        const int start = max(a.pad[b], cur - a.window + 1);
+        const int t0 = start + split * a.split_tokens, t1 = min(cur, t0 + a.split_tokens);
+        const int32_t* table = a.page_table + static_cast<size_t>(b) * a.ring_pages;
+        constexpr int kLines = DH * 2 / 128;
+        for (int i = threadIdx.x; i < (t1 - t0) * kLines; i += kMT) {
+          const size_t off = kv_offset(table, a.ring_pages, a.heads, DH, head, t0 + i / kLines) + (i % kLines) * 64;
+          prefetch_l2(lw.kpool + off);
+          prefetch_l2(lw.vpool + off);
+        }
+      }
+    }
 
     // ---- in-projection ------------------------------------------------------------------------
     const int nch = (d + 255) >> 8;
-    bool qkv_signalled = false;
-    for (int u0 = 0; u0 < n1; u0 += GW) {
-      const int u = u0 + gw;
-      if (u < n1) {
-        float acc[2][BT];
-#pragma unroll
-        for (int r = 0; r < 2; ++r)
-#pragma unroll
-          for (int bt = 0; bt < BT; ++bt) acc[r][bt] = 0.f;
-        warp_gemv2<BT, true>(lw.w_in + static_cast<size_t>(2 * u) * d, d, nch, 0, 1, xn, nullptr, 0, lane, acc);
-#pragma unroll
-        for (int r = 0; r < 2; ++r)
-#pragma unroll
-          for (int bt = 0; bt < BT; ++bt) acc[r][bt] = warp_sum(acc[r][bt]);
-        const float val = pick_lane_value<BT>(acc, lane);
-        const float partner = __shfl_xor_sync(0xffffffffu, val, 1);
-        const int r = lane & 1, bt = lane >> 1;
-        const int n = 2 * u + r;
-        if (lane < 2 * BT && bt < B) {
-          if (n < 3 * dl) {
-            const int region = n / dl;
-            const int nn = n - region * dl;
-            const int head = nn / DH, j = nn % DH;
-            float y = val;
-            if (region < 2 && j < a.rot) {
-              const float2 sc = a.sincos[static_cast<size_t>(cur) * (a.rot >> 1) + (j >> 1)];
-              y = (j & 1) ? (val * sc.y + partner * sc.x) : (val * sc.y - partner * sc.x);
-            }
-            if (region == 0) {
-              a.q[static_cast<size_t>(bt) * dl + nn] = y;
-            } else if (cur >= a.pad[bt]) {
-              __nv_bfloat16* pool = region == 1 ? lw.kpool : lw.vpool;
-              const size_t off = kv_offset(a.page_table + static_cast<size_t>(bt) * a.ring_pages, a.ring_pages,
-                                           a.heads, DH, head, cur);
-              pool[off + j] = __float2bfloat16_rn(y);
-            }
-          } else {
-            const int f = n - 3 * dl;
-            a.act2[static_cast<size_t>(bt) * (dl + ffl) + dl + f] = gelu_tanh(val + lw.b_ff[f]);
+    auto in_epi = [&](int u, float val) {
+      const float partner = __shfl_xor_sync(0xffffffffu, val, 1);
+      const int r = lane & 1, bt = lane >> 1;
+      const int n = 2 * u + r;
+      if (lane < 2 * BT && bt < B) {
+        if (n < 3 * dl) {
+          const int region = n / dl;
+          const int nn = n - region * dl;
+          const int head = nn / DH, j = nn % DH;
+          float y = val;
+          if (region < 2 && j < a.rot) {
+            const float2 sc = a.sincos[static_cast<size_t>(cur) * (a.rot >> 1) + (j >> 1)];
+            y = (j & 1) ? (val * sc.y + partner * sc.x) : (val * sc.y - partner * sc.x);
           }
+          if (region == 0) {
+            a.q[static_cast<size_t>(bt) * dl + nn] = y;
+          } else if (cur >= a.pad[bt]) {
+            __nv_bfloat16* pool = region == 1 ? lw.kpool : lw.vpool;
+            const size_t off = kv_offset(a.page_table + static_cast<size_t>(bt) * a.ring_pages, a.ring_pages,
+                                         a.heads, DH, head, cur);
+            pool[off + j] = __float2bfloat16_rn(y);
+          }
+        } else {
+          const int f = n - 3 * dl;
+          a.act2[static_cast<size_t>(bt) * (dl + ffl) + dl + f] = gelu_tanh(val + lw.b_ff[f]);
         }
       }
-      // once every Q/K/V unit of this block is behind it, tell the attention phase
-      if (!qkv_signalled && u0 + GW >= nq) {
-        phase_arrive(c_qkv + l);
-        qkv_signalled = true;
-      }
-    }
-    if (!qkv_signalled) phase_arrive(c_qkv + l);
+    };
+    // Q/K/V rows first; once this block's share is behind it the attention phase may count on it
+    warp_stream<BT, true>(lw.w_in, d, nch, gw, GW, nq, xn, nullptr, 0, lane, in_epi);
+    phase_arrive(c_qkv + l);
+    // FF-in rows: continue the round-robin where the Q/K/V units stopped, so the load stays even
+    const int ff_first = nq + ((gw - nq % GW) + GW) % GW;
+    warp_stream<BT, true>(lw.w_in, d, nch, ff_first, GW, n1, xn, nullptr, 0, lane, in_epi);
+    phase_arrive(c_ff + l);
 
-    // ---- attention: one unit = (sequence, head, 64-token page) ---------------------------------
-    phase_wait(c_qkv + l, target, a.dev_err);          // also: every warp of this block left shared x
+    // ---- attention: one unit = (sequence, head, contiguous range of up to a.split_tokens keys) ------
+    // Every block gets at most one unit per round; its warps read their keys / values straight from the
+    // paged cache with all loads of a batch in flight at once (no staging, no block-level waits).
+    __syncthreads();
+    trace(a.trace, 6 * l + 2);                         // this block's in-projection rows are done
+    phase_wait(c_qkv + l, target, a.dev_err);
     {
       constexpr int EPL = DH / 32;
-      constexpr int TPW = kPageTokens / kMW;
-      constexpr uint32_t kSlab = kPageTokens * DH * 2;
-      __nv_bfloat16* sk = reinterpret_cast<__nv_bfloat16*>(mega_smem);
-      __nv_bfloat16* sv = reinterpret_cast<__nv_bfloat16*>(mega_smem + kSlab);
+      constexpr int TB = 8;                            // keys per batch and warp
+      constexpr float scale = DH == 256 ? 0.0625f : 0.125f;
       const int splits = a.grid_splits;
       const int units = B * a.heads * splits;
       for (int unit = blockIdx.x; unit < units; unit += G) {
         const int split = unit % splits, head = (unit / splits) % a.heads, b = unit / (splits * a.heads);
         const int start = max(a.pad[b], cur - a.window + 1);
-        const int first_page = start / kPageTokens;
-        const int nsplit = cur / kPageTokens - first_page + 1;
+        const int len = cur + 1 - start;
+        const int nsplit = (len + a.split_tokens - 1) / a.split_tokens;
         if (split >= nsplit) continue;                 // uniform for the block
-        const int page_pos0 = (first_page + split) * kPageTokens;
-        const int t0 = max(start, page_pos0), t1 = min(cur + 1, page_pos0 + kPageTokens);
-        if (threadIdx.x == 0) {
-          const int32_t* table = a.page_table + static_cast<size_t>(b) * a.ring_pages;
-          const int page = table[(first_page + split) % a.ring_pages];
-          const size_t off = (static_cast<size_t>(page) * a.heads + head) * kPageTokens * DH;
-          const uint64_t pol = l2_evict_first_policy();
-          // generic-proxy reads of the previous unit are ordered before these async writes by the block barrier
-          mbar_expect_tx(bar_u32, 2 * kSlab);
-          bulk_load(smem_u32(sk), lw.kpool + off, kSlab, bar_u32, pol);
-          bulk_load(smem_u32(sv), lw.vpool + off, kSlab, bar_u32, pol);
-        }
-        constexpr float scale = DH == 256 ? 0.0625f : 0.125f;
+        const int t0 = start + split * a.split_tokens, t1 = min(cur + 1, t0 + a.split_tokens);
+        const int32_t* table = a.page_table + static_cast<size_t>(b) * a.ring_pages;
         float q[EPL];
         {
           const float* qp = a.q + (static_cast<size_t>(b) * a.heads + head) * DH + lane * EPL;
 #pragma unroll
           for (int e = 0; e < EPL; ++e) q[e] = __ldcg(qp + e) * scale;
         }
-        const bool arrived = mbar_wait(bar_u32, bar_phase & 1);
-        bar_phase++;
-        if (!arrived && threadIdx.x == 0 && a.dev_err) atomicOr(a.dev_err, kDevErrTimeout);
         float m = -INFINITY, lsum = 0.f, o[EPL];
 #pragma unroll
         for (int e = 0; e < EPL; ++e) o[e] = 0.f;
-        {
-          float s[TPW];
-          bool ok[TPW];
+        // warp w takes keys t0 + w*per .. of this range, in batches of TB
+        const int per = (t1 - t0 + kMW - 1) / kMW;
+        const int w0 = t0 + warp * per, w1 = min(t1, w0 + per);
+        for (int tb = w0; tb < w1; tb += TB) {
+          uint4 kraw[TB], vraw[TB];
+          bool ok[TB];
 #pragma unroll
-          for (int t = 0; t < TPW; ++t) {
-            const int tt = page_pos0 + warp * TPW + t;
-            ok[t] = arrived && tt >= t0 && tt < t1;
-            const __nv_bfloat16* kp = sk + static_cast<size_t>(warp * TPW + t) * DH + lane * EPL;
-            float kf[EPL];
-            if (EPL == 8) unpack8(*reinterpret_cast<const uint4*>(kp), kf);
-            else { const uint32_t w2 = *reinterpret_cast<const uint32_t*>(kp); kf[0] = bf16_lo(w2); kf[1] = bf16_hi(w2); }
+          for (int t = 0; t < TB; ++t) {
+            const int tt = tb + t;
+            ok[t] = tt < w1;
+            const size_t off = kv_offset(table, a.ring_pages, a.heads, DH, head, ok[t] ? tt : tb) + lane * EPL;
+            if (EPL == 8) {
+              kraw[t] = ld_stream16(lw.kpool + off);
+              vraw[t] = ld_stream16(lw.vpool + off);
+            } else {
+              kraw[t].x = ld_stream4(lw.kpool + off);
+              vraw[t].x = ld_stream4(lw.vpool + off);
+            }
+          }
+          float sc[TB];
+#pragma unroll
+          for (int t = 0; t < TB; ++t) {
+            float kf[8];
+            if (EPL == 8) unpack8(kraw[t], kf);
+            else { kf[0] = bf16_lo(kraw[t].x); kf[1] = bf16_hi(kraw[t].x); }
             float dsum = 0.f;
 #pragma unroll
             for (int e = 0; e < EPL; ++e) dsum = fmaf(q[e], kf[e], dsum);
-            s[t] = dsum;
+            sc[t] = dsum;
           }
 #pragma unroll
           for (int o2 = 16; o2 > 0; o2 >>= 1)
 #pragma unroll
-            for (int t = 0; t < TPW; ++t) s[t] += __shfl_xor_sync(0xffffffffu, s[t], o2);
+            for (int t = 0; t < TB; ++t) sc[t] += __shfl_xor_sync(0xffffffffu, sc[t], o2);
+          float mn = m;
 #pragma unroll
-          for (int t = 0; t < TPW; ++t)
-            if (ok[t]) m = fmaxf(m, s[t]);
+          for (int t = 0; t < TB; ++t)
+            if (ok[t]) mn = fmaxf(mn, sc[t]);
+          const float corr = m == -INFINITY ? 0.f : __expf(m - mn);
+          lsum *= corr;
 #pragma unroll
-          for (int t = 0; t < TPW; ++t) {
+          for (int e = 0; e < EPL; ++e) o[e] *= corr;
+#pragma unroll
+          for (int t = 0; t < TB; ++t) {
             if (!ok[t]) continue;
-            const float p = __expf(s[t] - m);
-            const __nv_bfloat16* vp = sv + static_cast<size_t>(warp * TPW + t) * DH + lane * EPL;
-            float vf[EPL];
-            if (EPL == 8) unpack8(*reinterpret_cast<const uint4*>(vp), vf);
-            else { const uint32_t w2 = *reinterpret_cast<const uint32_t*>(vp); vf[0] = bf16_lo(w2); vf[1] = bf16_hi(w2); }
+            const float p = __expf(sc[t] - mn);
+            float vf[8];
+            if (EPL == 8) unpack8(vraw[t], vf);
+            else { vf[0] = bf16_lo(vraw[t].x); vf[1] = bf16_hi(vraw[t].x); }
             lsum += p;
 #pragma unroll
             for (int e = 0; e < EPL; ++e) o[e] = fmaf(p, vf[e], o[e]);
           }
+          m = mn;
         }
         if (lane == 0) {
           sm_m[warp] = m;
@@ -459,25 +570,41 @@ __global__ void __launch_bounds__(kMT, BT == 1 ? 2 : 1) decode_mega_kernel(const
       const int K2 = dl + ffl;
       const int rg = gw;
       if (rg < (d >> 1)) {
-        prefetch_l2(lw.w_out + static_cast<size_t>(2 * rg) * K2 + lane * 8);
-        prefetch_l2(lw.w_out + static_cast<size_t>(2 * rg + 1) * K2 + lane * 8);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          if (c * 256 + lane * 8 < K2) {
+            prefetch_l2(lw.w_out + static_cast<size_t>(2 * rg) * K2 + c * 256 + lane * 8);
+            prefetch_l2(lw.w_out + static_cast<size_t>(2 * rg + 1) * K2 + c * 256 + lane * 8);
+          }
+        }
       }
     }
+    trace(a.trace, 6 * l + 3);                         // attention units done
     phase_arrive(c_af + l);
-    phase_wait(c_af + l, target, a.dev_err);
 
-    // ---- out-projection + bias + residual: a block owns two rows, its warps split K ------------
+    // ---- out-projection + bias + residual: a warp owns two output rows over the whole K ---------
+    // K = [attention vector | gelu(ff)].  The FF columns only need every block's FF-in rows, which were
+    // finished before attention started, so they are accumulated first; the attention columns follow
+    // once every (sequence, head) has been merged -- the wait for the slowest attention unit is spent
+    // streaming weights.  For one sequence the activations are staged in shared memory.
     {
       const int K2 = dl + ffl;
       const int nch2 = (K2 + 255) >> 8;
-      for (int rg = gw; rg < (d >> 1); rg += GW) {     // a warp owns two output rows over the whole K
-        float acc[2][BT];
-#pragma unroll
-        for (int r = 0; r < 2; ++r)
-#pragma unroll
-          for (int bt = 0; bt < BT; ++bt) acc[r][bt] = 0.f;
-        warp_gemv2<BT, false>(lw.w_out + static_cast<size_t>(2 * rg) * K2, K2, nch2, 0, 1, nullptr, a.act2, K2,
-                              lane, acc);
+      constexpr bool kStage = (BT == 1);
+      const int cS = (dl & 255) == 0 ? (dl >> 8) : 0;  // chunks [0, cS) are attention columns (0: no split)
+      const int n8 = K2 >> 3;
+      auto stage = [&](int e8_begin, int e8_end) {     // copy act2[8*e8_begin .. 8*e8_end) into the smem layout
+        if (kStage) {
+          float4* lo = xn;
+          float4* hi = xn + n8;
+          for (int c = e8_begin + threadIdx.x; c < e8_end; c += kMT) {
+            lo[c] = __ldcg(reinterpret_cast<const float4*>(a.act2) + 2 * c);
+            hi[c] = __ldcg(reinterpret_cast<const float4*>(a.act2) + 2 * c + 1);
+          }
+        }
+        __syncthreads();
+      };
+      auto finish = [&](int rg, float (&acc)[2][BT]) {
 #pragma unroll
         for (int r = 0; r < 2; ++r)
 #pragma unroll
@@ -489,8 +616,37 @@ __global__ void __launch_bounds__(kMT, BT == 1 ? 2 : 1) decode_mega_kernel(const
           float* xp = a.x + static_cast<size_t>(bt) * d + n;
           *xp = val + lw.b_out[n] + *xp;
         }
+      };
+      const int nrg = d >> 1;
+      const __nv_bfloat16* wrow = lw.w_out + static_cast<size_t>(2 * (gw < nrg ? gw : 0)) * K2;
+      float acc[2][BT];
+#pragma unroll
+      for (int r = 0; r < 2; ++r)
+#pragma unroll
+        for (int bt = 0; bt < BT; ++bt) acc[r][bt] = 0.f;
+      phase_wait(c_ff + l, target, a.dev_err);
+      const int sS = cS > 0 ? cS * 32 : n8;           // no split: everything is staged after the attention wait
+      stage(sS, n8);
+      if (gw < nrg && cS > 0) warp_rows2<BT, kStage>(wrow, K2, cS, nch2, xn, a.act2, K2, lane, acc);
+      phase_wait(c_af + l, target, a.dev_err);
+      trace(a.trace, 6 * l + 4);
+      stage(0, sS);
+      if (gw < nrg) {
+        warp_rows2<BT, kStage>(wrow, K2, 0, cS > 0 ? cS : nch2, xn, a.act2, K2, lane, acc);
+        finish(gw, acc);
+      }
+      // more row pairs than warps: everything is ready, plain passes
+      for (int rg = gw + GW; rg < nrg; rg += GW) {
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
+#pragma unroll
+          for (int bt = 0; bt < BT; ++bt) acc[r][bt] = 0.f;
+        warp_rows2<BT, kStage>(lw.w_out + static_cast<size_t>(2 * rg) * K2, K2, 0, nch2, xn, a.act2, K2, lane, acc);
+        finish(rg, acc);
       }
     }
+    __syncthreads();
+    trace(a.trace, 6 * l + 5);                         // out-projection rows done
     phase_arrive(c_x + l + 1);
   }
 
@@ -501,29 +657,21 @@ __global__ void __launch_bounds__(kMT, BT == 1 ? 2 : 1) decode_mega_kernel(const
       prefetch_l2(a.proj_w + static_cast<size_t>(2 * gw) * d + lane * 8);
       prefetch_l2(a.proj_w + static_cast<size_t>(2 * gw + 1) * d + lane * 8);
     }
+    trace(a.trace, 6 * L + 0);
     phase_wait(c_x + L, target, a.dev_err);
+    trace(a.trace, 6 * L + 1);
     layer_norm_to_smem<BT>(a.x, B, d, a.lnf_scale, a.lnf_offset, xn, red);
     const int nch = (d + 255) >> 8;
-    for (int u = gw; u < nv; u += GW) {
-      float acc[2][BT];
-#pragma unroll
-      for (int r = 0; r < 2; ++r)
-#pragma unroll
-        for (int bt = 0; bt < BT; ++bt) acc[r][bt] = 0.f;
-      warp_gemv2<BT, true>(a.proj_w + static_cast<size_t>(2 * u) * d, d, nch, 0, 1, xn, nullptr, 0, lane, acc);
-#pragma unroll
-      for (int r = 0; r < 2; ++r)
-#pragma unroll
-        for (int bt = 0; bt < BT; ++bt) acc[r][bt] = warp_sum(acc[r][bt]);
-      const float val = pick_lane_value<BT>(acc, lane);
+    warp_stream<BT, true>(a.proj_w, d, nch, gw, GW, nv, xn, nullptr, 0, lane, [&](int u, float val) {
       const int r = lane & 1, bt = lane >> 1;
       const int n = 2 * u + r;
       if (lane < 2 * BT && bt < B) a.logits[static_cast<size_t>(bt) * a.V + n] = val + a.proj_b[n];
-    }
+    });
   }
 
   // ---- the last block to finish resets the arrival counters for the next launch -----------------
   __syncthreads();
+  trace(a.trace, 6 * L + 2);
   if (threadIdx.x == 0) {
     __threadfence();
     const uint32_t ticket = atomicAdd(c_end, 1u);
@@ -531,14 +679,14 @@ __global__ void __launch_bounds__(kMT, BT == 1 ? 2 : 1) decode_mega_kernel(const
   }
   __syncthreads();
   if (is_last)
-    for (int i = threadIdx.x; i < 3 * L + 2; i += kMT) a.sync[i] = 0u;
+    for (int i = threadIdx.x; i < 4 * L + 2; i += kMT) a.sync[i] = 0u;
 }
 
 template <int BT, int DH>
 cudaError_t launch_mega_t(const MegaArgs& a, cudaStream_t s, int* grid_out) {
-  const int smem_attn = 2 * kPageTokens * DH * 2;
-  const int smem_x = BT * a.d * 4;
-  const int smem = smem_attn > smem_x ? smem_attn : smem_x;
+  const int smem_x = BT * a.d * 4;                                  // LayerNorm output of BT rows
+  const int smem_o = BT == 1 ? (a.dl + a.ffl) * 4 : 0;             // staged out-projection input (one sequence)
+  const int smem = smem_o > smem_x ? smem_o : smem_x;
   static int cached_blocks = 0, cached_smem = -1;
   if (cached_smem != smem) {
     cudaError_t e = cudaFuncSetAttribute(decode_mega_kernel<BT, DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -553,6 +701,13 @@ cudaError_t launch_mega_t(const MegaArgs& a, cudaStream_t s, int* grid_out) {
     cached_smem = smem;
   }
   if (grid_out) *grid_out = cached_blocks;
+  // attention: one round of units over the resident blocks, at most 64 splits per (sequence, head)
+  MegaArgs b = a;
+  int want = cached_blocks / (a.B * a.heads);
+  want = want < 1 ? 1 : (want > 64 ? 64 : want);
+  if (want > a.max_splits) want = a.max_splits;
+  b.split_tokens = (a.window + want - 1) / want;
+  b.grid_splits = (a.window + b.split_tokens - 1) / b.split_tokens;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(cached_blocks);
   cfg.blockDim = dim3(kMT);
@@ -563,14 +718,14 @@ cudaError_t launch_mega_t(const MegaArgs& a, cudaStream_t s, int* grid_out) {
   attr[0].val.cooperative = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, decode_mega_kernel<BT, DH>, a);
+  return cudaLaunchKernelEx(&cfg, decode_mega_kernel<BT, DH>, b);
 }
 
 }  // namespace
 
 cudaError_t launch_decode_mega(const MegaArgs& a, cudaStream_t s, int* grid_out) {
   if (a.B < 1 || a.B > 4 || (a.d & 255) || a.d > 8192 || (a.dl & 1) || (a.V & 1) || ((3 * a.dl + a.ffl) & 1) ||
-      ((a.dl + a.ffl) & 7) || a.grid_splits > 64)
+      ((a.dl + a.ffl) & 7) || a.max_splits < 1 || (a.dl + a.ffl) * 4 > 200 * 1024)
     return cudaErrorInvalidValue;
   if (a.dh == 256) {
     if (a.B == 1) return launch_mega_t<1, 256>(a, s, grid_out);

@@ -135,7 +135,8 @@ struct MegaLayer {
   __nv_bfloat16* vpool;
 };
 struct MegaArgs {
-  int L, d, dl, ffl, heads, dh, rot, V, B, window, ring_pages, grid_splits, max_splits;
+  int L, d, dl, ffl, heads, dh, rot, V, B, window, ring_pages;
+  int grid_splits, split_tokens, max_splits;   // attention: splits per (sequence, head), keys per split
   const MegaLayer* layers;     // device array [L]
   const __nv_bfloat16* emb_w;
   const float* emb_b;
@@ -155,7 +156,8 @@ struct MegaArgs {
   float* part_ml;
   uint32_t* head_counters;     // [B * heads], zero between launches
   float* logits;               // [B, V]
-  uint32_t* sync;              // [3 L + 2] phase arrival counters, zero between launches
+  uint32_t* sync;              // [4 L + 2] phase arrival counters, zero between launches
+  unsigned long long* trace;   // optional [6 L + 3] phase time stamps of block 0 (ns)
   uint32_t* dev_err;
 };
 cudaError_t launch_decode_mega(const MegaArgs& a, cudaStream_t s, int* grid_out);

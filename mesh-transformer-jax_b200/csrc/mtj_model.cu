@@ -143,6 +143,8 @@ struct mtj_handle {
   bool use_mega = true;
   mtj::MegaLayer* mega_layers = nullptr;   // device copy of the per-layer pointers
   uint32_t* mega_sync = nullptr;           // [3 L + 2] phase counters
+  unsigned long long* mega_trace = nullptr;  // [6 L + 3] phase time stamps (profiling read-out)
+  bool mega_trace_on = false;
   // decode: attention runs on a side stream next to the FF half of the in-projection
   bool fork_attn = true;
   bool fork_pdl = false;            // let the out-projection start early although it also waits on the side stream
@@ -226,7 +228,8 @@ struct mtj_handle {
     ce_sum = c.take<float>(R * 2);
     ce_hit = c.take<uint8_t>(R);
     mega_layers = c.take<mtj::MegaLayer>(L);
-    mega_sync = c.take<uint32_t>(3 * L + 2);
+    mega_sync = c.take<uint32_t>(4 * L + 2);
+    mega_trace = c.take<unsigned long long>(6 * L + 3);
     tokens = c.take<uint32_t>(max_batch);
     cur = c.take<int32_t>(4);
     pad = c.take<int32_t>(max_batch);
@@ -820,7 +823,7 @@ int32_t mtj_bind_arenas(mtj_handle* h, void* wdev, int64_t wbytes, void* sdev, i
       ml[l] = {lw.w_in, lw.b_ff, lw.w_out, lw.b_out, lw.ln_scale, lw.ln_offset, kv.kpool, kv.vpool};
     }
     MTJ_CUDA(cudaMemcpyAsync(h->mega_layers, ml.data(), sizeof(mtj::MegaLayer) * h->L, cudaMemcpyHostToDevice, s));
-    MTJ_CUDA(cudaMemsetAsync(h->mega_sync, 0, sizeof(uint32_t) * (3 * h->L + 2), s));
+    MTJ_CUDA(cudaMemsetAsync(h->mega_sync, 0, sizeof(uint32_t) * (4 * h->L + 2), s));
     MTJ_CUDA(cudaStreamSynchronize(s));   // `ml` goes out of scope
   }
   MTJ_CUDA(cudaStreamSynchronize(s));   // `tab` is about to go out of scope
@@ -1085,6 +1088,7 @@ int32_t mtj_decode_step(mtj_handle* h, const uint32_t* tokens_in, const float* t
       ma.tokens = h->tokens; ma.cur = h->cur; ma.pad = h->pad; ma.page_table = h->page_table;
       ma.x = h->x; ma.q = h->q; ma.act2 = h->act2; ma.part_o = h->part_o; ma.part_ml = h->part_ml;
       ma.head_counters = h->counters; ma.logits = h->logits; ma.sync = h->mega_sync; ma.dev_err = h->dev_err;
+      ma.trace = h->mega_trace_on ? h->mega_trace : nullptr;
       MTJ_CUDA(mtj::launch_decode_mega(ma, st, nullptr));
       h->launches++;
     }
@@ -1292,6 +1296,24 @@ int32_t mtj_sample_top_p(const float* logits, const float* uniforms, const float
   sa.scratch = scratch;
   sa.tokens = tokens_out;
   MTJ_CUDA(mtj::launch_sample_top_p(sa, static_cast<cudaStream_t>(stream), false));
+  return MTJ_OK;
+}
+
+int32_t mtj_mega_trace(mtj_handle* h, int32_t enable, uint64_t* out, int32_t n, mtj_stream stream) {
+  if (!h || !h->bound) return fail(MTJ_ERR_STATE, "not bound");
+  if (out) {
+    if (n > 6 * h->L + 3) n = 6 * h->L + 3;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    MTJ_CUDA(cudaMemcpyAsync(out, h->mega_trace, sizeof(uint64_t) * n, cudaMemcpyDeviceToHost, s));
+    MTJ_CUDA(cudaStreamSynchronize(s));
+  }
+  if ((enable != 0) != h->mega_trace_on) {
+    h->mega_trace_on = enable != 0;
+    if (h->graph_exec) {            // the trace pointer is baked into the captured step
+      cudaGraphExecDestroy(h->graph_exec);
+      h->graph_exec = nullptr;
+    }
+  }
   return MTJ_OK;
 }
 

@@ -54,6 +54,7 @@ def _load():
         "mtj_sample_top_p": (i32, [vp, vp, vp, vp, i32, i32, vp, i64, vp, vp]),
         "mtj_launch_count": (i64, [vp]),
         "mtj_check_device_status": (i32, [vp, vp]),
+        "mtj_mega_trace": (i32, [vp, i32, ctypes.POINTER(ctypes.c_uint64), i32, vp]),
         "mtj_profile_enable": (i32, [vp, i32]),
         "mtj_profile_read": (i32, [vp, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(i64), vp]),
         "mtj_k_embed": (i32, [vp, vp, i32, vp, vp, vp]),

@@ -238,6 +238,13 @@ class ShardRuntime:
         check(lib.mtj_profile_read(self._h, ms, cnt, self.stream))
         return {f: (ms[i], cnt[i]) for i, f in enumerate(self.FAMILIES)}
 
+    def mega_trace(self, enable: bool, read: bool = False):
+        """Phase time stamps (ns) of the persistent decode kernel's block 0."""
+        n = 6 * self.config["layers"] + 3
+        buf = (ctypes.c_uint64 * n)() if read else None
+        check(lib.mtj_mega_trace(self._h, 1 if enable else 0, buf, n if read else 0, self.stream))
+        return list(buf) if read else None
+
     def launch_count(self) -> int:
         return int(lib.mtj_launch_count(self._h))
 
