@@ -70,6 +70,59 @@ __device__ __forceinline__ void phase_wait(const uint32_t* counter, uint32_t tar
   __syncthreads();
 }
 
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// g_psum over the "shard" axis inside the persistent kernel (tensor parallel decode).  Every rank
+// has written its [B, d] partial sums into slot (k & 1) of its exchange buffer (k = all-reduces done
+// so far).  The last block to arrive publishes flag[rank] = k + 1 to all peers; every block waits
+// (bounded) for the peers' flags, then adds its slice of the peers' slots in rank order into x
+// (x += sum, or x = sum when `accumulate` is false).  Same protocol as mtj_p2p.cu.
+__device__ __forceinline__ void mega_all_reduce(const MegaArgs& a, uint32_t k, uint32_t* c_local, uint32_t target,
+                                                int n_elems, bool accumulate) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const uint32_t ticket = atomicAdd(c_local, 1u);
+    if (ticket == target - 1) {                      // every block's partial sums are in place
+      __threadfence_system();
+      for (int r = 0; r < a.world; ++r)
+        if (r != a.rank) st_release_sys_u32(a.peer_flags[r] + a.rank, k + 1);
+    }
+  }
+  if (threadIdx.x < a.world && threadIdx.x != a.rank) {
+    const uint32_t* f = a.local_flags + threadIdx.x;
+    int spins = 0;
+    while (static_cast<int32_t>(ld_acquire_sys_u32(f) - (k + 1)) < 0) {
+      if (++spins > kWaitLimit) {
+        if (a.dev_err) atomicOr(a.dev_err, kDevErrTimeout);
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  const size_t slot = static_cast<size_t>(k & 1u) * a.slot_elems;
+  for (int i = (blockIdx.x * kMT + threadIdx.x) * 4; i < n_elems; i += gridDim.x * kMT * 4) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r = 0; r < a.world; ++r) {
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(a.peer_data[r] + slot + i));
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    float4* xp = reinterpret_cast<float4*>(a.x + i);
+    if (accumulate) {
+      const float4 o = *xp;
+      acc.x += o.x; acc.y += o.y; acc.z += o.z; acc.w += o.w;
+    }
+    *xp = acc;
+  }
+}
+
 __device__ __forceinline__ float block_sum(float v, float* red) {
   v = warp_sum(v);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -318,18 +371,24 @@ __global__ void __launch_bounds__(kMT, BT == 1 ? 2 : 1) decode_mega_kernel(const
   uint32_t* c_af = a.sync + (2 * L + 1);             // [L] attention (incl. merges) done
   uint32_t* c_ff = a.sync + (3 * L + 1);             // [L] FF-in rows done
   uint32_t* c_end = a.sync + (4 * L + 1);
+  uint32_t* c_red = a.sync + (4 * L + 2);            // [L + 1] partial sums written (tensor parallel)
+  const bool tp = a.world > 1;
+  const uint32_t seq0 = tp ? *a.seq : 0u;            // all-reduces completed before this step
+  float* partial = tp ? a.slot_base : nullptr;       // this rank's exchange buffer (two slots)
   const uint32_t target = static_cast<uint32_t>(G);
 
   const int cur = *a.cur;                            // absolute position of this step's token
 
   // ---- embedding: x[b] = table[token_b] + bias ------------------------------------------------
   for (int b = blockIdx.x; b < B; b += G) {
-    const uint32_t id = a.tokens[b];
-    const bool hit = id < static_cast<uint32_t>(a.V);
+    const int64_t id = static_cast<int64_t>(a.tokens[b]) - a.vocab_start;
+    const bool hit = id >= 0 && id < a.V;
     const __nv_bfloat16* row = a.emb_w + static_cast<size_t>(hit ? id : 0) * d;
+    float* dst = tp ? partial + static_cast<size_t>(seq0 & 1u) * a.slot_elems : a.x;
     for (int i = threadIdx.x; i < d; i += kMT)
-      a.x[static_cast<size_t>(b) * d + i] = (hit ? __bfloat162float(row[i]) : 0.f) + a.emb_b[i];
+      dst[static_cast<size_t>(b) * d + i] = (hit ? __bfloat162float(row[i]) : 0.f) + a.emb_b[i];
   }
+  if (tp) mega_all_reduce(a, seq0, c_red, target, B * d, false);
   phase_arrive(c_x);
 
   for (int l = 0; l < L; ++l) {
@@ -613,8 +672,13 @@ __global__ void __launch_bounds__(kMT, BT == 1 ? 2 : 1) decode_mega_kernel(const
         const int r = lane & 1, bt = lane >> 1;
         const int n = 2 * rg + r;
         if (lane < 2 * BT && bt < B) {
-          float* xp = a.x + static_cast<size_t>(bt) * d + n;
-          *xp = val + lw.b_out[n] + *xp;
+          if (tp) {
+            partial[static_cast<size_t>((seq0 + 1 + l) & 1u) * a.slot_elems + static_cast<size_t>(bt) * d + n] =
+                val + lw.b_out[n];
+          } else {
+            float* xp = a.x + static_cast<size_t>(bt) * d + n;
+            *xp = val + lw.b_out[n] + *xp;
+          }
         }
       };
       const int nrg = d >> 1;
@@ -647,6 +711,7 @@ __global__ void __launch_bounds__(kMT, BT == 1 ? 2 : 1) decode_mega_kernel(const
     }
     __syncthreads();
     trace(a.trace, 6 * l + 5);                         // out-projection rows done
+    if (tp) mega_all_reduce(a, seq0 + 1 + l, c_red + 1 + l, target, B * d, true);
     phase_arrive(c_x + l + 1);
   }
 
@@ -678,8 +743,10 @@ __global__ void __launch_bounds__(kMT, BT == 1 ? 2 : 1) decode_mega_kernel(const
     is_last = (ticket == target - 1);
   }
   __syncthreads();
-  if (is_last)
-    for (int i = threadIdx.x; i < 4 * L + 2; i += kMT) a.sync[i] = 0u;
+  if (is_last) {
+    for (int i = threadIdx.x; i < 5 * L + 3; i += kMT) a.sync[i] = 0u;
+    if (tp && threadIdx.x == 0) *a.seq = seq0 + 1 + L;
+  }
 }
 
 template <int BT, int DH>
@@ -724,7 +791,7 @@ cudaError_t launch_mega_t(const MegaArgs& a, cudaStream_t s, int* grid_out) {
 }  // namespace
 
 cudaError_t launch_decode_mega(const MegaArgs& a, cudaStream_t s, int* grid_out) {
-  if (a.B < 1 || a.B > 4 || (a.d & 255) || a.d > 8192 || (a.dl & 1) || (a.V & 1) || ((3 * a.dl + a.ffl) & 1) ||
+  if (a.world < 1 || a.world > 8 || a.B < 1 || a.B > 4 || (a.d & 255) || a.d > 8192 || (a.dl & 1) || (a.V & 1) || ((3 * a.dl + a.ffl) & 1) ||
       ((a.dl + a.ffl) & 7) || a.max_splits < 1 || (a.dl + a.ffl) * 4 > 200 * 1024)
     return cudaErrorInvalidValue;
   if (a.dh == 256) {

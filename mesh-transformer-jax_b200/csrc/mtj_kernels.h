@@ -156,7 +156,15 @@ struct MegaArgs {
   float* part_ml;
   uint32_t* head_counters;     // [B * heads], zero between launches
   float* logits;               // [B, V]
-  uint32_t* sync;              // [4 L + 2] phase arrival counters, zero between launches
+  uint32_t* sync;              // [5 L + 3] phase arrival counters, zero between launches
+  // tensor parallel (world > 1): the peer exchange buffers of mtj_p2p.cu
+  int rank, world, vocab_start;
+  float* slot_base;            // this rank's two data slots
+  size_t slot_elems;
+  const float* peer_data[8];
+  uint32_t* peer_flags[8];
+  const uint32_t* local_flags;
+  uint32_t* seq;
   unsigned long long* trace;   // optional [6 L + 3] phase time stamps of block 0 (ns)
   uint32_t* dev_err;
 };

@@ -228,7 +228,7 @@ struct mtj_handle {
     ce_sum = c.take<float>(R * 2);
     ce_hit = c.take<uint8_t>(R);
     mega_layers = c.take<mtj::MegaLayer>(L);
-    mega_sync = c.take<uint32_t>(4 * L + 2);
+    mega_sync = c.take<uint32_t>(5 * L + 3);
     mega_trace = c.take<unsigned long long>(6 * L + 3);
     tokens = c.take<uint32_t>(max_batch);
     cur = c.take<int32_t>(4);
@@ -823,7 +823,7 @@ int32_t mtj_bind_arenas(mtj_handle* h, void* wdev, int64_t wbytes, void* sdev, i
       ml[l] = {lw.w_in, lw.b_ff, lw.w_out, lw.b_out, lw.ln_scale, lw.ln_offset, kv.kpool, kv.vpool};
     }
     MTJ_CUDA(cudaMemcpyAsync(h->mega_layers, ml.data(), sizeof(mtj::MegaLayer) * h->L, cudaMemcpyHostToDevice, s));
-    MTJ_CUDA(cudaMemsetAsync(h->mega_sync, 0, sizeof(uint32_t) * (4 * h->L + 2), s));
+    MTJ_CUDA(cudaMemsetAsync(h->mega_sync, 0, sizeof(uint32_t) * (5 * h->L + 3), s));
     MTJ_CUDA(cudaStreamSynchronize(s));   // `ml` goes out of scope
   }
   MTJ_CUDA(cudaStreamSynchronize(s));   // `tab` is about to go out of scope
@@ -1073,7 +1073,7 @@ int32_t mtj_decode_step(mtj_handle* h, const uint32_t* tokens_in, const float* t
   auto enqueue = [&](cudaStream_t st) -> int32_t {
     mtj::RowMap rows = {0, 1, 0, h->cur};
     mtj::RowMap erows = {0, 1, 0, nullptr};
-    const bool mega = h->use_mega && h->mp == 1 && B <= 4 && !h->profile && (h->d % 256) == 0;
+    const bool mega = h->use_mega && (h->mp == 1 || use_p2p(h, B)) && B <= 4 && !h->profile && (h->d % 256) == 0;
     int32_t r = mega ? MTJ_OK : run_embed(h, h->tokens, 1, B, erows, true, st);
     if (r) return r;
     if (mega) {
@@ -1089,6 +1089,17 @@ int32_t mtj_decode_step(mtj_handle* h, const uint32_t* tokens_in, const float* t
       ma.x = h->x; ma.q = h->q; ma.act2 = h->act2; ma.part_o = h->part_o; ma.part_ml = h->part_ml;
       ma.head_counters = h->counters; ma.logits = h->logits; ma.sync = h->mega_sync; ma.dev_err = h->dev_err;
       ma.trace = h->mega_trace_on ? h->mega_trace : nullptr;
+      ma.rank = h->rank; ma.world = h->mp; ma.vocab_start = h->rank * h->Vl;
+      if (h->mp > 1) {
+        ma.slot_base = reinterpret_cast<float*>(h->p2p_local);
+        ma.slot_elems = partial_slot_stride(h);
+        for (int r = 0; r < h->mp; ++r) {
+          ma.peer_data[r] = reinterpret_cast<const float*>(h->p2p_peer[r]);
+          ma.peer_flags[r] = reinterpret_cast<uint32_t*>(h->p2p_peer[r] + h->p2p_flag_off);
+        }
+        ma.local_flags = reinterpret_cast<const uint32_t*>(h->p2p_local + h->p2p_flag_off);
+        ma.seq = reinterpret_cast<uint32_t*>(h->p2p_local + h->p2p_flag_off + 256);
+      }
       MTJ_CUDA(mtj::launch_decode_mega(ma, st, nullptr));
       h->launches++;
     }
