@@ -263,7 +263,7 @@ def run_mtj(args):
     rt.profile_enable(False)
     # phase time stamps of the persistent decode kernel (when it is the path in use)
     phases = None
-    if world == 1 and B <= 4 and os.environ.get("MTJ_NO_MEGA") != "1":
+    if B <= 4 and os.environ.get("MTJ_NO_MEGA") != "1" and os.environ.get("MTJ_NO_P2P") != "1":
         rt.mega_trace(True)
         for _ in range(3):
             rt.decode_step(None, tok_out, None, greedy=True)
