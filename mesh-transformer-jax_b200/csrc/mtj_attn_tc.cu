@@ -133,7 +133,8 @@ __global__ void __launch_bounds__(kThreadsTc) prefill_attn_tc_kernel(const __gri
   fence_after();
   const uint32_t tmem = tmem_slot;
 
-  const int tile = blockIdx.x, head = blockIdx.y, bi = blockIdx.z;
+  // causal: later query tiles walk more key blocks, so they are started first
+  const int tile = gridDim.x - 1 - blockIdx.x, head = blockIdx.y, bi = blockIdx.z;
   const int b = a.rows.b0 + bi;
   const int pos0 = a.rows.pos0_host;
   const int Tc = a.rows.Tc;

@@ -114,8 +114,10 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
   pdl_wait();                      // the activations come from the predecessor kernel
   pdl_launch_dependents();
 
-  const int n0 = blockIdx.x * kBM;           // first weight row of the tile
-  const int m0 = blockIdx.y * BN;            // first token row of the tile
+  // Token tiles vary fastest: the blocks that run together share one weight tile (read from HBM once,
+  // then served by L2) and walk the activations, which stay L2-resident.
+  const int n0 = blockIdx.y * kBM;           // first weight row of the tile
+  const int m0 = blockIdx.x * BN;            // first token row of the tile
   // split-K: block z covers k-blocks [kb0, kb0 + nk) and leaves a partial sum
   const int nk_total = a.K / kBK;
   const int per_z = (nk_total + gridDim.z - 1) / gridDim.z;
@@ -298,7 +300,7 @@ cudaError_t launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const GemmTc
     configured = true;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((a.N + kBM - 1) / kBM, (a.M + BN - 1) / BN, a.partial ? a.ksplit : 1);
+  cfg.gridDim = dim3((a.M + BN - 1) / BN, (a.N + kBM - 1) / kBM, a.partial ? a.ksplit : 1);
   cfg.blockDim = dim3(kTcThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = s;
