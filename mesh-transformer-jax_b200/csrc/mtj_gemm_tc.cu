@@ -244,6 +244,243 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
   if (threadIdx.x == 0 && failed && a.dev_err) atomicOr(a.dev_err, kDevErrTimeout);
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Persistent variant for many token rows (prefill / eval): one block per SM walks the tile list, a
+// tile is 128 weight rows x 256 token rows (UMMA 128 x 256 x 16), and the accumulator is double
+// buffered in tensor memory (2 x 256 columns) so that the epilogue of tile i runs while the tensor
+// core works on tile i + 1.  Warp 0 = TMA producer, warp 1 = MMA issuer, warps 2-9 = epilogue
+// (lane quadrant = warp % 4, column half = (warp - 2) / 4).  Token tiles vary fastest in the tile
+// list, so the blocks that run together share weight tiles through L2.
+constexpr int kPBN = 256;
+constexpr int kPStages = 4;
+constexpr int kPEpiWarps = 8;
+constexpr int kPThreads = 64 + 32 * kPEpiWarps;
+
+__device__ __forceinline__ void mbar_arrive_cta(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// tanh-form GELU written as x * sigmoid(2u), u = sqrt(2/pi) (x + 0.044715 x^3)
+__device__ __forceinline__ float gelu_tanh_fast(float x) {
+  const float u2 = 1.5957691216057308f * x * fmaf(0.044715f * x, x, 1.0f);
+  return __fdividef(x, 1.0f + __expf(-u2));
+}
+
+template <int EPI>
+__global__ void __launch_bounds__(kPThreads, 1) gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap map_w,
+                                                                       const __grid_constant__ CUtensorMap map_x,
+                                                                       const GemmTcArgs a) {
+  constexpr uint32_t kABytes = kBM * kBK * 2, kBBytes = kPBN * kBK * 2, kStageBytes = kABytes + kBBytes;
+  constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kPBN >> 3) << 17) |
+                              (static_cast<uint32_t>(kBM >> 4) << 24);
+  extern __shared__ unsigned char tc_smem_raw[];
+  const uint32_t smem_base = (smem_u32(tc_smem_raw) + 1023u) & ~1023u;
+  __shared__ __align__(8) uint64_t bars[2 * kPStages + 4];
+  __shared__ uint32_t tmem_slot;
+  __shared__ uint32_t failed;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t bar0 = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (kPStages + s); };
+  auto acc_full = [&](int b) { return bar0 + 8u * (2 * kPStages + b); };
+  auto acc_empty = [&](int b) { return bar0 + 8u * (2 * kPStages + 2 + b); };
+  volatile uint32_t* failed_v = &failed;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < 2 * kPStages + 2; ++s) mbar_init(bar0 + 8u * s, 1);
+    mbar_init(acc_empty(0), kPEpiWarps);
+    mbar_init(acc_empty(1), kPEpiWarps);
+    mbar_fence_init();
+    failed = 0;
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
+                 "r"(512u)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_acc = tmem_slot;
+
+  pdl_wait();
+  pdl_launch_dependents();
+
+  const int m_tiles = (a.M + kPBN - 1) / kPBN;
+  const int n_tiles = (a.N + kBM - 1) / kBM;
+  const int total = m_tiles * n_tiles;
+  const int nk = a.K / kBK;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool alive = true;
+      for (int t = blockIdx.x; t < total && alive; t += gridDim.x) {
+        const int n0 = (t / m_tiles) * kBM, m0 = (t % m_tiles) * kPBN;
+        for (int kb = 0; kb < nk; ++kb, ++it) {
+          const int s = it % kPStages;
+          if (it >= kPStages && !mbar_wait(empty_bar(s), ((it / kPStages) - 1) & 1)) {
+            atomicOr(&failed, 1u);
+            alive = false;
+            break;
+          }
+          mbar_expect_tx(full_bar(s), kStageBytes);
+          const uint32_t dst = smem_base + s * kStageBytes;
+          tma_load_2d(dst, &map_w, kb * kBK, n0, full_bar(s));
+          tma_load_2d(dst + kABytes, &map_x, kb * kBK, a.x_row0 + m0, full_bar(s));
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool alive = true;
+      int i = 0;
+      for (int t = blockIdx.x; t < total && alive; t += gridDim.x, ++i) {
+        const int b = i & 1;
+        if (i >= 2 && !mbar_wait(acc_empty(b), ((i >> 1) - 1) & 1)) {
+          atomicOr(&failed, 1u);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d = tmem_acc + static_cast<uint32_t>(b * kPBN);
+        for (int kb = 0; kb < nk; ++kb, ++it) {
+          const int s = it % kPStages;
+          if (!mbar_wait(full_bar(s), (it / kPStages) & 1)) {
+            atomicOr(&failed, 1u);
+            alive = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_base + s * kStageBytes;
+          const uint64_t adesc = smem_desc_sw128(sa), bdesc = smem_desc_sw128(sa + kABytes);
+#pragma unroll
+          for (int k4 = 0; k4 < kBK / 16; ++k4)
+            tc_mma_bf16(d, adesc + 2 * k4, bdesc + 2 * k4, kIdesc, (kb > 0 || k4 > 0) ? 1u : 0u);
+          tc_commit(empty_bar(s));
+        }
+        if (alive) tc_commit(acc_full(b));
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int Tc = a.rows.Tc;
+    int pos0 = 0;
+    if (EPI == kEpiInProj) pos0 = a.rows.pos0_dev ? *a.rows.pos0_dev : a.rows.pos0_host;
+    int i = 0;
+    for (int t = blockIdx.x; t < total; t += gridDim.x, ++i) {
+      const int b = i & 1;
+      if (*failed_v || !mbar_wait(acc_full(b), (i >> 1) & 1)) {
+        atomicOr(&failed, 1u);
+        break;
+      }
+      tc_fence_after();
+      const int n0 = (t / m_tiles) * kBM, m0 = (t % m_tiles) * kPBN + half * (kPBN / 2);
+      const int n = n0 + quad * 32 + lane;
+      const bool n_ok = n < a.N;
+      int region = 0, nn = 0, head = 0, j = 0;
+      float bias = 0.f;
+      if (EPI == kEpiInProj) {
+        if (n_ok) {
+          if (n < 3 * a.dl) {
+            region = n / a.dl;
+            nn = n - region * a.dl;
+            head = nn / a.d_head;
+            j = nn - head * a.d_head;
+          } else {
+            region = 3;
+            nn = n - 3 * a.dl;
+            bias = a.b_ff[nn];
+          }
+        }
+      } else if (n_ok) {
+        bias = a.bias[n];
+      }
+      // (sequence, position) of the chunk's rows, advanced incrementally (uniform over the warp)
+      int seq = 0, tin = 0, last_pg = -1, last_seq = -1, page = 0, padv = 0;
+      if (EPI == kEpiInProj) {
+        seq = a.rows.b0 + m0 / Tc;
+        tin = m0 % Tc;
+      }
+      const bool rotary = EPI == kEpiInProj && region < 2 && j < a.rot;
+      const uint32_t tbase = tmem_acc + (static_cast<uint32_t>(quad * 32) << 16) +
+                             static_cast<uint32_t>(b * kPBN + half * (kPBN / 2));
+#pragma unroll 1
+      for (int c0 = 0; c0 < kPBN / 2; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld32(tbase + c0, r);
+        if (c0 + 32 == kPBN / 2) {
+          // this warp has read its part of the accumulator: hand the buffer back to the MMA warp
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cta(acc_empty(b));
+        }
+#pragma unroll
+        for (int q = 0; q < 32; ++q) {
+          const int m = m0 + c0 + q;
+          const float v = __uint_as_float(r[q]);
+          if (EPI == kEpiInProj) {
+            const float partner = __shfl_xor_sync(0xffffffffu, v, 1);
+            const int pos = pos0 + tin;
+            if (m < a.M && n_ok) {
+              if (region < 3) {
+                float y = v;
+                if (rotary) {
+                  const float2 sc = a.sincos[static_cast<size_t>(pos) * (a.rot >> 1) + (j >> 1)];
+                  y = (j & 1) ? fmaf(v, sc.y, partner * sc.x) : fmaf(v, sc.y, -partner * sc.x);
+                }
+                if (region == 0) {
+                  if (a.q_bf16)
+                    a.q_bf16[static_cast<size_t>(m) * a.dl + nn] = __float2bfloat16_rn(y);
+                  else
+                    a.q_out[static_cast<size_t>(m) * a.dl + nn] = y;
+                } else {
+                  const int pg = pos / kPageTokens;
+                  if (pg != last_pg || seq != last_seq) {
+                    last_pg = pg;
+                    last_seq = seq;
+                    page = a.kv.page_table[static_cast<size_t>(seq) * a.kv.ring_pages + pg % a.kv.ring_pages];
+                    padv = a.kv.pad[seq];
+                  }
+                  if (pos >= padv) {
+                    __nv_bfloat16* pool = region == 1 ? a.kv.kpool : a.kv.vpool;
+                    pool[((static_cast<size_t>(page) * a.heads + head) * kPageTokens + (pos % kPageTokens)) *
+                             static_cast<size_t>(a.d_head) + j] = __float2bfloat16_rn(y);
+                  }
+                }
+              } else {
+                a.act_out[static_cast<size_t>(m) * (a.dl + a.ffl) + a.dl + nn] =
+                    __float2bfloat16_rn(gelu_tanh_fast(v + bias));
+              }
+            }
+            if (++tin == Tc) {
+              tin = 0;
+              ++seq;
+            }
+          } else if (m < a.M && n_ok) {
+            if (EPI == kEpiOut) {
+              float y = v + bias;
+              if (a.residual) y += a.residual[static_cast<size_t>(m) * a.N + n];
+              a.out[static_cast<size_t>(m) * a.N + n] = y;
+            } else {
+              a.out[static_cast<size_t>(m) * a.ld_out + n] = v + bias;
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(512u) : "memory");
+  }
+  if (threadIdx.x == 0 && failed && a.dev_err) atomicOr(a.dev_err, kDevErrTimeout);
+}
+
 // LayerNorm of fp32 rows into bf16 (the GEMM's activation operand), layers.py:17-36.
 __global__ void __launch_bounds__(256) ln_rows_kernel(const float* __restrict__ x, const float* __restrict__ scale,
                                                       const float* __restrict__ offset,
@@ -312,9 +549,40 @@ cudaError_t launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const GemmTc
   return cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, STAGES, EPI>, mw, mx, a);
 }
 
+template <int EPI>
+cudaError_t launch_tc_persist(const CUtensorMap& mw, const CUtensorMap& mx, const GemmTcArgs& a, cudaStream_t s) {
+  constexpr int smem = kPStages * (kBM * kBK * 2 + kPBN * kBK * 2) + 1024;
+  static int sms = 0;
+  if (!sms) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_persist_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         smem);
+    if (e != cudaSuccess) return e;
+    int dev = 0, n = 0;
+    if ((e = cudaGetDevice(&dev)) != cudaSuccess) return e;
+    if ((e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
+    sms = n;
+  }
+  const int total = ((a.M + kPBN - 1) / kPBN) * ((a.N + kBM - 1) / kBM);
+  gemm_tc_persist_kernel<EPI><<<std::min(total, sms), kPThreads, smem, s>>>(mw, mx, a);
+  return cudaGetLastError();
+}
+
 }  // namespace
 
 int gemm_tc_token_tile() { return 128; }
+int gemm_tc_wide_token_tile() { return kPBN; }
+
+cudaError_t launch_gemm_tc_wide(GemvEpilogue epi, const void* map_w, const void* map_x, const GemmTcArgs& a,
+                                cudaStream_t s) {
+  if (a.M <= 0 || a.N <= 0 || a.K <= 0 || a.K % kBK || a.partial) return cudaErrorInvalidValue;
+  const CUtensorMap& mw = *static_cast<const CUtensorMap*>(map_w);
+  const CUtensorMap& mx = *static_cast<const CUtensorMap*>(map_x);
+  switch (epi) {
+    case kEpiInProj: return launch_tc_persist<kEpiInProj>(mw, mx, a, s);
+    case kEpiOut: return launch_tc_persist<kEpiOut>(mw, mx, a, s);
+    default: return launch_tc_persist<kEpiLogits>(mw, mx, a, s);
+  }
+}
 
 cudaError_t make_tensor_map_bf16(void* map_out, const void* base, int64_t rows, int64_t K, int box_rows) {
   PFN_cuTensorMapEncodeTiled_v12000 fn = encode_fn();

@@ -207,6 +207,11 @@ cudaError_t launch_splitk_reduce(const float* partial, int ksplit, int M, int N,
 cudaError_t make_tensor_map_bf16(void* map_out_128B, const void* base, int64_t rows, int64_t K, int box_rows);
 cudaError_t launch_gemm_tc(GemvEpilogue epi, const void* map_w, const void* map_x, const GemmTcArgs& a,
                            cudaStream_t s, bool pdl);
+// Persistent 128 x 256 variant for many token rows; map_x must have been made with box_rows =
+// gemm_tc_wide_token_tile().  No split-K.
+int gemm_tc_wide_token_tile();
+cudaError_t launch_gemm_tc_wide(GemvEpilogue epi, const void* map_w, const void* map_x, const GemmTcArgs& a,
+                                cudaStream_t s);
 cudaError_t launch_ln_rows(const float* x, const float* scale, const float* offset, __nv_bfloat16* out, int rows,
                            int d, cudaStream_t s);
 

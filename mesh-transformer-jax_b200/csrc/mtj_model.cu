@@ -111,8 +111,10 @@ struct mtj_handle {
   __nv_bfloat16* xn_bf16 = nullptr;   // [max_rows, d] LayerNorm output
   __nv_bfloat16* act_bf16 = nullptr;  // [max_rows, dl + ffl] attention vector | gelu(ff)
   TensorMap map_xn, map_act, map_proj, map_q;
+  TensorMap map_xn_wide, map_act_wide;   // 256-row boxes for the persistent GEMM
   __nv_bfloat16* q_bf16 = nullptr;    // [max_rows, dl] rotated queries for the tensor-core attention
   bool attn_tc_ok = false;
+  bool tc_wide_ok = false;   // persistent 128 x 256 GEMM for long chunks
   float* tc_partial = nullptr;        // [kTcSplitMax, kTcSplitRows, d] split-K partial sums of small-M out-projections
   int eval_rows = 0;                // rows of logits materialised at a time by the loss path
   float* eval_logits = nullptr;     // [eval_rows, Vl]
@@ -435,6 +437,8 @@ int32_t run_layer(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, bool
   return MTJ_OK;
 }
 
+bool use_tc_wide(const mtj_handle* h, int M) { return h->tc_wide_ok && M > 192; }
+
 // The same layer for many token rows on the tensor cores: LayerNorm to bf16, in-proj GEMM
 // (RoPE / KV / GELU epilogue), causal attention, out-proj GEMM (+ bias + residual).
 int32_t run_layer_tc(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, const int32_t* key_limit,
@@ -459,7 +463,11 @@ int32_t run_layer_tc(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, c
   a.kv = h->kv(layer);
   a.dev_err = h->dev_err;
   h->prof_begin(MTJ_FAMILY_INPROJ, s);
-  MTJ_CUDA(mtj::launch_gemm_tc(mtj::kEpiInProj, &lw.map_in, &h->map_xn, a, s, false));
+  const bool wide = use_tc_wide(h, M) && !decode;
+  if (wide)
+    MTJ_CUDA(mtj::launch_gemm_tc_wide(mtj::kEpiInProj, &lw.map_in, &h->map_xn_wide, a, s));
+  else
+    MTJ_CUDA(mtj::launch_gemm_tc(mtj::kEpiInProj, &lw.map_in, &h->map_xn, a, s, false));
   h->prof_end(s);
 
   h->prof_begin(MTJ_FAMILY_ATTN, s);
@@ -533,6 +541,8 @@ int32_t run_layer_tc(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, c
     MTJ_CUDA(mtj::launch_splitk_reduce(h->tc_partial, ksplit, M, h->d, lw.b_out, res, dst, h->d,
                                        to_slot ? partial_slot_sel(h, M) : nullptr, partial_slot_stride(h), s));
     h->launches++;
+  } else if (wide) {
+    MTJ_CUDA(mtj::launch_gemm_tc_wide(mtj::kEpiOut, &lw.map_out, &h->map_act_wide, o, s));
   } else {
     MTJ_CUDA(mtj::launch_gemm_tc(mtj::kEpiOut, &lw.map_out, &h->map_act, o, s, false));
   }
@@ -563,7 +573,10 @@ int32_t run_logits_tc(mtj_handle* h, int M, int row0, float* out, cudaStream_t s
   a.ld_out = h->Vl;
   a.dev_err = h->dev_err;
   h->prof_begin(MTJ_FAMILY_LOGITS, s);
-  MTJ_CUDA(mtj::launch_gemm_tc(mtj::kEpiLogits, &h->map_proj, &h->map_xn, a, s, false));
+  if (use_tc_wide(h, M))
+    MTJ_CUDA(mtj::launch_gemm_tc_wide(mtj::kEpiLogits, &h->map_proj, &h->map_xn_wide, a, s));
+  else
+    MTJ_CUDA(mtj::launch_gemm_tc(mtj::kEpiLogits, &h->map_proj, &h->map_xn, a, s, false));
   h->prof_end(s);
   h->launches += 2;
   return MTJ_OK;
@@ -840,6 +853,10 @@ int32_t mtj_bind_arenas(mtj_handle* h, void* wdev, int64_t wbytes, void* sdev, i
     ok = ok && mtj::make_tensor_map_bf16(&h->map_proj, h->proj_w, h->Vl, h->d, 128) == cudaSuccess;
     ok = ok && mtj::make_tensor_map_bf16(&h->map_xn, h->xn_bf16, h->max_rows, h->d, bn) == cudaSuccess;
     ok = ok && mtj::make_tensor_map_bf16(&h->map_act, h->act_bf16, h->max_rows, h->dl + h->ffl, bn) == cudaSuccess;
+    const int bw = mtj::gemm_tc_wide_token_tile();
+    ok = ok && mtj::make_tensor_map_bf16(&h->map_xn_wide, h->xn_bf16, h->max_rows, h->d, bw) == cudaSuccess;
+    ok = ok && mtj::make_tensor_map_bf16(&h->map_act_wide, h->act_bf16, h->max_rows, h->dl + h->ffl, bw) == cudaSuccess;
+    h->tc_wide_ok = ok && !getenv("MTJ_NO_TC_WIDE");
     if (!ok) return fail(MTJ_ERR_CUDA, "cuTensorMapEncodeTiled failed");
     h->tc_ok = true;
     const char* no_atc = getenv("MTJ_NO_ATTN_TC");

@@ -132,8 +132,10 @@ int32_t mtj_k_gemm_tc(const void* w, const void* x, const float* bias, int32_t M
   if (!w || !x || !bias || !out) return mtj_set_error(MTJ_ERR_INVALID, "null argument");
   if (M <= 0 || N <= 0 || K <= 0 || K % 64) return mtj_set_error(MTJ_ERR_INVALID, "K must be a positive multiple of 64");
   struct alignas(64) Map { unsigned char b[128]; } mw, mx;
+  const bool wide = M > 192;     // same rule as the model: long chunks take the persistent 128 x 256 kernel
   if (mtj::make_tensor_map_bf16(&mw, w, N, K, 128) != cudaSuccess ||
-      mtj::make_tensor_map_bf16(&mx, x, M, K, mtj::gemm_tc_token_tile()) != cudaSuccess)
+      mtj::make_tensor_map_bf16(&mx, x, M, K, wide ? mtj::gemm_tc_wide_token_tile() : mtj::gemm_tc_token_tile()) !=
+          cudaSuccess)
     return mtj_set_error(MTJ_ERR_CUDA, "cuTensorMapEncodeTiled failed (pointers must be 16-byte aligned)");
   mtj::GemmTcArgs a = {};
   a.M = M;
@@ -142,7 +144,8 @@ int32_t mtj_k_gemm_tc(const void* w, const void* x, const float* bias, int32_t M
   a.bias = bias;
   a.out = out;
   a.ld_out = N;
-  cudaError_t e = mtj::launch_gemm_tc(mtj::kEpiLogits, &mw, &mx, a, static_cast<cudaStream_t>(s), false);
+  cudaError_t e = wide ? mtj::launch_gemm_tc_wide(mtj::kEpiLogits, &mw, &mx, a, static_cast<cudaStream_t>(s))
+                       : mtj::launch_gemm_tc(mtj::kEpiLogits, &mw, &mx, a, static_cast<cudaStream_t>(s), false);
   if (e != cudaSuccess) return mtj_set_error(MTJ_ERR_CUDA, cudaGetErrorString(e));
   return MTJ_OK;
 }
