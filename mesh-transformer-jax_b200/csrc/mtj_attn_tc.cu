@@ -12,7 +12,11 @@
 //     P            = exp2(S*c - m)              4 softmax warps, one row per thread
 //     O[128, 256] += P[128, 64] . V[64, 256]    4 MMAs (V is MN-major: no transpose)
 // Warp 0 feeds TMA, warp 1 issues the MMAs, warps 2-5 do the softmax and the
-// epilogue.  O is only rescaled when a row's running maximum grows by more
+// epilogue.  S is double buffered in tensor memory and issued two key blocks
+// ahead (K and V travel through separate two-slot rings: a K slot is free as
+// soon as its S product is done), so the tensor core computes S[j+2] and
+// P.V[j] while the softmax warps work on block j+1.  Key blocks that every row
+// of a warp sees in full skip the mask arithmetic.  O is only rescaled when a row's running maximum grows by more
 // than 2^8 (the stale maximum stays the reference, which is exact because the
 // final normalisation uses the same reference).  Masked keys are excluded,
 // which equals the reference's -1e10 whenever a row sees at least one key;
@@ -35,7 +39,7 @@ constexpr uint32_t kKBytes = kKB * kDH * 2;          // 32 KB
 constexpr uint32_t kStage = 2 * kKBytes;             // K + V of one key block
 constexpr uint32_t kPBytes = kQT * kKB * 2;          // 16 KB
 constexpr uint32_t kSmemTc = kQBytes + 2 * kStage + kPBytes + 1024;
-constexpr uint32_t kColS = 0, kColO = 64, kTmemCols = 512;
+constexpr uint32_t kColS = 0, kColO = 128, kTmemCols = 512;   // S0 | S1 | O (256 columns)
 
 __device__ __forceinline__ void tma2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
   asm volatile(
@@ -67,6 +71,11 @@ __device__ __forceinline__ uint64_t sdesc(uint32_t addr, uint32_t lbo, uint32_t 
   d |= static_cast<uint64_t>(1) << 46;
   d |= static_cast<uint64_t>(2) << 61;
   return d;
+}
+__device__ __forceinline__ float ex2_fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 __device__ __forceinline__ void tm_ld32(uint32_t taddr, uint32_t* r) {
   asm volatile(
@@ -101,24 +110,18 @@ __global__ void __launch_bounds__(kThreadsTc) prefill_attn_tc_kernel(const __gri
   const uint32_t base = (smem_u32(att_smem_raw) + 1023u) & ~1023u;
   unsigned char* base_ptr = att_smem_raw + (base - smem_u32(att_smem_raw));
   const uint32_t sQ = base, sKV = base + kQBytes, sP = base + kQBytes + 2 * kStage;
-  __shared__ __align__(8) uint64_t bars[8];
+  __shared__ __align__(8) uint64_t bars[13];
   __shared__ uint32_t tmem_slot;
   __shared__ uint32_t failed;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t bar0 = smem_u32(bars);
-  const uint32_t q_full = bar0, kv_full0 = bar0 + 8, kv_empty0 = bar0 + 24, s_full = bar0 + 40,
-                 p_full = bar0 + 48, o_done = bar0 + 56;
+  const uint32_t q_full = bar0, k_full0 = bar0 + 8, k_empty0 = bar0 + 24, v_full0 = bar0 + 40,
+                 v_empty0 = bar0 + 56, s_full0 = bar0 + 72, p_full = bar0 + 88, o_done = bar0 + 96;
 
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
-    mbar_init(kv_full0, 1);
-    mbar_init(kv_full0 + 8, 1);
-    mbar_init(kv_empty0, 1);
-    mbar_init(kv_empty0 + 8, 1);
-    mbar_init(s_full, 1);
+    for (int i = 0; i < 13; ++i) mbar_init(bar0 + 8u * i, 1);
     mbar_init(p_full, 128);
-    mbar_init(o_done, 1);
     mbar_fence_init();
     failed = 0;
   }
@@ -133,8 +136,9 @@ __global__ void __launch_bounds__(kThreadsTc) prefill_attn_tc_kernel(const __gri
   fence_after();
   const uint32_t tmem = tmem_slot;
 
-  // causal: later query tiles walk more key blocks, so they are started first
-  const int tile = gridDim.x - 1 - blockIdx.x, head = blockIdx.y, bi = blockIdx.z;
+  // causal: later query tiles walk more key blocks; the block order is longest tile first, heads
+  // within a tile, so the tail of the grid is made of the short tiles
+  const int tile = gridDim.y - 1 - blockIdx.y, head = blockIdx.x, bi = blockIdx.z;
   const int b = a.rows.b0 + bi;
   const int pos0 = a.rows.pos0_host;
   const int Tc = a.rows.Tc;
@@ -152,22 +156,35 @@ __global__ void __launch_bounds__(kThreadsTc) prefill_attn_tc_kernel(const __gri
 #pragma unroll
       for (int kb = 0; kb < 4; ++kb) tma2d(sQ + kb * (kQT * 128), &map_q, head * kDH + kb * 64, row0, q_full);
       const int32_t* table = a.kv.page_table + static_cast<size_t>(b) * a.kv.ring_pages;
-      for (int j = 0; j < nb; ++j) {
+      auto slab_row = [&](int j) { return (table[(first_blk + j) % a.kv.ring_pages] * a.heads + head) * kKB; };
+      auto load_k = [&](int j) {
         const int st = j & 1;
-        if (j >= 2 && !mbar_wait(kv_empty0 + 8 * st, ((j >> 1) - 1) & 1)) {
-          atomicOr(&failed, 1u);
-          break;
-        }
-        const int page = table[(first_blk + j) % a.kv.ring_pages];
-        const int row = (page * a.heads + head) * kKB;
-        const uint32_t dk = sKV + st * kStage, dv = dk + kKBytes;
-        mbar_expect_tx(kv_full0 + 8 * st, kStage);
+        if (j >= 2 && !mbar_wait(k_empty0 + 8 * st, ((j >> 1) - 1) & 1)) return false;
+        const int row = slab_row(j);
+        const uint32_t dk = sKV + st * kStage;
+        mbar_expect_tx(k_full0 + 8 * st, kKBytes);
 #pragma unroll
-        for (int kb = 0; kb < 4; ++kb) {
-          tma2d(dk + kb * (kKB * 128), &map_k, kb * 64, row, kv_full0 + 8 * st);
-          tma2d(dv + kb * (kKB * 128), &map_v, kb * 64, row, kv_full0 + 8 * st);
-        }
+        for (int kb = 0; kb < 4; ++kb) tma2d(dk + kb * (kKB * 128), &map_k, kb * 64, row, k_full0 + 8 * st);
+        return true;
+      };
+      auto load_v = [&](int j) {
+        const int st = j & 1;
+        if (j >= 2 && !mbar_wait(v_empty0 + 8 * st, ((j >> 1) - 1) & 1)) return false;
+        const int row = slab_row(j);
+        const uint32_t dv = sKV + st * kStage + kKBytes;
+        mbar_expect_tx(v_full0 + 8 * st, kKBytes);
+#pragma unroll
+        for (int kb = 0; kb < 4; ++kb) tma2d(dv + kb * (kKB * 128), &map_v, kb * 64, row, v_full0 + 8 * st);
+        return true;
+      };
+      // the waits follow the tensor core's order: S0 S1 | PV0 S2 | PV1 S3 | ...
+      bool okp = load_k(0);
+      if (okp && nb > 1) okp = load_k(1);
+      for (int j = 0; okp && j < nb; ++j) {
+        okp = load_v(j);
+        if (okp && j + 2 < nb) okp = load_k(j + 2);
       }
+      if (!okp) atomicOr(&failed, 1u);
     }
   } else if (warp == 1) {
     if (lane == 0 && nb > 0) {
@@ -176,29 +193,32 @@ __global__ void __launch_bounds__(kThreadsTc) prefill_attn_tc_kernel(const __gri
       constexpr uint32_t kIdO = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((kDH >> 3) << 17) | ((kQT >> 4) << 24);
       auto issue_s = [&](int j) {
         const uint32_t dk = sKV + (j & 1) * kStage;
+        const uint32_t ds = tmem + kColS + (j & 1) * kKB;
 #pragma unroll
         for (int kb = 0; kb < 4; ++kb) {
           const uint64_t ad = sdesc(sQ + kb * (kQT * 128), 16, 1024), bd = sdesc(dk + kb * (kKB * 128), 16, 1024);
 #pragma unroll
-          for (int k4 = 0; k4 < 4; ++k4) mma_bf16(tmem + kColS, ad + 2 * k4, bd + 2 * k4, kIdS, (kb | k4) ? 1u : 0u);
+          for (int k4 = 0; k4 < 4; ++k4) mma_bf16(ds, ad + 2 * k4, bd + 2 * k4, kIdS, (kb | k4) ? 1u : 0u);
         }
-        commit(s_full);
+        commit(s_full0 + 8 * (j & 1));
+        commit(k_empty0 + 8 * (j & 1));                        // the K slot is free once S_j is done
       };
-      bool ok = mbar_wait(q_full, 0) && mbar_wait(kv_full0, 0);
+      bool ok = mbar_wait(q_full, 0) && mbar_wait(k_full0, 0);
       if (ok) {
         fence_after();
         issue_s(0);
       }
+      if (ok && nb > 1) {
+        ok = mbar_wait(k_full0 + 8, 0);
+        if (ok) {
+          fence_after();
+          issue_s(1);
+        }
+      }
       for (int j = 0; ok && j < nb; ++j) {
-        ok = mbar_wait(p_full, j & 1);                         // P_j written, S_j consumed
+        ok = mbar_wait(p_full, j & 1) && mbar_wait(v_full0 + 8 * (j & 1), (j >> 1) & 1);   // P_j written, S_j consumed
         if (!ok) break;
         fence_after();
-        if (j + 1 < nb) {
-          ok = mbar_wait(kv_full0 + 8 * ((j + 1) & 1), ((j + 1) >> 1) & 1);
-          if (!ok) break;
-          fence_after();
-          issue_s(j + 1);
-        }
         // O += P . V : V tile is [64 keys][256 dh] -> MN-major B operand, 64-column blocks 8 KB apart
         const uint32_t dv = sKV + (j & 1) * kStage + kKBytes;
 #pragma unroll
@@ -207,8 +227,14 @@ __global__ void __launch_bounds__(kThreadsTc) prefill_attn_tc_kernel(const __gri
           const uint64_t bd = sdesc(dv + k4 * 2048, kKB * 128, 1024);
           mma_bf16(tmem + kColO, ad, bd, kIdO, (j | k4) ? 1u : 0u);
         }
-        commit(kv_empty0 + 8 * (j & 1));
+        commit(v_empty0 + 8 * (j & 1));
         commit(o_done);
+        if (j + 2 < nb) {
+          ok = mbar_wait(k_full0 + 8 * (j & 1), ((j + 2) >> 1) & 1);
+          if (!ok) break;
+          fence_after();
+          issue_s(j + 2);                                      // into the S buffer that P_j was made from
+        }
       }
       if (!ok) atomicOr(&failed, 1u);
     }
@@ -220,37 +246,49 @@ __global__ void __launch_bounds__(kThreadsTc) prefill_attn_tc_kernel(const __gri
     const int qpos = pos0 + tile * kQT + r;
     const float c2 = 0.0625f * 1.4426950408889634f;            // 1/sqrt(256) * log2(e)
     float m_ref = -INFINITY, l = 0.f;
+    const bool warp_rows_ok = quad * 32 + 31 < q_rows;
+    const int warp_qpos0 = pos0 + tile * kQT + quad * 32;       // smallest query position of this warp
     bool ok = nb > 0;
     for (int j = 0; ok && j < nb; ++j) {
-      ok = mbar_wait(s_full, j & 1);
+      ok = mbar_wait(s_full0 + 8 * (j & 1), (j >> 1) & 1);
       if (!ok) break;
       fence_after();
       uint32_t sr[64];
-      tm_ld32(tmem + lane_addr + kColS, sr);
-      tm_ld32(tmem + lane_addr + kColS + 32, sr + 32);
+      const uint32_t s_addr = tmem + lane_addr + kColS + (j & 1) * kKB;
+      tm_ld32(s_addr, sr);
+      tm_ld32(s_addr + 32, sr + 32);
       const int kbase = (first_blk + j) * kKB;
+      // every row of this warp sees the whole key block: no mask arithmetic
+      const bool full_blk = warp_rows_ok && kbase >= pad && kbase + kKB - 1 <= min(warp_qpos0, limit);
       float mx = -INFINITY;
+      if (full_blk) {
 #pragma unroll
-      for (int c = 0; c < 64; ++c) {
-        const int key = kbase + c;
-        const bool vis = row_ok && key >= pad && key <= qpos && key <= limit;
-        const float v = vis ? __uint_as_float(sr[c]) * c2 : -INFINITY;
-        sr[c] = __float_as_uint(v);
-        mx = fmaxf(mx, v);
+        for (int c = 0; c < 64; ++c) mx = fmaxf(mx, __uint_as_float(sr[c]));
+        mx *= c2;
+      } else {
+#pragma unroll
+        for (int c = 0; c < 64; ++c) {
+          const int key = kbase + c;
+          const bool vis = row_ok && key >= pad && key <= qpos && key <= limit;
+          const float v = vis ? __uint_as_float(sr[c]) : -INFINITY;
+          sr[c] = __float_as_uint(v);
+          mx = fmaxf(mx, v * c2);
+        }
       }
       float m_new = m_ref;
       if (mx > m_ref + 8.0f || (m_ref == -INFINITY && mx > -INFINITY)) m_new = mx;
       const float corr = (m_new == m_ref || m_ref == -INFINITY) ? 1.0f : exp2f(m_ref - m_new);
+      // p = 2^(s c - m); a masked score is -inf and gives 0; a row that has seen no key yet (m = -inf)
+      // takes a finite stand-in so that -inf - (-inf) does not appear
+      const float neg_m = m_new == -INFINITY ? 0.f : -m_new;
       float psum = 0.f;
       uint32_t pk[32];
 #pragma unroll
       for (int c = 0; c < 64; c += 2) {
-        const float v0 = __uint_as_float(sr[c]), v1 = __uint_as_float(sr[c + 1]);
-        const float p0 = v0 == -INFINITY ? 0.f : exp2f(v0 - m_new);
-        const float p1 = v1 == -INFINITY ? 0.f : exp2f(v1 - m_new);
-        // the row sum uses the values the tensor core will see
+        const float p0 = ex2_fast(fmaf(__uint_as_float(sr[c]), c2, neg_m));
+        const float p1 = ex2_fast(fmaf(__uint_as_float(sr[c + 1]), c2, neg_m));
+        psum += p0 + p1;
         const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
-        psum += __bfloat162float(pb.x) + __bfloat162float(pb.y);
         pk[c >> 1] = *reinterpret_cast<const uint32_t*>(&pb);
       }
       l = l * corr + psum;
@@ -333,7 +371,7 @@ cudaError_t launch_prefill_attn_tc(const void* map_q, const void* map_k, const v
     if (e != cudaSuccess) return e;
     configured = true;
   }
-  const dim3 grid((a.rows.Tc + kQT - 1) / kQT, a.heads, a.M / a.rows.Tc);
+  const dim3 grid(a.heads, (a.rows.Tc + kQT - 1) / kQT, a.M / a.rows.Tc);
   prefill_attn_tc_kernel<<<grid, kThreadsTc, kSmemTc, s>>>(*static_cast<const CUtensorMap*>(map_q),
                                                            *static_cast<const CUtensorMap*>(map_k),
                                                            *static_cast<const CUtensorMap*>(map_v), a);
