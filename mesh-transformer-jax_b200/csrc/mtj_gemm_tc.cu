@@ -398,13 +398,17 @@ __global__ void __launch_bounds__(kPThreads, 1) gemm_tc_persist_kernel(const __g
       } else if (n_ok) {
         bias = a.bias[n];
       }
-      // (sequence, position) of the chunk's rows, advanced incrementally (uniform over the warp)
-      int seq = 0, tin = 0, last_pg = -1, last_seq = -1, page = 0, padv = 0;
+      // (sequence, position) of the chunk's first row, advanced chunk by chunk (uniform over the warp)
+      int seq = 0, tin = 0;
       if (EPI == kEpiInProj) {
         seq = a.rows.b0 + m0 / Tc;
         tin = m0 % Tc;
       }
-      const bool rotary = EPI == kEpiInProj && region < 2 && j < a.rot;
+      const bool rotary = EPI == kEpiInProj && n_ok && region < 2 && j < a.rot;
+      const bool any_rot = __any_sync(0xffffffffu, rotary);
+      const float sgn = (j & 1) ? 1.f : -1.f;
+      const int half_rot = a.rot >> 1;
+      const size_t ld_act = static_cast<size_t>(a.dl + a.ffl);
       const uint32_t tbase = tmem_acc + (static_cast<uint32_t>(quad * 32) << 16) +
                              static_cast<uint32_t>(b * kPBN + half * (kPBN / 2));
 #pragma unroll 1
@@ -417,57 +421,112 @@ __global__ void __launch_bounds__(kPThreads, 1) gemm_tc_persist_kernel(const __g
           __syncwarp();
           if (lane == 0) mbar_arrive_cta(acc_empty(b));
         }
-#pragma unroll
-        for (int q = 0; q < 32; ++q) {
-          const int m = m0 + c0 + q;
-          const float v = __uint_as_float(r[q]);
-          if (EPI == kEpiInProj) {
-            const float partner = __shfl_xor_sync(0xffffffffu, v, 1);
+        const int mc = m0 + c0;                          // first token row of the chunk
+        const int valid = min(32, a.M - mc);             // rows of the chunk that exist
+        if (EPI == kEpiInProj) {
+          if (valid == 32 && tin + 32 <= Tc) {
+            // all 32 rows exist and belong to one sequence: positions pos .. pos + 31
             const int pos = pos0 + tin;
-            if (m < a.M && n_ok) {
-              if (region < 3) {
-                float y = v;
+            if (any_rot) {
+              const float2* sc = a.sincos + static_cast<size_t>(pos) * half_rot + (rotary ? (j >> 1) : 0);
+#pragma unroll
+              for (int q = 0; q < 32; ++q) {
+                const float v = __uint_as_float(r[q]);
+                const float partner = __shfl_xor_sync(0xffffffffu, v, 1);
                 if (rotary) {
-                  const float2 sc = a.sincos[static_cast<size_t>(pos) * (a.rot >> 1) + (j >> 1)];
-                  y = (j & 1) ? fmaf(v, sc.y, partner * sc.x) : fmaf(v, sc.y, -partner * sc.x);
+                  const float2 t = sc[q * half_rot];
+                  r[q] = __float_as_uint(fmaf(v, t.y, (sgn * partner) * t.x));
                 }
-                if (region == 0) {
-                  if (a.q_bf16)
-                    a.q_bf16[static_cast<size_t>(m) * a.dl + nn] = __float2bfloat16_rn(y);
-                  else
-                    a.q_out[static_cast<size_t>(m) * a.dl + nn] = y;
-                } else {
-                  const int pg = pos / kPageTokens;
-                  if (pg != last_pg || seq != last_seq) {
-                    last_pg = pg;
-                    last_seq = seq;
-                    page = a.kv.page_table[static_cast<size_t>(seq) * a.kv.ring_pages + pg % a.kv.ring_pages];
-                    padv = a.kv.pad[seq];
-                  }
-                  if (pos >= padv) {
-                    __nv_bfloat16* pool = region == 1 ? a.kv.kpool : a.kv.vpool;
-                    pool[((static_cast<size_t>(page) * a.heads + head) * kPageTokens + (pos % kPageTokens)) *
-                             static_cast<size_t>(a.d_head) + j] = __float2bfloat16_rn(y);
-                  }
-                }
-              } else {
-                a.act_out[static_cast<size_t>(m) * (a.dl + a.ffl) + a.dl + nn] =
-                    __float2bfloat16_rn(gelu_tanh_fast(v + bias));
               }
             }
-            if (++tin == Tc) {
+            if (!n_ok) {
+            } else if (region == 3) {
+              __nv_bfloat16* dst = a.act_out + static_cast<size_t>(mc) * ld_act + a.dl + nn;
+#pragma unroll
+              for (int q = 0; q < 32; ++q)
+                dst[q * ld_act] = __float2bfloat16_rn(gelu_tanh_fast(__uint_as_float(r[q]) + bias));
+            } else if (region == 0) {
+              if (a.q_bf16) {
+                __nv_bfloat16* dst = a.q_bf16 + static_cast<size_t>(mc) * a.dl + nn;
+#pragma unroll
+                for (int q = 0; q < 32; ++q) dst[static_cast<size_t>(q) * a.dl] = __float2bfloat16_rn(__uint_as_float(r[q]));
+              } else {
+                float* dst = a.q_out + static_cast<size_t>(mc) * a.dl + nn;
+#pragma unroll
+                for (int q = 0; q < 32; ++q) dst[static_cast<size_t>(q) * a.dl] = __uint_as_float(r[q]);
+              }
+            } else {
+              __nv_bfloat16* pool = (region == 1 ? a.kv.kpool : a.kv.vpool) + j;
+              const int32_t* trow = a.kv.page_table + static_cast<size_t>(seq) * a.kv.ring_pages;
+              const int padv = a.kv.pad[seq];
+              const size_t slab = static_cast<size_t>(kPageTokens) * a.d_head;
+              int pg = pos / kPageTokens, off = pos % kPageTokens;
+              __nv_bfloat16* dst = pool + (static_cast<size_t>(trow[pg % a.kv.ring_pages]) * a.heads + head) * slab;
+#pragma unroll
+              for (int q = 0; q < 32; ++q) {
+                if (off == kPageTokens) {
+                  off = 0;
+                  ++pg;
+                  dst = pool + (static_cast<size_t>(trow[pg % a.kv.ring_pages]) * a.heads + head) * slab;
+                }
+                if (pos + q >= padv) dst[off * a.d_head] = __float2bfloat16_rn(__uint_as_float(r[q]));
+                ++off;
+              }
+            }
+            tin += 32;
+            if (tin == Tc) {
               tin = 0;
               ++seq;
             }
-          } else if (m < a.M && n_ok) {
-            if (EPI == kEpiOut) {
-              float y = v + bias;
-              if (a.residual) y += a.residual[static_cast<size_t>(m) * a.N + n];
-              a.out[static_cast<size_t>(m) * a.N + n] = y;
-            } else {
-              a.out[static_cast<size_t>(m) * a.ld_out + n] = v + bias;
+          } else {
+            // ragged chunk (end of the rows, or a sequence boundary inside it): element by element
+#pragma unroll
+            for (int q = 0; q < 32; ++q) {
+              const int m = mc + q;
+              const float v = __uint_as_float(r[q]);
+              const float partner = __shfl_xor_sync(0xffffffffu, v, 1);
+              const int pos = pos0 + tin;
+              if (m < a.M && n_ok) {
+                if (region < 3) {
+                  float y = v;
+                  if (rotary) {
+                    const float2 t = a.sincos[static_cast<size_t>(pos) * half_rot + (j >> 1)];
+                    y = fmaf(v, t.y, (sgn * partner) * t.x);
+                  }
+                  if (region == 0) {
+                    if (a.q_bf16)
+                      a.q_bf16[static_cast<size_t>(m) * a.dl + nn] = __float2bfloat16_rn(y);
+                    else
+                      a.q_out[static_cast<size_t>(m) * a.dl + nn] = y;
+                  } else if (pos >= a.kv.pad[seq]) {
+                    __nv_bfloat16* pool = region == 1 ? a.kv.kpool : a.kv.vpool;
+                    const size_t o = kv_offset(a.kv.page_table + static_cast<size_t>(seq) * a.kv.ring_pages,
+                                               a.kv.ring_pages, a.heads, a.d_head, head, pos);
+                    pool[o + j] = __float2bfloat16_rn(y);
+                  }
+                } else {
+                  a.act_out[static_cast<size_t>(m) * ld_act + a.dl + nn] = __float2bfloat16_rn(gelu_tanh_fast(v + bias));
+                }
+              }
+              if (++tin == Tc) {
+                tin = 0;
+                ++seq;
+              }
             }
           }
+        } else if (n_ok && valid > 0) {
+          const size_t ldo = EPI == kEpiOut ? static_cast<size_t>(a.N) : static_cast<size_t>(a.ld_out);
+          float* dst = a.out + static_cast<size_t>(mc) * ldo + n;
+          if (EPI == kEpiOut && a.residual) {
+            // all residual loads first (the output may alias the residual, which pins the order otherwise)
+            const float* res = a.residual + static_cast<size_t>(mc) * ldo + n;
+#pragma unroll
+            for (int q = 0; q < 32; ++q)
+              if (q < valid) r[q] = __float_as_uint(__uint_as_float(r[q]) + res[q * ldo]);
+          }
+#pragma unroll
+          for (int q = 0; q < 32; ++q)
+            if (q < valid) dst[q * ldo] = __uint_as_float(r[q]) + bias;
         }
       }
     }
