@@ -191,6 +191,57 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
 #pragma unroll
           for (int i = 0; i < 32; ++i) r[i] = 0u;      // an empty K range contributes zeros
         }
+        if (EPI == kEpiInProj && a.rows.Tc == 1) {
+          // decode: row m is sequence b0 + m and every row sits at the same position, so the rotation
+          // factors and the page slot are per-thread constants
+          const int pos = a.rows.pos0_dev ? *a.rows.pos0_dev : a.rows.pos0_host;
+          const bool rotary = n_ok && region < 2 && j < a.rot;
+          const bool any_rot = __any_sync(0xffffffffu, rotary);
+          if (any_rot) {
+            const float2 t = rotary ? a.sincos[static_cast<size_t>(pos) * (a.rot >> 1) + (j >> 1)] : make_float2(0.f, 1.f);
+            const float sx = (j & 1) ? t.x : -t.x;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const float v = __uint_as_float(r[i]);
+              const float partner = __shfl_xor_sync(0xffffffffu, v, 1);
+              if (rotary) r[i] = __float_as_uint(fmaf(v, t.y, partner * sx));
+            }
+          }
+          const int valid = min(32, a.M - (m0 + c0));
+          if (!n_ok || valid <= 0) {
+          } else if (region == 3) {
+            __nv_bfloat16* dst = a.act_out + static_cast<size_t>(m0 + c0) * (a.dl + a.ffl) + a.dl + nn;
+            const size_t ld = static_cast<size_t>(a.dl + a.ffl);
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (i < valid) dst[i * ld] = __float2bfloat16_rn(gelu_tanh(__uint_as_float(r[i]) + bias));
+          } else if (region == 0) {
+            float* dst = a.q_out + static_cast<size_t>(m0 + c0) * a.dl + nn;
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (i < valid) dst[static_cast<size_t>(i) * a.dl] = __uint_as_float(r[i]);
+            if (a.q_bf16) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (i < valid)
+                  a.q_bf16[static_cast<size_t>(m0 + c0 + i) * a.dl + nn] = __float2bfloat16_rn(__uint_as_float(r[i]));
+            }
+          } else {
+            __nv_bfloat16* pool = (region == 1 ? a.kv.kpool : a.kv.vpool) +
+                                  (static_cast<size_t>(head) * kPageTokens + (pos % kPageTokens)) * a.d_head + j;
+            const size_t page_stride = static_cast<size_t>(a.heads) * kPageTokens * a.d_head;
+            const int slot = (pos / kPageTokens) % a.kv.ring_pages;
+            const int seq0 = a.rows.b0 + m0 + c0;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              if (i < valid && pos >= a.kv.pad[seq0 + i]) {
+                const int page = a.kv.page_table[static_cast<size_t>(seq0 + i) * a.kv.ring_pages + slot];
+                pool[page * page_stride] = __float2bfloat16_rn(__uint_as_float(r[i]));
+              }
+            }
+          }
+          continue;
+        }
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           const int m = m0 + c0 + i;
@@ -629,6 +680,7 @@ cudaError_t launch_tc_persist(const CUtensorMap& mw, const CUtensorMap& mx, cons
 }  // namespace
 
 int gemm_tc_token_tile() { return 128; }
+int gemm_tc_token_tile_for(int M) { return M <= 32 ? 32 : (M <= 64 ? 64 : 128); }
 int gemm_tc_wide_token_tile() { return kPBN; }
 
 cudaError_t launch_gemm_tc_wide(GemvEpilogue epi, const void* map_w, const void* map_x, const GemmTcArgs& a,
@@ -662,6 +714,23 @@ cudaError_t launch_gemm_tc(GemvEpilogue epi, const void* map_w, const void* map_
   if (a.M <= 0 || a.N <= 0 || a.K <= 0 || a.K % kBK) return cudaErrorInvalidValue;
   const CUtensorMap& mw = *static_cast<const CUtensorMap*>(map_w);
   const CUtensorMap& mx = *static_cast<const CUtensorMap*>(map_x);
+  // Few token rows (batched decode) stream the weights once: a narrower token tile leaves room for a
+  // deeper TMA ring, i.e. more weight bytes in flight per block.
+  const int bn = gemm_tc_token_tile_for(a.M);
+  if (bn == 32) {
+    switch (epi) {
+      case kEpiInProj: return launch_tc<32, 5, kEpiInProj>(mw, mx, a, s, pdl);
+      case kEpiOut: return launch_tc<32, 5, kEpiOut>(mw, mx, a, s, pdl);
+      default: return launch_tc<32, 5, kEpiLogits>(mw, mx, a, s, pdl);
+    }
+  }
+  if (bn == 64) {
+    switch (epi) {
+      case kEpiInProj: return launch_tc<64, 4, kEpiInProj>(mw, mx, a, s, pdl);
+      case kEpiOut: return launch_tc<64, 4, kEpiOut>(mw, mx, a, s, pdl);
+      default: return launch_tc<64, 4, kEpiLogits>(mw, mx, a, s, pdl);
+    }
+  }
   switch (epi) {
     case kEpiInProj: return launch_tc<128, 3, kEpiInProj>(mw, mx, a, s, pdl);
     case kEpiOut: return launch_tc<128, 3, kEpiOut>(mw, mx, a, s, pdl);

@@ -200,7 +200,9 @@ struct GemmTcArgs {
   int ksplit;
   uint32_t* dev_err;
 };
-int gemm_tc_token_tile();
+int gemm_tc_token_tile();                 // widest token tile of launch_gemm_tc (128)
+// Token tile launch_gemm_tc uses for M rows (32, 64 or 128): map_x must have been made with this box_rows.
+int gemm_tc_token_tile_for(int M);
 cudaError_t launch_splitk_reduce(const float* partial, int ksplit, int M, int N, const float* bias,
                                  const float* residual, float* out, int ld_out, const uint32_t* slot_sel,
                                  size_t slot_stride, cudaStream_t s);

@@ -110,7 +110,7 @@ struct mtj_handle {
   bool tc_ok = false;
   __nv_bfloat16* xn_bf16 = nullptr;   // [max_rows, d] LayerNorm output
   __nv_bfloat16* act_bf16 = nullptr;  // [max_rows, dl + ffl] attention vector | gelu(ff)
-  TensorMap map_xn, map_act, map_proj, map_q;
+  TensorMap map_xn[3], map_act[3], map_proj, map_q;   // activation views with 32 / 64 / 128-row boxes
   TensorMap map_xn_wide, map_act_wide;   // 256-row boxes for the persistent GEMM
   __nv_bfloat16* q_bf16 = nullptr;    // [max_rows, dl] rotated queries for the tensor-core attention
   bool attn_tc_ok = false;
@@ -437,6 +437,7 @@ int32_t run_layer(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, bool
   return MTJ_OK;
 }
 
+int tc_tile_index(int M) { return mtj::gemm_tc_token_tile_for(M) == 32 ? 0 : (mtj::gemm_tc_token_tile_for(M) == 64 ? 1 : 2); }
 bool use_tc_wide(const mtj_handle* h, int M) { return h->tc_wide_ok && M > 192; }
 
 // The same layer for many token rows on the tensor cores: LayerNorm to bf16, in-proj GEMM
@@ -467,7 +468,7 @@ int32_t run_layer_tc(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, c
   if (wide)
     MTJ_CUDA(mtj::launch_gemm_tc_wide(mtj::kEpiInProj, &lw.map_in, &h->map_xn_wide, a, s));
   else
-    MTJ_CUDA(mtj::launch_gemm_tc(mtj::kEpiInProj, &lw.map_in, &h->map_xn, a, s, false));
+    MTJ_CUDA(mtj::launch_gemm_tc(mtj::kEpiInProj, &lw.map_in, &h->map_xn[tc_tile_index(M)], a, s, false));
   h->prof_end(s);
 
   h->prof_begin(MTJ_FAMILY_ATTN, s);
@@ -537,14 +538,14 @@ int32_t run_layer_tc(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, c
     const float* res = o.residual;
     o.partial = h->tc_partial;
     o.ksplit = ksplit;
-    MTJ_CUDA(mtj::launch_gemm_tc(mtj::kEpiOut, &lw.map_out, &h->map_act, o, s, false));
+    MTJ_CUDA(mtj::launch_gemm_tc(mtj::kEpiOut, &lw.map_out, &h->map_act[tc_tile_index(M)], o, s, false));
     MTJ_CUDA(mtj::launch_splitk_reduce(h->tc_partial, ksplit, M, h->d, lw.b_out, res, dst, h->d,
                                        to_slot ? partial_slot_sel(h, M) : nullptr, partial_slot_stride(h), s));
     h->launches++;
   } else if (wide) {
     MTJ_CUDA(mtj::launch_gemm_tc_wide(mtj::kEpiOut, &lw.map_out, &h->map_act_wide, o, s));
   } else {
-    MTJ_CUDA(mtj::launch_gemm_tc(mtj::kEpiOut, &lw.map_out, &h->map_act, o, s, false));
+    MTJ_CUDA(mtj::launch_gemm_tc(mtj::kEpiOut, &lw.map_out, &h->map_act[tc_tile_index(M)], o, s, false));
   }
   h->prof_end(s);
   h->launches += 4;
@@ -576,7 +577,7 @@ int32_t run_logits_tc(mtj_handle* h, int M, int row0, float* out, cudaStream_t s
   if (use_tc_wide(h, M))
     MTJ_CUDA(mtj::launch_gemm_tc_wide(mtj::kEpiLogits, &h->map_proj, &h->map_xn_wide, a, s));
   else
-    MTJ_CUDA(mtj::launch_gemm_tc(mtj::kEpiLogits, &h->map_proj, &h->map_xn, a, s, false));
+    MTJ_CUDA(mtj::launch_gemm_tc(mtj::kEpiLogits, &h->map_proj, &h->map_xn[tc_tile_index(M)], a, s, false));
   h->prof_end(s);
   h->launches += 2;
   return MTJ_OK;
@@ -844,15 +845,17 @@ int32_t mtj_bind_arenas(mtj_handle* h, void* wdev, int64_t wbytes, void* sdev, i
   h->tc_ok = false;
   const char* no_tc = getenv("MTJ_NO_TC");
   if (h->d % 64 == 0 && (h->dl + h->ffl) % 64 == 0 && !(no_tc && no_tc[0] == '1')) {
-    const int bn = mtj::gemm_tc_token_tile();
     bool ok = true;
     for (auto& lw : h->layers) {
       ok = ok && mtj::make_tensor_map_bf16(&lw.map_in, lw.w_in, 3 * h->dl + h->ffl, h->d, 128) == cudaSuccess;
       ok = ok && mtj::make_tensor_map_bf16(&lw.map_out, lw.w_out, h->d, h->dl + h->ffl, 128) == cudaSuccess;
     }
     ok = ok && mtj::make_tensor_map_bf16(&h->map_proj, h->proj_w, h->Vl, h->d, 128) == cudaSuccess;
-    ok = ok && mtj::make_tensor_map_bf16(&h->map_xn, h->xn_bf16, h->max_rows, h->d, bn) == cudaSuccess;
-    ok = ok && mtj::make_tensor_map_bf16(&h->map_act, h->act_bf16, h->max_rows, h->dl + h->ffl, bn) == cudaSuccess;
+    for (int i = 0; i < 3; ++i) {
+      const int box = 32 << i;
+      ok = ok && mtj::make_tensor_map_bf16(&h->map_xn[i], h->xn_bf16, h->max_rows, h->d, box) == cudaSuccess;
+      ok = ok && mtj::make_tensor_map_bf16(&h->map_act[i], h->act_bf16, h->max_rows, h->dl + h->ffl, box) == cudaSuccess;
+    }
     const int bw = mtj::gemm_tc_wide_token_tile();
     ok = ok && mtj::make_tensor_map_bf16(&h->map_xn_wide, h->xn_bf16, h->max_rows, h->d, bw) == cudaSuccess;
     ok = ok && mtj::make_tensor_map_bf16(&h->map_act_wide, h->act_bf16, h->max_rows, h->dl + h->ffl, bw) == cudaSuccess;

@@ -134,7 +134,7 @@ int32_t mtj_k_gemm_tc(const void* w, const void* x, const float* bias, int32_t M
   struct alignas(64) Map { unsigned char b[128]; } mw, mx;
   const bool wide = M > 192;     // same rule as the model: long chunks take the persistent 128 x 256 kernel
   if (mtj::make_tensor_map_bf16(&mw, w, N, K, 128) != cudaSuccess ||
-      mtj::make_tensor_map_bf16(&mx, x, M, K, wide ? mtj::gemm_tc_wide_token_tile() : mtj::gemm_tc_token_tile()) !=
+      mtj::make_tensor_map_bf16(&mx, x, M, K, wide ? mtj::gemm_tc_wide_token_tile() : mtj::gemm_tc_token_tile_for(M)) !=
           cudaSuccess)
     return mtj_set_error(MTJ_ERR_CUDA, "cuTensorMapEncodeTiled failed (pointers must be 16-byte aligned)");
   mtj::GemmTcArgs a = {};
