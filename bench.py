@@ -197,8 +197,19 @@ def run_mtj(args):
     ctx_dev = torch.from_numpy(ctx.view(np.int32)).to(device)
     lens = [seq] * B
 
-    # ---- prefill (reported beside the headline) ----
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # ---- eval / loss over the same ids with next-token targets (reported beside the headline) ----
+    tgt_dev = torch.roll(ctx_dev, -1, dims=1).contiguous()
+    rt.eval_loss(ctx_dev, tgt_dev, None)
+    barrier()
+    e0.record()
+    ev_loss, _ = rt.eval_loss(ctx_dev, tgt_dev, None)
+    e1.record()
+    barrier()
+    eval_ms = e0.elapsed_time(e1)
+    eval_mean_loss = float(ev_loss[:, :-1].mean().item())
+
+    # ---- prefill (reported beside the headline) ----
     rt.prefill(ctx_dev, lens)
     barrier()
     e0.record()
@@ -361,6 +372,10 @@ def run_mtj(args):
                      if top == "mega" else
                      ("kernel with the largest share of the decode step; time from CUDA events around each "
                       "launch in a separate pass (no graph replay, so launch gaps are included)")},
+        "eval": {"tokens_per_s": B * seq / (eval_ms * 1e-3), "ms": eval_ms, "tokens": B * seq,
+                 "mean_loss": eval_mean_loss,
+                 "note": "full-sequence causal forward, vocab-sharded logits and cross-entropy; random-init weights, "
+                         "so the loss sits near ln(n_vocab)"},
         "mega_phases": phases,
         "kernel_families": fam,
         "step_hbm": {"algorithmic_bytes_per_step": step_bytes, "achieved_gbs": step_bytes / (ms_step * 1e-3) / 1e9,
