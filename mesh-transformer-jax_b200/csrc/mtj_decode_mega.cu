@@ -123,6 +123,49 @@ __device__ __forceinline__ void mega_all_reduce(const MegaArgs& a, uint32_t k, u
   }
 }
 
+// The layer's g_psum without flags, fences or a grid-wide hand-over.  Block b of every rank computes
+// the same 2 * kMW output rows.  Each partial sum (bias included) travels as one 8-byte packet
+// (value, k + 1) stored straight into every rank's receive buffer [slot k & 1][source rank]; an aligned
+// 8-byte store is indivisible, so a packet whose second word reads k + 1 carries this exchange's value.
+// The block then polls (bounded) the `world` packets of each of its rows and adds them in rank order to
+// x.  A receive row is written by the peers' block b and read by this rank's block b alone, and a peer
+// reaches exchange k + 2 only after it has seen this block's packets of exchange k + 1, which are sent
+// after slot k & 1 was read: two slots suffice.  Only blocks that own rows take part.
+__device__ __forceinline__ void st_packet(uint2* p, float v, uint32_t tag) {
+  asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(tag) : "memory");
+}
+__device__ __forceinline__ uint2 ld_packet(const uint2* p) {
+  uint2 v;
+  asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void mega_push_reduce(const MegaArgs& a, uint32_t k, int B, int d) {
+  const int n_first = blockIdx.x * 2 * kMW;
+  if (n_first >= d) return;
+  const int rows = min(2 * kMW, d - n_first);
+  if (threadIdx.x < rows * B) {
+    const int n = n_first + threadIdx.x % rows, bt = threadIdx.x / rows;
+    const uint2* src = a.peer_recv[a.rank] + static_cast<size_t>(k & 1u) * a.world * kMegaPushRows * d +
+                       static_cast<size_t>(bt) * d + n;
+    float* xp = a.x + static_cast<size_t>(bt) * d + n;
+    float acc = *xp;
+    for (int r = 0; r < a.world; ++r) {
+      const uint2* p = src + static_cast<size_t>(r) * kMegaPushRows * d;
+      uint2 v = ld_packet(p);
+      int spins = 0;
+      while (v.y != k + 1) {
+        if (++spins > kWaitLimit) {
+          if (a.dev_err) atomicOr(a.dev_err, kDevErrTimeout);
+          break;
+        }
+        v = ld_packet(p);
+      }
+      acc += __uint_as_float(v.x);
+    }
+    *xp = acc;
+  }
+}
+
 __device__ __forceinline__ float block_sum(float v, float* red) {
   v = warp_sum(v);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -376,6 +419,8 @@ __global__ void __launch_bounds__(kMT, BT == 1 ? 2 : 1) decode_mega_kernel(const
   const uint32_t seq0 = tp ? *a.seq : 0u;            // all-reduces completed before this step
   float* partial = tp ? a.slot_base : nullptr;       // this rank's exchange buffer (two slots)
   const uint32_t target = static_cast<uint32_t>(G);
+  // the push exchange needs one pass of row pairs over the grid's warps (block b owns rows [16 b, 16 b + 16))
+  const bool push = tp && a.peer_recv[0] != nullptr && (d >> 1) <= GW && B <= kMegaPushRows;
 
   const int cur = *a.cur;                            // absolute position of this step's token
 
@@ -672,7 +717,11 @@ __global__ void __launch_bounds__(kMT, BT == 1 ? 2 : 1) decode_mega_kernel(const
         const int r = lane & 1, bt = lane >> 1;
         const int n = 2 * rg + r;
         if (lane < 2 * BT && bt < B) {
-          if (tp) {
+          if (push) {
+            const float v = val + lw.b_out[n];
+            const size_t off = (static_cast<size_t>(((seq0 + 1 + l) & 1u) * a.world + a.rank) * kMegaPushRows + bt) * d + n;
+            for (int r = 0; r < a.world; ++r) st_packet(a.peer_recv[r] + off, v, seq0 + 2 + l);
+          } else if (tp) {
             partial[static_cast<size_t>((seq0 + 1 + l) & 1u) * a.slot_elems + static_cast<size_t>(bt) * d + n] =
                 val + lw.b_out[n];
           } else {
@@ -711,7 +760,10 @@ __global__ void __launch_bounds__(kMT, BT == 1 ? 2 : 1) decode_mega_kernel(const
     }
     __syncthreads();
     trace(a.trace, 6 * l + 5);                         // out-projection rows done
-    if (tp) mega_all_reduce(a, seq0 + 1 + l, c_red + 1 + l, target, B * d, true);
+    if (push)
+      mega_push_reduce(a, seq0 + 1 + l, B, d);
+    else if (tp)
+      mega_all_reduce(a, seq0 + 1 + l, c_red + 1 + l, target, B * d, true);
     phase_arrive(c_x + l + 1);
   }
 

@@ -134,6 +134,7 @@ struct MegaLayer {
   __nv_bfloat16* kpool;
   __nv_bfloat16* vpool;
 };
+constexpr int kMegaPushRows = 4;       // sequences per source rank in the push exchange
 struct MegaArgs {
   int L, d, dl, ffl, heads, dh, rot, V, B, window, ring_pages;
   int grid_splits, split_tokens, max_splits;   // attention: splits per (sequence, head), keys per split
@@ -165,6 +166,9 @@ struct MegaArgs {
   uint32_t* peer_flags[8];
   const uint32_t* local_flags;
   uint32_t* seq;
+  // push exchange of the layer all-reduce (null pointers: fall back to the slot protocol): every rank owns
+  // recv [2 slots][world sources][kMegaPushRows * d] packets of (value, exchange number + 1)
+  uint2* peer_recv[8];
   unsigned long long* trace;   // optional [6 L + 3] phase time stamps of block 0 (ns)
   uint32_t* dev_err;
 };

@@ -102,6 +102,7 @@ struct mtj_handle {
   char* p2p_local = nullptr;        // [2 slots][p2p_rows * d] floats | flags | seq | ticket
   char* p2p_peer[mtj::kP2pMaxWorld] = {};
   size_t p2p_flag_off = 0;
+  size_t p2p_recv_off = 0;          // push exchange of the persistent decode kernel
   float* uniforms = nullptr;        // [max_batch, V] sampler inputs of the current step
   float* top_p = nullptr;           // [max_batch]
   float* temp = nullptr;            // [max_batch]
@@ -114,7 +115,8 @@ struct mtj_handle {
   TensorMap map_xn_wide, map_act_wide;   // 256-row boxes for the persistent GEMM
   __nv_bfloat16* q_bf16 = nullptr;    // [max_rows, dl] rotated queries for the tensor-core attention
   bool attn_tc_ok = false;
-  bool tc_wide_ok = false;   // persistent 128 x 256 GEMM for long chunks
+  bool tc_wide_ok = false;
+  bool mega_push = true;     // per-block push exchange inside the persistent decode kernel (MTJ_NO_MEGA_PUSH=1: slot protocol)   // persistent 128 x 256 GEMM for long chunks
   float* tc_partial = nullptr;        // [kTcSplitMax, kTcSplitRows, d] split-K partial sums of small-M out-projections
   int eval_rows = 0;                // rows of logits materialised at a time by the loss path
   float* eval_logits = nullptr;     // [eval_rows, Vl]
@@ -748,6 +750,8 @@ int32_t mtj_create(const mtj_config* c, mtj_handle** out) {
   h->use_pdl = !(e && e[0] == '1');
   e = getenv("MTJ_NO_MEGA");
   h->use_mega = !(e && e[0] == '1');
+  e = getenv("MTJ_NO_MEGA_PUSH");
+  h->mega_push = !(e && e[0] == '1');
   e = getenv("MTJ_NO_FORK");
   h->fork_attn = !(e && e[0] == '1');
   e = getenv("MTJ_FORK_PDL");
@@ -1018,7 +1022,8 @@ int32_t mtj_p2p_export(mtj_handle* h, uint8_t* handle64) {
   h->p2p_rows = std::min(h->max_rows, std::max(h->max_batch, 1));
   const size_t data = 2 * static_cast<size_t>(h->p2p_rows) * h->d * sizeof(float);
   h->p2p_flag_off = (data + 255) / 256 * 256;
-  const size_t total = h->p2p_flag_off + 512;
+  h->p2p_recv_off = h->p2p_flag_off + 512;
+  const size_t total = h->p2p_recv_off + 2 * static_cast<size_t>(h->mp) * mtj::kMegaPushRows * h->d * sizeof(uint2);
   MTJ_CUDA(cudaMalloc(reinterpret_cast<void**>(&h->p2p_local), total));
   MTJ_CUDA(cudaMemset(h->p2p_local, 0, total));
   cudaIpcMemHandle_t ih;
@@ -1116,6 +1121,9 @@ int32_t mtj_decode_step(mtj_handle* h, const uint32_t* tokens_in, const float* t
         for (int r = 0; r < h->mp; ++r) {
           ma.peer_data[r] = reinterpret_cast<const float*>(h->p2p_peer[r]);
           ma.peer_flags[r] = reinterpret_cast<uint32_t*>(h->p2p_peer[r] + h->p2p_flag_off);
+          if (h->mega_push) {
+            ma.peer_recv[r] = reinterpret_cast<uint2*>(h->p2p_peer[r] + h->p2p_recv_off);
+          }
         }
         ma.local_flags = reinterpret_cast<const uint32_t*>(h->p2p_local + h->p2p_flag_off);
         ma.seq = reinterpret_cast<uint32_t*>(h->p2p_local + h->p2p_flag_off + 256);
