@@ -39,6 +39,14 @@ GPTJ_6B = {
 
 
 def workload_config(args, n_gpus):
+    if getattr(args, "workload", "headline") == "serving":
+        return {
+            "workload": "GPT-J-6B (L28 d4096 h16 dh256 rot64 ff16384 V50400) bf16 random-init; serving: prompts of "
+                        "1024 uniform-random ids in [0, 50257) left-padded into seq 2048, then nucleus sampling "
+                        "(top_p 0.9, temperature 1.0, seeded uniforms) one token per sequence per step",
+            "batch": args.batch, "window": "1024 + generated tokens", "parallelism": f"mp{n_gpus}",
+            "l2": "every step streams 11.7 GB of weights plus the KV cache (>> 126 MB L2), no flush needed",
+        }
     return {
         "workload": "GPT-J-6B (L28 d4096 h16 dh256 rot64 ff16384 V50400) bf16 random-init; prefill 1x2048 "
                     "uniform-random ids, then greedy decode at a full 2047-token sliding window",
@@ -193,9 +201,29 @@ def run_mtj(args):
         torch.cuda.synchronize()
 
     rng = np.random.Generator(np.random.PCG64(0))
-    ctx = rng.integers(0, cfg["n_vocab"], size=(B, seq)).astype(np.uint32)
+    serving = args.workload == "serving"
+    prompt = 1024 if serving else seq
+    ctx = rng.integers(0, 50257 if serving else cfg["n_vocab"], size=(B, seq)).astype(np.uint32)
+    ctx[:, :seq - prompt] = 0                      # left padding
     ctx_dev = torch.from_numpy(ctx.view(np.int32)).to(device)
-    lens = [seq] * B
+    lens = [prompt] * B
+    if serving:
+        gen = torch.Generator(device=device)
+        gen.manual_seed(1234)
+        tiny = float(np.finfo(np.float32).tiny)
+        u_pool = [torch.rand((B, cfg["n_vocab"]), generator=gen, device=device).clamp_(tiny, 1.0 - 2.0 ** -24)
+                  for _ in range(4)]
+        top_p_dev = torch.full((B,), 0.9, device=device)
+        temp_dev = torch.full((B,), 1.0, device=device)
+    n_calls = [0]
+
+    def decode(tok_in, tok_out):
+        if serving:
+            n_calls[0] += 1
+            rt.decode_step(tok_in, tok_out, None, greedy=False, top_p=top_p_dev, temp=temp_dev,
+                           uniforms=u_pool[n_calls[0] % len(u_pool)])
+        else:
+            decode(tok_in, tok_out)
 
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     # ---- eval / loss over the same ids with next-token targets (reported beside the headline) ----
@@ -230,13 +258,13 @@ def run_mtj(args):
     # ---- device-resident decode: the headline `value` ----
     tok_out = torch.empty((B,), dtype=torch.int32, device=device)
     for _ in range(args.warmup):
-        rt.decode_step(None, tok_out, None, greedy=True)
+        decode(None, tok_out)
     barrier()
     launches0 = rt.launch_count()
     t_wall0 = time.time()
     e0.record()
     for _ in range(args.steps):
-        rt.decode_step(None, tok_out, None, greedy=True)
+        decode(None, tok_out)
     e1.record()
     barrier()
     t_wall1 = time.time()
@@ -255,7 +283,7 @@ def run_mtj(args):
     e0.record()
     for _ in range(args.steps):
         tok_in.copy_(pin_in, non_blocking=True)
-        rt.decode_step(tok_in, tok_out, None, greedy=True)
+        decode(tok_in, tok_out)
         pin_out.copy_(tok_out, non_blocking=True)
         torch.cuda.current_stream().synchronize()
         pin_in.copy_(pin_out)
@@ -270,7 +298,7 @@ def run_mtj(args):
     rt.profile_enable(True)
     n_prof = min(args.steps, 32)
     for _ in range(n_prof):
-        rt.decode_step(None, tok_out, None, greedy=True)
+        decode(None, tok_out)
     prof = rt.profile_read()
     rt.profile_enable(False)
     # phase time stamps of the persistent decode kernel (when it is the path in use)
@@ -278,7 +306,7 @@ def run_mtj(args):
     if B <= 4 and os.environ.get("MTJ_NO_MEGA") != "1" and os.environ.get("MTJ_NO_P2P") != "1":
         rt.mega_trace(True)
         for _ in range(3):
-            rt.decode_step(None, tok_out, None, greedy=True)
+            decode(None, tok_out)
         torch.cuda.synchronize()
         tr = np.array(rt.mega_trace(False, read=True), dtype=np.float64)
         Lc = cfg["layers"]
@@ -310,12 +338,14 @@ def run_mtj(args):
 
     d, dl, ffl = cfg["d_model"], cfg["d_model"] // world, 4 * cfg["d_model"] // world
     Vl, L = cfg["n_vocab"] // world, cfg["layers"]
+    # keys a decode step attends to: the full window, or (serving) the prompt plus what has been generated so far
+    ctx_avg = (seq - 1) if not serving else min(seq - 1, prompt + n_calls[0] // 2)
     # algorithmic bytes per launch of each decode kernel family (weights dominate)
     fam_bytes = {
         "in_proj": ((3 * dl + (0 if prof["ff_in_proj"][1] else ffl)) * d * 2 + 2 * d * 4
                     + B * (d * 4 + dl * 4 + 2 * dl * 2)),
         "ff_in_proj": ffl * d * 2 + ffl * 4 + 2 * d * 4 + B * (d * 4 + ffl * 4),
-        "attention": B * (seq - 1) * 2 * dl * 2 + B * 2 * dl * 4,
+        "attention": B * ctx_avg * 2 * dl * 2 + B * 2 * dl * 4,
         "out_proj": d * (dl + ffl) * 2 + d * 4 + B * ((dl + ffl) * 4 + 2 * d * 4),
         "logits": Vl * d * 2 + Vl * 4 + 2 * d * 4 + B * (d * 4 + Vl * 4),
     }
@@ -337,14 +367,14 @@ def run_mtj(args):
     top = max(fam, key=lambda k: fam[k]["ms_per_step"]) if fam else None
     achieved = fam[top]["gbs"] if top else None
     pf = {k: v[0] for k, v in prefill_prof.items() if v[1]}
-    gemm_flops = 2.0 * (L * 12 * d * d // world) * B * (seq - 1)
-    attn_flops = L * 2.0 * (d // world) * (seq - 1) * seq * B
+    gemm_flops = 2.0 * (L * 12 * d * d // world) * B * (prompt - 1)
+    attn_flops = L * 2.0 * (d // world) * (prompt - 1) * prompt * B
     tc_peak = float(peaks.get("bf16_tflops_sustained", 1400.0))
     gemm_ms = pf.get("in_proj", 0.0) + pf.get("out_proj", 0.0)
 
     ms_step = ms_total / args.steps
     value = B * args.steps / (ms_total * 1e-3)
-    step_bytes = decode_bytes_per_step(cfg, B, seq - 1)
+    step_bytes = decode_bytes_per_step(cfg, B, ctx_avg)
     if phases is not None:
         # one persistent kernel does the whole step: it is the dominant kernel
         top = "mega"
@@ -380,7 +410,7 @@ def run_mtj(args):
         "kernel_families": fam,
         "step_hbm": {"algorithmic_bytes_per_step": step_bytes, "achieved_gbs": step_bytes / (ms_step * 1e-3) / 1e9,
                      "frac_of_peak": step_bytes / (ms_step * 1e-3) / 1e9 / hbm_peak / world},
-        "prefill": {"tokens_per_s": B * (seq - 1) / (prefill_ms * 1e-3), "ms": prefill_ms, "tokens": B * (seq - 1),
+        "prefill": {"tokens_per_s": B * (prompt - 1) / (prefill_ms * 1e-3), "ms": prefill_ms, "tokens": B * (prompt - 1),
                     "family_ms": pf,
                     "gemm_tflops": (gemm_flops / (gemm_ms * 1e-3) / 1e12) if gemm_ms else None,
                     "gemm_frac_of_sustained_peak": (gemm_flops / (gemm_ms * 1e-3) / 1e12 / tc_peak) if gemm_ms else None,
@@ -405,6 +435,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="mtj", choices=["mtj", "reference"])
     ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--workload", default="headline", choices=["headline", "serving"],
+                    help="headline: full-window greedy decode; serving: 1024-token prompts + nucleus sampling")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--layers", type=int, default=0,
                     help="profiling aid: run a reduced-depth model (same layer shapes) so that an ncu capture "

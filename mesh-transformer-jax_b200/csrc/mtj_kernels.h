@@ -226,8 +226,9 @@ struct SampleArgs {
   const float* uniforms;       // [rows, V] in [tiny, 1)
   const float* top_p;          // [rows]
   const float* temp;           // [rows]
-  int rows, V;                 // V <= 65535
-  void* scratch;               // sample_scratch_bytes(rows, V)
+  int rows, V;
+  void* scratch;               // sample_scratch_bytes(rows, V): receives the Gumbel noise of the uniforms
+  const float* gumbel;         // set by the launcher
   uint32_t* tokens;            // [rows]
   uint32_t* tokens_copy;       // optional second destination
   int32_t* cur_dev;            // incremented by one after the step (may be null)

@@ -669,13 +669,16 @@ int32_t setup_sequences(mtj_handle* h, const std::vector<int32_t>& pad,
 // After each chunk `after_chunk(b0, nseq, t0, Tc)` may read h->x / h->stats.
 template <typename F>
 int32_t forward_chunks(mtj_handle* h, const uint32_t* ids, int ids_ld, int batch, int T,
-                       const int32_t* key_limit, cudaStream_t s, F&& after_chunk) {
-  int Tc = std::min(T, h->max_rows);
+                       const int32_t* key_limit, cudaStream_t s, F&& after_chunk, int t_begin = 0) {
+  // positions [0, t_begin) are left padding in every sequence: their rows are never read, so they are not computed
+  const int Tv = T - t_begin;
+  if (Tv <= 0) return MTJ_OK;
+  int Tc = std::min(Tv, h->max_rows);
   int nseq = std::max(1, h->max_rows / Tc);
-  if (Tc < T) nseq = 1;
+  if (Tc < Tv) nseq = 1;
   for (int b0 = 0; b0 < batch; b0 += nseq) {
     const int ns = std::min(nseq, batch - b0);
-    for (int t0 = 0; t0 < T; t0 += Tc) {
+    for (int t0 = t_begin; t0 < T; t0 += Tc) {
       const int tc = std::min(Tc, T - t0);
       mtj::RowMap rows = {b0, tc, t0, nullptr};
       const int M = ns * tc;
@@ -1069,7 +1072,8 @@ int32_t mtj_prefill(mtj_handle* h, const uint32_t* ctx, const uint32_t* ctx_len,
   MTJ_CUDA(cudaMemcpy2DAsync(h->tokens, sizeof(uint32_t), ctx + (h->seq - 1), sizeof(uint32_t) * h->seq,
                              sizeof(uint32_t), batch, cudaMemcpyDeviceToDevice, s));
   rc = forward_chunks(h, ctx, h->seq, batch, h->W, nullptr, s,
-                      [](int, int, int, int) { return static_cast<int32_t>(MTJ_OK); });
+                      [](int, int, int, int) { return static_cast<int32_t>(MTJ_OK); },
+                      *std::min_element(pad.begin(), pad.end()));
   if (rc) return rc;
   h->batch = batch;
   h->prefilled = true;
@@ -1088,7 +1092,6 @@ int32_t mtj_decode_step(mtj_handle* h, const uint32_t* tokens_in, const float* t
   const int B = h->batch;
   if (!greedy) {
     if (!top_p || !temp || !uniforms) return fail(MTJ_ERR_INVALID, "sampling needs top_p, temp and uniforms");
-    if (h->V > 65535) return fail(MTJ_ERR_UNSUPPORTED, "the sampler handles n_vocab <= 65535");
     MTJ_CUDA(cudaMemcpyAsync(h->top_p, top_p, sizeof(float) * B, cudaMemcpyDeviceToDevice, s));
     MTJ_CUDA(cudaMemcpyAsync(h->temp, temp, sizeof(float) * B, cudaMemcpyDeviceToDevice, s));
     MTJ_CUDA(cudaMemcpyAsync(h->uniforms, uniforms, sizeof(float) * B * h->V, cudaMemcpyDeviceToDevice, s));
@@ -1323,7 +1326,6 @@ int32_t mtj_sample_top_p(const float* logits, const float* uniforms, const float
   if (!logits || !uniforms || !top_p || !temp || !scratch || !tokens_out)
     return fail(MTJ_ERR_INVALID, "null argument");
   if (rows <= 0 || vocab <= 0) return fail(MTJ_ERR_INVALID, "rows and vocab must be positive");
-  if (vocab > 65535) return fail(MTJ_ERR_UNSUPPORTED, "the sampler handles vocab <= 65535");
   if (scratch_bytes < mtj::sample_scratch_bytes(rows, vocab)) return fail(MTJ_ERR_INVALID, "scratch too small");
   mtj::SampleArgs sa = {};
   sa.logits = logits;

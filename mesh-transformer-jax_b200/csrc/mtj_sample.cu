@@ -1,20 +1,28 @@
 // Nucleus (top-p) + temperature sampling, one 1024-thread block per row
 // (reference: mesh_transformer/sampling.py:6-44).
 //
-//   1. descending stable sort of the row (value desc, higher index first among
-//      equal values, -0 == +0): LSD radix sort, 4-bit digits, on a key that is
-//      the bitwise complement of the order-preserving integer image of the
-//      logit, starting from positions laid out by descending index;
-//   2. softmax of the sorted values, cumulative sum, "remove where the
-//      cumulative probability of the PREVIOUS entry exceeds top_p";
-//   3. argmax over (logit - 1e10*removed) / temp + Gumbel(uniform), lowest
-//      index on ties (jax.random.categorical).
+// The reference sorts the row in descending order (higher index first among
+// equal values, -0 == +0), removes every entry for which the cumulative softmax
+// probability of the entries sorted BEFORE it exceeds top_p (the head always
+// stays), and takes argmax((logit - 1e10 * removed) / temp + Gumbel(uniform)),
+// lowest index on ties (jax.random.categorical).
 //
-// Every floating-point operation is individually rounded (no FMA contraction)
-// and sums follow a fixed association -- 1024 consecutive runs, a Hillis-Steele
-// scan over the 32 run totals of each warp, then over the 32 warp totals -- so
-// that the token ids can be reproduced bit for bit by a CPU restatement.
+// Here the softmax numerators e_i = exp(l_i - max) become fixed-point weights
+// q_i = floor(e_i * 2^40); sums of weights are exact integers, so they do not
+// depend on the order of addition and the test reads
+//     (weight sorted before entry j)  >  T = floor(top_p * total weight).
+// With exact sums the removed entries are a suffix of the sorted order: it is
+// enough to find the entry whose weight interval [before, before + q) contains
+// T.  That is a most-significant-digit radix SELECTION on the 32-bit sort key
+// (four passes of weighted 256-bin histograms, no sort); entries with a larger
+// key are removed, entries with the same key (equal logits) are ranked by
+// descending index in a separate pass that only runs when the cut falls inside
+// such a group.  exp and log are fixed polynomials of individually rounded
+// fp32 operations (no FMA contraction), so a CPU restatement reproduces the
+// token ids bit for bit.
 #include <math.h>
+
+#include <algorithm>
 
 #include "mtj_common.cuh"
 #include "mtj_kernels.h"
@@ -71,82 +79,203 @@ __device__ __forceinline__ uint32_t sort_key(float v) {
   return ~u;                                                // ascending key == descending value
 }
 
-// Hillis-Steele inclusive scan over the 32 lanes of a warp (x[i] += x[i-off]).
-__device__ __forceinline__ float warp_scan_hs(float x, int lane) {
+__device__ __forceinline__ float inv_sort_key(uint32_t key) {
+  const uint32_t u = ~key;
+  return __uint_as_float((u & 0x80000000u) ? (u & 0x7fffffffu) : ~u);
+}
+
+// q = floor(exp(l - vmax) * 2^40): a power-of-two scaling (exact) and a truncation
+__device__ __forceinline__ unsigned long long weight_of(float l, float vmax) {
+  return __float2ull_rz(__fmul_rn(exp_pinned(__fsub_rn(l, vmax)), 1099511627776.0f));
+}
+
+// h[dig] += q for the participating lanes of a warp; h belongs to this warp alone.  Lanes whose digit
+// no other lane shares add directly (distinct addresses); the others are summed group by group.
+__device__ __forceinline__ void warp_hist_add(unsigned long long* h, uint32_t dig, unsigned long long q, bool part,
+                                              int lane) {
+  const uint32_t same = __match_any_sync(0xffffffffu, dig);
+  const bool alone = __popc(same) == 1;
+  if (part && alone) h[dig] += q;
+  uint32_t rem = __ballot_sync(0xffffffffu, part && !alone);
+  while (rem) {
+    const int src = __ffs(rem) - 1;
+    const uint32_t dsel = __shfl_sync(0xffffffffu, dig, src);
+    const bool member = dig == dsel;
+    unsigned long long sum = member ? q : 0ull;
 #pragma unroll
-  for (int off = 1; off < 32; off <<= 1) {
-    const float y = __shfl_up_sync(0xffffffffu, x, off);
-    if (lane >= off) x = __fadd_rn(x, y);
+    for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+    if (lane == src) h[dsel] += sum;
+    rem &= ~__ballot_sync(0xffffffffu, member);
   }
-  return x;
+  __syncwarp();
 }
 
-// Prefix of this thread's run and the grand total, in the pinned association.
-__device__ __forceinline__ float block_prefix(float run_total, float* warp_tot, float* total_out) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const float inc = warp_scan_hs(run_total, lane);
-  float exc = __shfl_up_sync(0xffffffffu, inc, 1);
-  if (lane == 0) exc = 0.f;
-  if (lane == 31) warp_tot[warp] = inc;
-  __syncthreads();
-  if (warp == 0) {
-    const float ginc = warp_scan_hs(warp_tot[lane], lane);
-    float gexc = __shfl_up_sync(0xffffffffu, ginc, 1);
-    if (lane == 0) gexc = 0.f;
-    warp_tot[lane] = gexc;
-    if (lane == 31) warp_tot[32] = ginc;
-  }
-  __syncthreads();
-  const float prefix = __fadd_rn(warp_tot[warp], exc);
-  *total_out = warp_tot[32];
-  __syncthreads();
-  return prefix;
-}
-
-__global__ void __launch_bounds__(kSampThreads) sample_top_p_kernel(const SampleArgs a) {
-  __shared__ uint16_t cnt[16][kSampThreads];
-  __shared__ uint32_t wsum[33];
-  __shared__ float warp_tot[33];
-  __shared__ float last_cum[kSampThreads];
-  __shared__ float red_v[32];
-  __shared__ int red_i[32];
-
+// g = -log(-log(u)), the Gumbel noise of jax.random.categorical, for rows * V uniforms
+__global__ void __launch_bounds__(256) gumbel_kernel(const float* __restrict__ u, float* __restrict__ g, size_t n) {
   pdl_wait();
   pdl_launch_dependents();
+  for (size_t i = static_cast<size_t>(blockIdx.x) * 256 + threadIdx.x; i < n; i += static_cast<size_t>(gridDim.x) * 256) {
+    const float tl = log_pinned(u[i]);
+    g[i] = -log_pinned(-tl);
+  }
+}
+
+constexpr int kBins = 256;
+
+__global__ void __launch_bounds__(kSampThreads, 1) sample_top_p_kernel(const SampleArgs a) {
+  extern __shared__ __align__(16) unsigned char samp_smem[];
+  unsigned long long* hist = reinterpret_cast<unsigned long long*>(samp_smem);          // [32 warps][256]
+  unsigned long long* bins = hist + 32 * kBins;                                         // [256]
+  uint32_t* bitmap = reinterpret_cast<uint32_t*>(bins + kBins);                         // [ceil(V / 32)]
+  __shared__ float red_v[32];
+  __shared__ int red_i[32];
+  __shared__ uint32_t wsum[33];
+  __shared__ uint32_t sel_digit, sel_none;
+  __shared__ unsigned long long sel_before, sel_sum, sel_T;
 
   const int row = blockIdx.x, t = threadIdx.x, V = a.V;
   const int lane = t & 31, warp = t >> 5;
   const float* logits = a.logits + static_cast<size_t>(row) * V;
-  const float* unif = a.uniforms + static_cast<size_t>(row) * V;
-  uint32_t* base = reinterpret_cast<uint32_t*>(a.scratch) + static_cast<size_t>(row) * 5 * V;
-  uint32_t* key_a = base;
-  uint32_t* key_b = base + V;
-  uint32_t* idx_a = base + 2 * static_cast<size_t>(V);
-  uint32_t* idx_b = base + 3 * static_cast<size_t>(V);
-  float* val = reinterpret_cast<float*>(base + 4 * static_cast<size_t>(V));
-  const int per = (V + kSampThreads - 1) / kSampThreads;
-  const int j0 = min(V, t * per), j1 = min(V, j0 + per);
+  const float* gum = a.gumbel + static_cast<size_t>(row) * V;
 
-  // start from descending index order so that the stable sort puts the higher index first
-  for (int j = j0; j < j1; ++j) {
-    const int i = V - 1 - j;
-    key_a[j] = sort_key(logits[i]);
-    idx_a[j] = static_cast<uint32_t>(i);
-  }
+  // ---- row maximum (the head of the sorted order) ----
+  float vmax = -INFINITY;
+  for (int i = t; i < V; i += kSampThreads) vmax = fmaxf(vmax, logits[i]);
+  vmax = warp_max(vmax);
+  if (lane == 0) red_v[warp] = vmax;
+  __syncthreads();
+  vmax = red_v[0];
+#pragma unroll
+  for (int w = 1; w < 32; ++w) vmax = fmaxf(vmax, red_v[w]);
   __syncthreads();
 
-  uint32_t *kin = key_a, *kout = key_b, *iin = idx_a, *iout = idx_b;
-  for (int shift = 0; shift < 32; shift += 4) {
-#pragma unroll
-    for (int d = 0; d < 16; ++d) cnt[d][t] = 0;
-    for (int j = j0; j < j1; ++j) cnt[(kin[j] >> shift) & 15][t]++;
+  // ---- radix selection of the entry whose weight interval contains T ----
+  const float top_p = a.top_p[row], temp = a.temp[row];
+  uint32_t prefix = 0;                     // the selected key's digits so far
+  unsigned long long before = 0;           // weight of all keys below the selected prefix
+  unsigned long long T = 0, group_sum = 0;
+  bool cut = true;                         // false: nothing is removed
+  unsigned long long* my_hist = hist + warp * kBins;
+  for (int level = 0; level < 4 && cut; ++level) {
+    const int shift = 24 - 8 * level;
+    for (int i = t; i < 32 * kBins; i += kSampThreads) hist[i] = 0ull;
     __syncthreads();
-    // exclusive scan over the flattened [digit][thread] counts; thread t owns 16 consecutive entries
-    uint16_t* flat = &cnt[0][0] + t * 16;
-    uint32_t s = 0;
+    for (int i0 = 0; i0 < V; i0 += 4 * kSampThreads) {
+      float l[4];
 #pragma unroll
-    for (int k = 0; k < 16; ++k) s += flat[k];
-    uint32_t inc = s;
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * kSampThreads + t;
+        l[u] = i < V ? logits[i] : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (i0 + u * kSampThreads >= V) break;             // block-uniform
+        const int i = i0 + u * kSampThreads + t;
+        const uint32_t key = sort_key(l[u]);
+        const bool part = i < V && (level == 0 || (key >> (shift + 8)) == prefix);
+        const uint32_t dig = part ? ((key >> shift) & 255u) : 0xFFFFu;
+        const unsigned long long q = part ? weight_of(l[u], vmax) : 0ull;
+        warp_hist_add(my_hist, dig, q, part, lane);
+      }
+    }
+    __syncthreads();
+    if (t < kBins) {
+      unsigned long long sum = 0ull;
+#pragma unroll 8
+      for (int w = 0; w < 32; ++w) sum += hist[w * kBins + t];
+      bins[t] = sum;
+    }
+    __syncthreads();
+    if (warp == 0) {
+      unsigned long long b[8], local = 0ull;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        b[k] = bins[lane * 8 + k];
+        local += b[k];
+      }
+      unsigned long long inc = local;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const unsigned long long y = __shfl_up_sync(0xffffffffu, inc, off);
+        if (lane >= off) inc += y;
+      }
+      if (level == 0) {
+        // the grand total gives the threshold T = floor(top_p * total), evaluated exactly (same in every lane)
+        const unsigned long long total = __shfl_sync(0xffffffffu, inc, 31);
+        bool none = false;
+        const uint32_t pb = __float_as_uint(top_p);
+        const int ex = static_cast<int>((pb >> 23) & 0xFFu);
+        if (top_p != top_p || (ex == 255 && !(pb >> 31))) {
+          none = true;                                     // NaN or +inf: nothing exceeds it
+        } else if ((pb >> 31) || ex == 0) {
+          T = 0ull;                                        // negative, zero or subnormal (top_p * total < 1)
+        } else {
+          const unsigned long long m = (pb & 0x007FFFFFu) | 0x00800000u;   // top_p = m * 2^(ex - 150)
+          const unsigned long long lo = total * m, hi = __umul64hi(total, m);
+          const int sh = 150 - ex;                         // right shift of the 128-bit product
+          if (sh <= 0) {
+            none = true;                                   // top_p >= 2^23
+          } else if (sh >= 128) {
+            T = 0ull;
+          } else if (sh >= 64) {
+            T = hi >> (sh - 64);
+          } else {
+            if (hi >> sh) none = true;                     // does not fit 64 bits: far above the total
+            T = (lo >> sh) | (hi << (64 - sh));
+          }
+        }
+        if (!none && T >= total) none = true;              // no entry has that much weight before it
+        if (lane == 0) {
+          sel_T = T;
+          sel_none = none ? 1u : 0u;
+        }
+        if (none) cut = false;
+      }
+      if (cut) {
+        // the bin whose weight interval [run, run + b) contains T
+        unsigned long long run = before + inc - local;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          if (T >= run && T - run < b[k]) {
+            sel_digit = static_cast<uint32_t>(lane * 8 + k);
+            sel_before = run;
+            sel_sum = b[k];
+          }
+          run += b[k];
+        }
+      }
+    }
+    __syncthreads();
+    if (level == 0) {
+      T = sel_T;
+      cut = sel_none == 0u;
+    }
+    if (cut) {
+      prefix = (prefix << 8) | sel_digit;
+      before = sel_before;
+      group_sum = sel_sum;
+    }
+    __syncthreads();
+  }
+
+  // ---- the selected key k0: larger keys are removed; equal keys by rank (descending index) ----
+  const uint32_t k0 = prefix;
+  bool tie_cut = false;
+  unsigned long long r0 = 0ull;
+  if (cut) {
+    const unsigned long long qt = weight_of(inv_sort_key(k0), vmax);     // > 0: the interval contains T
+    const unsigned long long cnt = group_sum / qt;
+    r0 = (T - before) / qt;                                              // rank of the entry that holds T
+    tie_cut = r0 + 1 < cnt;
+  }
+  if (tie_cut) {
+    // thread t owns a contiguous index range, thread 0 the highest indices
+    const int per = (V + kSampThreads - 1) / kSampThreads;
+    const int hi_i = V - 1 - t * per, lo_i = max(-1, hi_i - per);
+    for (int i = t; i < (V + 31) / 32; i += kSampThreads) bitmap[i] = 0u;
+    uint32_t mine = 0;
+    for (int i = hi_i; i > lo_i && i >= 0; --i) mine += sort_key(logits[i]) == k0 ? 1u : 0u;
+    uint32_t inc = mine;
 #pragma unroll
     for (int off = 1; off < 32; off <<= 1) {
       const uint32_t y = __shfl_up_sync(0xffffffffu, inc, off);
@@ -155,7 +284,7 @@ __global__ void __launch_bounds__(kSampThreads) sample_top_p_kernel(const Sample
     if (lane == 31) wsum[warp] = inc;
     __syncthreads();
     if (warp == 0) {
-      uint32_t w = wsum[lane];
+      const uint32_t w = wsum[lane];
       uint32_t winc = w;
 #pragma unroll
       for (int off = 1; off < 32; off <<= 1) {
@@ -165,68 +294,26 @@ __global__ void __launch_bounds__(kSampThreads) sample_top_p_kernel(const Sample
       wsum[lane] = winc - w;
     }
     __syncthreads();
-    uint32_t run = wsum[warp] + inc - s;
-#pragma unroll
-    for (int k = 0; k < 16; ++k) {
-      const uint32_t c = flat[k];
-      flat[k] = static_cast<uint16_t>(run);
-      run += c;
+    unsigned long long rank = wsum[warp] + inc - mine;
+    for (int i = hi_i; i > lo_i && i >= 0; --i) {
+      if (sort_key(logits[i]) == k0) {
+        if (rank > r0) atomicOr(bitmap + (i >> 5), 1u << (i & 31));
+        ++rank;
+      }
     }
     __syncthreads();
-    for (int j = j0; j < j1; ++j) {
-      const uint32_t k = kin[j];
-      const uint32_t pos = cnt[(k >> shift) & 15][t]++;
-      kout[pos] = k;
-      iout[pos] = iin[j];
-    }
-    __syncthreads();
-    uint32_t* tk = kin; kin = kout; kout = tk;
-    uint32_t* ti = iin; iin = iout; iout = ti;
   }
-  // eight passes: the sorted order is back in (key_a, idx_a)
 
-  // softmax numerators of the sorted values and their total
-  const float vmax = logits[idx_a[0]];
-  float run_sum = 0.f;
-  for (int j = j0; j < j1; ++j) {
-    const float e = exp_pinned(__fsub_rn(logits[idx_a[j]], vmax));
-    val[j] = e;
-    run_sum = __fadd_rn(run_sum, e);
-  }
-  float denom;
-  block_prefix(run_sum, warp_tot, &denom);
-
-  // probabilities and their cumulative sum
-  run_sum = 0.f;
-  for (int j = j0; j < j1; ++j) {
-    const float p = __fdiv_rn(val[j], denom);
-    val[j] = p;
-    run_sum = __fadd_rn(run_sum, p);
-  }
-  float unused;
-  const float prefix = block_prefix(run_sum, warp_tot, &unused);
-  float c = prefix;
-  for (int j = j0; j < j1; ++j) {
-    c = __fadd_rn(c, val[j]);
-    val[j] = c;
-  }
-  last_cum[t] = c;
-  __syncthreads();
-
-  // Gumbel-max over the filtered, tempered logits
-  const float top_p = a.top_p[row], temp = a.temp[row];
+  // ---- Gumbel-max over the filtered, tempered logits ----
   float best = -INFINITY;
   int best_i = 0x7fffffff;
-  float prev = (t > 0 && j0 < j1) ? last_cum[t - 1] : 0.f;
-  for (int j = j0; j < j1; ++j) {
-    const bool removed = (j > 0) && (prev > top_p);        // shifted by one: the head always stays
-    prev = val[j];
-    const int i = static_cast<int>(idx_a[j]);
-    const float lm = __fsub_rn(logits[i], removed ? 1e10f : 0.0f);
-    const float tl = log_pinned(unif[i]);
-    const float g = -log_pinned(-tl);
-    const float score = __fadd_rn(__fdiv_rn(lm, temp), g);
-    if (score > best || (score == best && i < best_i)) {
+  for (int i = t; i < V; i += kSampThreads) {
+    const float lg = logits[i];
+    const uint32_t key = sort_key(lg);
+    const bool removed = cut && (key > k0 || (tie_cut && key == k0 && ((bitmap[i >> 5] >> (i & 31)) & 1u)));
+    const float lm = __fsub_rn(lg, removed ? 1e10f : 0.0f);
+    const float score = __fadd_rn(__fdiv_rn(lm, temp), gum[i]);
+    if (score > best) {                                    // ascending i: the first maximum stays
       best = score;
       best_i = i;
     }
@@ -265,24 +352,41 @@ __global__ void __launch_bounds__(kSampThreads) sample_top_p_kernel(const Sample
   }
 }
 
-}  // namespace
-
-int64_t sample_scratch_bytes(int rows, int vocab) {
-  return static_cast<int64_t>(rows) * 5 * vocab * 4;
+inline size_t sample_smem_bytes(int V) {
+  return sizeof(unsigned long long) * (32 * kBins + kBins) + sizeof(uint32_t) * static_cast<size_t>((V + 31) / 32);
 }
 
+}  // namespace
+
+// one float per logit: the Gumbel noise derived from the uniforms
+int64_t sample_scratch_bytes(int rows, int vocab) { return static_cast<int64_t>(rows) * vocab * 4; }
+
 cudaError_t launch_sample_top_p(const SampleArgs& a, cudaStream_t s, bool pdl) {
-  if (a.rows <= 0 || a.V <= 0 || a.V > 65535) return cudaErrorInvalidValue;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(a.rows);
-  cfg.blockDim = dim3(kSampThreads);
-  cfg.stream = s;
+  const size_t smem = sample_smem_bytes(a.V);
+  if (a.rows <= 0 || a.V <= 0 || smem > 220 * 1024 || !a.scratch) return cudaErrorInvalidValue;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(sample_top_p_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  const size_t n = static_cast<size_t>(a.rows) * a.V;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(std::min<size_t>((n + 255) / 256, 148 * 8)));
+  cfg.blockDim = dim3(256);
+  cfg.stream = s;
   cfg.attrs = attr;
   cfg.numAttrs = pdl ? 1 : 0;
-  return cudaLaunchKernelEx(&cfg, sample_top_p_kernel, a);
+  float* g = static_cast<float*>(a.scratch);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gumbel_kernel, a.uniforms, g, n);
+  if (e != cudaSuccess) return e;
+  SampleArgs b = a;
+  b.gumbel = g;
+  sample_top_p_kernel<<<a.rows, kSampThreads, smem, s>>>(b);
+  return cudaGetLastError();
 }
 
 }  // namespace mtj

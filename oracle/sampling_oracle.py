@@ -12,16 +12,21 @@ Two layers:
   floating-point operation pinned down, so that a GPU kernel can reproduce the
   sampled token ids bit for bit given identical logits and uniforms.  What is
   pinned is exactly what the reference leaves to XLA (jax 0.2.12, not part of
-  the reference tree): the exp / log polynomials, and the association order of
-  the softmax denominator and of the cumulative sum.
+  the reference tree): the exp / log polynomials, and the rounding of the
+  softmax denominator and of the cumulative sum.
 
   - exp and log are fixed polynomials evaluated with individually rounded fp32
     multiplies and adds (no fused multiply-add);
-  - sums run over the descending-sorted sequence cut into 1024 consecutive
-    runs of ceil(V/1024) elements: each run is added sequentially, the 1024 run
-    totals are combined by a Hillis-Steele scan over groups of 32 and then over
-    the 32 group totals, and an element's cumulative value is
-    (group prefix + run prefix) followed by the sequential adds inside its run.
+  - the softmax numerators e_i = exp(l_i - max) are turned into fixed-point
+    weights q_i = floor(e_i * 2^40); all sums of weights are exact integers
+    (they do not depend on the order of addition), and the reference's test
+    "cumulative probability of the entries sorted before this one > top_p" is
+    evaluated exactly:  sum_{k before j} q_k  >  floor(top_p * sum_k q_k).
+    Because the sums are exact, the entries removed are a suffix of the sorted
+    order, which a selection on the sort key finds without sorting.
+
+  ``blocked_cumsum`` (a fixed-association fp32 cumulative sum) is kept as a
+  checked helper; the pinned filter no longer uses it.
 
 The sort order is the reference's: ``jnp.sort(x)[::-1]`` / ``jnp.argsort(x)[::-1]``
 (stable ascending, reversed), i.e. descending by value and, among equal
@@ -162,6 +167,29 @@ def blocked_cumsum(v):
     return cum.reshape(-1)[:n], F32(ginc[-1])
 
 
+WEIGHT_BITS = 40
+
+
+def fixed_point_weights(e):
+    """q = floor(e * 2^40) as uint64 for fp32 e in [0, 1] (exact: a power-of-two scaling, then truncation)."""
+    return np.floor(np.asarray(e, F32).astype(np.float64) * 2.0 ** WEIGHT_BITS).astype(np.uint64)
+
+
+def weight_threshold(top_p, total):
+    """floor(top_p * total) for the exact value of the fp32 ``top_p`` and the integer ``total``;
+    negative top_p counts as 0; None means "nothing can exceed it" (top_p is NaN)."""
+    from fractions import Fraction
+    tp = float(F32(top_p))
+    if np.isnan(tp):
+        return None
+    if np.isinf(tp):
+        return None if tp > 0 else 0
+    if tp <= 0:
+        return 0
+    fr = Fraction(tp) * int(total)
+    return fr.numerator // fr.denominator
+
+
 def nucleaus_filter(logits, top_p=0.9):
     """sampling.py:10-38 (top_k=None) with pinned arithmetic; returns (filtered, removed)."""
     logits = np.asarray(logits, F32)
@@ -169,11 +197,13 @@ def nucleaus_filter(logits, top_p=0.9):
     removed = np.zeros(logits.shape, bool)
     for r in range(logits.shape[0]):
         s, order = _sorted_desc(logits[r])
-        e = exp_f32((s - s[0]).astype(F32))
-        _, denom = blocked_cumsum(e)
-        p = (e / denom).astype(F32)
-        cum, _ = blocked_cumsum(p)
-        remove_sorted = np.concatenate(([False], cum[:-1] > F32(top_p)))
+        q = fixed_point_weights(exp_f32((s - s[0]).astype(F32)))
+        before = np.cumsum(q, dtype=np.uint64) - q           # weight sorted before each entry (< 2^56: exact)
+        thr = weight_threshold(top_p, int(q.sum(dtype=np.uint64)))
+        if thr is None or thr >= 2 ** 63:
+            remove_sorted = np.zeros(q.shape, bool)
+        else:
+            remove_sorted = before > np.uint64(thr)          # the head (before == 0) always stays
         removed[r, order] = remove_sorted
         out[r] = (logits[r] - F32(1e10) * removed[r].astype(F32)).astype(F32)
     return out, removed
