@@ -101,10 +101,14 @@ __device__ __forceinline__ void warp_hist_add(unsigned long long* h, uint32_t di
     const int src = __ffs(rem) - 1;
     const uint32_t dsel = __shfl_sync(0xffffffffu, dig, src);
     const bool member = dig == dsel;
-    unsigned long long sum = member ? q : 0ull;
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
-    if (lane == src) h[dsel] += sum;
+    // q < 2^41: three 14-bit limbs, whose sums over 32 lanes fit 32 bits, one warp reduction each
+    const unsigned long long qm = member ? q : 0ull;
+    const uint32_t s0 = __reduce_add_sync(0xffffffffu, static_cast<uint32_t>(qm) & 0x3FFFu);
+    const uint32_t s1 = __reduce_add_sync(0xffffffffu, static_cast<uint32_t>(qm >> 14) & 0x3FFFu);
+    const uint32_t s2 = __reduce_add_sync(0xffffffffu, static_cast<uint32_t>(qm >> 28));
+    if (lane == src)
+      h[dsel] += static_cast<unsigned long long>(s0) + (static_cast<unsigned long long>(s1) << 14) +
+                 (static_cast<unsigned long long>(s2) << 28);
     rem &= ~__ballot_sync(0xffffffffu, member);
   }
   __syncwarp();
