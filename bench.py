@@ -38,13 +38,35 @@ GPTJ_6B = {
 }
 
 
+GPTJ_22B = dict(GPTJ_6B, layers=48, d_model=6144, n_heads=24)   # the ~22B scale-up (d_head 256, d_ff 24576)
+
+
+def model_config(args):
+    return GPTJ_22B if getattr(args, "model", "6b") == "22b" else GPTJ_6B
+
+
 def workload_config(args, n_gpus):
+    cfg = workload_config_6b(args, n_gpus)
+    if getattr(args, "model", "6b") == "22b":
+        cfg["workload"] = cfg["workload"].replace("GPT-J-6B (L28 d4096 h16 dh256 rot64 ff16384 V50400)",
+                                                  "GPT-J-style 22B (L48 d6144 h24 dh256 rot64 ff24576 V50400)")
+        cfg["l2"] = cfg["l2"].replace("11.7 GB", "44.1 GB")
+        if getattr(args, "workload", "headline") == "serving":
+            cfg["workload"] = cfg["workload"].replace("prompts of 1024", f"prompts of {serving_prompt(args)}")
+    return cfg
+
+
+def serving_prompt(args):
+    return 1792 if getattr(args, "model", "6b") == "22b" else 1024
+
+
+def workload_config_6b(args, n_gpus):
     if getattr(args, "workload", "headline") == "serving":
         return {
             "workload": "GPT-J-6B (L28 d4096 h16 dh256 rot64 ff16384 V50400) bf16 random-init; serving: prompts of "
                         "1024 uniform-random ids in [0, 50257) left-padded into seq 2048, then nucleus sampling "
                         "(top_p 0.9, temperature 1.0, seeded uniforms) one token per sequence per step",
-            "batch": args.batch, "window": "1024 + generated tokens", "parallelism": f"mp{n_gpus}",
+            "batch": args.batch, "window": "prompt + generated tokens", "parallelism": f"mp{n_gpus}",
             "l2": "every step streams 11.7 GB of weights plus the KV cache (>> 126 MB L2), no flush needed",
         }
     return {
@@ -185,7 +207,7 @@ def run_mtj(args):
     if world > 1:
         dist.barrier()
 
-    cfg = dict(GPTJ_6B, cores_per_replica=world)
+    cfg = dict(model_config(args), cores_per_replica=world)
     if args.layers > 0:
         cfg["layers"] = args.layers
     seq, B = cfg["seq"], args.batch
@@ -202,7 +224,7 @@ def run_mtj(args):
 
     rng = np.random.Generator(np.random.PCG64(0))
     serving = args.workload == "serving"
-    prompt = 1024 if serving else seq
+    prompt = serving_prompt(args) if serving else seq
     ctx = rng.integers(0, 50257 if serving else cfg["n_vocab"], size=(B, seq)).astype(np.uint32)
     ctx[:, :seq - prompt] = 0                      # left padding
     ctx_dev = torch.from_numpy(ctx.view(np.int32)).to(device)
@@ -435,6 +457,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="mtj", choices=["mtj", "reference"])
     ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--model", default="6b", choices=["6b", "22b"],
+                    help="6b: GPT-J-6B (the headline); 22b: the L48 d6144 h24 scale-up (fits 8 GPUs)")
     ap.add_argument("--workload", default="headline", choices=["headline", "serving"],
                     help="headline: full-window greedy decode; serving: 1024-token prompts + nucleus sampling")
     ap.add_argument("--no-cpu-baseline", action="store_true")

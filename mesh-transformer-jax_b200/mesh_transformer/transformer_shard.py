@@ -123,10 +123,39 @@ class CausalTransformer:
         return to_bf16(state)
 
     def write_ckpt(self, path, shard):
-        raise NotImplementedError("checkpoint I/O is outside the forward/decode path")
+        """transformer_shard.py:282-283.  One process holds one shard: the call
+        writes ``<path>shard_{shard}/`` when ``shard`` is this process's rank and
+        does nothing otherwise, so the reference's loop over all shards works."""
+        from .checkpoint import write_ckpt
+        if shard == self.rank:
+            write_ckpt(self._state, path, shard)
 
-    def load_ckpt(self, path):
-        raise NotImplementedError("checkpoint I/O is outside the forward/decode path")
+    def load_ckpt(self, path, shards_in=None):
+        """transformer_shard.py:285-286.  Reads this rank's shard directory; with
+        ``shards_in`` different from cores_per_replica the checkpoint is
+        re-sharded by parameter role first."""
+        from .checkpoint import read_ckpt, tree_flatten, tree_unflatten
+        mp = self.config["cores_per_replica"]
+        shards_in = mp if shards_in is None else shards_in
+        if shards_in == mp:
+            from .checkpoint import _from_numpy, read_shard
+            leaves = [_from_numpy(a) for a in read_shard(f"{path}shard_{self.rank}/")]
+            slim = {k: v for k, v in self._state.items() if k != "opt_state"}
+            flat = tree_flatten(slim)
+            if len(leaves) != len(flat):
+                raise AssertionError(f"Incompatible checkpoints: {len(leaves)} leaves on disk, {len(flat)} expected")
+            new = tree_unflatten(slim, [a if a.dim() == 0 or tuple(a.shape) == tuple(old.shape) else a[None]
+                                        for a, (_, old) in zip(leaves, flat)])
+        else:
+            template = {"params": {m: {k: torch.empty((mp,) + tuple(v.shape[1:]), dtype=v.dtype, device="meta")
+                                       for k, v in leaves.items()}
+                                   for m, leaves in self._state["params"].items()},
+                        "step": self._state.get("step")}
+            full = read_ckpt(template, path, shards_in, mp, by_role=True)
+            new = {"params": {m: {k: v[self.rank:self.rank + 1] for k, v in leaves.items()}
+                              for m, leaves in full["params"].items()}, "step": full["step"]}
+        new["opt_state"] = self._state.get("opt_state")
+        self.state = new
 
     def train(self, sample):
         raise NotImplementedError("training is outside the forward/decode path")

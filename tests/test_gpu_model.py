@@ -276,3 +276,23 @@ def test_tensor_core_prefill_attention_d_head_256(cuda_device, seq):
     assert _rel(gen[2], ref[2]) <= LOGIT_TOL
     assert np.array_equal(gen[0], ref[0])
     net._rt.check_device_status()
+
+
+@pytest.mark.gpu
+def test_checkpoint_round_trip_through_the_network(cuda_device, tmp_path):
+    """write_ckpt / load_ckpt (transformer_shard.py:282-286): a second network that loads the files
+    generates the same tokens; the files are the reference's shard_{s}/{0..15}.npz layout."""
+    import os
+    cfg = spec.tiny_config(1, seq=64)
+    net = _net(cfg, spec.make_params(cfg, seed=8, stress=True), cuda_device)
+    ctx = spec.left_pad(spec.token_ids(3, 1, 30, 512), 64)
+    want = net.generate(ctx, [30], 8, {"top_p": np.zeros(1), "temp": np.ones(1)})[1][0]
+    path = str(tmp_path) + "/"
+    net.write_ckpt(path, 0)
+    net.write_ckpt(path, 1)                                     # another process's shard: nothing to do here
+    assert sorted(os.listdir(path)) == ["shard_0"]
+    assert sorted(os.listdir(path + "shard_0")) == sorted(f"{i}.npz" for i in range(16))
+    other = _net(cfg, spec.make_params(cfg, seed=9), cuda_device)
+    other.load_ckpt(path)
+    got = other.generate(ctx, [30], 8, {"top_p": np.zeros(1), "temp": np.ones(1)})[1][0]
+    assert np.array_equal(got, want)
