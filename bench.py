@@ -245,7 +245,7 @@ def run_mtj(args):
             rt.decode_step(tok_in, tok_out, None, greedy=False, top_p=top_p_dev, temp=temp_dev,
                            uniforms=u_pool[n_calls[0] % len(u_pool)])
         else:
-            decode(tok_in, tok_out)
+            rt.decode_step(tok_in, tok_out, None, greedy=True)
 
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     # ---- eval / loss over the same ids with next-token targets (reported beside the headline) ----
