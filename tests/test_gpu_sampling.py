@@ -98,3 +98,36 @@ def test_sampled_generate_follows_the_oracle_sampler(cuda_device):
     random.seed(5)
     b2 = net.generate(ctx, lens, 6, opts)[1][0]
     assert np.array_equal(a, b2)
+
+
+def test_sampler_edge_thresholds_and_large_vocab(cuda_device):
+    """top_p at and beyond its range, a vocabulary above 65535, and a row dominated by one logit."""
+    vocab = 70001
+    rng = np.random.default_rng(21)
+    rows = 9
+    lg = (rng.standard_normal((rows, vocab)) * 2.0).astype(np.float32)
+    lg[3, 123] = 40.0                                           # one entry holds nearly all the weight
+    lg[4, :] = 0.25                                             # every logit equal: ranking by index decides
+    un = rng.random((rows, vocab), dtype=np.float32).clip(so.TINY, None)
+    top_p = np.array([-1.0, 1e-30, 1.0, 0.5, 0.37, 1.5, np.inf, 0.9999999, 2.0 ** -20], np.float32)
+    temp = np.array([1.0, 1.0, 0.5, 1.0, 1.0, 3.0, 1.0, 0.1, 1.0], np.float32)
+    got = _sample_gpu(cuda_device, lg, un, top_p, temp)
+    assert np.array_equal(got, so.nucleaus_sample(un, lg, top_p, temp))
+
+
+def test_sampler_cut_inside_a_group_of_equal_logits(cuda_device):
+    """Quantised logits: the threshold falls inside a run of equal values, so the higher indices of the
+    run stay and the lower ones go (descending index order among equals)."""
+    vocab = 50400
+    rng = np.random.default_rng(22)
+    lg = np.round(rng.standard_normal((5, vocab)) * 1.5).astype(np.float32) * 0.5
+    un = rng.random((5, vocab), dtype=np.float32).clip(so.TINY, None)
+    for top_p in (0.11, 0.5, 0.93):
+        tp = np.full(5, top_p, np.float32)
+        got = _sample_gpu(cuda_device, lg, un, tp, np.ones(5, np.float32))
+        assert np.array_equal(got, so.nucleaus_sample(un, lg, tp, 1.0))
+    # the filter itself: the kept set is a prefix of the (value desc, index desc) order
+    _, removed = so.nucleaus_filter(lg[:1], 0.5)
+    order = np.lexsort((-np.arange(vocab), -lg[0]))
+    kept_sorted = ~removed[0][order]
+    assert kept_sorted[0] and not np.any(np.diff(kept_sorted.astype(np.int8)) > 0)
