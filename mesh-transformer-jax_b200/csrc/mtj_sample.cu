@@ -125,33 +125,75 @@ __global__ void __launch_bounds__(256) gumbel_kernel(const float* __restrict__ u
 }
 
 constexpr int kBins = 256;
+constexpr int kMaxCluster = 8;
 
+// thread-block cluster helpers: the blocks of one row exchange small results through each other's shared memory
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_size() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t peer_smem(const void* p, uint32_t rank) {
+  uint32_t a;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(smem_u32(p)), "r"(rank));
+  return a;
+}
+__device__ __forceinline__ unsigned long long ld_peer_u64(const void* p, uint32_t rank) {
+  unsigned long long v;
+  asm volatile("ld.shared::cluster.u64 %0, [%1];" : "=l"(v) : "r"(peer_smem(p, rank)) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint32_t ld_peer_u32(const void* p, uint32_t rank) {
+  uint32_t v;
+  asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(peer_smem(p, rank)) : "memory");
+  return v;
+}
+
+// One row = one cluster of C blocks (C = 1, 2, 4 or 8); block c owns the vocabulary slice
+// [c * slice, (c + 1) * slice).  Every block computes the histogram of its slice, reads the other blocks'
+// 256 bin sums through distributed shared memory and makes the same selection, so control flow stays
+// uniform over the cluster (every block reaches every cluster barrier).
 __global__ void __launch_bounds__(kSampThreads, 1) sample_top_p_kernel(const SampleArgs a) {
   extern __shared__ __align__(16) unsigned char samp_smem[];
   unsigned long long* hist = reinterpret_cast<unsigned long long*>(samp_smem);          // [32 warps][256]
-  unsigned long long* bins = hist + 32 * kBins;                                         // [256]
-  uint32_t* bitmap = reinterpret_cast<uint32_t*>(bins + kBins);                         // [ceil(V / 32)]
+  unsigned long long* bins = hist + 32 * kBins;                                         // [2][256] by level parity
+  unsigned long long* gbins = bins + 2 * kBins;                                         // [256] sums over the cluster
+  uint32_t* bitmap = reinterpret_cast<uint32_t*>(gbins + kBins);                        // [ceil(slice / 32)]
   __shared__ float red_v[32];
   __shared__ int red_i[32];
   __shared__ uint32_t wsum[33];
   __shared__ uint32_t sel_digit, sel_none;
   __shared__ unsigned long long sel_before, sel_sum, sel_T;
+  __shared__ uint32_t x_max, x_ties, x_best_v, x_best_i;      // read by the other blocks of the cluster
 
-  const int row = blockIdx.x, t = threadIdx.x, V = a.V;
+  const uint32_t C = cluster_size(), crank = cluster_rank();
+  const int row = blockIdx.x / C, t = threadIdx.x, V = a.V;
   const int lane = t & 31, warp = t >> 5;
   const float* logits = a.logits + static_cast<size_t>(row) * V;
   const float* gum = a.gumbel + static_cast<size_t>(row) * V;
+  const int slice = ((V + static_cast<int>(C) - 1) / static_cast<int>(C) + 31) & ~31;
+  const int i_begin = min(V, static_cast<int>(crank) * slice), i_end = min(V, i_begin + slice);
 
   // ---- row maximum (the head of the sorted order) ----
   float vmax = -INFINITY;
-  for (int i = t; i < V; i += kSampThreads) vmax = fmaxf(vmax, logits[i]);
+  for (int i = i_begin + t; i < i_end; i += kSampThreads) vmax = fmaxf(vmax, logits[i]);
   vmax = warp_max(vmax);
   if (lane == 0) red_v[warp] = vmax;
   __syncthreads();
   vmax = red_v[0];
 #pragma unroll
   for (int w = 1; w < 32; ++w) vmax = fmaxf(vmax, red_v[w]);
-  __syncthreads();
+  if (t == 0) x_max = __float_as_uint(vmax);
+  cluster_sync();
+  for (uint32_t c = 0; c < C; ++c) vmax = fmaxf(vmax, __uint_as_float(ld_peer_u32(&x_max, c)));
 
   // ---- radix selection of the entry whose weight interval contains T ----
   const float top_p = a.top_p[row], temp = a.temp[row];
@@ -162,21 +204,22 @@ __global__ void __launch_bounds__(kSampThreads, 1) sample_top_p_kernel(const Sam
   unsigned long long* my_hist = hist + warp * kBins;
   for (int level = 0; level < 4 && cut; ++level) {
     const int shift = 24 - 8 * level;
+    unsigned long long* lbins = bins + (level & 1) * kBins;
     for (int i = t; i < 32 * kBins; i += kSampThreads) hist[i] = 0ull;
     __syncthreads();
-    for (int i0 = 0; i0 < V; i0 += 4 * kSampThreads) {
+    for (int i0 = i_begin; i0 < i_end; i0 += 4 * kSampThreads) {
       float l[4];
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         const int i = i0 + u * kSampThreads + t;
-        l[u] = i < V ? logits[i] : 0.f;
+        l[u] = i < i_end ? logits[i] : 0.f;
       }
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
-        if (i0 + u * kSampThreads >= V) break;             // block-uniform
+        if (i0 + u * kSampThreads >= i_end) break;         // block-uniform
         const int i = i0 + u * kSampThreads + t;
         const uint32_t key = sort_key(l[u]);
-        const bool part = i < V && (level == 0 || (key >> (shift + 8)) == prefix);
+        const bool part = i < i_end && (level == 0 || (key >> (shift + 8)) == prefix);
         const uint32_t dig = part ? ((key >> shift) & 255u) : 0xFFFFu;
         const unsigned long long q = part ? weight_of(l[u], vmax) : 0ull;
         warp_hist_add(my_hist, dig, q, part, lane);
@@ -187,14 +230,20 @@ __global__ void __launch_bounds__(kSampThreads, 1) sample_top_p_kernel(const Sam
       unsigned long long sum = 0ull;
 #pragma unroll 8
       for (int w = 0; w < 32; ++w) sum += hist[w * kBins + t];
-      bins[t] = sum;
+      lbins[t] = sum;
+    }
+    cluster_sync();                                        // every block's bin sums of this level are in place
+    if (t < kBins) {
+      unsigned long long sum = 0ull;
+      for (uint32_t c = 0; c < C; ++c) sum += ld_peer_u64(lbins + t, c);
+      gbins[t] = sum;
     }
     __syncthreads();
     if (warp == 0) {
       unsigned long long b[8], local = 0ull;
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
-        b[k] = bins[lane * 8 + k];
+        b[k] = gbins[lane * 8 + k];
         local += b[k];
       }
       unsigned long long inc = local;
@@ -272,13 +321,14 @@ __global__ void __launch_bounds__(kSampThreads, 1) sample_top_p_kernel(const Sam
     r0 = (T - before) / qt;                                              // rank of the entry that holds T
     tie_cut = r0 + 1 < cnt;
   }
-  if (tie_cut) {
-    // thread t owns a contiguous index range, thread 0 the highest indices
-    const int per = (V + kSampThreads - 1) / kSampThreads;
-    const int hi_i = V - 1 - t * per, lo_i = max(-1, hi_i - per);
-    for (int i = t; i < (V + 31) / 32; i += kSampThreads) bitmap[i] = 0u;
+  if (tie_cut) {                                                         // uniform over the cluster
+    // thread t owns a contiguous index range of this block's slice, thread 0 the highest indices
+    const int n_own = i_end - i_begin;
+    const int per = (n_own + kSampThreads - 1) / kSampThreads;
+    const int hi_i = i_end - 1 - t * per, lo_i = max(i_begin - 1, hi_i - per);
+    for (int i = t; i < (n_own + 31) / 32; i += kSampThreads) bitmap[i] = 0u;
     uint32_t mine = 0;
-    for (int i = hi_i; i > lo_i && i >= 0; --i) mine += sort_key(logits[i]) == k0 ? 1u : 0u;
+    for (int i = hi_i; i > lo_i; --i) mine += sort_key(logits[i]) == k0 ? 1u : 0u;
     uint32_t inc = mine;
 #pragma unroll
     for (int off = 1; off < 32; off <<= 1) {
@@ -296,12 +346,14 @@ __global__ void __launch_bounds__(kSampThreads, 1) sample_top_p_kernel(const Sam
         if (lane >= off) winc += y;
       }
       wsum[lane] = winc - w;
+      if (lane == 31) x_ties = winc;                                     // equal keys in this block's slice
     }
-    __syncthreads();
+    cluster_sync();
     unsigned long long rank = wsum[warp] + inc - mine;
-    for (int i = hi_i; i > lo_i && i >= 0; --i) {
+    for (uint32_t c = crank + 1; c < C; ++c) rank += ld_peer_u32(&x_ties, c);   // slices with higher indices come first
+    for (int i = hi_i; i > lo_i; --i) {
       if (sort_key(logits[i]) == k0) {
-        if (rank > r0) atomicOr(bitmap + (i >> 5), 1u << (i & 31));
+        if (rank > r0) atomicOr(bitmap + ((i - i_begin) >> 5), 1u << ((i - i_begin) & 31));
         ++rank;
       }
     }
@@ -311,10 +363,11 @@ __global__ void __launch_bounds__(kSampThreads, 1) sample_top_p_kernel(const Sam
   // ---- Gumbel-max over the filtered, tempered logits ----
   float best = -INFINITY;
   int best_i = 0x7fffffff;
-  for (int i = t; i < V; i += kSampThreads) {
+  for (int i = i_begin + t; i < i_end; i += kSampThreads) {
     const float lg = logits[i];
     const uint32_t key = sort_key(lg);
-    const bool removed = cut && (key > k0 || (tie_cut && key == k0 && ((bitmap[i >> 5] >> (i & 31)) & 1u)));
+    const int j = i - i_begin;
+    const bool removed = cut && (key > k0 || (tie_cut && key == k0 && ((bitmap[j >> 5] >> (j & 31)) & 1u)));
     const float lm = __fsub_rn(lg, removed ? 1e10f : 0.0f);
     const float score = __fadd_rn(__fdiv_rn(lm, temp), gum[i]);
     if (score > best) {                                    // ascending i: the first maximum stays
@@ -349,15 +402,31 @@ __global__ void __launch_bounds__(kSampThreads, 1) sample_top_p_kernel(const Sam
       }
     }
     if (lane == 0) {
-      a.tokens[row] = static_cast<uint32_t>(best_i);
-      if (a.tokens_copy) a.tokens_copy[row] = static_cast<uint32_t>(best_i);
-      if (a.cur_dev && row == 0) *a.cur_dev += 1;
+      x_best_v = __float_as_uint(best);
+      x_best_i = static_cast<uint32_t>(best_i);
     }
   }
+  cluster_sync();
+  if (crank == 0 && t == 0) {
+    for (uint32_t c = 1; c < C; ++c) {
+      const float ov = __uint_as_float(ld_peer_u32(&x_best_v, c));
+      const int oi = static_cast<int>(ld_peer_u32(&x_best_i, c));
+      if (ov > best || (ov == best && oi < best_i)) {
+        best = ov;
+        best_i = oi;
+      }
+    }
+    a.tokens[row] = static_cast<uint32_t>(best_i);
+    if (a.tokens_copy) a.tokens_copy[row] = static_cast<uint32_t>(best_i);
+    if (a.cur_dev && row == 0) *a.cur_dev += 1;
+  }
+  cluster_sync();                                          // no block leaves while its shared memory may be read
 }
 
-inline size_t sample_smem_bytes(int V) {
-  return sizeof(unsigned long long) * (32 * kBins + kBins) + sizeof(uint32_t) * static_cast<size_t>((V + 31) / 32);
+inline int sample_cluster(int rows) { return rows <= 18 ? 8 : (rows <= 37 ? 4 : (rows <= 74 ? 2 : 1)); }
+inline size_t sample_smem_bytes(int V, int cluster) {
+  const int slice = ((V + cluster - 1) / cluster + 31) & ~31;
+  return sizeof(unsigned long long) * (32 * kBins + 3 * kBins) + sizeof(uint32_t) * static_cast<size_t>((slice + 31) / 32);
 }
 
 }  // namespace
@@ -366,7 +435,8 @@ inline size_t sample_smem_bytes(int V) {
 int64_t sample_scratch_bytes(int rows, int vocab) { return static_cast<int64_t>(rows) * vocab * 4; }
 
 cudaError_t launch_sample_top_p(const SampleArgs& a, cudaStream_t s, bool pdl) {
-  const size_t smem = sample_smem_bytes(a.V);
+  const int cluster = sample_cluster(a.rows);              // blocks per row: as many as keep one wave on 148 SMs
+  const size_t smem = sample_smem_bytes(a.V, cluster);
   if (a.rows <= 0 || a.V <= 0 || smem > 220 * 1024 || !a.scratch) return cudaErrorInvalidValue;
   static bool configured = false;
   if (!configured) {
@@ -389,8 +459,19 @@ cudaError_t launch_sample_top_p(const SampleArgs& a, cudaStream_t s, bool pdl) {
   if (e != cudaSuccess) return e;
   SampleArgs b = a;
   b.gumbel = g;
-  sample_top_p_kernel<<<a.rows, kSampThreads, smem, s>>>(b);
-  return cudaGetLastError();
+  cudaLaunchAttribute cattr[1];
+  cattr[0].id = cudaLaunchAttributeClusterDimension;
+  cattr[0].val.clusterDim.x = cluster;
+  cattr[0].val.clusterDim.y = 1;
+  cattr[0].val.clusterDim.z = 1;
+  cudaLaunchConfig_t scfg = {};
+  scfg.gridDim = dim3(static_cast<unsigned>(a.rows * cluster));
+  scfg.blockDim = dim3(kSampThreads);
+  scfg.dynamicSmemBytes = smem;
+  scfg.stream = s;
+  scfg.attrs = cattr;
+  scfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&scfg, sample_top_p_kernel, b);
 }
 
 }  // namespace mtj
