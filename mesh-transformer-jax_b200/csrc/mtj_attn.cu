@@ -17,6 +17,7 @@
 // skipped, which equals the reference's additive -1e10 whenever at least one
 // key is visible (exp underflows to exactly 0 in fp32).
 #include <math.h>
+#include <stdlib.h>
 
 #include "mtj_common.cuh"
 #include "mtj_kernels.h"
@@ -232,6 +233,221 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attn_kernel(const DecodeA
   if (threadIdx.x == 0) a.counters[b * a.heads + head] = 0u;
 }
 
+// The same decode attention for many sequences: one block walks kStreamPages consecutive pages of one
+// (sequence, head) as half-page tiles (32 keys: 16 KB of K + 16 KB of V) through a 3-stage ring fed by a
+// producer warp, so the block's loads stay in flight while its eight consumer warps work, and the
+// per-block costs (launch, warp merge, partial write, ticket) are spread over up to 256 keys.  Each
+// consumer warp keeps its own running (max, sum, weighted V) over the 4 keys it takes from every tile.
+constexpr int kStreamPages = 4;
+constexpr int kStreamStages = 3;
+constexpr int kTileTokens = 32;
+constexpr int kStreamThreads = kAttnThreads + 32;
+
+template <int DH>
+__global__ void __launch_bounds__(kStreamThreads) decode_attn_stream_kernel(const DecodeAttnArgs a) {
+  constexpr int EPL = DH / 32;
+  constexpr int TPW = kTileTokens / kAttnWarps;            // keys per warp and tile: 4
+  constexpr uint32_t kHalf = kTileTokens * DH * 2;         // bytes of K (or V) per tile
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int split = blockIdx.x, head = blockIdx.y, b = blockIdx.z;
+
+  extern __shared__ __align__(128) unsigned char attn_smem[];
+  __shared__ __align__(8) uint64_t bars[2 * kStreamStages];
+  __shared__ float sm_m[kAttnWarps], sm_l[kAttnWarps];
+  __shared__ float sm_o[kAttnWarps][DH];
+  __shared__ bool is_last;
+  __shared__ uint32_t failed;
+
+  const int cur = *a.cur_dev;                              // written before the predecessor kernel started
+  const int start = max(a.kv.pad[b], cur - a.window + 1);
+  const int end = cur + 1;
+  const int first_page = start / kPageTokens;
+  const int n_pages = cur / kPageTokens - first_page + 1;
+  const int nsplit = (n_pages + kStreamPages - 1) / kStreamPages;
+  const int page0 = first_page + split * kStreamPages;     // first page of this block
+  const int my_pages = min(kStreamPages, first_page + n_pages - page0);
+  const int n_tiles = 2 * max(my_pages, 0);
+  const uint32_t bar0 = smem_u32(bars);
+  auto full_bar = [&](int st) { return bar0 + 8u * st; };
+  auto empty_bar = [&](int st) { return bar0 + 8u * (kStreamStages + st); };
+  if (threadIdx.x == 0) {
+    for (int st = 0; st < kStreamStages; ++st) {
+      mbar_init(full_bar(st), 1);
+      mbar_init(empty_bar(st), kAttnWarps);
+    }
+    mbar_fence_init();
+    failed = 0;
+  }
+  __syncthreads();
+  pdl_launch_dependents();
+  if (split >= nsplit) return;                             // uniform for the block
+
+  float m = -INFINITY, l = 0.f, o[EPL];
+#pragma unroll
+  for (int e = 0; e < EPL; ++e) o[e] = 0.f;
+
+  if (warp == kAttnWarps) {
+    // ---- producer ----
+    if (lane == 0) {
+      const int32_t* table = a.kv.page_table + static_cast<size_t>(b) * a.kv.ring_pages;
+      const uint64_t pol = l2_evict_first_policy();
+      bool waited = false;
+      for (int tile = 0; tile < n_tiles; ++tile) {
+        const int st = tile % kStreamStages;
+        if (tile >= kStreamStages && !mbar_wait(empty_bar(st), ((tile / kStreamStages) - 1) & 1)) {
+          atomicOr(&failed, 1u);
+          break;
+        }
+        const int page_pos = (page0 + (tile >> 1)) * kPageTokens + (tile & 1) * kTileTokens;
+        if (!waited && page_pos + kTileTokens > cur) {      // this tile holds the token the predecessor wrote
+          pdl_wait();
+          waited = true;
+        }
+        const int page = table[(page0 + (tile >> 1)) % a.kv.ring_pages];
+        const size_t off = ((static_cast<size_t>(page) * a.heads + head) * kPageTokens + (tile & 1) * kTileTokens) * DH;
+        const uint32_t dst = smem_u32(attn_smem) + st * 2 * kHalf;
+        mbar_expect_tx(full_bar(st), 2 * kHalf);
+        bulk_load(dst, a.kv.kpool + off, kHalf, full_bar(st), pol);
+        bulk_load(dst + kHalf, a.kv.vpool + off, kHalf, full_bar(st), pol);
+      }
+    }
+  } else {
+    // ---- consumers ----
+    pdl_wait();                                            // the query comes from the predecessor kernel
+    constexpr float scale = DH == 256 ? 0.0625f : 0.125f;  // 1 / sqrt(d_head), exact
+    float q[EPL];
+    {
+      const float* qp = a.q + (static_cast<size_t>(b) * a.heads + head) * DH + lane * EPL;
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) q[e] = qp[e] * scale;
+    }
+    for (int tile = 0; tile < n_tiles; ++tile) {
+      const int st = tile % kStreamStages;
+      if (!mbar_wait(full_bar(st), (tile / kStreamStages) & 1)) {
+        atomicOr(&failed, 1u);
+        break;
+      }
+      const __nv_bfloat16* sk = reinterpret_cast<const __nv_bfloat16*>(attn_smem + st * 2 * kHalf);
+      const __nv_bfloat16* sv = reinterpret_cast<const __nv_bfloat16*>(attn_smem + st * 2 * kHalf + kHalf);
+      const int pos0 = (page0 + (tile >> 1)) * kPageTokens + (tile & 1) * kTileTokens + warp * TPW;
+      float sc[TPW];
+      bool ok[TPW];
+#pragma unroll
+      for (int u = 0; u < TPW; ++u) {
+        ok[u] = pos0 + u >= start && pos0 + u < end;
+        KvVec<EPL> kv;
+        kv.load_shared(sk + static_cast<size_t>(warp * TPW + u) * DH + lane * EPL);
+        float kf[EPL];
+        kv.get(kf);
+        float d = 0.f;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) d = fmaf(q[e], kf[e], d);
+        sc[u] = d;
+      }
+#pragma unroll
+      for (int o2 = 16; o2 > 0; o2 >>= 1)
+#pragma unroll
+        for (int u = 0; u < TPW; ++u) sc[u] += __shfl_xor_sync(0xffffffffu, sc[u], o2);
+      float m_new = m;
+#pragma unroll
+      for (int u = 0; u < TPW; ++u)
+        if (ok[u]) m_new = fmaxf(m_new, sc[u]);
+      if (m_new > -INFINITY) {
+        const float corr = m == -INFINITY ? 0.f : __expf(m - m_new);
+        l *= corr;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) o[e] *= corr;
+#pragma unroll
+        for (int u = 0; u < TPW; ++u) {
+          if (!ok[u]) continue;
+          const float pw = __expf(sc[u] - m_new);
+          KvVec<EPL> vv;
+          vv.load_shared(sv + static_cast<size_t>(warp * TPW + u) * DH + lane * EPL);
+          float vf[EPL];
+          vv.get(vf);
+          l += pw;
+#pragma unroll
+          for (int e = 0; e < EPL; ++e) o[e] = fmaf(pw, vf[e], o[e]);
+        }
+        m = m_new;
+      }
+      __syncwarp();
+      if (lane == 0) {
+        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty_bar(st)) : "memory");
+      }
+    }
+    if (lane == 0) {
+      sm_m[warp] = m;
+      sm_l[warp] = l;
+    }
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) sm_o[warp][lane * EPL + e] = o[e];
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && failed && a.dev_err) atomicOr(a.dev_err, kDevErrTimeout);
+  const size_t pidx = (static_cast<size_t>(b) * a.heads + head) * a.max_splits + split;
+  if (threadIdx.x < DH) {
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kAttnWarps; ++w) M = fmaxf(M, sm_m[w]);
+    float L = 0.f, O = 0.f;
+#pragma unroll
+    for (int w = 0; w < kAttnWarps; ++w) {
+      const float f = sm_m[w] == -INFINITY ? 0.f : __expf(sm_m[w] - M);
+      L = fmaf(sm_l[w], f, L);
+      O = fmaf(sm_o[w][threadIdx.x], f, O);
+    }
+    a.part_o[pidx * DH + threadIdx.x] = O;
+    if (threadIdx.x == 0) {
+      a.part_ml[pidx * 2] = M;
+      a.part_ml[pidx * 2 + 1] = L;
+    }
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t ticket = atomicAdd(a.counters + b * a.heads + head, 1u);
+    is_last = (ticket == static_cast<uint32_t>(nsplit - 1));
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  {
+    __shared__ float wgt[64];
+    __shared__ float inv_l;
+    const size_t base = (static_cast<size_t>(b) * a.heads + head) * a.max_splits;
+    if (warp == 0) {
+      float ms[2], ls[2];
+#pragma unroll
+      for (int h2 = 0; h2 < 2; ++h2) {
+        const int sidx = lane + 32 * h2;
+        ms[h2] = sidx < nsplit ? __ldcg(a.part_ml + (base + sidx) * 2) : -INFINITY;
+        ls[h2] = sidx < nsplit ? __ldcg(a.part_ml + (base + sidx) * 2 + 1) : 0.f;
+      }
+      const float M = warp_max(fmaxf(ms[0], ms[1]));
+      float lsum = 0.f;
+#pragma unroll
+      for (int h2 = 0; h2 < 2; ++h2) {
+        const float f = ms[h2] == -INFINITY ? 0.f : __expf(ms[h2] - M);
+        wgt[lane + 32 * h2] = f;
+        lsum = fmaf(ls[h2], f, lsum);
+      }
+      lsum = warp_sum(lsum);
+      if (lane == 0) inv_l = 1.0f / lsum;
+    }
+    __syncthreads();
+    if (threadIdx.x < DH) {
+      const float* po = a.part_o + base * DH + threadIdx.x;
+      float O = 0.f;
+      for (int sidx = 0; sidx < nsplit; ++sidx) O = fmaf(__ldcg(po + static_cast<size_t>(sidx) * DH), wgt[sidx], O);
+      const size_t oi = static_cast<size_t>(b) * a.ld_out + head * DH + threadIdx.x;
+      if (a.out_bf16) a.out_bf16[oi] = __float2bfloat16_rn(O * inv_l);
+      else a.out[oi] = O * inv_l;
+    }
+  }
+  if (threadIdx.x == 0) a.counters[b * a.heads + head] = 0u;
+}
+
 // Causal attention for a chunk of rows; one warp owns QPW consecutive queries
 // of one (sequence, head) and walks the keys once for all of them.
 template <int DH, int QPW>
@@ -349,6 +565,28 @@ cudaError_t launch_decode_dh(const DecodeAttnArgs& a, cudaStream_t s, bool pdl) 
   return cudaLaunchKernelEx(&cfg, decode_attn_kernel<DH>, a);
 }
 
+template <int DH>
+cudaError_t launch_decode_stream_dh(const DecodeAttnArgs& a, cudaStream_t s, bool pdl) {
+  constexpr int smem = kStreamStages * 2 * kTileTokens * DH * 2;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(decode_attn_stream_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((a.grid_splits + kStreamPages - 1) / kStreamPages, a.heads, a.B);
+  cfg.blockDim = dim3(kStreamThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, decode_attn_stream_kernel<DH>, a);
+}
+
 // Splits of the visible window: one per 64-token page it can touch.
 int decode_attn_splits(int window) { return (window + kPageTokens - 1) / kPageTokens + 1; }
 
@@ -356,6 +594,16 @@ cudaError_t launch_decode_attn(const DecodeAttnArgs& a, cudaStream_t s, bool pdl
   if (a.B <= 0 || a.grid_splits <= 0 || a.grid_splits > a.max_splits || a.kv.ring_pages < a.grid_splits ||
       (a.grid_splits < decode_attn_splits(a.window) && a.grid_splits < a.kv.ring_pages))
     return cudaErrorInvalidValue;
+  // many sequences: enough blocks even with several pages per block, which keeps each block streaming
+  static int stream_min_b = -1;
+  if (stream_min_b < 0) {
+    const char* e = getenv("MTJ_ATTN_STREAM_MIN_B");
+    stream_min_b = e ? atoi(e) : 1 << 30;
+  }
+  if (a.B >= stream_min_b) {
+    if (a.d_head == 256) return launch_decode_stream_dh<256>(a, s, pdl);
+    if (a.d_head == 64) return launch_decode_stream_dh<64>(a, s, pdl);
+  }
   if (a.d_head == 256) return launch_decode_dh<256>(a, s, pdl);
   if (a.d_head == 64) return launch_decode_dh<64>(a, s, pdl);
   return cudaErrorInvalidValue;

@@ -744,6 +744,8 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int kspl
                                      const float* __restrict__ bias, const float* residual, float* out, int ld_out,
                                      const uint32_t* slot_sel, size_t slot_stride) {
   const size_t total = static_cast<size_t>(M) * N;
+  pdl_wait();                      // the partial sums come from the predecessor kernel
+  pdl_launch_dependents();
   if (slot_sel) out += static_cast<size_t>(*slot_sel & 1u) * slot_stride;
   for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
        i += static_cast<size_t>(gridDim.x) * blockDim.x) {
@@ -760,17 +762,34 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int kspl
 
 cudaError_t launch_splitk_reduce(const float* partial, int ksplit, int M, int N, const float* bias,
                                  const float* residual, float* out, int ld_out, const uint32_t* slot_sel,
-                                 size_t slot_stride, cudaStream_t s) {
+                                 size_t slot_stride, cudaStream_t s, bool pdl) {
   const size_t total = static_cast<size_t>(M) * N;
   const int grid = static_cast<int>(std::min<size_t>((total + 255) / 256, 148 * 8));
-  splitk_reduce_kernel<<<grid, 256, 0, s>>>(partial, ksplit, M, N, bias, residual, out, ld_out, slot_sel, slot_stride);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(256);
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, splitk_reduce_kernel, partial, ksplit, M, N, bias, residual, out, ld_out, slot_sel,
+                            slot_stride);
 }
 
 cudaError_t launch_ln_rows(const float* x, const float* scale, const float* offset, __nv_bfloat16* out, int rows,
-                           int d, cudaStream_t s) {
-  ln_rows_kernel<<<rows, 256, 0, s>>>(x, scale, offset, out, d);
-  return cudaGetLastError();
+                           int d, cudaStream_t s, bool pdl) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(rows);
+  cfg.blockDim = dim3(256);
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, ln_rows_kernel, x, scale, offset, out, d);
 }
 
 }  // namespace mtj

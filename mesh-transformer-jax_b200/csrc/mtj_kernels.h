@@ -209,7 +209,7 @@ int gemm_tc_token_tile();                 // widest token tile of launch_gemm_tc
 int gemm_tc_token_tile_for(int M);
 cudaError_t launch_splitk_reduce(const float* partial, int ksplit, int M, int N, const float* bias,
                                  const float* residual, float* out, int ld_out, const uint32_t* slot_sel,
-                                 size_t slot_stride, cudaStream_t s);
+                                 size_t slot_stride, cudaStream_t s, bool pdl = false);
 cudaError_t make_tensor_map_bf16(void* map_out_128B, const void* base, int64_t rows, int64_t K, int box_rows);
 cudaError_t launch_gemm_tc(GemvEpilogue epi, const void* map_w, const void* map_x, const GemmTcArgs& a,
                            cudaStream_t s, bool pdl);
@@ -219,7 +219,7 @@ int gemm_tc_wide_token_tile();
 cudaError_t launch_gemm_tc_wide(GemvEpilogue epi, const void* map_w, const void* map_x, const GemmTcArgs& a,
                                 cudaStream_t s);
 cudaError_t launch_ln_rows(const float* x, const float* scale, const float* offset, __nv_bfloat16* out, int rows,
-                           int d, cudaStream_t s);
+                           int d, cudaStream_t s, bool pdl = false);
 
 struct SampleArgs {
   const float* logits;         // [rows, V]

@@ -151,6 +151,7 @@ struct mtj_handle {
   bool mega_trace_on = false;
   // decode: attention runs on a side stream next to the FF half of the in-projection
   bool fork_attn = true;
+  bool tc_pdl = false;              // programmatic dependent launch on the tensor-core decode chain (MTJ_TC_PDL=1)
   bool fork_pdl = false;            // let the out-projection start early although it also waits on the side stream
   cudaStream_t side_stream = nullptr;
   cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
@@ -447,7 +448,10 @@ bool use_tc_wide(const mtj_handle* h, int M) { return h->tc_wide_ok && M > 192; 
 int32_t run_layer_tc(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, const int32_t* key_limit,
                      cudaStream_t s, float* detached_out = nullptr, bool decode = false) {
   LayerWeights& lw = h->layers[layer];
-  MTJ_CUDA(mtj::launch_ln_rows(h->x, lw.ln_scale, lw.ln_offset, h->xn_bf16, M, h->d, s));
+  // decode (graph-replayed, launch-latency sensitive): every kernel of the chain waits on its predecessor with
+  // griddepcontrol.wait, so each may be scheduled while the previous one drains
+  const bool pdl = h->use_pdl && h->tc_pdl && decode;
+  MTJ_CUDA(mtj::launch_ln_rows(h->x, lw.ln_scale, lw.ln_offset, h->xn_bf16, M, h->d, s, pdl));
   mtj::GemmTcArgs a = {};
   a.M = M;
   a.N = 3 * h->dl + h->ffl;
@@ -470,7 +474,7 @@ int32_t run_layer_tc(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, c
   if (wide)
     MTJ_CUDA(mtj::launch_gemm_tc_wide(mtj::kEpiInProj, &lw.map_in, &h->map_xn_wide, a, s));
   else
-    MTJ_CUDA(mtj::launch_gemm_tc(mtj::kEpiInProj, &lw.map_in, &h->map_xn[tc_tile_index(M)], a, s, false));
+    MTJ_CUDA(mtj::launch_gemm_tc(mtj::kEpiInProj, &lw.map_in, &h->map_xn[tc_tile_index(M)], a, s, pdl));
   h->prof_end(s);
 
   h->prof_begin(MTJ_FAMILY_ATTN, s);
@@ -491,7 +495,7 @@ int32_t run_layer_tc(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, c
     d.counters = h->counters;
     d.out_bf16 = h->act_bf16;
     d.ld_out = h->dl + h->ffl;
-    MTJ_CUDA(mtj::launch_decode_attn(d, s, false));
+    MTJ_CUDA(mtj::launch_decode_attn(d, s, pdl));
   } else if (h->attn_tc_ok) {
     mtj::PrefillAttnTcArgs p = {};
     p.kv = h->kv(layer);
@@ -540,14 +544,14 @@ int32_t run_layer_tc(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, c
     const float* res = o.residual;
     o.partial = h->tc_partial;
     o.ksplit = ksplit;
-    MTJ_CUDA(mtj::launch_gemm_tc(mtj::kEpiOut, &lw.map_out, &h->map_act[tc_tile_index(M)], o, s, false));
+    MTJ_CUDA(mtj::launch_gemm_tc(mtj::kEpiOut, &lw.map_out, &h->map_act[tc_tile_index(M)], o, s, pdl));
     MTJ_CUDA(mtj::launch_splitk_reduce(h->tc_partial, ksplit, M, h->d, lw.b_out, res, dst, h->d,
-                                       to_slot ? partial_slot_sel(h, M) : nullptr, partial_slot_stride(h), s));
+                                       to_slot ? partial_slot_sel(h, M) : nullptr, partial_slot_stride(h), s, pdl));
     h->launches++;
   } else if (wide) {
     MTJ_CUDA(mtj::launch_gemm_tc_wide(mtj::kEpiOut, &lw.map_out, &h->map_act_wide, o, s));
   } else {
-    MTJ_CUDA(mtj::launch_gemm_tc(mtj::kEpiOut, &lw.map_out, &h->map_act[tc_tile_index(M)], o, s, false));
+    MTJ_CUDA(mtj::launch_gemm_tc(mtj::kEpiOut, &lw.map_out, &h->map_act[tc_tile_index(M)], o, s, pdl));
   }
   h->prof_end(s);
   h->launches += 4;
@@ -558,14 +562,14 @@ int32_t run_layer_tc(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, c
     MTJ_CUDA(cudaMemcpyAsync(detached_out, h->part, sizeof(float) * M * h->d, cudaMemcpyDeviceToDevice, s));
     return MTJ_OK;
   }
-  if (h->mp > 1) return reduce_into_x(h, M, true, false, s);
+  if (h->mp > 1) return reduce_into_x(h, M, true, pdl, s);
   return MTJ_OK;
 }
 
 // final LayerNorm + vocab-sharded logits for rows [row0, row0 + M) of h->x on the tensor cores
-int32_t run_logits_tc(mtj_handle* h, int M, int row0, float* out, cudaStream_t s) {
+int32_t run_logits_tc(mtj_handle* h, int M, int row0, float* out, cudaStream_t s, bool pdl = false) {
   MTJ_CUDA(mtj::launch_ln_rows(h->x + static_cast<size_t>(row0) * h->d, h->lnf_scale, h->lnf_offset,
-                               h->xn_bf16 + static_cast<size_t>(row0) * h->d, M, h->d, s));
+                               h->xn_bf16 + static_cast<size_t>(row0) * h->d, M, h->d, s, pdl));
   mtj::GemmTcArgs a = {};
   a.M = M;
   a.N = h->Vl;
@@ -579,7 +583,7 @@ int32_t run_logits_tc(mtj_handle* h, int M, int row0, float* out, cudaStream_t s
   if (use_tc_wide(h, M))
     MTJ_CUDA(mtj::launch_gemm_tc_wide(mtj::kEpiLogits, &h->map_proj, &h->map_xn_wide, a, s));
   else
-    MTJ_CUDA(mtj::launch_gemm_tc(mtj::kEpiLogits, &h->map_proj, &h->map_xn[tc_tile_index(M)], a, s, false));
+    MTJ_CUDA(mtj::launch_gemm_tc(mtj::kEpiLogits, &h->map_proj, &h->map_xn[tc_tile_index(M)], a, s, pdl));
   h->prof_end(s);
   h->launches += 2;
   return MTJ_OK;
@@ -753,6 +757,8 @@ int32_t mtj_create(const mtj_config* c, mtj_handle** out) {
   h->use_pdl = !(e && e[0] == '1');
   e = getenv("MTJ_NO_MEGA");
   h->use_mega = !(e && e[0] == '1');
+  e = getenv("MTJ_TC_PDL");
+  h->tc_pdl = e && e[0] == '1';
   e = getenv("MTJ_NO_MEGA_PUSH");
   h->mega_push = !(e && e[0] == '1');
   e = getenv("MTJ_NO_FORK");
@@ -1140,7 +1146,7 @@ int32_t mtj_decode_step(mtj_handle* h, const uint32_t* tokens_in, const float* t
       if (r) return r;
     }
     if (!mega) {
-      r = tc ? run_logits_tc(h, B, 0, h->logits, st) : run_logits(h, B, nullptr, h->logits, true, st);
+      r = tc ? run_logits_tc(h, B, 0, h->logits, st, h->use_pdl && h->tc_pdl) : run_logits(h, B, nullptr, h->logits, true, st);
       if (r) return r;
     }
     if (h->mp > 1) {

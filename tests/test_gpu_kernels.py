@@ -12,6 +12,10 @@ pytestmark = pytest.mark.gpu
     (256, 2, 3, 300, 310, [0, 250, 310], 64),        # left pad, and a sequence that sees only itself
     (64, 4, 2, 127, 127, [100, 3], 32),              # tiny config
     (64, 4, 2, 127, 200, [0, 0], 8),                 # many splits
+    # eight or more sequences take the multi-page streaming kernel
+    (256, 4, 9, 2047, 2047 + 70, [0, 1500, 2100, 0, 77, 64, 2116, 1000, 2117], 128),
+    (256, 2, 8, 300, 255, [0, 250, 255, 1, 63, 64, 65, 200], 64),      # window not yet full, cut pages
+    (64, 4, 12, 127, 127, [100, 3, 0, 127, 64, 63, 1, 2, 90, 31, 32, 33], 32),
 ])
 def test_decode_attention_matches_reference(cuda_device, d_head, heads, batch, window, cur, pads, split):
     import torch
