@@ -598,7 +598,7 @@ cudaError_t launch_decode_attn(const DecodeAttnArgs& a, cudaStream_t s, bool pdl
   static int stream_min_b = -1;
   if (stream_min_b < 0) {
     const char* e = getenv("MTJ_ATTN_STREAM_MIN_B");
-    stream_min_b = e ? atoi(e) : 1 << 30;
+    stream_min_b = e ? atoi(e) : 8;
   }
   if (a.B >= stream_min_b) {
     if (a.d_head == 256) return launch_decode_stream_dh<256>(a, s, pdl);

@@ -151,7 +151,7 @@ struct mtj_handle {
   bool mega_trace_on = false;
   // decode: attention runs on a side stream next to the FF half of the in-projection
   bool fork_attn = true;
-  bool tc_pdl = false;              // programmatic dependent launch on the tensor-core decode chain (MTJ_TC_PDL=1)
+  bool tc_pdl = true;               // programmatic dependent launch on the tensor-core decode chain (MTJ_NO_TC_PDL=1: off)
   bool fork_pdl = false;            // let the out-projection start early although it also waits on the side stream
   cudaStream_t side_stream = nullptr;
   cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
@@ -757,8 +757,8 @@ int32_t mtj_create(const mtj_config* c, mtj_handle** out) {
   h->use_pdl = !(e && e[0] == '1');
   e = getenv("MTJ_NO_MEGA");
   h->use_mega = !(e && e[0] == '1');
-  e = getenv("MTJ_TC_PDL");
-  h->tc_pdl = e && e[0] == '1';
+  e = getenv("MTJ_NO_TC_PDL");
+  h->tc_pdl = !(e && e[0] == '1');
   e = getenv("MTJ_NO_MEGA_PUSH");
   h->mega_push = !(e && e[0] == '1');
   e = getenv("MTJ_NO_FORK");
