@@ -157,9 +157,6 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
       tc_commit(acc_bar);                          // accumulator complete
     }
   } else {
-    const bool ok = nk > 0 && mbar_wait(acc_bar, 0);
-    if (!ok && nk > 0) atomicOr(&failed, 1u);
-    tc_fence_after();
     const int quad = warp & 3;                     // TMEM lanes this warp may read
     const int n = n0 + quad * 32 + lane;
     const bool n_ok = n < a.N;
@@ -182,8 +179,35 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
     } else if (n_ok) {
       bias = a.bias[n];
     }
+    // decode (row m = sequence b0 + m, every row at the same position): the rotation factors, and per
+    // 32-row chunk the left-pad limit and cache page of the sequence this LANE's index names, are fetched
+    // now, while the main loop runs; the store loop gets them by shuffle instead of dependent loads
+    constexpr int kChunks = BN / 32;
+    const bool dec = EPI == kEpiInProj && a.rows.Tc == 1;
+    int dpos = 0, dpad[kChunks], dpage[kChunks];
+    float2 dsc = make_float2(0.f, 1.f);
+    const bool rotary = EPI == kEpiInProj && n_ok && region < 2 && j < a.rot;
+    const bool kv_lane = EPI == kEpiInProj && n_ok && (region == 1 || region == 2);
+    const bool kv_warp = __any_sync(0xffffffffu, kv_lane);
+    if (dec) {
+      dpos = a.rows.pos0_dev ? *a.rows.pos0_dev : a.rows.pos0_host;
+      if (rotary) dsc = a.sincos[static_cast<size_t>(dpos) * (a.rot >> 1) + (j >> 1)];
+      const int slot = (dpos / kPageTokens) % a.kv.ring_pages;
+#pragma unroll
+      for (int c = 0; c < kChunks; ++c) {
+        const int m = m0 + c * 32 + lane;
+        const bool have = kv_warp && m < a.M;
+        dpad[c] = have ? a.kv.pad[a.rows.b0 + m] : 0x7fffffff;
+        dpage[c] = have ? a.kv.page_table[static_cast<size_t>(a.rows.b0 + m) * a.kv.ring_pages + slot] : 0;
+      }
+    }
+    const bool ok = nk > 0 && mbar_wait(acc_bar, 0);
+    if (!ok && nk > 0) atomicOr(&failed, 1u);
+    tc_fence_after();
     if (ok || (nk == 0 && a.partial)) {
-      for (int c0 = 0; c0 < BN; c0 += 32) {
+#pragma unroll
+      for (int cc = 0; cc < kChunks; ++cc) {
+        const int c0 = cc * 32;
         uint32_t r[32];
         if (ok) {
           tmem_ld32(tmem_acc + (static_cast<uint32_t>(quad * 32) << 16) + c0, r);
@@ -191,31 +215,26 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
 #pragma unroll
           for (int i = 0; i < 32; ++i) r[i] = 0u;      // an empty K range contributes zeros
         }
-        if (EPI == kEpiInProj && a.rows.Tc == 1) {
-          // decode: row m is sequence b0 + m and every row sits at the same position, so the rotation
-          // factors and the page slot are per-thread constants
-          const int pos = a.rows.pos0_dev ? *a.rows.pos0_dev : a.rows.pos0_host;
-          const bool rotary = n_ok && region < 2 && j < a.rot;
+        if (dec) {
+          const int pos = dpos;
           const bool any_rot = __any_sync(0xffffffffu, rotary);
           if (any_rot) {
-            const float2 t = rotary ? a.sincos[static_cast<size_t>(pos) * (a.rot >> 1) + (j >> 1)] : make_float2(0.f, 1.f);
-            const float sx = (j & 1) ? t.x : -t.x;
+            const float sx = (j & 1) ? dsc.x : -dsc.x;
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
               const float v = __uint_as_float(r[i]);
               const float partner = __shfl_xor_sync(0xffffffffu, v, 1);
-              if (rotary) r[i] = __float_as_uint(fmaf(v, t.y, partner * sx));
+              if (rotary) r[i] = __float_as_uint(fmaf(v, dsc.y, partner * sx));
             }
           }
           const int valid = min(32, a.M - (m0 + c0));
-          if (!n_ok || valid <= 0) {
-          } else if (region == 3) {
+          if (n_ok && valid > 0 && region == 3) {
             __nv_bfloat16* dst = a.act_out + static_cast<size_t>(m0 + c0) * (a.dl + a.ffl) + a.dl + nn;
             const size_t ld = static_cast<size_t>(a.dl + a.ffl);
 #pragma unroll
             for (int i = 0; i < 32; ++i)
               if (i < valid) dst[i * ld] = __float2bfloat16_rn(gelu_tanh(__uint_as_float(r[i]) + bias));
-          } else if (region == 0) {
+          } else if (n_ok && valid > 0 && region == 0) {
             float* dst = a.q_out + static_cast<size_t>(m0 + c0) * a.dl + nn;
 #pragma unroll
             for (int i = 0; i < 32; ++i)
@@ -226,18 +245,17 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
                 if (i < valid)
                   a.q_bf16[static_cast<size_t>(m0 + c0 + i) * a.dl + nn] = __float2bfloat16_rn(__uint_as_float(r[i]));
             }
-          } else {
+          }
+          if (kv_warp) {                               // warp-uniform: the shuffles below need every lane
             __nv_bfloat16* pool = (region == 1 ? a.kv.kpool : a.kv.vpool) +
                                   (static_cast<size_t>(head) * kPageTokens + (pos % kPageTokens)) * a.d_head + j;
             const size_t page_stride = static_cast<size_t>(a.heads) * kPageTokens * a.d_head;
-            const int slot = (pos / kPageTokens) % a.kv.ring_pages;
-            const int seq0 = a.rows.b0 + m0 + c0;
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
-              if (i < valid && pos >= a.kv.pad[seq0 + i]) {
-                const int page = a.kv.page_table[static_cast<size_t>(seq0 + i) * a.kv.ring_pages + slot];
+              const int padv = __shfl_sync(0xffffffffu, dpad[cc], i);
+              const int page = __shfl_sync(0xffffffffu, dpage[cc], i);
+              if (kv_lane && i < valid && pos >= padv)
                 pool[page * page_stride] = __float2bfloat16_rn(__uint_as_float(r[i]));
-              }
             }
           }
           continue;
