@@ -23,7 +23,7 @@ from oracle import spec  # noqa: E402
 
 def main():
     cfg = spec.tiny_config(1, seq=128)
-    params = spec.make_params(cfg, seed=0, stress=False)        # BASELINE config 0: N(0, 0.02), LN 1/0, biases 0
+    params = spec.make_params(cfg, seed=0, stress=False)        # the tiny CPU-parity configuration: N(0, 0.02), LN 1/0, biases 0
     ids = spec.token_ids(0, 2, 128, 512)                        # uniform ids [2, 128]
     net = go.CausalTransformer(cfg, params)
     logits = np.stack([net._shard().logits(ids[b]) for b in range(2)])
