@@ -32,7 +32,8 @@ int32_t fail(int32_t code, const std::string& msg) {
   } while (0)
 
 constexpr int kTcSplitMax = 8;      // split-K factor limit of the small-M out-projection
-constexpr int kTcSplitRows = 128;   // it is used up to this many token rows
+constexpr int kTcSplitRows = 128;
+constexpr int kTpPipeMinRows = 128; // a chunk is cut in two for all-reduce overlap only if each half keeps this many rows   // it is used up to this many token rows
 
 struct alignas(64) TensorMap { unsigned char bytes[128]; };   // a CUtensorMap
 
@@ -154,6 +155,31 @@ struct mtj_handle {
   bool tc_pdl = true;               // programmatic dependent launch on the tensor-core decode chain (MTJ_NO_TC_PDL=1: off)
   bool fork_pdl = false;            // let the out-projection start early although it also waits on the side stream
   cudaStream_t side_stream = nullptr;
+  // tensor-parallel prefill / eval: two row chunks are in flight, the all-reduce of one (on comm_stream)
+  // overlapping the layer of the other.  A view = one half of the row-indexed activation buffers.
+  struct ActView {
+    float *x, *stats, *part, *q;
+    __nv_bfloat16 *xn_bf16, *act_bf16, *q_bf16;
+    TensorMap map_xn[3], map_act[3], map_xn_wide, map_act_wide, map_q;
+  };
+  ActView views[2];
+  bool views_ok = false;
+  int view_rows[2] = {0, 0};
+  cudaStream_t comm_stream = nullptr;
+  cudaEvent_t ev_layer[2] = {nullptr, nullptr}, ev_reduced[2] = {nullptr, nullptr};
+  bool tp_pipe = false;             // MTJ_TP_PIPE=1: overlap the all-reduce of one chunk with the layer of the next
+  void save_view(int i) {
+    ActView& v = views[i];
+    v.x = x; v.stats = stats; v.part = part; v.q = q; v.xn_bf16 = xn_bf16; v.act_bf16 = act_bf16; v.q_bf16 = q_bf16;
+    for (int k = 0; k < 3; ++k) { v.map_xn[k] = map_xn[k]; v.map_act[k] = map_act[k]; }
+    v.map_xn_wide = map_xn_wide; v.map_act_wide = map_act_wide; v.map_q = map_q;
+  }
+  void use_view(int i) {
+    const ActView& v = views[i];
+    x = v.x; stats = v.stats; part = v.part; q = v.q; xn_bf16 = v.xn_bf16; act_bf16 = v.act_bf16; q_bf16 = v.q_bf16;
+    for (int k = 0; k < 3; ++k) { map_xn[k] = v.map_xn[k]; map_act[k] = v.map_act[k]; }
+    map_xn_wide = v.map_xn_wide; map_act_wide = v.map_act_wide; map_q = v.map_q;
+  }
   cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
 
   // decode step captured once per batch size and replayed (the step counter,
@@ -446,7 +472,7 @@ bool use_tc_wide(const mtj_handle* h, int M) { return h->tc_wide_ok && M > 192; 
 // The same layer for many token rows on the tensor cores: LayerNorm to bf16, in-proj GEMM
 // (RoPE / KV / GELU epilogue), causal attention, out-proj GEMM (+ bias + residual).
 int32_t run_layer_tc(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, const int32_t* key_limit,
-                     cudaStream_t s, float* detached_out = nullptr, bool decode = false) {
+                     cudaStream_t s, float* detached_out = nullptr, bool decode = false, bool defer_reduce = false) {
   LayerWeights& lw = h->layers[layer];
   // decode (graph-replayed, launch-latency sensitive): every kernel of the chain waits on its predecessor with
   // griddepcontrol.wait, so each may be scheduled while the previous one drains
@@ -562,7 +588,7 @@ int32_t run_layer_tc(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, c
     MTJ_CUDA(cudaMemcpyAsync(detached_out, h->part, sizeof(float) * M * h->d, cudaMemcpyDeviceToDevice, s));
     return MTJ_OK;
   }
-  if (h->mp > 1) return reduce_into_x(h, M, true, pdl, s);
+  if (h->mp > 1 && !defer_reduce) return reduce_into_x(h, M, true, pdl, s);
   return MTJ_OK;
 }
 
@@ -677,27 +703,88 @@ int32_t forward_chunks(mtj_handle* h, const uint32_t* ids, int ids_ld, int batch
   // positions [0, t_begin) are left padding in every sequence: their rows are never read, so they are not computed
   const int Tv = T - t_begin;
   if (Tv <= 0) return MTJ_OK;
-  int Tc = std::min(Tv, h->max_rows);
-  int nseq = std::max(1, h->max_rows / Tc);
+  // Tensor parallel, tensor-core path: pairs of chunks are walked layer by layer together, each in its own
+  // half of the activation buffers; while one chunk's partial sums are all-reduced on the communication
+  // stream the other chunk's layer runs.  Two position chunks of the same sequences keep their order
+  // inside a layer (the later one attends to the keys the earlier one has just written).
+  const bool piped = h->mp > 1 && h->tp_pipe && h->views_ok && h->view_rows[1] >= 64;
+  const int R = piped ? h->view_rows[1] : h->max_rows;
+  int Tc = std::min(Tv, R);
+  int nseq = std::max(1, R / Tc);
   if (Tc < Tv) nseq = 1;
-  for (int b0 = 0; b0 < batch; b0 += nseq) {
-    const int ns = std::min(nseq, batch - b0);
-    for (int t0 = t_begin; t0 < T; t0 += Tc) {
-      const int tc = std::min(Tc, T - t0);
-      mtj::RowMap rows = {b0, tc, t0, nullptr};
-      const int M = ns * tc;
-      int32_t rc = run_embed(h, ids, ids_ld, M, rows, false, s);
-      if (rc) return rc;
-      for (int l = 0; l < h->L; ++l) {
-        rc = use_tc(h, M) ? run_layer_tc(h, l, M, rows, key_limit, s)
-                          : run_layer(h, l, M, rows, false, key_limit, s);
-        if (rc) return rc;
-      }
-      rc = after_chunk(b0, ns, t0, tc);
-      if (rc) return rc;
+  struct Chunk { int b0, ns, t0, tc; };
+  std::vector<Chunk> chunks;
+  for (int b0 = 0; b0 < batch; b0 += nseq)
+    for (int t0 = t_begin; t0 < T; t0 += Tc) chunks.push_back({b0, std::min(nseq, batch - b0), t0, std::min(Tc, T - t0)});
+  if (piped && chunks.size() == 1 && chunks[0].ns * chunks[0].tc >= 2 * kTpPipeMinRows) {
+    // everything fits one chunk: cut it in two so that there is something to overlap with
+    const Chunk c = chunks[0];
+    chunks.clear();
+    if (c.ns >= 2) {
+      chunks.push_back({c.b0, c.ns / 2, c.t0, c.tc});
+      chunks.push_back({c.b0 + c.ns / 2, c.ns - c.ns / 2, c.t0, c.tc});
+    } else {
+      const int half = (c.tc + 1) / 2;
+      chunks.push_back({c.b0, 1, c.t0, half});
+      chunks.push_back({c.b0, 1, c.t0 + half, c.tc - half});
     }
   }
-  return MTJ_OK;
+  if (piped && !h->comm_stream) {
+    MTJ_CUDA(cudaStreamCreateWithFlags(&h->comm_stream, cudaStreamNonBlocking));
+    for (int i = 0; i < 2; ++i) {
+      MTJ_CUDA(cudaEventCreateWithFlags(&h->ev_layer[i], cudaEventDisableTiming));
+      MTJ_CUDA(cudaEventCreateWithFlags(&h->ev_reduced[i], cudaEventDisableTiming));
+    }
+  }
+  int32_t rc = MTJ_OK;
+  for (size_t i = 0; i < chunks.size() && !rc; i += 2) {
+    const int n = (i + 1 < chunks.size()) ? 2 : 1;
+    const bool overlap = piped && n == 2 && use_tc(h, chunks[i].ns * chunks[i].tc) &&
+                         use_tc(h, chunks[i + 1].ns * chunks[i + 1].tc);
+    if (!overlap) {
+      for (int k = 0; k < n && !rc; ++k) {
+        const Chunk& c = chunks[i + k];
+        mtj::RowMap rows = {c.b0, c.tc, c.t0, nullptr};
+        const int M = c.ns * c.tc;
+        rc = run_embed(h, ids, ids_ld, M, rows, false, s);
+        for (int l = 0; l < h->L && !rc; ++l)
+          rc = use_tc(h, M) ? run_layer_tc(h, l, M, rows, key_limit, s) : run_layer(h, l, M, rows, false, key_limit, s);
+        if (!rc) rc = after_chunk(c.b0, c.ns, c.t0, c.tc);
+      }
+      continue;
+    }
+    for (int k = 0; k < 2 && !rc; ++k) {
+      const Chunk& c = chunks[i + k];
+      mtj::RowMap rows = {c.b0, c.tc, c.t0, nullptr};
+      h->use_view(k);
+      rc = run_embed(h, ids, ids_ld, c.ns * c.tc, rows, false, s);
+    }
+    for (int l = 0; l < h->L && !rc; ++l) {
+      for (int k = 0; k < 2 && !rc; ++k) {
+        const Chunk& c = chunks[i + k];
+        mtj::RowMap rows = {c.b0, c.tc, c.t0, nullptr};
+        const int M = c.ns * c.tc;
+        h->use_view(k);
+        if (l > 0) MTJ_CUDA(cudaStreamWaitEvent(s, h->ev_reduced[k], 0));       // x of this chunk is complete
+        rc = run_layer_tc(h, l, M, rows, key_limit, s, nullptr, false, /*defer_reduce=*/true);
+        if (rc) break;
+        MTJ_CUDA(cudaEventRecord(h->ev_layer[k], s));
+        MTJ_CUDA(cudaStreamWaitEvent(h->comm_stream, h->ev_layer[k], 0));
+        rc = reduce_into_x(h, M, true, false, h->comm_stream);
+        if (rc) break;
+        MTJ_CUDA(cudaEventRecord(h->ev_reduced[k], h->comm_stream));
+      }
+    }
+    for (int k = 0; k < 2; ++k) MTJ_CUDA(cudaStreamWaitEvent(s, h->ev_reduced[k], 0));
+    for (int k = 0; k < 2 && !rc; ++k) {
+      const Chunk& c = chunks[i + k];
+      h->use_view(k);
+      rc = after_chunk(c.b0, c.ns, c.t0, c.tc);
+    }
+    h->use_view(0);
+  }
+  if (piped) h->use_view(0);
+  return rc;
 }
 
 }  // namespace
@@ -785,6 +872,11 @@ int32_t mtj_destroy(mtj_handle* h) {
     if (h->ev_fork) cudaEventDestroy(h->ev_fork);
     if (h->ev_join) cudaEventDestroy(h->ev_join);
     if (h->side_stream) cudaStreamDestroy(h->side_stream);
+    if (h->comm_stream) cudaStreamDestroy(h->comm_stream);
+    for (int i = 0; i < 2; ++i) {
+      if (h->ev_layer[i]) cudaEventDestroy(h->ev_layer[i]);
+      if (h->ev_reduced[i]) cudaEventDestroy(h->ev_reduced[i]);
+    }
     if (h->comm) mtj::comm_destroy(h->comm);
     for (int r = 0; r < mtj::kP2pMaxWorld; ++r)
       if (h->p2p_peer[r] && h->p2p_peer[r] != h->p2p_local) cudaIpcCloseMemHandle(h->p2p_peer[r]);
@@ -887,6 +979,36 @@ int32_t mtj_bind_arenas(mtj_handle* h, void* wdev, int64_t wbytes, void* sdev, i
       if (!ok) return fail(MTJ_ERR_CUDA, "cuTensorMapEncodeTiled failed (attention)");
       h->attn_tc_ok = true;
     }
+  }
+  // the two halves of the row-indexed activation buffers used by the tensor-parallel chunk pipeline
+  h->save_view(0);
+  h->views_ok = false;
+  if (h->mp > 1 && h->tc_ok) {
+    const int64_t r0 = (h->max_rows + 1) / 2, r1 = h->max_rows - r0;
+    mtj_handle::ActView& v = h->views[1];
+    v = h->views[0];
+    v.x = h->x + r0 * h->d;
+    v.stats = h->stats + r0 * 2;
+    v.part = h->part + r0 * h->d;
+    v.q = h->q + r0 * h->dl;
+    v.xn_bf16 = h->xn_bf16 + r0 * h->d;
+    v.act_bf16 = h->act_bf16 + r0 * (h->dl + h->ffl);
+    v.q_bf16 = h->q_bf16 + r0 * h->dl;
+    bool ok = r1 >= 1;
+    for (int i = 0; i < 3 && ok; ++i) {
+      const int box = 32 << i;
+      ok = ok && mtj::make_tensor_map_bf16(&v.map_xn[i], v.xn_bf16, r1, h->d, box) == cudaSuccess;
+      ok = ok && mtj::make_tensor_map_bf16(&v.map_act[i], v.act_bf16, r1, h->dl + h->ffl, box) == cudaSuccess;
+    }
+    const int bw = mtj::gemm_tc_wide_token_tile();
+    ok = ok && mtj::make_tensor_map_bf16(&v.map_xn_wide, v.xn_bf16, r1, h->d, bw) == cudaSuccess;
+    ok = ok && mtj::make_tensor_map_bf16(&v.map_act_wide, v.act_bf16, r1, h->dl + h->ffl, bw) == cudaSuccess;
+    if (h->attn_tc_ok) ok = ok && mtj::make_tensor_map_bf16(&v.map_q, v.q_bf16, r1, h->dl, 128) == cudaSuccess;
+    h->views_ok = ok;
+    h->view_rows[0] = static_cast<int>(r0);
+    h->view_rows[1] = static_cast<int>(r1);
+    const char* np = getenv("MTJ_TP_PIPE");
+    h->tp_pipe = np && np[0] == '1';
   }
   h->bound = true;
   h->loaded = 0;
