@@ -30,9 +30,10 @@ def test_shard_axis_host_helpers_on_two_cpu_ranks():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("mp", [2, 4])
-def test_tensor_parallel_generate_matches_oracle(mp):
+@pytest.mark.parametrize("mp,chunk_pipeline", [(2, "0"), (2, "1"), (4, "0")])
+def test_tensor_parallel_generate_matches_oracle(mp, chunk_pipeline):
+    """chunk_pipeline = "1": prefill / eval run as chunk pairs whose all-reduce overlaps the other chunk's layer."""
     import torch
     if torch.cuda.device_count() < mp:
         pytest.skip(f"needs {mp} GPUs")
-    _run(mp, {"NCCL_DEBUG": "WARN"}, 240)
+    _run(mp, {"NCCL_DEBUG": "WARN", "MTJ_TP_PIPE": chunk_pipeline}, 240)
