@@ -152,6 +152,8 @@ struct mtj_handle {
   bool mega_trace_on = false;
   // decode: attention runs on a side stream next to the FF half of the in-projection
   bool fork_attn = true;
+  int mega_max_b = 4;               // sequences the whole-step decode kernel is used for (MTJ_MEGA_MAX_B, up to 4)
+  int tc_decode_min_b = 8;          // from this many sequences on decode takes the tensor-core GEMM path (MTJ_TC_DECODE_MIN_B)
   bool tc_pdl = true;               // programmatic dependent launch on the tensor-core decode chain (MTJ_NO_TC_PDL=1: off)
   bool fork_pdl = false;            // let the out-projection start early although it also waits on the side stream
   cudaStream_t side_stream = nullptr;
@@ -617,7 +619,7 @@ int32_t run_logits_tc(mtj_handle* h, int M, int row0, float* out, cudaStream_t s
 
 bool use_tc(const mtj_handle* h, int M) { return h->tc_ok && M >= 32; }
 // decode: from this many sequences on, one tensor-core pass over the weights beats ceil(B/4) GEMV passes
-bool use_tc_decode(const mtj_handle* h, int B) { return h->tc_ok && B >= 8; }
+bool use_tc_decode(const mtj_handle* h, int B) { return h->tc_ok && B >= h->tc_decode_min_b; }
 
 int32_t run_embed(mtj_handle* h, const uint32_t* ids, int ids_ld, int M, const mtj::RowMap& rows,
                   bool decode, cudaStream_t s) {
@@ -844,6 +846,10 @@ int32_t mtj_create(const mtj_config* c, mtj_handle** out) {
   h->use_pdl = !(e && e[0] == '1');
   e = getenv("MTJ_NO_MEGA");
   h->use_mega = !(e && e[0] == '1');
+  e = getenv("MTJ_MEGA_MAX_B");
+  if (e) h->mega_max_b = std::max(0, std::min(4, atoi(e)));
+  e = getenv("MTJ_TC_DECODE_MIN_B");
+  if (e) h->tc_decode_min_b = std::max(1, atoi(e));
   e = getenv("MTJ_NO_TC_PDL");
   h->tc_pdl = !(e && e[0] == '1');
   e = getenv("MTJ_NO_MEGA_PUSH");
@@ -1229,7 +1235,7 @@ int32_t mtj_decode_step(mtj_handle* h, const uint32_t* tokens_in, const float* t
   auto enqueue = [&](cudaStream_t st) -> int32_t {
     mtj::RowMap rows = {0, 1, 0, h->cur};
     mtj::RowMap erows = {0, 1, 0, nullptr};
-    const bool mega = h->use_mega && (h->mp == 1 || use_p2p(h, B)) && B <= 4 && !h->profile && (h->d % 256) == 0;
+    const bool mega = h->use_mega && (h->mp == 1 || use_p2p(h, B)) && B <= h->mega_max_b && !h->profile && (h->d % 256) == 0;
     int32_t r = mega ? MTJ_OK : run_embed(h, h->tokens, 1, B, erows, true, st);
     if (r) return r;
     if (mega) {

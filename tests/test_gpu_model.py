@@ -296,3 +296,22 @@ def test_checkpoint_round_trip_through_the_network(cuda_device, tmp_path):
     other.load_ckpt(path)
     got = other.generate(ctx, [30], 8, {"top_p": np.zeros(1), "temp": np.ones(1)})[1][0]
     assert np.array_equal(got, want)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("batch", [2, 4])
+def test_whole_step_kernel_with_several_sequences(cuda_device, monkeypatch, batch):
+    """The persistent decode kernel is the default for one sequence only; MTJ_MEGA_MAX_B extends it to four."""
+    monkeypatch.setenv("MTJ_MEGA_MAX_B", "4")
+    cfg = spec.tiny_config(1, seq=128)
+    params = spec.make_params(cfg, seed=12, stress=True)
+    lens = np.array([90, 37, 128, 1][:batch], np.uint32)
+    ctx = np.zeros((batch, 128), np.uint32)
+    for b in range(batch):
+        ctx[b, 128 - lens[b]:] = spec.token_ids(40 + b, 1, int(lens[b]), 512)[0]
+    net = _net(cfg, params, cuda_device)
+    _, out = net.generate(ctx, lens, 16, {"top_p": np.zeros(batch), "temp": np.ones(batch)}, return_logits=True)
+    _, ref = go.CausalTransformer(cfg, params).generate(ctx, lens, 16, return_logits=True)
+    assert _rel(out[2], ref[2]) <= LOGIT_TOL
+    assert np.array_equal(out[0], ref[0])
+    net._rt.check_device_status()
