@@ -153,7 +153,7 @@ struct mtj_handle {
   // decode: attention runs on a side stream next to the FF half of the in-projection
   bool fork_attn = true;
   int mega_max_b = 4;               // sequences the whole-step decode kernel is used for (MTJ_MEGA_MAX_B, up to 4)
-  int tc_decode_min_b = 8;          // from this many sequences on decode takes the tensor-core GEMM path (MTJ_TC_DECODE_MIN_B)
+  int tc_decode_min_b = 5;          // from this many sequences on decode takes the tensor-core GEMM path (MTJ_TC_DECODE_MIN_B)
   bool tc_pdl = true;               // programmatic dependent launch on the tensor-core decode chain (MTJ_NO_TC_PDL=1: off)
   bool fork_pdl = false;            // let the out-projection start early although it also waits on the side stream
   cudaStream_t side_stream = nullptr;
