@@ -325,7 +325,7 @@ def run_mtj(args):
     rt.profile_enable(False)
     # phase time stamps of the persistent decode kernel (when it is the path in use)
     phases = None
-    if B <= int(os.environ.get("MTJ_MEGA_MAX_B", "4")) and os.environ.get("MTJ_NO_MEGA") != "1" \
+    if B <= int(os.environ.get("MTJ_MEGA_MAX_B", "1")) and os.environ.get("MTJ_NO_MEGA") != "1" \
             and os.environ.get("MTJ_NO_P2P") != "1":
         rt.mega_trace(True)
         for _ in range(3):

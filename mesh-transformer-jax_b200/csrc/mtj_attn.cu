@@ -226,8 +226,14 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attn_kernel(const DecodeA
       }
       for (; sidx < nsplit; ++sidx) O = fmaf(__ldcg(po + static_cast<size_t>(sidx) * DH), wgt[sidx], O);
       const size_t oi = static_cast<size_t>(b) * a.ld_out + head * DH + threadIdx.x;
-      if (a.out_bf16) a.out_bf16[oi] = __float2bfloat16_rn(O * inv_l);
-      else a.out[oi] = O * inv_l;
+      if (a.out_bf16) {
+        const float y = O * inv_l;
+        const __nv_bfloat16 hi = __float2bfloat16_rn(y);
+        a.out_bf16[oi] = hi;
+        if (a.out_lo) a.out_lo[oi] = __float2bfloat16_rn(y - __bfloat162float(hi));
+      } else {
+        a.out[oi] = O * inv_l;
+      }
     }
   }
   if (threadIdx.x == 0) a.counters[b * a.heads + head] = 0u;
@@ -441,8 +447,14 @@ __global__ void __launch_bounds__(kStreamThreads) decode_attn_stream_kernel(cons
       float O = 0.f;
       for (int sidx = 0; sidx < nsplit; ++sidx) O = fmaf(__ldcg(po + static_cast<size_t>(sidx) * DH), wgt[sidx], O);
       const size_t oi = static_cast<size_t>(b) * a.ld_out + head * DH + threadIdx.x;
-      if (a.out_bf16) a.out_bf16[oi] = __float2bfloat16_rn(O * inv_l);
-      else a.out[oi] = O * inv_l;
+      if (a.out_bf16) {
+        const float y = O * inv_l;
+        const __nv_bfloat16 hi = __float2bfloat16_rn(y);
+        a.out_bf16[oi] = hi;
+        if (a.out_lo) a.out_lo[oi] = __float2bfloat16_rn(y - __bfloat162float(hi));
+      } else {
+        a.out[oi] = O * inv_l;
+      }
     }
   }
   if (threadIdx.x == 0) a.counters[b * a.heads + head] = 0u;

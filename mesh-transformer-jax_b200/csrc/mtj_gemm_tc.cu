@@ -76,11 +76,16 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-template <int BN, int STAGES, int EPI>
+// HILO: the activations arrive as two bf16 operands, x = hi + lo (lo = the rounding error of hi), both
+// multiplied into the same accumulator: the product carries the activations to about 16 mantissa bits,
+// which is what keeps few-sequence decode on the tensor cores as accurate as the fp32-activation path.
+template <int BN, int STAGES, int EPI, bool HILO>
 __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
                                                              const __grid_constant__ CUtensorMap map_x,
+                                                             const __grid_constant__ CUtensorMap map_xlo,
                                                              const GemmTcArgs a) {
-  constexpr uint32_t kABytes = kBM * kBK * 2, kBBytes = BN * kBK * 2, kStageBytes = kABytes + kBBytes;
+  constexpr uint32_t kABytes = kBM * kBK * 2, kBBytes = BN * kBK * 2,
+                     kStageBytes = kABytes + (HILO ? 2 : 1) * kBBytes;
   constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
                               (static_cast<uint32_t>(kBM >> 4) << 24);
   extern __shared__ unsigned char tc_smem_raw[];
@@ -136,6 +141,7 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
         const uint32_t dst = smem_base + s * kStageBytes;
         tma_load_2d(dst, &map_w, (kb0 + kb) * kBK, n0, full_bar(s));
         tma_load_2d(dst + kABytes, &map_x, (kb0 + kb) * kBK, a.x_row0 + m0, full_bar(s));
+        if (HILO) tma_load_2d(dst + kABytes + kBBytes, &map_xlo, (kb0 + kb) * kBK, a.x_row0 + m0, full_bar(s));
       }
     }
   } else if (warp == 1) {
@@ -149,9 +155,12 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
         tc_fence_after();
         const uint32_t sa = smem_base + s * kStageBytes;
         const uint64_t adesc = smem_desc_sw128(sa), bdesc = smem_desc_sw128(sa + kABytes);
+        const uint64_t bdesc_lo = smem_desc_sw128(sa + kABytes + kBBytes);
 #pragma unroll
-        for (int k4 = 0; k4 < kBK / 16; ++k4)      // UMMA K = 16 bf16 = 32 bytes = 2 descriptor units
+        for (int k4 = 0; k4 < kBK / 16; ++k4) {    // UMMA K = 16 bf16 = 32 bytes = 2 descriptor units
           tc_mma_bf16(tmem_acc, adesc + 2 * k4, bdesc + 2 * k4, kIdesc, (kb > 0 || k4 > 0) ? 1u : 0u);
+          if (HILO) tc_mma_bf16(tmem_acc, adesc + 2 * k4, bdesc_lo + 2 * k4, kIdesc, 1u);
+        }
         tc_commit(empty_bar(s));                   // frees the stage once these MMAs have read it
       }
       tc_commit(acc_bar);                          // accumulator complete
@@ -232,8 +241,15 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
             __nv_bfloat16* dst = a.act_out + static_cast<size_t>(m0 + c0) * (a.dl + a.ffl) + a.dl + nn;
             const size_t ld = static_cast<size_t>(a.dl + a.ffl);
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (i < valid) dst[i * ld] = __float2bfloat16_rn(gelu_tanh(__uint_as_float(r[i]) + bias));
+            for (int i = 0; i < 32; ++i) {
+              if (i < valid) {
+                const float g = gelu_tanh(__uint_as_float(r[i]) + bias);
+                const __nv_bfloat16 hi = __float2bfloat16_rn(g);
+                dst[i * ld] = hi;
+                if (a.act_lo)
+                  a.act_lo[static_cast<size_t>(m0 + c0 + i) * ld + a.dl + nn] = __float2bfloat16_rn(g - __bfloat162float(hi));
+              }
+            }
           } else if (n_ok && valid > 0 && region == 0) {
             float* dst = a.q_out + static_cast<size_t>(m0 + c0) * a.dl + nn;
 #pragma unroll
@@ -612,7 +628,7 @@ __global__ void __launch_bounds__(kPThreads, 1) gemm_tc_persist_kernel(const __g
 // LayerNorm of fp32 rows into bf16 (the GEMM's activation operand), layers.py:17-36.
 __global__ void __launch_bounds__(256) ln_rows_kernel(const float* __restrict__ x, const float* __restrict__ scale,
                                                       const float* __restrict__ offset,
-                                                      __nv_bfloat16* __restrict__ out, int d) {
+                                                      __nv_bfloat16* __restrict__ out, __nv_bfloat16* out_lo, int d) {
   __shared__ float red[8];
   pdl_wait();
   pdl_launch_dependents();
@@ -638,8 +654,12 @@ __global__ void __launch_bounds__(256) ln_rows_kernel(const float* __restrict__ 
     v = fmaf(t, t, v);
   }
   const float rstd = 1.0f / sqrtf(block_sum(v) / static_cast<float>(d) + 1e-5f);
-  for (int i = threadIdx.x; i < d; i += 256)
-    o[i] = __float2bfloat16_rn(fmaf(scale[i] * rstd, xr[i] - mu, offset[i]));
+  for (int i = threadIdx.x; i < d; i += 256) {
+    const float y = fmaf(scale[i] * rstd, xr[i] - mu, offset[i]);
+    const __nv_bfloat16 hi = __float2bfloat16_rn(y);
+    o[i] = hi;
+    if (out_lo) out_lo[static_cast<size_t>(blockIdx.x) * d + i] = __float2bfloat16_rn(y - __bfloat162float(hi));
+  }
 }
 
 PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
@@ -654,12 +674,13 @@ PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
   return fn;
 }
 
-template <int BN, int STAGES, int EPI>
-cudaError_t launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const GemmTcArgs& a, cudaStream_t s, bool pdl) {
-  constexpr int smem = STAGES * (kBM * kBK * 2 + BN * kBK * 2) + 1024;
+template <int BN, int STAGES, int EPI, bool HILO = false>
+cudaError_t launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const GemmTcArgs& a, cudaStream_t s, bool pdl,
+                      const CUtensorMap* mxlo = nullptr) {
+  constexpr int smem = STAGES * (kBM * kBK * 2 + (HILO ? 2 : 1) * BN * kBK * 2) + 1024;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, EPI>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, EPI, HILO>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
     configured = true;
@@ -674,7 +695,7 @@ cudaError_t launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const GemmTc
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl ? 1 : 0;
-  return cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, STAGES, EPI>, mw, mx, a);
+  return cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, STAGES, EPI, HILO>, mw, mx, mxlo ? *mxlo : mx, a);
 }
 
 template <int EPI>
@@ -728,10 +749,30 @@ cudaError_t make_tensor_map_bf16(void* map_out, const void* base, int64_t rows, 
 }
 
 cudaError_t launch_gemm_tc(GemvEpilogue epi, const void* map_w, const void* map_x, const GemmTcArgs& a,
-                           cudaStream_t s, bool pdl) {
+                           cudaStream_t s, bool pdl, const void* map_x_lo) {
   if (a.M <= 0 || a.N <= 0 || a.K <= 0 || a.K % kBK) return cudaErrorInvalidValue;
   const CUtensorMap& mw = *static_cast<const CUtensorMap*>(map_w);
   const CUtensorMap& mx = *static_cast<const CUtensorMap*>(map_x);
+  if (map_x_lo) {
+    // hi + lo activations: token tiles of 32 or 64 rows only (few-sequence decode)
+    const CUtensorMap* ml = static_cast<const CUtensorMap*>(map_x_lo);
+    const int bnl = gemm_tc_token_tile_for(a.M);
+    if (bnl == 32) {
+      switch (epi) {
+        case kEpiInProj: return launch_tc<32, 4, kEpiInProj, true>(mw, mx, a, s, pdl, ml);
+        case kEpiOut: return launch_tc<32, 4, kEpiOut, true>(mw, mx, a, s, pdl, ml);
+        default: return launch_tc<32, 4, kEpiLogits, true>(mw, mx, a, s, pdl, ml);
+      }
+    }
+    if (bnl == 64) {
+      switch (epi) {
+        case kEpiInProj: return launch_tc<64, 3, kEpiInProj, true>(mw, mx, a, s, pdl, ml);
+        case kEpiOut: return launch_tc<64, 3, kEpiOut, true>(mw, mx, a, s, pdl, ml);
+        default: return launch_tc<64, 3, kEpiLogits, true>(mw, mx, a, s, pdl, ml);
+      }
+    }
+    return cudaErrorInvalidValue;
+  }
   // Few token rows (batched decode) stream the weights once: a narrower token tile leaves room for a
   // deeper TMA ring, i.e. more weight bytes in flight per block.
   const int bn = gemm_tc_token_tile_for(a.M);
@@ -797,7 +838,7 @@ cudaError_t launch_splitk_reduce(const float* partial, int ksplit, int M, int N,
 }
 
 cudaError_t launch_ln_rows(const float* x, const float* scale, const float* offset, __nv_bfloat16* out, int rows,
-                           int d, cudaStream_t s, bool pdl) {
+                           int d, cudaStream_t s, bool pdl, __nv_bfloat16* out_lo) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(rows);
   cfg.blockDim = dim3(256);
@@ -807,7 +848,7 @@ cudaError_t launch_ln_rows(const float* x, const float* scale, const float* offs
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl ? 1 : 0;
-  return cudaLaunchKernelEx(&cfg, ln_rows_kernel, x, scale, offset, out, d);
+  return cudaLaunchKernelEx(&cfg, ln_rows_kernel, x, scale, offset, out, out_lo, d);
 }
 
 }  // namespace mtj

@@ -92,6 +92,7 @@ struct DecodeAttnArgs {
   uint32_t* counters;          // [B*heads] zero-initialised, self-resetting
   float* out;                  // act2 base: out[b*ld_out + head*d_head + j] (fp32), or
   __nv_bfloat16* out_bf16;     // the same element in bf16 (operand of the tensor-core out-proj)
+  __nv_bfloat16* out_lo;       // optional, with out_bf16: the bf16 rounding error of that element
   int ld_out;
   uint32_t* dev_err;           // may be null
 };
@@ -195,6 +196,7 @@ struct GemmTcArgs {
   float* q_out;                // [M, dl] fp32
   __nv_bfloat16* q_bf16;       // optional [M, dl] bf16 copy (operand of the tensor-core attention)
   __nv_bfloat16* act_out;      // [M, dl + ffl] bf16: gelu(ff) goes to columns [dl, dl + ffl)
+  __nv_bfloat16* act_lo;       // optional [M, dl + ffl]: bf16 rounding error of act_out (decode epilogue only)
   KvCache kv;
   const float* bias;           // [N] (out-proj, logits)
   const float* residual;       // [M, N] or null
@@ -211,15 +213,17 @@ cudaError_t launch_splitk_reduce(const float* partial, int ksplit, int M, int N,
                                  const float* residual, float* out, int ld_out, const uint32_t* slot_sel,
                                  size_t slot_stride, cudaStream_t s, bool pdl = false);
 cudaError_t make_tensor_map_bf16(void* map_out_128B, const void* base, int64_t rows, int64_t K, int box_rows);
+// map_x_lo (optional, M <= 64): a second activation view holding the bf16 rounding error of the first
+// (x = hi + lo); both are multiplied into the same accumulator.
 cudaError_t launch_gemm_tc(GemvEpilogue epi, const void* map_w, const void* map_x, const GemmTcArgs& a,
-                           cudaStream_t s, bool pdl);
+                           cudaStream_t s, bool pdl, const void* map_x_lo = nullptr);
 // Persistent 128 x 256 variant for many token rows; map_x must have been made with box_rows =
 // gemm_tc_wide_token_tile().  No split-K.
 int gemm_tc_wide_token_tile();
 cudaError_t launch_gemm_tc_wide(GemvEpilogue epi, const void* map_w, const void* map_x, const GemmTcArgs& a,
                                 cudaStream_t s);
 cudaError_t launch_ln_rows(const float* x, const float* scale, const float* offset, __nv_bfloat16* out, int rows,
-                           int d, cudaStream_t s, bool pdl = false);
+                           int d, cudaStream_t s, bool pdl = false, __nv_bfloat16* out_lo = nullptr);
 
 struct SampleArgs {
   const float* logits;         // [rows, V]

@@ -33,6 +33,7 @@ int32_t fail(int32_t code, const std::string& msg) {
 
 constexpr int kTcSplitMax = 8;      // split-K factor limit of the small-M out-projection
 constexpr int kTcSplitRows = 128;
+constexpr int kHiLoRows = 64;       // decode rows that can carry hi + lo activations
 constexpr int kTpPipeMinRows = 128; // a chunk is cut in two for all-reduce overlap only if each half keeps this many rows   // it is used up to this many token rows
 
 struct alignas(64) TensorMap { unsigned char bytes[128]; };   // a CUtensorMap
@@ -116,6 +117,12 @@ struct mtj_handle {
   TensorMap map_xn_wide, map_act_wide;   // 256-row boxes for the persistent GEMM
   __nv_bfloat16* q_bf16 = nullptr;    // [max_rows, dl] rotated queries for the tensor-core attention
   bool attn_tc_ok = false;
+  // few-sequence decode: the bf16 rounding errors of the two activation operands (x = hi + lo), rows [0, kHiLoRows)
+  __nv_bfloat16* xn_lo = nullptr;
+  __nv_bfloat16* act_lo = nullptr;
+  TensorMap map_xn_lo[2], map_act_lo[2];   // 32 / 64-row boxes
+  bool hilo_ok = false;
+  int tc_hilo_max_b = 4;            // up to this many sequences the activations travel as hi + lo (MTJ_TC_HILO_MAX_B, 0: never)
   bool tc_wide_ok = false;
   bool mega_push = true;     // per-block push exchange inside the persistent decode kernel (MTJ_NO_MEGA_PUSH=1: slot protocol)   // persistent 128 x 256 GEMM for long chunks
   float* tc_partial = nullptr;        // [kTcSplitMax, kTcSplitRows, d] split-K partial sums of small-M out-projections
@@ -152,8 +159,8 @@ struct mtj_handle {
   bool mega_trace_on = false;
   // decode: attention runs on a side stream next to the FF half of the in-projection
   bool fork_attn = true;
-  int mega_max_b = 4;               // sequences the whole-step decode kernel is used for (MTJ_MEGA_MAX_B, up to 4)
-  int tc_decode_min_b = 5;          // from this many sequences on decode takes the tensor-core GEMM path (MTJ_TC_DECODE_MIN_B)
+  int mega_max_b = 1;               // sequences the whole-step decode kernel is used for (MTJ_MEGA_MAX_B, up to 4)
+  int tc_decode_min_b = 2;          // from this many sequences on decode takes the tensor-core GEMM path (MTJ_TC_DECODE_MIN_B)
   bool tc_pdl = true;               // programmatic dependent launch on the tensor-core decode chain (MTJ_NO_TC_PDL=1: off)
   bool fork_pdl = false;            // let the out-projection start early although it also waits on the side stream
   cudaStream_t side_stream = nullptr;
@@ -254,6 +261,8 @@ struct mtj_handle {
     q_bf16 = c.take<__nv_bfloat16>(R * dl);
     xn_bf16 = c.take<__nv_bfloat16>(R * d);
     act_bf16 = c.take<__nv_bfloat16>(R * (dl + ffl));
+    xn_lo = c.take<__nv_bfloat16>(std::min<int64_t>(R, kHiLoRows) * d);
+    act_lo = c.take<__nv_bfloat16>(std::min<int64_t>(R, kHiLoRows) * (dl + ffl));
     eval_rows = static_cast<int>(std::min<int64_t>(R, 256));
     eval_logits = c.take<float>(static_cast<int64_t>(eval_rows) * Vl);
     ce_max = c.take<float>(R);
@@ -479,7 +488,9 @@ int32_t run_layer_tc(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, c
   // decode (graph-replayed, launch-latency sensitive): every kernel of the chain waits on its predecessor with
   // griddepcontrol.wait, so each may be scheduled while the previous one drains
   const bool pdl = h->use_pdl && h->tc_pdl && decode;
-  MTJ_CUDA(mtj::launch_ln_rows(h->x, lw.ln_scale, lw.ln_offset, h->xn_bf16, M, h->d, s, pdl));
+  // few sequences: activations go through the GEMMs as hi + lo bf16 pairs
+  const bool hilo = decode && h->hilo_ok && M <= h->tc_hilo_max_b;
+  MTJ_CUDA(mtj::launch_ln_rows(h->x, lw.ln_scale, lw.ln_offset, h->xn_bf16, M, h->d, s, pdl, hilo ? h->xn_lo : nullptr));
   mtj::GemmTcArgs a = {};
   a.M = M;
   a.N = 3 * h->dl + h->ffl;
@@ -495,6 +506,7 @@ int32_t run_layer_tc(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, c
   a.q_out = h->q;
   a.q_bf16 = (h->attn_tc_ok && !decode) ? h->q_bf16 : nullptr;
   a.act_out = h->act_bf16;
+  a.act_lo = hilo ? h->act_lo : nullptr;
   a.kv = h->kv(layer);
   a.dev_err = h->dev_err;
   h->prof_begin(MTJ_FAMILY_INPROJ, s);
@@ -502,7 +514,8 @@ int32_t run_layer_tc(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, c
   if (wide)
     MTJ_CUDA(mtj::launch_gemm_tc_wide(mtj::kEpiInProj, &lw.map_in, &h->map_xn_wide, a, s));
   else
-    MTJ_CUDA(mtj::launch_gemm_tc(mtj::kEpiInProj, &lw.map_in, &h->map_xn[tc_tile_index(M)], a, s, pdl));
+    MTJ_CUDA(mtj::launch_gemm_tc(mtj::kEpiInProj, &lw.map_in, &h->map_xn[tc_tile_index(M)], a, s, pdl,
+                                 hilo ? &h->map_xn_lo[tc_tile_index(M)] : nullptr));
   h->prof_end(s);
 
   h->prof_begin(MTJ_FAMILY_ATTN, s);
@@ -522,6 +535,7 @@ int32_t run_layer_tc(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, c
     d.part_ml = h->part_ml;
     d.counters = h->counters;
     d.out_bf16 = h->act_bf16;
+    d.out_lo = hilo ? h->act_lo : nullptr;
     d.ld_out = h->dl + h->ffl;
     MTJ_CUDA(mtj::launch_decode_attn(d, s, pdl));
   } else if (h->attn_tc_ok) {
@@ -572,14 +586,16 @@ int32_t run_layer_tc(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, c
     const float* res = o.residual;
     o.partial = h->tc_partial;
     o.ksplit = ksplit;
-    MTJ_CUDA(mtj::launch_gemm_tc(mtj::kEpiOut, &lw.map_out, &h->map_act[tc_tile_index(M)], o, s, pdl));
+    MTJ_CUDA(mtj::launch_gemm_tc(mtj::kEpiOut, &lw.map_out, &h->map_act[tc_tile_index(M)], o, s, pdl,
+                                 hilo ? &h->map_act_lo[tc_tile_index(M)] : nullptr));
     MTJ_CUDA(mtj::launch_splitk_reduce(h->tc_partial, ksplit, M, h->d, lw.b_out, res, dst, h->d,
                                        to_slot ? partial_slot_sel(h, M) : nullptr, partial_slot_stride(h), s, pdl));
     h->launches++;
   } else if (wide) {
     MTJ_CUDA(mtj::launch_gemm_tc_wide(mtj::kEpiOut, &lw.map_out, &h->map_act_wide, o, s));
   } else {
-    MTJ_CUDA(mtj::launch_gemm_tc(mtj::kEpiOut, &lw.map_out, &h->map_act[tc_tile_index(M)], o, s, pdl));
+    MTJ_CUDA(mtj::launch_gemm_tc(mtj::kEpiOut, &lw.map_out, &h->map_act[tc_tile_index(M)], o, s, pdl,
+                                 hilo ? &h->map_act_lo[tc_tile_index(M)] : nullptr));
   }
   h->prof_end(s);
   h->launches += 4;
@@ -595,9 +611,12 @@ int32_t run_layer_tc(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, c
 }
 
 // final LayerNorm + vocab-sharded logits for rows [row0, row0 + M) of h->x on the tensor cores
-int32_t run_logits_tc(mtj_handle* h, int M, int row0, float* out, cudaStream_t s, bool pdl = false) {
+int32_t run_logits_tc(mtj_handle* h, int M, int row0, float* out, cudaStream_t s, bool pdl = false,
+                      bool decode = false) {
+  const bool hilo = decode && row0 == 0 && h->hilo_ok && M <= h->tc_hilo_max_b;
   MTJ_CUDA(mtj::launch_ln_rows(h->x + static_cast<size_t>(row0) * h->d, h->lnf_scale, h->lnf_offset,
-                               h->xn_bf16 + static_cast<size_t>(row0) * h->d, M, h->d, s, pdl));
+                               h->xn_bf16 + static_cast<size_t>(row0) * h->d, M, h->d, s, pdl,
+                               hilo ? h->xn_lo : nullptr));
   mtj::GemmTcArgs a = {};
   a.M = M;
   a.N = h->Vl;
@@ -611,7 +630,8 @@ int32_t run_logits_tc(mtj_handle* h, int M, int row0, float* out, cudaStream_t s
   if (use_tc_wide(h, M))
     MTJ_CUDA(mtj::launch_gemm_tc_wide(mtj::kEpiLogits, &h->map_proj, &h->map_xn_wide, a, s));
   else
-    MTJ_CUDA(mtj::launch_gemm_tc(mtj::kEpiLogits, &h->map_proj, &h->map_xn[tc_tile_index(M)], a, s, pdl));
+    MTJ_CUDA(mtj::launch_gemm_tc(mtj::kEpiLogits, &h->map_proj, &h->map_xn[tc_tile_index(M)], a, s, pdl,
+                                 hilo ? &h->map_xn_lo[tc_tile_index(M)] : nullptr));
   h->prof_end(s);
   h->launches += 2;
   return MTJ_OK;
@@ -971,6 +991,17 @@ int32_t mtj_bind_arenas(mtj_handle* h, void* wdev, int64_t wbytes, void* sdev, i
     ok = ok && mtj::make_tensor_map_bf16(&h->map_xn_wide, h->xn_bf16, h->max_rows, h->d, bw) == cudaSuccess;
     ok = ok && mtj::make_tensor_map_bf16(&h->map_act_wide, h->act_bf16, h->max_rows, h->dl + h->ffl, bw) == cudaSuccess;
     h->tc_wide_ok = ok && !getenv("MTJ_NO_TC_WIDE");
+    {
+      const int64_t rl = std::min<int64_t>(h->max_rows, kHiLoRows);
+      bool okl = ok;
+      for (int i = 0; i < 2 && okl; ++i) {
+        okl = okl && mtj::make_tensor_map_bf16(&h->map_xn_lo[i], h->xn_lo, rl, h->d, 32 << i) == cudaSuccess;
+        okl = okl && mtj::make_tensor_map_bf16(&h->map_act_lo[i], h->act_lo, rl, h->dl + h->ffl, 32 << i) == cudaSuccess;
+      }
+      h->hilo_ok = okl;
+      const char* hl = getenv("MTJ_TC_HILO_MAX_B");
+      if (hl) h->tc_hilo_max_b = std::max(0, std::min(kHiLoRows, atoi(hl)));
+    }
     if (!ok) return fail(MTJ_ERR_CUDA, "cuTensorMapEncodeTiled failed");
     h->tc_ok = true;
     const char* no_atc = getenv("MTJ_NO_ATTN_TC");
@@ -1274,7 +1305,7 @@ int32_t mtj_decode_step(mtj_handle* h, const uint32_t* tokens_in, const float* t
       if (r) return r;
     }
     if (!mega) {
-      r = tc ? run_logits_tc(h, B, 0, h->logits, st, h->use_pdl && h->tc_pdl) : run_logits(h, B, nullptr, h->logits, true, st);
+      r = tc ? run_logits_tc(h, B, 0, h->logits, st, h->use_pdl && h->tc_pdl, true) : run_logits(h, B, nullptr, h->logits, true, st);
       if (r) return r;
     }
     if (h->mp > 1) {
