@@ -34,7 +34,7 @@ int32_t fail(int32_t code, const std::string& msg) {
 constexpr int kTcSplitMax = 8;      // split-K factor limit of the small-M out-projection
 constexpr int kTcSplitRows = 128;
 constexpr int kHiLoRows = 64;       // decode rows that can carry hi + lo activations
-constexpr int kTpPipeMinRows = 128; // a chunk is cut in two for all-reduce overlap only if each half keeps this many rows   // it is used up to this many token rows
+constexpr int kTpPipeMinRows = 128; // a chunk is cut in two for all-reduce overlap only if each half keeps this many rows
 
 struct alignas(64) TensorMap { unsigned char bytes[128]; };   // a CUtensorMap
 
@@ -81,7 +81,8 @@ struct mtj_handle {
   __nv_bfloat16* proj_w = nullptr;
   float* proj_b = nullptr;
   float2* sincos = nullptr;
-  int64_t loaded = 0, expected = 0;
+  std::vector<uint8_t> leaf_loaded;   // one mark per parameter leaf (embedding 2, 10 per layer, projection 4)
+  int64_t expected = 0;
 
   // workspace
   float* x = nullptr;
@@ -123,8 +124,8 @@ struct mtj_handle {
   TensorMap map_xn_lo[2], map_act_lo[2];   // 32 / 64-row boxes
   bool hilo_ok = false;
   int tc_hilo_max_b = 4;            // up to this many sequences the activations travel as hi + lo (MTJ_TC_HILO_MAX_B, 0: never)
-  bool tc_wide_ok = false;
-  bool mega_push = true;     // per-block push exchange inside the persistent decode kernel (MTJ_NO_MEGA_PUSH=1: slot protocol)   // persistent 128 x 256 GEMM for long chunks
+  bool tc_wide_ok = false;   // persistent 128 x 256 GEMM for long chunks
+  bool mega_push = true;     // per-block push exchange inside the persistent decode kernel (MTJ_NO_MEGA_PUSH=1: slot protocol)
   float* tc_partial = nullptr;        // [kTcSplitMax, kTcSplitRows, d] split-K partial sums of small-M out-projections
   int eval_rows = 0;                // rows of logits materialised at a time by the loss path
   float* eval_logits = nullptr;     // [eval_rows, Vl]
@@ -694,8 +695,10 @@ int32_t run_logits(mtj_handle* h, int M, const int32_t* row_select, float* out, 
 int32_t check_ready(const mtj_handle* h) {
   if (!h) return fail(MTJ_ERR_INVALID, "null handle");
   if (!h->bound) return fail(MTJ_ERR_STATE, "arenas not bound (mtj_bind_arenas)");
-  if (h->loaded != h->expected)
-    return fail(MTJ_ERR_STATE, "parameters missing: loaded " + std::to_string(h->loaded) + " of " +
+  int64_t loaded = 0;
+  for (uint8_t m : h->leaf_loaded) loaded += m;
+  if (loaded != h->expected)
+    return fail(MTJ_ERR_STATE, "parameters missing: loaded " + std::to_string(loaded) + " of " +
                                    std::to_string(h->expected));
   return MTJ_OK;
 }
@@ -1048,7 +1051,7 @@ int32_t mtj_bind_arenas(mtj_handle* h, void* wdev, int64_t wbytes, void* sdev, i
     h->tp_pipe = np && np[0] == '1';
   }
   h->bound = true;
-  h->loaded = 0;
+  h->leaf_loaded.assign(static_cast<size_t>(h->expected), 0);
   return MTJ_OK;
 }
 
@@ -1084,8 +1087,11 @@ int32_t mtj_load_param(mtj_handle* h, const char* name, const void* src, int32_t
   };
   auto bad_shape = [&]() { return fail(MTJ_ERR_INVALID, std::string("shape mismatch for ") + name); };
   const int d = h->d, dl = h->dl, ffl = h->ffl, Vl = h->Vl;
+  // which leaf this is: a leaf loaded twice overwrites itself and cannot stand in for a missing one
+  int64_t leaf_id = -1;
 
   if (mod == "embedding_shard" && lay == "linear") {
+    leaf_id = leaf == "w" ? 0 : 1;
     if (leaf == "w") {
       if (!want({Vl, d})) return bad_shape();
       MTJ_CUDA(mtj::launch_to_bf16(src, bf, static_cast<int64_t>(Vl) * d, h->emb_w, s));
@@ -1096,13 +1102,17 @@ int32_t mtj_load_param(mtj_handle* h, const char* name, const void* src, int32_t
       return fail(MTJ_ERR_INVALID, std::string("unknown leaf: ") + name);
     }
   } else if (mod == "projection_shard") {
+    const int64_t base = 2 + 10LL * h->L;
     if (lay == "replicated_layer_norm" && (leaf == "scale" || leaf == "offset")) {
       if (!want({d})) return bad_shape();
+      leaf_id = base + (leaf == "scale" ? 0 : 1);
       MTJ_CUDA(mtj::launch_to_f32(src, bf, d, leaf == "scale" ? h->lnf_scale : h->lnf_offset, s));
     } else if (lay == "linear" && leaf == "w") {
+      leaf_id = base + 2;
       if (!want({d, Vl})) return bad_shape();
       MTJ_CUDA(mtj::launch_pack_transpose(src, bf, d, Vl, h->proj_w, d, 0, s));
     } else if (lay == "linear" && leaf == "b") {
+      leaf_id = base + 3;
       if (!want({Vl})) return bad_shape();
       MTJ_CUDA(mtj::launch_to_f32(src, bf, Vl, h->proj_b, s));
     } else {
@@ -1113,18 +1123,23 @@ int32_t mtj_load_param(mtj_handle* h, const char* name, const void* src, int32_t
     if (li < 0 || li >= h->L) return fail(MTJ_ERR_INVALID, std::string("layer out of range: ") + name);
     LayerWeights& lw = h->layers[li];
     const int kin = dl + ffl;
+    const int64_t base = 2 + 10LL * li;
     if (lay == "replicated_layer_norm" && (leaf == "scale" || leaf == "offset")) {
+      leaf_id = base + (leaf == "scale" ? 0 : 1);
       if (!want({d})) return bad_shape();
       MTJ_CUDA(mtj::launch_to_f32(src, bf, d, leaf == "scale" ? lw.ln_scale : lw.ln_offset, s));
     } else if (leaf == "w" && (lay == "linear" || lay == "linear_1" || lay == "linear_2")) {
       // q -> rows [0, dl), k (linear_2) -> [dl, 2dl), v (linear_1) -> [2dl, 3dl)
       if (!want({d, dl})) return bad_shape();
       const int region = lay == "linear" ? 0 : (lay == "linear_2" ? 1 : 2);
+      leaf_id = base + 2 + region;
       MTJ_CUDA(mtj::launch_pack_transpose(src, bf, d, dl, lw.w_in + static_cast<size_t>(region) * dl * d, d, 0, s));
     } else if (leaf == "w" && lay == "linear_3") {
       if (!want({dl, d})) return bad_shape();
+      leaf_id = base + 5;
       MTJ_CUDA(mtj::launch_pack_transpose(src, bf, dl, d, lw.w_out, kin, 0, s));
     } else if (lay == "linear_4") {
+      leaf_id = base + (leaf == "w" ? 6 : 7);
       if (leaf == "w") {
         if (!want({d, ffl})) return bad_shape();
         MTJ_CUDA(mtj::launch_pack_transpose(src, bf, d, ffl, lw.w_in + static_cast<size_t>(3) * dl * d, d, 0, s));
@@ -1135,6 +1150,7 @@ int32_t mtj_load_param(mtj_handle* h, const char* name, const void* src, int32_t
         return fail(MTJ_ERR_INVALID, std::string("unknown leaf: ") + name);
       }
     } else if (lay == "linear_5") {
+      leaf_id = base + (leaf == "w" ? 8 : 9);
       if (leaf == "w") {
         if (!want({ffl, d})) return bad_shape();
         MTJ_CUDA(mtj::launch_pack_transpose(src, bf, ffl, d, lw.w_out, kin, dl, s));
@@ -1150,7 +1166,9 @@ int32_t mtj_load_param(mtj_handle* h, const char* name, const void* src, int32_t
   } else {
     return fail(MTJ_ERR_INVALID, std::string("unknown module: ") + name);
   }
-  h->loaded++;
+  if (leaf_id < 0 || leaf_id >= static_cast<int64_t>(h->leaf_loaded.size()))
+    return fail(MTJ_ERR_INVALID, std::string("unknown leaf: ") + name);
+  h->leaf_loaded[static_cast<size_t>(leaf_id)] = 1;
   return MTJ_OK;
 }
 

@@ -142,8 +142,16 @@ class CausalTransformer:
             leaves = [_from_numpy(a) for a in read_shard(f"{path}shard_{self.rank}/")]
             slim = {k: v for k, v in self._state.items() if k != "opt_state"}
             flat = tree_flatten(slim)
+            if len(leaves) > len(flat):
+                # a training checkpoint: optimizer-state leaves come first in flatten order
+                # ("opt_state" < "params" < "step"); the callers of this path delete them (device_sample.py:74-79)
+                leaves = leaves[len(leaves) - len(flat):]
             if len(leaves) != len(flat):
                 raise AssertionError(f"Incompatible checkpoints: {len(leaves)} leaves on disk, {len(flat)} expected")
+            for a, (_, old) in zip(leaves, flat):
+                if a.numel() > 1 and tuple(a.shape) != tuple(old.shape) and tuple(a.shape) != tuple(old.shape[1:]):
+                    raise AssertionError(f"Incompatible checkpoints: leaf of shape {tuple(a.shape)} where "
+                                         f"{tuple(old.shape)} is expected")
             new = tree_unflatten(slim, [a if a.dim() == 0 or tuple(a.shape) == tuple(old.shape) else a[None]
                                         for a, (_, old) in zip(leaves, flat)])
         else:
@@ -201,12 +209,14 @@ class CausalTransformer:
             loss, correct = rt.eval_loss(torch.from_numpy(obs.view(np.int32)).to(self.device),
                                          torch.from_numpy(tgt.view(np.int32)).to(self.device), ctx_length)
             all_loss = loss.cpu().numpy()
+            rt.check_device_status()
             return {"loss": all_loss.mean(-1), "last_loss": all_loss[:, -1], "all_loss": all_loss,
                     "correct": correct.cpu().numpy().astype(bool)}
 
     # -- generate ------------------------------------------------------------
     def generate(self, ctx, ctx_length, gen_length, sampler_options=None, return_logits=False, uniforms=None):
-        """transformer_shard.py:326-339.  ``ctx`` is [batch, seq] left-padded
+        """transformer_shard.py:326-339.  A config without ``"sampler"`` (a KeyError in the reference,
+        :191) samples with ``nucleaus_sample``.  ``ctx`` is [batch, seq] left-padded
         token ids, ``ctx_length`` the number of real tokens per row.  Returns
         ``(final_state, (tokens[batch, gen, 1] uint32, None[, logits]))`` like
         the reference's scan output.  ``uniforms`` ([gen, batch, n_vocab] in
@@ -233,7 +243,9 @@ class CausalTransformer:
         if sampler is not None and name not in ("nucleaus_sample", "softmax_sample"):
             raise NotImplementedError("only nucleaus_sample / softmax_sample run on the device path")
         rt = self._runtime(batch, gen_length)
-        top_p = np.asarray(sampler_options.get("top_p", np.zeros(batch)), dtype=np.float32).reshape(batch)
+        # options the caller leaves out take nucleaus_sample's own defaults (sampling.py:41: top_p 0.9, temp 1);
+        # the arg-max shortcut below is taken only for an explicit top_p == 0 on every row
+        top_p = np.asarray(sampler_options.get("top_p", np.full(batch, 0.9)), dtype=np.float32).reshape(batch)
         temp = np.asarray(sampler_options.get("temp", np.ones(batch)), dtype=np.float32).reshape(batch)
         if "top_k" in sampler_options and sampler_options["top_k"] is not None:
             raise NotImplementedError("the reference's top_k branch is outside this path")
@@ -267,6 +279,7 @@ class CausalTransformer:
                         draw_uniforms(gen, (batch, self.config["n_vocab"]), self.device)
                 shard.generate_once(None, toks[t], None if logits is None else logits[t], **samp)
             out_tokens = toks.cpu().numpy().view(np.uint32).T[:, :, None]
+            rt.check_device_status()       # a bounded device-side wait that ran out must not pass as a result
             output = (out_tokens, None)
             if return_logits:
                 output = output + (logits.permute(1, 0, 2)[:, :, None, :].cpu().numpy(),)

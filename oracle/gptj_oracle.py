@@ -126,7 +126,7 @@ class EmbeddingShard:
             hit = (local >= 0) & (local < self.in_dim_per_shard)
             rows = self.w[s][np.where(hit, local, 0)].astype(F32)
             rows = rows * hit[:, None].astype(F32)
-            outs.append(rows + self.b[s].astype(F32))
+            outs.append(rows + self.b[s].astype(F32, copy=False))
         return g_psum(outs)
 
 
@@ -171,20 +171,20 @@ class TransformerLayerShard:
         weights = softmax(logits)
         vec = np.einsum("htT,Thd->thd", weights, v, optimize=True).astype(F32)
         vec = vec.reshape((-1, self.dim_per_shard))
-        return vec @ self.o_w[s].astype(F32)
+        return vec @ self.o_w[s].astype(F32, copy=False)
 
     # layers.py:287-290
     def ff(self, s, x):
-        h = x @ self.ff_in["w"][s].astype(F32) + self.ff_in["b"][s].astype(F32)
+        h = x @ self.ff_in["w"][s].astype(F32, copy=False) + self.ff_in["b"][s].astype(F32, copy=False)
         h = gelu(h)
-        return h @ self.ff_out["w"][s].astype(F32) + self.ff_out["b"][s].astype(F32)
+        return h @ self.ff_out["w"][s].astype(F32, copy=False) + self.ff_out["b"][s].astype(F32, copy=False)
 
     # layers.py:292-297
     def qvk_proj(self, s, x):
         shp = x.shape[:-1] + (self.heads_per_shard, self.dim_per_head)
-        q = (x @ self.q_w[s].astype(F32)).reshape(shp)
-        v = (x @ self.v_w[s].astype(F32)).reshape(shp)
-        k = (x @ self.k_w[s].astype(F32)).reshape(shp)
+        q = (x @ self.q_w[s].astype(F32, copy=False)).reshape(shp)
+        v = (x @ self.v_w[s].astype(F32, copy=False)).reshape(shp)
+        k = (x @ self.k_w[s].astype(F32, copy=False)).reshape(shp)
         return q, v, k
 
     def _norm(self, xs):
@@ -254,7 +254,7 @@ class ProjectionShard:
 
     def _local_logits(self, xs):
         xs = replicated_layer_norm(xs, self.ln["scale"], self.ln["offset"])
-        return [(x @ self.lin["w"][s].astype(F32) + self.lin["b"][s].astype(F32)).astype(F32)
+        return [(x @ self.lin["w"][s].astype(F32, copy=False) + self.lin["b"][s].astype(F32, copy=False)).astype(F32)
                 for s, x in enumerate(xs)]
 
     def __call__(self, xs):

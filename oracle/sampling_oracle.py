@@ -234,3 +234,27 @@ def nucleus_sampler(uniforms_row, logits, _aux, top_p=0.9, temp=1.0):
     where the "key" is the row of pre-drawn uniforms for this step."""
     tok = nucleaus_sample(np.asarray(uniforms_row, F32)[None, :], logits, top_p, temp)
     return tok, None
+
+
+# ----------------------------------------------------------------------------
+# batched "how many sorted entries stay" for both definitions (the removed entries are a suffix of
+# the sorted order under either, so the count fixes the removed set)
+# ----------------------------------------------------------------------------
+def kept_count_plain(logits, top_p=0.9):
+    """Entries kept per row by ``nucleaus_filter_plain`` (rows, V) -> int64 [rows]."""
+    s = -np.sort(-np.asarray(logits, F32), axis=-1)
+    e = np.exp(s - s[:, :1])
+    cum = np.cumsum(e / e.sum(axis=-1, keepdims=True, dtype=F32), axis=-1, dtype=F32)
+    return 1 + np.sum(cum[:, :-1] <= F32(top_p), axis=-1)   # entry j stays iff cum[j-1] <= top_p (cum is monotone)
+
+
+def kept_count(logits, top_p=0.9):
+    """Entries kept per row by the pinned ``nucleaus_filter``."""
+    s = -np.sort(-np.asarray(logits, F32), axis=-1)
+    q = fixed_point_weights(exp_f32((s - s[:, :1]).astype(F32)))
+    before = np.cumsum(q, axis=-1, dtype=np.uint64) - q
+    out = np.zeros(s.shape[0], np.int64)
+    for r in range(s.shape[0]):
+        thr = weight_threshold(top_p, int(q[r].sum(dtype=np.uint64)))
+        out[r] = s.shape[1] if (thr is None or thr >= 2 ** 63) else int(np.sum(before[r] <= np.uint64(thr)))
+    return out

@@ -36,9 +36,10 @@ def gptj6b_config(mp: int = 1) -> dict:
 def round_bf16(a: np.ndarray) -> np.ndarray:
     """Round fp32 to the nearest bf16 (ties to even) and return it as fp32."""
     a = np.ascontiguousarray(a, dtype=np.float32)
-    u = a.view(np.uint32).astype(np.uint64)
-    u = (u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000
-    return u.astype(np.uint32).view(np.float32).reshape(a.shape)
+    u = a.view(np.uint32)
+    r = u + (np.uint32(0x7FFF) + ((u >> np.uint32(16)) & np.uint32(1)))   # wraps like the low 32 bits of a wider sum
+    r &= np.uint32(0xFFFF0000)
+    return r.view(np.float32).reshape(a.shape)
 
 
 def full_weights(config: dict, seed: int = 0, stress: bool = False,

@@ -52,3 +52,43 @@ def test_top_p_zero_is_argmax_with_highest_index_on_ties():
     assert so.nucleaus_sample_plain(un, lg, 0.0, 1.0)[0] == 40
     from oracle.gptj_oracle import greedy_sampler
     assert greedy_sampler(None, lg, None)[0][0] == 40
+
+
+def test_batched_kept_counts_are_the_filters_removed_sets():
+    rng = np.random.default_rng(11)
+    lg = (rng.standard_normal((6, 50400)) * 2.0).astype(np.float32)
+    for tp in (0.5, 0.9):
+        assert np.array_equal(50400 - so.kept_count(lg, tp), so.nucleaus_filter(lg, tp)[1].sum(-1))
+        removed_plain = (so.nucleaus_filter_plain(lg, tp) != lg).sum(-1)
+        assert np.array_equal(50400 - so.kept_count_plain(lg, tp), removed_plain)
+
+
+def test_pinned_cut_against_plain_fp32_and_exact_cuts_over_ten_thousand_rows():
+    """Where the nucleus ends (sampling.py:13,29) is decided by an fp32 cumulative sum in the reference;
+    its association order belongs to XLA.  Over 10 080 rows of 50 400 logits (three logit scales, three
+    top_p) the pinned fixed-point rule is compared with (a) the plain restatement (NumPy's sequential fp32
+    cumsum) and (b) the same rule in float64.  The pinned rule must coincide with the float64 cut; the
+    fp32 cut may differ from both by a few entries at the boundary, whose total probability is tiny."""
+    rng = np.random.default_rng(7)
+    rows = mism_plain = mism_exact = 0
+    worst_entries, worst_mass = 0, 0.0
+    for scale in (0.5, 2.0, 6.0):
+        for tp in (0.5, 0.9, 0.99):
+            for _ in range(4):
+                lg = (rng.standard_normal((280, 50400)) * scale).astype(np.float32)
+                plain, pinned = so.kept_count_plain(lg, tp), so.kept_count(lg, tp)
+                s = -np.sort(-lg.astype(np.float64), axis=-1)
+                e = np.exp(s - s[:, :1])
+                cum = np.cumsum(e / e.sum(-1, keepdims=True), axis=-1)
+                exact = 1 + np.sum(cum[:, :-1] <= float(np.float32(tp)), axis=-1)
+                r = np.arange(len(lg))
+                rows += len(lg)
+                mism_plain += int((plain != pinned).sum())
+                mism_exact += int((exact != pinned).sum())
+                worst_entries = max(worst_entries, int(np.abs(plain - pinned).max()))
+                worst_mass = max(worst_mass, float(np.abs(cum[r, plain - 1] - cum[r, pinned - 1]).max()))
+    print(f"rows {rows}: pinned != plain fp32 on {mism_plain} rows (at most {worst_entries} entries, "
+          f"probability mass {worst_mass:.2e}); pinned != float64 on {mism_exact} rows")
+    assert rows >= 10000
+    assert mism_exact <= rows // 1000
+    assert worst_entries <= 32 and worst_mass <= 5e-4
