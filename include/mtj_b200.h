@@ -56,7 +56,24 @@ typedef struct mtj_config {
   int32_t max_batch;           /* sequences resident in the KV cache          */
   int32_t max_gen;             /* generated tokens per generate() call        */
   int32_t max_rows;            /* token rows processed per forward chunk      */
-  int32_t reserved;
+  /* Path selection and limits; 0 selects the default of each.  They are part of
+   * the configuration because they change results (summation order, operand
+   * precision), not only speed.                                                */
+  int32_t hilo_max_batch;      /* decode batches up to this many sequences carry
+                                  their activations through the tensor-core GEMMs
+                                  as bf16 hi + lo pairs (about 16 mantissa bits;
+                                  keeps 32-step greedy ids equal to an fp32 run);
+                                  larger batches use plain bf16 activations.
+                                  Default 64 (the most the path holds); < 0: never */
+  int32_t mega_max_batch;      /* sequences served by the whole-step persistent
+                                  decode kernel (fp32 activations); default 1,
+                                  at most 4                                      */
+  int32_t tc_decode_min_batch; /* from this many sequences on a decode step takes
+                                  the tensor-core GEMMs; default 2               */
+  int32_t wait_limit;          /* iteration limit of every bounded device-side
+                                  wait on a peer or a phase counter; default
+                                  1 << 22 (seconds); a wait that runs out sets
+                                  the device error word (MTJ_ERR_TIMEOUT)        */
 } mtj_config;
 
 const char* mtj_last_error(void);
@@ -235,6 +252,50 @@ int32_t mtj_k_ln_gemv(const void* w_dev, const float* x_dev, const float* stats_
  * fp32 accumulation in tensor memory, out_dev f32 [M, N].  K % 64 == 0. */
 int32_t mtj_k_gemm_tc(const void* w_dev, const void* x_dev, const float* bias_dev, int32_t M, int32_t N,
                       int32_t K, float* out_dev, mtj_stream s);
+
+/* nucleaus_filter (sampling.py:10-38 with top_k = None) on its own:
+ * filtered_out_dev[r, i] = logits[r, i] - 1e10 * removed[r, i], where an entry
+ * is removed when the softmax mass of the entries sorted before it (descending,
+ * higher index first among equals) exceeds top_p[r]; the first entry stays. */
+int32_t mtj_nucleus_filter(const float* logits_dev, const float* top_p_dev, int32_t rows, int32_t vocab,
+                           float* filtered_out_dev, mtj_stream s);
+
+/* The attention of self_attn before the output projection (layers.py:275-283)
+ * for the rows of a forward chunk, with the causal mask of :305-308, the
+ * left-pad mask of :353-360 and the eval key mask of transformer_shard.py:130:
+ * flash-style on the tensor cores, d_head 256.  q_bf16_dev [batch*T, heads*d_head]
+ * bf16 (rotated, unscaled), row (b, t) being the query at absolute position
+ * pos0 + t of sequence b; the keys and values of positions [pad[b], pos0 + T)
+ * must already be in the paged pools (kpool/vpool [n_pages][heads][64][d_head]
+ * bf16, keys rotated; page_table_dev [batch, ring_pages]).  A query sees the
+ * keys at positions pad[b] <= p <= min(its own, key_limit_dev[b]) (key_limit_dev
+ * may be NULL).  out_bf16_dev[(b*T + t)*ld_out + head*d_head + j]; rows that see
+ * no key give zeros.  status_dev (may be NULL): a device word that receives bit 0
+ * if a bounded wait inside the kernel ran out. */
+int32_t mtj_k_prefill_attn(const void* q_bf16_dev, const void* kpool_dev, const void* vpool_dev, int32_t n_pages,
+                           const int32_t* page_table_dev, const int32_t* pad_dev, const int32_t* key_limit_dev,
+                           int32_t batch, int32_t T, int32_t pos0, int32_t heads, int32_t d_head,
+                           int32_t ring_pages, void* out_bf16_dev, int32_t ld_out, uint32_t* status_dev,
+                           mtj_stream s);
+
+/* g_psum (util.py:134-136) for decode-size messages over peer memory, fused
+ * with the residual add of the caller (transformer_shard.py:60,112) and the
+ * LayerNorm statistics of the next layer (layers.py:18-19,32):
+ *   x[rows, d_model] (+)= sum over ranks of partial;  stats[rows, 2] = (mean, rstd).
+ * Every rank owns one exchange buffer of mtj_k_all_reduce_buffer_bytes bytes,
+ * zeroed once and mapped into its peers (CUDA IPC or peer access);
+ * bufs_host[r] is rank r's buffer as seen from this process (bufs_host[rank] the
+ * rank's own).  All ranks make the same sequence of calls with the same rows_cap;
+ * call n of a rank waits -- at most mtj_config.wait_limit polls per peer -- for
+ * call n of every peer.  A wait that runs out leaves x unchanged for this call
+ * and is reported by mtj_check_device_status as MTJ_ERR_TIMEOUT; the handle and
+ * the CUDA context stay usable.  partial_dev [rows, d_model] f32 is read before
+ * the call's kernels end; the handle supplies d_model, the wait limit and the
+ * error word. */
+int64_t mtj_k_all_reduce_buffer_bytes(const mtj_handle* h, int32_t rows_cap);
+int32_t mtj_k_all_reduce(mtj_handle* h, void* const* bufs_host, int32_t rank, int32_t world, int32_t rows_cap,
+                         int32_t rows, const float* partial_dev, float* x_dev, float* stats_dev,
+                         int32_t accumulate, mtj_stream s);
 
 /* No counterpart in the reference.  The same attention as mtj_k_decode_attn
  * for callers that can neither pass scratch memory nor tolerate an allocation

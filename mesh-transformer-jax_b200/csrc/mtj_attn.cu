@@ -558,11 +558,10 @@ cudaError_t launch_cfg(K kernel, dim3 grid, dim3 block, cudaStream_t s, bool pdl
 template <int DH>
 cudaError_t launch_decode_dh(const DecodeAttnArgs& a, cudaStream_t s, bool pdl) {
   constexpr int smem = 2 * kPageTokens * DH * 2;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(decode_attn_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  static DeviceOnce once;
+  {
+    cudaError_t e = once.run([&] { return cudaFuncSetAttribute(decode_attn_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); });
     if (e != cudaSuccess) return e;
-    configured = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(a.grid_splits, a.heads, a.B);
@@ -580,11 +579,10 @@ cudaError_t launch_decode_dh(const DecodeAttnArgs& a, cudaStream_t s, bool pdl) 
 template <int DH>
 cudaError_t launch_decode_stream_dh(const DecodeAttnArgs& a, cudaStream_t s, bool pdl) {
   constexpr int smem = kStreamStages * 2 * kTileTokens * DH * 2;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(decode_attn_stream_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  static DeviceOnce once;
+  {
+    cudaError_t e = once.run([&] { return cudaFuncSetAttribute(decode_attn_stream_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); });
     if (e != cudaSuccess) return e;
-    configured = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((a.grid_splits + kStreamPages - 1) / kStreamPages, a.heads, a.B);

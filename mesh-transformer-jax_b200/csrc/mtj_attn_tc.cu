@@ -364,12 +364,11 @@ __global__ void __launch_bounds__(kThreadsTc) prefill_attn_tc_kernel(const __gri
 cudaError_t launch_prefill_attn_tc(const void* map_q, const void* map_k, const void* map_v,
                                    const PrefillAttnTcArgs& a, cudaStream_t s) {
   if (a.M <= 0 || a.rows.Tc <= 0 || a.M % a.rows.Tc != 0 || a.d_head != kDH) return cudaErrorInvalidValue;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(prefill_attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(kSmemTc));
+  static DeviceOnce once;
+  {
+    cudaError_t e = once.run([&] { return cudaFuncSetAttribute(prefill_attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(kSmemTc)); });
     if (e != cudaSuccess) return e;
-    configured = true;
   }
   const dim3 grid(a.heads, (a.rows.Tc + kQT - 1) / kQT, a.M / a.rows.Tc);
   prefill_attn_tc_kernel<<<grid, kThreadsTc, kSmemTc, s>>>(*static_cast<const CUtensorMap*>(map_q),

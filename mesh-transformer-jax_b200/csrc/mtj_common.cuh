@@ -13,6 +13,23 @@ constexpr int kWarp = 32;
 constexpr uint32_t kDevErrTimeout = 1u;
 constexpr uint32_t kDevErrBadIndex = 2u;
 
+// A kernel's dynamic shared memory limit is an attribute of the (kernel, device) pair: set it once per
+// device, with that device current.  One DeviceOnce object per kernel instantiation.
+struct DeviceOnce {
+  bool done[64] = {};
+  template <typename F>
+  cudaError_t run(F&& set_attribute) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    const bool tracked = dev >= 0 && dev < 64;
+    if (tracked && done[dev]) return cudaSuccess;
+    e = set_attribute();
+    if (e == cudaSuccess && tracked) done[dev] = true;
+    return e;
+  }
+};
+
 // 16-byte streaming load of read-only data that is touched once per pass
 // (weights, KV pages): bypass L1 so the activations stay resident there.
 __device__ __forceinline__ uint4 ld_stream16(const void* p) {

@@ -28,7 +28,6 @@ namespace {
 
 constexpr int kMT = 256;                 // threads per block
 constexpr int kMW = kMT / 32;            // warps per block
-constexpr int kWaitLimit = 1 << 22;
 #ifndef MTJ_MEGA_NC
 #define MTJ_MEGA_NC 4
 #endif
@@ -56,11 +55,11 @@ __device__ __forceinline__ void phase_arrive(uint32_t* counter) {
     atomicAdd(counter, 1u);
   }
 }
-__device__ __forceinline__ void phase_wait(const uint32_t* counter, uint32_t target, uint32_t* dev_err) {
+__device__ __forceinline__ void phase_wait(const uint32_t* counter, uint32_t target, uint32_t* dev_err, int limit) {
   if (threadIdx.x == 0) {
     int spins = 0;
     while (ld_acquire_gpu(counter) < target) {
-      if (++spins > kWaitLimit) {
+      if (++spins > limit) {
         if (dev_err) atomicOr(dev_err, kDevErrTimeout);
         break;
       }
@@ -100,7 +99,7 @@ __device__ __forceinline__ void mega_all_reduce(const MegaArgs& a, uint32_t k, u
     const uint32_t* f = a.local_flags + threadIdx.x;
     int spins = 0;
     while (static_cast<int32_t>(ld_acquire_sys_u32(f) - (k + 1)) < 0) {
-      if (++spins > kWaitLimit) {
+      if (++spins > a.wait_limit) {
         if (a.dev_err) atomicOr(a.dev_err, kDevErrTimeout);
         break;
       }
@@ -154,7 +153,7 @@ __device__ __forceinline__ void mega_push_reduce(const MegaArgs& a, uint32_t k, 
       uint2 v = ld_packet(p);
       int spins = 0;
       while (v.y != k + 1) {
-        if (++spins > kWaitLimit) {
+        if (++spins > a.wait_limit) {
           if (a.dev_err) atomicOr(a.dev_err, kDevErrTimeout);
           break;
         }
@@ -287,9 +286,10 @@ __device__ __forceinline__ void warp_rows2(const __nv_bfloat16* __restrict__ w, 
       for (int bt = 0; bt < BT; ++bt) {
         float4 a, b;
         if (XS) {
+          // K need not be a multiple of 256 (tensor-parallel slices): the last chunk's upper lanes hold nothing
           const float4* lo = xn + static_cast<size_t>(bt) * 2 * (K >> 3);
-          a = lo[cc * 32 + lane];
-          b = lo[(K >> 3) + cc * 32 + lane];
+          a = in_k ? lo[cc * 32 + lane] : make_float4(0.f, 0.f, 0.f, 0.f);
+          b = in_k ? lo[(K >> 3) + cc * 32 + lane] : make_float4(0.f, 0.f, 0.f, 0.f);
         } else {
           const float* xr = xg + static_cast<size_t>(bt) * ldx + cc * 256 + lane * 8;
           a = in_k ? __ldcg(reinterpret_cast<const float4*>(xr)) : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -360,9 +360,10 @@ __device__ __forceinline__ void warp_stream(const __nv_bfloat16* __restrict__ W,
       for (int bt = 0; bt < BT; ++bt) {
         float4 a, b;
         if (XS) {
+          // K need not be a multiple of 256 (tensor-parallel slices): the last chunk's upper lanes hold nothing
           const float4* lo = xn + static_cast<size_t>(bt) * 2 * (K >> 3);
-          a = lo[cc * 32 + lane];
-          b = lo[(K >> 3) + cc * 32 + lane];
+          a = in_k ? lo[cc * 32 + lane] : make_float4(0.f, 0.f, 0.f, 0.f);
+          b = in_k ? lo[(K >> 3) + cc * 32 + lane] : make_float4(0.f, 0.f, 0.f, 0.f);
         } else {
           const float* xr = xg + static_cast<size_t>(bt) * ldx + cc * 256 + lane * 8;
           a = in_k ? *reinterpret_cast<const float4*>(xr) : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -451,7 +452,7 @@ __global__ void __launch_bounds__(kMT, BT == 1 ? 2 : 1) decode_mega_kernel(const
       }
     }
     trace(a.trace, 6 * l + 0);
-    phase_wait(c_x + l, target, a.dev_err);
+    phase_wait(c_x + l, target, a.dev_err, a.wait_limit);
     trace(a.trace, 6 * l + 1);
     layer_norm_to_smem<BT>(a.x, B, d, lw.ln_scale, lw.ln_offset, xn, red);
 
@@ -517,7 +518,7 @@ __global__ void __launch_bounds__(kMT, BT == 1 ? 2 : 1) decode_mega_kernel(const
     // paged cache with all loads of a batch in flight at once (no staging, no block-level waits).
     __syncthreads();
     trace(a.trace, 6 * l + 2);                         // this block's in-projection rows are done
-    phase_wait(c_qkv + l, target, a.dev_err);
+    phase_wait(c_qkv + l, target, a.dev_err, a.wait_limit);
     {
       constexpr int EPL = DH / 32;
       constexpr int TB = 8;                            // keys per batch and warp
@@ -737,11 +738,11 @@ __global__ void __launch_bounds__(kMT, BT == 1 ? 2 : 1) decode_mega_kernel(const
       for (int r = 0; r < 2; ++r)
 #pragma unroll
         for (int bt = 0; bt < BT; ++bt) acc[r][bt] = 0.f;
-      phase_wait(c_ff + l, target, a.dev_err);
+      phase_wait(c_ff + l, target, a.dev_err, a.wait_limit);
       const int sS = cS > 0 ? cS * 32 : n8;           // no split: everything is staged after the attention wait
       stage(sS, n8);
       if (gw < nrg && cS > 0) warp_rows2<BT, kStage>(wrow, K2, cS, nch2, xn, a.act2, K2, lane, acc);
-      phase_wait(c_af + l, target, a.dev_err);
+      phase_wait(c_af + l, target, a.dev_err, a.wait_limit);
       trace(a.trace, 6 * l + 4);
       stage(0, sS);
       if (gw < nrg) {
@@ -775,7 +776,7 @@ __global__ void __launch_bounds__(kMT, BT == 1 ? 2 : 1) decode_mega_kernel(const
       prefetch_l2(a.proj_w + static_cast<size_t>(2 * gw + 1) * d + lane * 8);
     }
     trace(a.trace, 6 * L + 0);
-    phase_wait(c_x + L, target, a.dev_err);
+    phase_wait(c_x + L, target, a.dev_err, a.wait_limit);
     trace(a.trace, 6 * L + 1);
     layer_norm_to_smem<BT>(a.x, B, d, a.lnf_scale, a.lnf_offset, xn, red);
     const int nch = (d + 255) >> 8;
@@ -806,19 +807,22 @@ cudaError_t launch_mega_t(const MegaArgs& a, cudaStream_t s, int* grid_out) {
   const int smem_x = BT * a.d * 4;                                  // LayerNorm output of BT rows
   const int smem_o = BT == 1 ? (a.dl + a.ffl) * 4 : 0;             // staged out-projection input (one sequence)
   const int smem = smem_o > smem_x ? smem_o : smem_x;
-  static int cached_blocks = 0, cached_smem = -1;
-  if (cached_smem != smem) {
+  // the shared memory limit and the resident block count belong to the (kernel, device) pair
+  static int blocks_of[64] = {}, smem_of[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (smem_of[dev] != smem + 1) {
     cudaError_t e = cudaFuncSetAttribute(decode_mega_kernel<BT, DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    int dev = 0, sms = 0, per_sm = 0;
-    cudaGetDevice(&dev);
+    int sms = 0, per_sm = 0;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_mega_kernel<BT, DH>, kMT, smem);
     if (e != cudaSuccess) return e;
     if (per_sm < 1) return cudaErrorLaunchOutOfResources;
-    cached_blocks = sms * per_sm;
-    cached_smem = smem;
+    blocks_of[dev] = sms * per_sm;
+    smem_of[dev] = smem + 1;
   }
+  const int cached_blocks = blocks_of[dev];
   if (grid_out) *grid_out = cached_blocks;
   // attention: one round of units over the resident blocks, at most 64 splits per (sequence, head)
   MegaArgs b = a;

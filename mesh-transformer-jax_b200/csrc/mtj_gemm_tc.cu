@@ -678,12 +678,11 @@ template <int BN, int STAGES, int EPI, bool HILO = false>
 cudaError_t launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const GemmTcArgs& a, cudaStream_t s, bool pdl,
                       const CUtensorMap* mxlo = nullptr) {
   constexpr int smem = STAGES * (kBM * kBK * 2 + (HILO ? 2 : 1) * BN * kBK * 2) + 1024;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, EPI, HILO>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  static DeviceOnce once;
+  {
+    cudaError_t e = once.run([&] { return cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, EPI, HILO>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem); });
     if (e != cudaSuccess) return e;
-    configured = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((a.M + BN - 1) / BN, (a.N + kBM - 1) / kBM, a.partial ? a.ksplit : 1);
@@ -812,7 +811,7 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int kspl
     const size_t m = i / N;
     float acc = 0.f;
     for (int z = 0; z < ksplit; ++z) acc += partial[static_cast<size_t>(z) * total + i];
-    acc += bias[n];
+    if (bias) acc += bias[n];
     if (residual) acc += residual[i];
     out[m * ld_out + n] = acc;
   }

@@ -172,6 +172,7 @@ struct MegaArgs {
   uint2* peer_recv[8];
   unsigned long long* trace;   // optional [6 L + 3] phase time stamps of block 0 (ns)
   uint32_t* dev_err;
+  int wait_limit;              // spins before a wait on a phase counter, flag or packet gives up
 };
 cudaError_t launch_decode_mega(const MegaArgs& a, cudaStream_t s, int* grid_out);
 
@@ -233,11 +234,14 @@ struct SampleArgs {
   int rows, V;
   void* scratch;               // sample_scratch_bytes(rows, V): receives the Gumbel noise of the uniforms
   const float* gumbel;         // set by the launcher
-  uint32_t* tokens;            // [rows]
+  uint32_t* tokens;            // [rows] (may be null)
   uint32_t* tokens_copy;       // optional second destination
   int32_t* cur_dev;            // incremented by one after the step (may be null)
+  float* filtered;             // optional [rows, V]: logits - 1e10 * removed (nucleaus_filter's return value)
 };
 int64_t sample_scratch_bytes(int rows, int vocab);
+cudaError_t launch_nucleus_filter(const float* logits, const float* top_p, int rows, int V, float* filtered,
+                                  cudaStream_t s);
 cudaError_t launch_sample_top_p(const SampleArgs& a, cudaStream_t s, bool pdl);
 
 struct CeArgs {

@@ -106,6 +106,12 @@ struct mtj_handle {
   char* p2p_peer[mtj::kP2pMaxWorld] = {};
   size_t p2p_flag_off = 0;
   size_t p2p_recv_off = 0;          // push exchange of the persistent decode kernel
+  size_t p2p_push_off = 0;          // receive area of the per-layer push all-reduce [2][mp][p2p_rows][d] floats
+  size_t p2p_pflag_off = 0;         // its row flags [mp][p2p_rows]
+  size_t p2p_amax_off = 0;          // greedy-token packets [2][mp][p2p_rows][2] uint2
+  bool tp_push = true;              // batched decode at mp > 1: push all-reduce fused with split-K reduction and
+                                    // LayerNorm, greedy token without gathering the logits (MTJ_NO_TP_PUSH=1: off)
+  bool xn_ready = false;            // the bf16 operand of the next projection has already been written
   float* uniforms = nullptr;        // [max_batch, V] sampler inputs of the current step
   float* top_p = nullptr;           // [max_batch]
   float* temp = nullptr;            // [max_batch]
@@ -123,7 +129,8 @@ struct mtj_handle {
   __nv_bfloat16* act_lo = nullptr;
   TensorMap map_xn_lo[2], map_act_lo[2];   // 32 / 64-row boxes
   bool hilo_ok = false;
-  int tc_hilo_max_b = 4;            // up to this many sequences the activations travel as hi + lo (MTJ_TC_HILO_MAX_B, 0: never)
+  int tc_hilo_max_b = kHiLoRows;    // up to this many sequences the activations travel as hi + lo (mtj_config.hilo_max_batch)
+  int wait_limit = 1 << 22;         // iteration limit of the bounded device-side waits (mtj_config.wait_limit)
   bool tc_wide_ok = false;   // persistent 128 x 256 GEMM for long chunks
   bool mega_push = true;     // per-block push exchange inside the persistent decode kernel (MTJ_NO_MEGA_PUSH=1: slot protocol)
   float* tc_partial = nullptr;        // [kTcSplitMax, kTcSplitRows, d] split-K partial sums of small-M out-projections
@@ -160,8 +167,8 @@ struct mtj_handle {
   bool mega_trace_on = false;
   // decode: attention runs on a side stream next to the FF half of the in-projection
   bool fork_attn = true;
-  int mega_max_b = 1;               // sequences the whole-step decode kernel is used for (MTJ_MEGA_MAX_B, up to 4)
-  int tc_decode_min_b = 2;          // from this many sequences on decode takes the tensor-core GEMM path (MTJ_TC_DECODE_MIN_B)
+  int mega_max_b = 1;               // sequences the whole-step decode kernel is used for (mtj_config.mega_max_batch, up to 4)
+  int tc_decode_min_b = 2;          // from this many sequences on decode takes the tensor-core GEMM path (mtj_config.tc_decode_min_batch)
   bool tc_pdl = true;               // programmatic dependent launch on the tensor-core decode chain (MTJ_NO_TC_PDL=1: off)
   bool fork_pdl = false;            // let the out-projection start early although it also waits on the side stream
   cudaStream_t side_stream = nullptr;
@@ -330,6 +337,7 @@ int32_t reduce_into_x(mtj_handle* h, int M, bool accumulate, bool pdl, cudaStrea
     a.stats = h->stats;
     a.accumulate = accumulate ? 1 : 0;
     a.dev_err = h->dev_err;
+    a.wait_limit = h->wait_limit;
     MTJ_CUDA(mtj::launch_p2p_allreduce(a, M, s, pdl));
     h->launches++;
     return MTJ_OK;
@@ -339,6 +347,41 @@ int32_t reduce_into_x(mtj_handle* h, int M, bool accumulate, bool pdl, cudaStrea
     return fail(MTJ_ERR_COMM, err);
   MTJ_CUDA(mtj::launch_residual_stats(h->x, h->part, h->stats, M, h->d, accumulate, s, pdl));
   h->launches += 2;
+  return MTJ_OK;
+}
+
+// The same g_psum for the batched decode step, push style: split-K partial sums (+ bias) -> every peer's
+// receive area -> x (+)= sum, LayerNorm statistics and the normalised bf16 operand of the next projection.
+bool use_push(const mtj_handle* h, int M) { return h->tp_push && h->mp > 1 && use_p2p(h, M); }
+
+int32_t push_reduce(mtj_handle* h, int M, const float* partial, int ksplit, const float* bias, bool accumulate,
+                    const float* ln_scale, const float* ln_offset, bool hilo, bool pdl, cudaStream_t s) {
+  mtj::TpReduceArgs a = {};
+  a.rank = h->rank;
+  a.world = h->mp;
+  a.d = h->d;
+  a.rows_cap = h->p2p_rows;
+  a.partial = partial;
+  a.ksplit = ksplit;
+  a.bias = bias;
+  for (int r = 0; r < h->mp; ++r) {
+    a.peer_recv[r] = reinterpret_cast<float*>(h->p2p_peer[r] + h->p2p_push_off);
+    a.peer_flags[r] = reinterpret_cast<uint32_t*>(h->p2p_peer[r] + h->p2p_pflag_off);
+  }
+  a.seq = reinterpret_cast<uint32_t*>(h->p2p_local + h->p2p_flag_off + 264);
+  a.ticket = a.seq + 1;
+  a.x = h->x;
+  a.stats = h->stats;
+  a.accumulate = accumulate ? 1 : 0;
+  a.ln_scale = ln_scale;
+  a.ln_offset = ln_offset;
+  a.xn = ln_scale ? h->xn_bf16 : nullptr;
+  a.xn_lo = (ln_scale && hilo) ? h->xn_lo : nullptr;
+  a.dev_err = h->dev_err;
+  a.wait_limit = h->wait_limit;
+  MTJ_CUDA(mtj::launch_tp_push_reduce(a, M, s, pdl));
+  h->xn_ready = ln_scale != nullptr;
+  h->launches++;
   return MTJ_OK;
 }
 
@@ -491,7 +534,10 @@ int32_t run_layer_tc(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, c
   const bool pdl = h->use_pdl && h->tc_pdl && decode;
   // few sequences: activations go through the GEMMs as hi + lo bf16 pairs
   const bool hilo = decode && h->hilo_ok && M <= h->tc_hilo_max_b;
-  MTJ_CUDA(mtj::launch_ln_rows(h->x, lw.ln_scale, lw.ln_offset, h->xn_bf16, M, h->d, s, pdl, hilo ? h->xn_lo : nullptr));
+  if (h->xn_ready)
+    h->xn_ready = false;            // the previous exchange has already written this layer's operand
+  else
+    MTJ_CUDA(mtj::launch_ln_rows(h->x, lw.ln_scale, lw.ln_offset, h->xn_bf16, M, h->d, s, pdl, hilo ? h->xn_lo : nullptr));
   mtj::GemmTcArgs a = {};
   a.M = M;
   a.N = 3 * h->dl + h->ffl;
@@ -581,7 +627,22 @@ int32_t run_layer_tc(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, c
   int ksplit = 1;
   if (M <= kTcSplitRows && tiles < 148) ksplit = std::max(1, std::min({kTcSplitMax, 296 / tiles, o.K / 64}));
   if (to_slot && ksplit == 1) ksplit = 2;          // the slot is selected by the reduction kernel
+  const bool push = decode && !detached_out && !defer_reduce && use_push(h, M) && M <= kTcSplitRows;
   h->prof_begin(MTJ_FAMILY_OUTPROJ, s);
+  if (push) {
+    // the exchange kernel sums the split-K planes itself, adds the bias, the peers' rows and the residual and
+    // writes the next projection's operand (next layer's LayerNorm, or the final one)
+    o.partial = h->tc_partial;
+    o.ksplit = ksplit;
+    MTJ_CUDA(mtj::launch_gemm_tc(mtj::kEpiOut, &lw.map_out, &h->map_act[tc_tile_index(M)], o, s, pdl,
+                                 hilo ? &h->map_act_lo[tc_tile_index(M)] : nullptr));
+    h->prof_end(s);
+    h->launches += 3;
+    const bool last = layer + 1 == h->L;
+    return push_reduce(h, M, h->tc_partial, ksplit, lw.b_out, true,
+                       last ? h->lnf_scale : h->layers[layer + 1].ln_scale,
+                       last ? h->lnf_offset : h->layers[layer + 1].ln_offset, hilo, pdl, s);
+  }
   if (ksplit > 1) {
     float* dst = o.out;
     const float* res = o.residual;
@@ -615,9 +676,12 @@ int32_t run_layer_tc(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, c
 int32_t run_logits_tc(mtj_handle* h, int M, int row0, float* out, cudaStream_t s, bool pdl = false,
                       bool decode = false) {
   const bool hilo = decode && row0 == 0 && h->hilo_ok && M <= h->tc_hilo_max_b;
-  MTJ_CUDA(mtj::launch_ln_rows(h->x + static_cast<size_t>(row0) * h->d, h->lnf_scale, h->lnf_offset,
-                               h->xn_bf16 + static_cast<size_t>(row0) * h->d, M, h->d, s, pdl,
-                               hilo ? h->xn_lo : nullptr));
+  if (h->xn_ready && decode && row0 == 0)
+    h->xn_ready = false;            // the last layer's exchange applied the final LayerNorm already
+  else
+    MTJ_CUDA(mtj::launch_ln_rows(h->x + static_cast<size_t>(row0) * h->d, h->lnf_scale, h->lnf_offset,
+                                 h->xn_bf16 + static_cast<size_t>(row0) * h->d, M, h->d, s, pdl,
+                                 hilo ? h->xn_lo : nullptr));
   mtj::GemmTcArgs a = {};
   a.M = M;
   a.N = h->Vl;
@@ -643,7 +707,9 @@ bool use_tc(const mtj_handle* h, int M) { return h->tc_ok && M >= 32; }
 bool use_tc_decode(const mtj_handle* h, int B) { return h->tc_ok && B >= h->tc_decode_min_b; }
 
 int32_t run_embed(mtj_handle* h, const uint32_t* ids, int ids_ld, int M, const mtj::RowMap& rows,
-                  bool decode, cudaStream_t s) {
+                  bool decode, cudaStream_t s, bool tc_decode = false) {
+  // batched decode at mp > 1: the rows go through the push exchange, which also applies layer 0's LayerNorm
+  const bool push = tc_decode && use_push(h, M) && M <= kTcSplitRows;
   mtj::EmbedArgs e = {};
   e.ids = ids;
   e.ids_ld = ids_ld;
@@ -654,14 +720,19 @@ int32_t run_embed(mtj_handle* h, const uint32_t* ids, int ids_ld, int M, const m
   e.vocab_start = h->rank * h->Vl;
   e.table = h->emb_w;
   e.bias = h->emb_b;
-  e.x = h->mp == 1 ? h->x : partial_dst(h, M);
-  if (h->mp > 1) {
+  e.x = h->mp == 1 ? h->x : (push ? h->tc_partial : partial_dst(h, M));
+  if (h->mp > 1 && !push) {
     e.slot_sel = partial_slot_sel(h, M);
     e.slot_stride = partial_slot_stride(h);
   }
   e.stats = h->mp == 1 ? h->stats : nullptr;
   MTJ_CUDA(mtj::launch_embed(e, s, h->use_pdl && decode));
   h->launches++;
+  if (push) {
+    const bool hilo = h->hilo_ok && M <= h->tc_hilo_max_b;
+    return push_reduce(h, M, h->tc_partial, 1, nullptr, false, h->layers[0].ln_scale, h->layers[0].ln_offset, hilo,
+                       h->use_pdl && h->tc_pdl, s);
+  }
   if (h->mp > 1) return reduce_into_x(h, M, false, h->use_pdl && decode, s);
   return MTJ_OK;
 }
@@ -818,7 +889,7 @@ extern "C" {
 
 const char* mtj_last_error(void) { return g_last_error.c_str(); }
 int32_t mtj_set_error(int32_t code, const char* msg) { return fail(code, msg ? msg : ""); }
-int32_t mtj_version(void) { return 1; }
+int32_t mtj_version(void) { return 2; }
 
 int32_t mtj_create(const mtj_config* c, mtj_handle** out) {
   if (!c || !out) return fail(MTJ_ERR_INVALID, "null argument");
@@ -836,6 +907,7 @@ int32_t mtj_create(const mtj_config* c, mtj_handle** out) {
   if (c->d_model % 8 || (c->d_model / mp) % 8) return fail(MTJ_ERR_UNSUPPORTED, "d_model / mp must be a multiple of 8");
   if ((c->n_vocab / mp) % 4) return fail(MTJ_ERR_UNSUPPORTED, "n_vocab / mp must be a multiple of 4");
   if (c->max_batch <= 0 || c->max_gen < 0 || c->max_rows <= 0) return fail(MTJ_ERR_INVALID, "bad capacity");
+  if (c->mega_max_batch > 4) return fail(MTJ_ERR_INVALID, "mega_max_batch is at most 4");
   if (mtj::decode_attn_splits(c->seq - 1) > 64)
     return fail(MTJ_ERR_UNSUPPORTED, "seq up to 4032 is supported (64 pages of 64 tokens per sliding window)");
 
@@ -869,14 +941,16 @@ int32_t mtj_create(const mtj_config* c, mtj_handle** out) {
   h->use_pdl = !(e && e[0] == '1');
   e = getenv("MTJ_NO_MEGA");
   h->use_mega = !(e && e[0] == '1');
-  e = getenv("MTJ_MEGA_MAX_B");
-  if (e) h->mega_max_b = std::max(0, std::min(4, atoi(e)));
-  e = getenv("MTJ_TC_DECODE_MIN_B");
-  if (e) h->tc_decode_min_b = std::max(1, atoi(e));
+  if (c->mega_max_batch != 0) h->mega_max_b = std::max(0, c->mega_max_batch);
+  if (c->tc_decode_min_batch > 0) h->tc_decode_min_b = c->tc_decode_min_batch;
+  if (c->hilo_max_batch != 0) h->tc_hilo_max_b = std::max(0, std::min(kHiLoRows, c->hilo_max_batch));
+  if (c->wait_limit > 0) h->wait_limit = c->wait_limit;
   e = getenv("MTJ_NO_TC_PDL");
   h->tc_pdl = !(e && e[0] == '1');
   e = getenv("MTJ_NO_MEGA_PUSH");
   h->mega_push = !(e && e[0] == '1');
+  e = getenv("MTJ_NO_TP_PUSH");
+  h->tp_push = !(e && e[0] == '1');
   e = getenv("MTJ_NO_FORK");
   h->fork_attn = !(e && e[0] == '1');
   e = getenv("MTJ_FORK_PDL");
@@ -1002,8 +1076,6 @@ int32_t mtj_bind_arenas(mtj_handle* h, void* wdev, int64_t wbytes, void* sdev, i
         okl = okl && mtj::make_tensor_map_bf16(&h->map_act_lo[i], h->act_lo, rl, h->dl + h->ffl, 32 << i) == cudaSuccess;
       }
       h->hilo_ok = okl;
-      const char* hl = getenv("MTJ_TC_HILO_MAX_B");
-      if (hl) h->tc_hilo_max_b = std::max(0, std::min(kHiLoRows, atoi(hl)));
     }
     if (!ok) return fail(MTJ_ERR_CUDA, "cuTensorMapEncodeTiled failed");
     h->tc_ok = true;
@@ -1209,7 +1281,10 @@ int32_t mtj_p2p_export(mtj_handle* h, uint8_t* handle64) {
   const size_t data = 2 * static_cast<size_t>(h->p2p_rows) * h->d * sizeof(float);
   h->p2p_flag_off = (data + 255) / 256 * 256;
   h->p2p_recv_off = h->p2p_flag_off + 512;
-  const size_t total = h->p2p_recv_off + 2 * static_cast<size_t>(h->mp) * mtj::kMegaPushRows * h->d * sizeof(uint2);
+  h->p2p_push_off = h->p2p_recv_off + 2 * static_cast<size_t>(h->mp) * mtj::kMegaPushRows * h->d * sizeof(uint2);
+  h->p2p_pflag_off = h->p2p_push_off + 2 * static_cast<size_t>(h->mp) * h->p2p_rows * h->d * sizeof(float);
+  h->p2p_amax_off = (h->p2p_pflag_off + static_cast<size_t>(h->mp) * h->p2p_rows * sizeof(uint32_t) + 255) / 256 * 256;
+  const size_t total = h->p2p_amax_off + 2 * static_cast<size_t>(h->mp) * h->p2p_rows * 2 * sizeof(uint2);
   MTJ_CUDA(cudaMalloc(reinterpret_cast<void**>(&h->p2p_local), total));
   MTJ_CUDA(cudaMemset(h->p2p_local, 0, total));
   cudaIpcMemHandle_t ih;
@@ -1285,7 +1360,9 @@ int32_t mtj_decode_step(mtj_handle* h, const uint32_t* tokens_in, const float* t
     mtj::RowMap rows = {0, 1, 0, h->cur};
     mtj::RowMap erows = {0, 1, 0, nullptr};
     const bool mega = h->use_mega && (h->mp == 1 || use_p2p(h, B)) && B <= h->mega_max_b && !h->profile && (h->d % 256) == 0;
-    int32_t r = mega ? MTJ_OK : run_embed(h, h->tokens, 1, B, erows, true, st);
+    const bool tc = use_tc_decode(h, B);
+    h->xn_ready = false;
+    int32_t r = mega ? MTJ_OK : run_embed(h, h->tokens, 1, B, erows, true, st, tc);
     if (r) return r;
     if (mega) {
       mtj::MegaArgs ma = {};
@@ -1300,6 +1377,7 @@ int32_t mtj_decode_step(mtj_handle* h, const uint32_t* tokens_in, const float* t
       ma.x = h->x; ma.q = h->q; ma.act2 = h->act2; ma.part_o = h->part_o; ma.part_ml = h->part_ml;
       ma.head_counters = h->counters; ma.logits = h->logits; ma.sync = h->mega_sync; ma.dev_err = h->dev_err;
       ma.trace = h->mega_trace_on ? h->mega_trace : nullptr;
+      ma.wait_limit = h->wait_limit;
       ma.rank = h->rank; ma.world = h->mp; ma.vocab_start = h->rank * h->Vl;
       if (h->mp > 1) {
         ma.slot_base = reinterpret_cast<float*>(h->p2p_local);
@@ -1317,7 +1395,6 @@ int32_t mtj_decode_step(mtj_handle* h, const uint32_t* tokens_in, const float* t
       MTJ_CUDA(mtj::launch_decode_mega(ma, st, nullptr));
       h->launches++;
     }
-    const bool tc = use_tc_decode(h, B);
     for (int l = 0; !mega && l < h->L; ++l) {
       r = tc ? run_layer_tc(h, l, B, rows, nullptr, st, nullptr, true) : run_layer(h, l, B, rows, true, nullptr, st);
       if (r) return r;
@@ -1325,6 +1402,28 @@ int32_t mtj_decode_step(mtj_handle* h, const uint32_t* tokens_in, const float* t
     if (!mega) {
       r = tc ? run_logits_tc(h, B, 0, h->logits, st, h->use_pdl && h->tc_pdl, true) : run_logits(h, B, nullptr, h->logits, true, st);
       if (r) return r;
+    }
+    // greedy and nobody asked for the logits: every rank pushes the arg-max of its vocabulary slice to all ranks
+    // and all pick the same winner; the gather of the logits (layers.py:565-567) is not needed for the token
+    const bool token_only = greedy && !logits_out && use_push(h, B);
+    if (token_only) {
+      mtj::TpArgmaxArgs am = {};
+      am.logits = h->logits;
+      am.Vl = h->Vl;
+      am.vocab_start = h->rank * h->Vl;
+      am.rank = h->rank;
+      am.world = h->mp;
+      am.rows_cap = h->p2p_rows;
+      for (int q = 0; q < h->mp; ++q) am.peer_amax[q] = reinterpret_cast<uint2*>(h->p2p_peer[q] + h->p2p_amax_off);
+      am.seq = reinterpret_cast<uint32_t*>(h->p2p_local + h->p2p_flag_off + 272);
+      am.ticket = am.seq + 1;
+      am.tokens = h->tokens;
+      am.cur_dev = h->cur;
+      am.dev_err = h->dev_err;
+      am.wait_limit = h->wait_limit;
+      MTJ_CUDA(mtj::launch_tp_argmax(am, B, st, h->use_pdl));
+      h->launches++;
+      return MTJ_OK;
     }
     if (h->mp > 1) {
       // all_gather + transpose + flatten of ProjectionShard.__call__ (layers.py:565-567)
@@ -1360,7 +1459,8 @@ int32_t mtj_decode_step(mtj_handle* h, const uint32_t* tokens_in, const float* t
     return MTJ_OK;
   };
   if (h->use_graph && !h->profile && (h->mp == 1 || h->steps_done > 0)) {
-    if (h->graph_exec == nullptr || h->graph_batch != B || h->graph_greedy != (greedy ? 1 : 0)) {
+    const int graph_kind = (greedy ? 1 : 0) | (logits_out ? 2 : 0);
+    if (h->graph_exec == nullptr || h->graph_batch != B || h->graph_greedy != graph_kind) {
       if (h->graph_exec) {
         cudaGraphExecDestroy(h->graph_exec);
         h->graph_exec = nullptr;
@@ -1382,7 +1482,7 @@ int32_t mtj_decode_step(mtj_handle* h, const uint32_t* tokens_in, const float* t
       cudaGraphDestroy(graph);
       if (ce != cudaSuccess) return fail(MTJ_ERR_CUDA, std::string("graph instantiate: ") + cudaGetErrorString(ce));
       h->graph_batch = B;
-      h->graph_greedy = greedy ? 1 : 0;
+      h->graph_greedy = graph_kind;
     }
     MTJ_CUDA(cudaGraphLaunch(h->graph_exec, s));
     h->launches += h->graph_kernels;
@@ -1690,6 +1790,51 @@ int32_t mtj_k_embed(mtj_handle* h, const uint32_t* ids, int32_t rows, float* x_o
   e.stats = stats_out;
   MTJ_CUDA(mtj::launch_embed(e, static_cast<cudaStream_t>(stream), false));
   h->launches++;
+  return MTJ_OK;
+}
+
+int64_t mtj_k_all_reduce_buffer_bytes(const mtj_handle* h, int32_t rows_cap) {
+  if (!h || rows_cap <= 0) return -1;
+  const int64_t data = 2LL * rows_cap * h->d * static_cast<int64_t>(sizeof(float));
+  return align_up(data, 256) + 512;
+}
+
+int32_t mtj_k_all_reduce(mtj_handle* h, void* const* bufs_host, int32_t rank, int32_t world, int32_t rows_cap,
+                         int32_t rows, const float* partial, float* x, float* stats, int32_t accumulate,
+                         mtj_stream stream) {
+  if (!h || !h->bound) return fail(MTJ_ERR_STATE, "not bound");
+  if (!bufs_host || !partial || !x || !stats) return fail(MTJ_ERR_INVALID, "null argument");
+  if (world < 2 || world > mtj::kP2pMaxWorld || rank < 0 || rank >= world)
+    return fail(MTJ_ERR_INVALID, "the peer all-reduce takes 2..8 ranks");
+  if (rows <= 0 || rows > rows_cap) return fail(MTJ_ERR_INVALID, "rows must be in [1, rows_cap]");
+  for (int r = 0; r < world; ++r)
+    if (!bufs_host[r] || (reinterpret_cast<uintptr_t>(bufs_host[r]) & 255))
+      return fail(MTJ_ERR_INVALID, "exchange buffers must be 256-byte aligned");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const size_t flag_off = static_cast<size_t>(align_up(2LL * rows_cap * h->d * static_cast<int64_t>(sizeof(float)), 256));
+  mtj::P2pArgs a = {};
+  a.rank = rank;
+  a.world = world;
+  a.d = h->d;
+  a.slot_elems = static_cast<size_t>(rows_cap) * h->d;
+  for (int r = 0; r < world; ++r) {
+    a.peer_data[r] = reinterpret_cast<const float*>(bufs_host[r]);
+    a.peer_flags[r] = reinterpret_cast<uint32_t*>(static_cast<char*>(bufs_host[r]) + flag_off);
+  }
+  char* mine = static_cast<char*>(bufs_host[rank]);
+  a.local_flags = reinterpret_cast<const uint32_t*>(mine + flag_off);
+  a.seq = reinterpret_cast<uint32_t*>(mine + flag_off + 256);
+  a.ticket = a.seq + 1;
+  a.x = x;
+  a.stats = stats;
+  a.accumulate = accumulate ? 1 : 0;
+  a.dev_err = h->dev_err;
+  a.wait_limit = h->wait_limit;
+  // this rank's partial sums go into the data slot the exchange counter selects
+  MTJ_CUDA(mtj::launch_splitk_reduce(partial, 1, rows, h->d, nullptr, nullptr, reinterpret_cast<float*>(mine), h->d,
+                                     a.seq, a.slot_elems, s, false));
+  MTJ_CUDA(mtj::launch_p2p_allreduce(a, rows, s, false));
+  h->launches += 2;
   return MTJ_OK;
 }
 

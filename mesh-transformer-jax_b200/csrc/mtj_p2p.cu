@@ -26,7 +26,6 @@ namespace mtj {
 namespace {
 
 constexpr int kThreads = 256;
-constexpr int kSpinLimit = 1 << 22;
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   uint32_t v;
@@ -71,7 +70,7 @@ __global__ void __launch_bounds__(kThreads) p2p_allreduce_kernel(const P2pArgs a
     const uint32_t* f = a.local_flags + threadIdx.x;
     int spins = 0;
     while (static_cast<int32_t>(ld_acquire_sys(f) - want) < 0) {
-      if (++spins > kSpinLimit) {
+      if (++spins > a.wait_limit) {
         atomicExch(&timed_out, 1);
         break;
       }

@@ -178,7 +178,7 @@ __global__ void __launch_bounds__(kSampThreads, 1) sample_top_p_kernel(const Sam
   const int row = blockIdx.x / C, t = threadIdx.x, V = a.V;
   const int lane = t & 31, warp = t >> 5;
   const float* logits = a.logits + static_cast<size_t>(row) * V;
-  const float* gum = a.gumbel + static_cast<size_t>(row) * V;
+  const float* gum = a.gumbel ? a.gumbel + static_cast<size_t>(row) * V : nullptr;   // null: filter only
   const int slice = ((V + static_cast<int>(C) - 1) / static_cast<int>(C) + 31) & ~31;
   const int i_begin = min(V, static_cast<int>(crank) * slice), i_end = min(V, i_begin + slice);
 
@@ -196,7 +196,7 @@ __global__ void __launch_bounds__(kSampThreads, 1) sample_top_p_kernel(const Sam
   for (uint32_t c = 0; c < C; ++c) vmax = fmaxf(vmax, __uint_as_float(ld_peer_u32(&x_max, c)));
 
   // ---- radix selection of the entry whose weight interval contains T ----
-  const float top_p = a.top_p[row], temp = a.temp[row];
+  const float top_p = a.top_p[row], temp = a.temp ? a.temp[row] : 1.0f;
   uint32_t prefix = 0;                     // the selected key's digits so far
   unsigned long long before = 0;           // weight of all keys below the selected prefix
   unsigned long long T = 0, group_sum = 0;
@@ -369,7 +369,8 @@ __global__ void __launch_bounds__(kSampThreads, 1) sample_top_p_kernel(const Sam
     const int j = i - i_begin;
     const bool removed = cut && (key > k0 || (tie_cut && key == k0 && ((bitmap[j >> 5] >> (j & 31)) & 1u)));
     const float lm = __fsub_rn(lg, removed ? 1e10f : 0.0f);
-    const float score = __fadd_rn(__fdiv_rn(lm, temp), gum[i]);
+    if (a.filtered) a.filtered[static_cast<size_t>(row) * V + i] = lm;       // nucleaus_filter's return value
+    const float score = __fadd_rn(__fdiv_rn(lm, temp), gum ? gum[i] : 0.0f);
     if (score > best) {                                    // ascending i: the first maximum stays
       best = score;
       best_i = i;
@@ -416,7 +417,7 @@ __global__ void __launch_bounds__(kSampThreads, 1) sample_top_p_kernel(const Sam
         best_i = oi;
       }
     }
-    a.tokens[row] = static_cast<uint32_t>(best_i);
+    if (a.tokens) a.tokens[row] = static_cast<uint32_t>(best_i);
     if (a.tokens_copy) a.tokens_copy[row] = static_cast<uint32_t>(best_i);
     if (a.cur_dev && row == 0) *a.cur_dev += 1;
   }
@@ -434,15 +435,55 @@ inline size_t sample_smem_bytes(int V, int cluster) {
 // one float per logit: the Gumbel noise derived from the uniforms
 int64_t sample_scratch_bytes(int rows, int vocab) { return static_cast<int64_t>(rows) * vocab * 4; }
 
+namespace {
+// the attribute belongs to the device, not to the process
+cudaError_t configure_sampler() {
+  static DeviceOnce once;
+  return once.run([] {
+    return cudaFuncSetAttribute(sample_top_p_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+  });
+}
+
+cudaError_t launch_selection(const SampleArgs& b, cudaStream_t s) {
+  const int cluster = sample_cluster(b.rows);
+  cudaLaunchAttribute cattr[1];
+  cattr[0].id = cudaLaunchAttributeClusterDimension;
+  cattr[0].val.clusterDim.x = cluster;
+  cattr[0].val.clusterDim.y = 1;
+  cattr[0].val.clusterDim.z = 1;
+  cudaLaunchConfig_t scfg = {};
+  scfg.gridDim = dim3(static_cast<unsigned>(b.rows * cluster));
+  scfg.blockDim = dim3(kSampThreads);
+  scfg.dynamicSmemBytes = sample_smem_bytes(b.V, cluster);
+  scfg.stream = s;
+  scfg.attrs = cattr;
+  scfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&scfg, sample_top_p_kernel, b);
+}
+}  // namespace
+
+// nucleaus_filter alone (sampling.py:10-38): filtered[r, i] = logits[r, i] - 1e10 * removed[r, i]
+cudaError_t launch_nucleus_filter(const float* logits, const float* top_p, int rows, int V, float* filtered,
+                                  cudaStream_t s) {
+  if (rows <= 0 || V <= 0 || sample_smem_bytes(V, sample_cluster(rows)) > 220 * 1024) return cudaErrorInvalidValue;
+  cudaError_t e = configure_sampler();
+  if (e != cudaSuccess) return e;
+  SampleArgs b = {};
+  b.logits = logits;
+  b.top_p = top_p;
+  b.rows = rows;
+  b.V = V;
+  b.filtered = filtered;
+  return launch_selection(b, s);
+}
+
 cudaError_t launch_sample_top_p(const SampleArgs& a, cudaStream_t s, bool pdl) {
   const int cluster = sample_cluster(a.rows);              // blocks per row: as many as keep one wave on 148 SMs
   const size_t smem = sample_smem_bytes(a.V, cluster);
   if (a.rows <= 0 || a.V <= 0 || smem > 220 * 1024 || !a.scratch) return cudaErrorInvalidValue;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(sample_top_p_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+  {
+    cudaError_t e = configure_sampler();
     if (e != cudaSuccess) return e;
-    configured = true;
   }
   const size_t n = static_cast<size_t>(a.rows) * a.V;
   cudaLaunchAttribute attr[1];
@@ -459,19 +500,7 @@ cudaError_t launch_sample_top_p(const SampleArgs& a, cudaStream_t s, bool pdl) {
   if (e != cudaSuccess) return e;
   SampleArgs b = a;
   b.gumbel = g;
-  cudaLaunchAttribute cattr[1];
-  cattr[0].id = cudaLaunchAttributeClusterDimension;
-  cattr[0].val.clusterDim.x = cluster;
-  cattr[0].val.clusterDim.y = 1;
-  cattr[0].val.clusterDim.z = 1;
-  cudaLaunchConfig_t scfg = {};
-  scfg.gridDim = dim3(static_cast<unsigned>(a.rows * cluster));
-  scfg.blockDim = dim3(kSampThreads);
-  scfg.dynamicSmemBytes = smem;
-  scfg.stream = s;
-  scfg.attrs = cattr;
-  scfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&scfg, sample_top_p_kernel, b);
+  return launch_selection(b, s);
 }
 
 }  // namespace mtj

@@ -150,4 +150,53 @@ int32_t mtj_k_gemm_tc(const void* w, const void* x, const float* bias, int32_t M
   return MTJ_OK;
 }
 
+
+int32_t mtj_nucleus_filter(const float* logits, const float* top_p, int32_t rows, int32_t vocab,
+                           float* filtered_out, mtj_stream s) {
+  if (!logits || !top_p || !filtered_out) return mtj_set_error(MTJ_ERR_INVALID, "null argument");
+  if (rows <= 0 || vocab <= 0) return mtj_set_error(MTJ_ERR_INVALID, "rows and vocab must be positive");
+  cudaError_t e = mtj::launch_nucleus_filter(logits, top_p, rows, vocab, filtered_out, static_cast<cudaStream_t>(s));
+  if (e != cudaSuccess) return mtj_set_error(MTJ_ERR_CUDA, cudaGetErrorString(e));
+  return MTJ_OK;
+}
+
+int32_t mtj_k_prefill_attn(const void* q_bf16, const void* kpool, const void* vpool, int32_t n_pages,
+                           const int32_t* page_table, const int32_t* pad, const int32_t* key_limit,
+                           int32_t batch, int32_t T, int32_t pos0, int32_t heads, int32_t d_head,
+                           int32_t ring_pages, void* out_bf16, int32_t ld_out, uint32_t* status,
+                           mtj_stream s) {
+  if (!q_bf16 || !kpool || !vpool || !page_table || !pad || !out_bf16)
+    return mtj_set_error(MTJ_ERR_INVALID, "null argument");
+  if (d_head != 256) return mtj_set_error(MTJ_ERR_UNSUPPORTED, "the tensor-core attention is built for d_head 256");
+  if (batch <= 0 || T <= 0 || pos0 < 0 || heads <= 0 || n_pages <= 0 || ring_pages <= 0 ||
+      ld_out < heads * d_head || (ld_out & 7))
+    return mtj_set_error(MTJ_ERR_INVALID, "bad shape (ld_out must cover heads * d_head and be a multiple of 8)");
+  if (pos0 + T > ring_pages * mtj::kPageTokens)
+    return mtj_set_error(MTJ_ERR_INVALID, "pos0 + T exceeds the positions the page ring holds");
+  struct alignas(64) Map { unsigned char b[128]; } mq, mk, mv;
+  const int64_t M = static_cast<int64_t>(batch) * T;
+  const int64_t pool_rows = static_cast<int64_t>(n_pages) * heads * mtj::kPageTokens;
+  if (mtj::make_tensor_map_bf16(&mq, q_bf16, M, static_cast<int64_t>(heads) * d_head, 128) != cudaSuccess ||
+      mtj::make_tensor_map_bf16(&mk, kpool, pool_rows, d_head, 64) != cudaSuccess ||
+      mtj::make_tensor_map_bf16(&mv, vpool, pool_rows, d_head, 64) != cudaSuccess)
+    return mtj_set_error(MTJ_ERR_CUDA, "cuTensorMapEncodeTiled failed (pointers must be 16-byte aligned)");
+  mtj::PrefillAttnTcArgs p = {};
+  p.kv.kpool = static_cast<__nv_bfloat16*>(const_cast<void*>(kpool));
+  p.kv.vpool = static_cast<__nv_bfloat16*>(const_cast<void*>(vpool));
+  p.kv.page_table = page_table;
+  p.kv.ring_pages = ring_pages;
+  p.kv.pad = pad;
+  p.rows = {0, T, pos0, nullptr};
+  p.M = static_cast<int>(M);
+  p.heads = heads;
+  p.d_head = d_head;
+  p.key_limit = key_limit;
+  p.out_bf16 = static_cast<__nv_bfloat16*>(out_bf16);
+  p.ld_out = ld_out;
+  p.dev_err = status;
+  cudaError_t e = mtj::launch_prefill_attn_tc(&mq, &mk, &mv, p, static_cast<cudaStream_t>(s));
+  if (e != cudaSuccess) return mtj_set_error(MTJ_ERR_CUDA, cudaGetErrorString(e));
+  return MTJ_OK;
+}
+
 }  // extern "C"

@@ -23,7 +23,8 @@ class MtjError(RuntimeError):
 class MtjConfig(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int32) for n in (
         "layers", "d_model", "n_heads", "n_vocab", "pe_rotary_dims", "seq",
-        "cores_per_replica", "rank", "max_batch", "max_gen", "max_rows", "reserved")]
+        "cores_per_replica", "rank", "max_batch", "max_gen", "max_rows",
+        "hilo_max_batch", "mega_max_batch", "tc_decode_min_batch", "wait_limit")]
 
 
 def _load():
@@ -65,6 +66,10 @@ def _load():
         "mtj_k_ln_gemv": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp]),
         "mtj_k_gemm_tc": (i32, [vp, vp, vp, i32, i32, i32, vp, vp]),
         "mtj_k_decode_attn_noalloc": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, i32, vp]),
+        "mtj_nucleus_filter": (i32, [vp, vp, i32, i32, vp, vp]),
+        "mtj_k_prefill_attn": (i32, [vp, vp, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, i32, vp, vp]),
+        "mtj_k_all_reduce_buffer_bytes": (i64, [vp, i32]),
+        "mtj_k_all_reduce": (i32, [vp, ctypes.POINTER(vp), i32, i32, i32, i32, vp, vp, vp, i32, vp]),
         "mtj_k_decode_attn": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, i64, vp, i32, vp]),
     }
     for name, (res, args) in sig.items():

@@ -61,8 +61,14 @@ def gather_vocab_shards(local: torch.Tensor) -> torch.Tensor:
 class ShardRuntime:
     """One shard (rank) of the model on one GPU."""
 
+    # Path-selection fields of mtj_config (include/mtj_b200.h); 0 = the library default.  Each can be given as a
+    # keyword, as an optional key of the config dict ("mtj_<name>"; the reference ignores unknown keys) or, for
+    # experiments, through the environment variable named here.
+    TUNING = {"hilo_max_batch": "MTJ_TC_HILO_MAX_B", "mega_max_batch": "MTJ_MEGA_MAX_B",
+              "tc_decode_min_batch": "MTJ_TC_DECODE_MIN_B", "wait_limit": "MTJ_WAIT_LIMIT"}
+
     def __init__(self, config: dict, rank: int = 0, device=None, max_batch: int = 1,
-                 max_gen: int = 256, max_rows: int | None = None):
+                 max_gen: int = 256, max_rows: int | None = None, **tuning):
         validate_config(config)
         if not torch.cuda.is_available():
             raise RuntimeError("libmtj_b200 needs a CUDA device; there is no CPU path")
@@ -74,9 +80,23 @@ class ShardRuntime:
         d_head = config["d_model"] // config["n_heads"]
         if max_rows is None:
             max_rows = min(max(seq, max_batch), 4096)
+        unknown = set(tuning) - set(self.TUNING)
+        if unknown:
+            raise TypeError(f"unknown runtime options: {sorted(unknown)}")
+        tune = []
+        for name, env in self.TUNING.items():
+            v = tuning.get(name)
+            if v is None:
+                v = config.get("mtj_" + name)
+            if v is None and os.environ.get(env) not in (None, ""):
+                v = int(os.environ[env])
+                if name == "hilo_max_batch" and v == 0:
+                    v = -1                         # the variable's 0 has always meant "never"
+            tune.append(int(v) if v is not None else 0)
+        self.tuning = dict(zip(self.TUNING, tune))
         cfg = MtjConfig(config["layers"], config["d_model"], config["n_heads"], config["n_vocab"],
                         config.get("pe_rotary_dims", d_head), seq, self.mp, rank,
-                        max_batch, max_gen, max_rows, 0)
+                        max_batch, max_gen, max_rows, *tune)
         self.max_batch, self.max_gen, self.max_rows = max_batch, max_gen, max_rows
         self._h = ctypes.c_void_p()
         check(lib.mtj_create(ctypes.byref(cfg), ctypes.byref(self._h)))

@@ -5,8 +5,9 @@
 (sampling.py:6-7,41-44).  ``key`` is what the randomness comes from: a float32
 tensor of pre-drawn uniforms in [tiny, 1) with the shape of ``logits`` (the
 form the parity tests use), a ``torch.Generator``, or an int seed.  The
-arithmetic runs in libmtj_b200's sampling kernel; the top-k branch of the
-reference filter (sampling.py:15-26) is not implemented.
+arithmetic runs in libmtj_b200's sampling kernel (``nucleaus_filter`` returns
+the kernel's own selection); the top-k branch of the reference filter
+(sampling.py:15-26) is not implemented.
 """
 from __future__ import annotations
 
@@ -67,5 +68,19 @@ def softmax_sample(key, logits, _=None, temp=1):
 
 
 def nucleaus_filter(logits, top_p=0.9, top_k=None):
-    raise NotImplementedError("the filter is fused into nucleaus_sample on this path; "
-                              "the filtered logits are not materialised")
+    """sampling.py:10-38 (top_k = None): ``logits - 1e10 * removed`` as a CUDA tensor [rows, vocab]."""
+    if top_k is not None:
+        raise NotImplementedError("the reference's top_k branch is outside this path")
+    if not isinstance(logits, torch.Tensor):
+        logits = torch.as_tensor(np.asarray(logits, dtype=np.float32))
+    if not logits.is_cuda:
+        logits = logits.cuda()
+    logits = logits.to(torch.float32).contiguous()
+    rows, vocab = logits.shape
+    dev = logits.device
+    with torch.cuda.device(dev):
+        out = torch.empty_like(logits)
+        tp = _per_row(top_p, rows, dev)
+        check(lib.mtj_nucleus_filter(logits.data_ptr(), tp.data_ptr(), rows, vocab, out.data_ptr(),
+                                     torch.cuda.current_stream(dev).cuda_stream))
+        return out

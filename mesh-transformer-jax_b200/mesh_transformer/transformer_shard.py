@@ -10,6 +10,7 @@ pjit "V2" model are outside this path.
 from __future__ import annotations
 
 import random
+import time
 
 import numpy as np
 import torch
@@ -67,6 +68,13 @@ class CausalTransformer:
         self._rt_caps = (0, 0)
         self._dirty = True
         self._state = None
+        self.last_generate_timing = None
+        # optional host-side liveness check of the shard group before every tensor-parallel call
+        # (config key "mtj_peer_timeout_s", seconds; see health.py)
+        self._monitor = None
+        if world > 1 and config.get("mtj_peer_timeout_s"):
+            from .health import PeerMonitor
+            self._monitor = PeerMonitor.from_process_group(float(config["mtj_peer_timeout_s"]))
         if init_weights:
             self.state = self._init_state(seed=42)
             n = sum(int(np.prod(v.shape)) for m in self._state["params"].values() for v in m.values())
@@ -204,6 +212,8 @@ class CausalTransformer:
             ctx_length = np.asarray(sample["ctx_length"]).reshape(-1)
         else:
             ctx_length = np.array([len(obs[0])] * len(obs))
+        if self._monitor is not None:
+            self._monitor.step()
         rt = self._runtime(obs.shape[0], max(self._rt_caps[1], 1))
         with torch.cuda.device(self.device):
             loss, correct = rt.eval_loss(torch.from_numpy(obs.view(np.int32)).to(self.device),
@@ -230,6 +240,8 @@ class CausalTransformer:
         lengths = np.asarray(ctx_length, dtype=np.uint32).reshape(batch)
         self.gen_length = gen_length
         self.return_logits = return_logits
+        if self._monitor is not None:
+            self._monitor.step()
         key = random.randint(0, 2 ** 60)   # the reference seeds its PRNG the same way (:327)
         if self.config["cores_per_replica"] > 1:
             # every shard samples the same token: all of them need the same key
@@ -253,7 +265,8 @@ class CausalTransformer:
             top_p = np.full(batch, np.inf, np.float32)
         greedy = bool(np.all(top_p == 0.0))
         with torch.cuda.device(self.device):
-            ctx_dev = torch.from_numpy(ctx.view(np.int32)).to(self.device)
+            t_start = time.perf_counter()
+            ctx_dev = torch.from_numpy(ctx.view(np.int32)).pin_memory().to(self.device, non_blocking=True)
             toks = torch.empty((gen_length, batch), dtype=torch.int32, device=self.device)
             logits = None
             if return_logits:
@@ -273,6 +286,8 @@ class CausalTransformer:
                     gen.manual_seed(key)
             shard = CausalTransformerShard(self.config, runtime=rt)
             shard.generate_initial(ctx_dev, lengths)
+            torch.cuda.current_stream(self.device).synchronize()
+            t_prefilled = time.perf_counter()
             for t in range(gen_length):
                 if not greedy:
                     samp["uniforms"] = uniforms[t].contiguous() if uniforms is not None else \
@@ -280,6 +295,11 @@ class CausalTransformer:
                 shard.generate_once(None, toks[t], None if logits is None else logits[t], **samp)
             out_tokens = toks.cpu().numpy().view(np.uint32).T[:, :, None]
             rt.check_device_status()       # a bounded device-side wait that ran out must not pass as a result
+            # wall-clock split of this call, like the timing prints of the reference's callers
+            # (device_serve.py:156,194): context upload + prefill, then the scan with the tokens back on the host
+            self.last_generate_timing = {"prefill_s": t_prefilled - t_start,
+                                         "decode_s": time.perf_counter() - t_prefilled,
+                                         "h2d_bytes": int(ctx.nbytes), "d2h_bytes": int(out_tokens.nbytes)}
             output = (out_tokens, None)
             if return_logits:
                 output = output + (logits.permute(1, 0, 2)[:, :, None, :].cpu().numpy(),)

@@ -28,7 +28,7 @@ def test_every_declared_symbol_is_exported(lib):
 
 def _create(lib, **kw):
     base = dict(layers=2, d_model=256, n_heads=4, n_vocab=512, pe_rotary_dims=16, seq=128,
-                cores_per_replica=1, rank=0, max_batch=2, max_gen=8, max_rows=128, reserved=0)
+                cores_per_replica=1, rank=0, max_batch=2, max_gen=8, max_rows=128)
     base.update(kw)
     cfg = lib.MtjConfig(**base)
     h = ctypes.c_void_p()
@@ -45,6 +45,10 @@ def test_create_validates_like_the_reference_asserts(lib):
     assert _create(lib, n_vocab=510, cores_per_replica=4, n_heads=4)[0] != 0
     assert _create(lib, n_heads=4, cores_per_replica=8)[0] != 0
     assert _create(lib, d_model=250)[0] != 0
+    assert _create(lib, rank=3, cores_per_replica=2)[0] != 0
+    assert _create(lib, mega_max_batch=5)[0] != 0
+    rc, h = _create(lib, hilo_max_batch=-1, mega_max_batch=4, tc_decode_min_batch=8, wait_limit=1000)
+    assert rc == 0 and lib.lib.mtj_destroy(h) == 0
     assert _create(lib, rank=3, cores_per_replica=2)[0] != 0
     assert b"cores_per_replica" in lib.lib.mtj_last_error()
 

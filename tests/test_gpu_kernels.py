@@ -64,3 +64,117 @@ def test_tensor_core_gemm_matches_fp32_matmul(cuda_device, M, N, K):
     ref = x.float() @ w.float().T + bias
     err = (out - ref).abs().max().item()
     assert err <= 2e-3 * max(1.0, ref.abs().max().item()), err
+
+
+@pytest.mark.parametrize("heads,batch,T,pos0,pads,limits", [
+    (2, 2, 200, 0, [0, 37], None),                    # two query tiles, the second partial; left padding
+    (3, 1, 128, 64, [10], [150]),                     # a later chunk: keys from the cache before pos0, key limit
+    (16, 1, 300, 0, [0], None),                       # the GPT-J-6B head count
+])
+def test_tensor_core_prefill_attention_unit(cuda_device, heads, batch, T, pos0, pads, limits):
+    """mtj_k_prefill_attn (d_head 256) against fp32 softmax attention over the same bf16 values."""
+    import torch
+    from mesh_transformer._lib import check, lib
+    d_head = 256
+    rng = np.random.Generator(np.random.PCG64(5 + heads))
+    end = pos0 + T
+    ring = (end + 63) // 64 + 1
+    table, kpool, vpool, keys, vals = build_paged_kv(rng, batch, heads, d_head, ring, [(p, end) for p in pads])
+    q = rng.standard_normal((batch, T, heads, d_head)).astype(np.float32)
+    dev = cuda_device
+    q_d = torch.from_numpy(q).to(dev).to(torch.bfloat16)
+    qf = q_d.float().cpu().numpy()
+    k_d = torch.from_numpy(kpool).to(dev).to(torch.bfloat16)
+    v_d = torch.from_numpy(vpool).to(dev).to(torch.bfloat16)
+    tab_d = torch.from_numpy(table).to(dev)
+    pad_d = torch.from_numpy(np.array(pads, np.int32)).to(dev)
+    lim_d = None if limits is None else torch.from_numpy(np.array(limits, np.int32)).to(dev)
+    ld = heads * d_head + 8
+    out = torch.zeros((batch * T, ld), dtype=torch.bfloat16, device=dev)
+    status = torch.zeros((1,), dtype=torch.int32, device=dev)
+    check(lib.mtj_k_prefill_attn(ptr(q_d), ptr(k_d), ptr(v_d), batch * ring, ptr(tab_d), ptr(pad_d),
+                                 None if lim_d is None else ptr(lim_d), batch, T, pos0, heads, d_head, ring,
+                                 ptr(out), ld, ptr(status), torch.cuda.current_stream().cuda_stream))
+    got = out.float().cpu().numpy()
+    assert int(status.item()) == 0
+    assert float(np.abs(got[:, heads * d_head:]).max()) == 0.0
+    got = got[:, :heads * d_head].reshape(batch, T, heads, d_head)
+    for b in range(batch):
+        for t in range(0, T, 7):
+            last = min(pos0 + t, limits[b] if limits is not None else 1 << 30)
+            n = last - pads[b] + 1                                       # keys[b][i] sits at position pads[b] + i
+            if n <= 0:
+                assert np.abs(got[b, t]).max() == 0.0
+                continue
+            ref = attention_reference(qf[b, t], keys[b][:n], vals[b][:n], d_head)
+            assert np.abs(got[b, t] - ref).max() <= 1.5e-2 * max(1.0, np.abs(ref).max()), (b, t)
+
+
+def _exchange_buffers(lib, rt, world, rows_cap, dev):
+    import ctypes
+    import torch
+    nbytes = lib.mtj_k_all_reduce_buffer_bytes(rt._h, rows_cap)
+    bufs = [torch.zeros((nbytes + 256,), dtype=torch.uint8, device=dev) for _ in range(world)]
+    base = [(b.data_ptr() + 255) // 256 * 256 for b in bufs]
+    arr = (ctypes.c_void_p * world)(*base)
+    d = rt.config["d_model"]
+    flag_off = (2 * rows_cap * d * 4 + 255) // 256 * 256
+
+    def view(r, dtype, off, count):
+        start = base[r] - bufs[r].data_ptr() + off
+        return bufs[r][start:start + count * 4].view(dtype)
+
+    return bufs, arr, flag_off, view
+
+
+def test_peer_all_reduce_unit_and_bounded_wait(cuda_device):
+    """mtj_k_all_reduce on one GPU: rank 0 of a world of two, the peer's buffer being a second local
+    allocation that the test fills by hand.  First the peer's flag is never published: the wait runs out
+    after mtj_config.wait_limit polls, the kernel returns, mtj_check_device_status reports MTJ_ERR_TIMEOUT
+    and nothing is faulted or hung.  Then the peer's data and flag are put in place and the same handle
+    reduces correctly."""
+    import torch
+    torch.cuda.set_device(cuda_device)
+    from mesh_transformer._lib import MtjError, check, lib
+    from mesh_transformer._runtime import ShardRuntime
+    from oracle import spec
+    cfg = spec.tiny_config(1, seq=64)
+    rt = ShardRuntime(cfg, max_batch=4, max_gen=2, wait_limit=20000)
+    d, rows, cap, world = cfg["d_model"], 3, 4, 2
+    bufs, arr, flag_off, view = _exchange_buffers(lib, rt, world, cap, cuda_device)
+    g = torch.Generator(device=cuda_device)
+    g.manual_seed(3)
+    mine = torch.randn((rows, d), generator=g, device=cuda_device)
+    theirs = torch.randn((rows, d), generator=g, device=cuda_device)
+    x0 = torch.randn((rows, d), generator=g, device=cuda_device)
+    x = x0.clone()
+    stats = torch.zeros((rows, 2), device=cuda_device)
+    s = torch.cuda.current_stream().cuda_stream
+
+    # exchange 0: nobody publishes the peer's flag
+    check(lib.mtj_k_all_reduce(rt._h, arr, 0, world, cap, rows, ptr(mine), ptr(x), ptr(stats), 1, s))
+    with pytest.raises(MtjError) as err:
+        rt.check_device_status()
+    assert err.value.code == 5                                            # MTJ_ERR_TIMEOUT
+    assert torch.equal(x, x0), "a timed-out exchange must leave x alone"
+    rt.check_device_status()                                              # the error word was cleared
+    seq = int(view(0, torch.int32, flag_off + 256, 1).item())
+    assert seq == 1, "the exchange counter moves on after a timeout, so the ranks stay in step"
+    assert int(view(1, torch.int32, flag_off, 1).item()) == 1            # rank 0 published its flag to the peer
+
+    # exchange 1: the "peer" has written its partial sums into slot 1 and published flag 2
+    view(1, torch.float32, cap * d * 4, rows * d).copy_(theirs.reshape(-1))
+    view(0, torch.int32, flag_off + 4, 1).fill_(2)
+    check(lib.mtj_k_all_reduce(rt._h, arr, 0, world, cap, rows, ptr(mine), ptr(x), ptr(stats), 1, s))
+    rt.check_device_status()
+    want = x0 + mine + theirs
+    assert torch.allclose(x, want, atol=1e-6)
+    assert torch.allclose(stats[:, 0], want.mean(-1), atol=1e-5)
+    assert torch.allclose(stats[:, 1], 1.0 / torch.sqrt(want.var(-1, unbiased=False) + 1e-5), rtol=1e-4)
+    # exchange 2, without accumulation: x = sum
+    view(1, torch.float32, 0, rows * d).copy_(theirs.reshape(-1))
+    view(0, torch.int32, flag_off + 4, 1).fill_(3)
+    check(lib.mtj_k_all_reduce(rt._h, arr, 0, world, cap, rows, ptr(mine), ptr(x), ptr(stats), 0, s))
+    rt.check_device_status()
+    assert torch.allclose(x, mine + theirs, atol=1e-6)
+    rt.close()

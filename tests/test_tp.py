@@ -29,8 +29,12 @@ def test_shard_axis_host_helpers_on_two_cpu_ranks():
     _run(2, {"MTJ_TP_CPU": "1"}, 300)
 
 
+def test_a_rank_that_leaves_between_calls_is_noticed_on_the_host():
+    _run(3, {"MTJ_TP_CPU": "2"}, 120)
+
+
 @pytest.mark.gpu
-@pytest.mark.parametrize("mp,chunk_pipeline", [(2, "0"), (2, "1"), (4, "0")])
+@pytest.mark.parametrize("mp,chunk_pipeline", [(2, "0"), (2, "1"), (4, "0"), (8, "0")])
 def test_tensor_parallel_generate_matches_oracle(mp, chunk_pipeline):
     """chunk_pipeline = "1": prefill / eval run as chunk pairs whose all-reduce overlaps the other chunk's layer."""
     import torch
