@@ -76,6 +76,25 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// thread-block cluster helpers (split-K over a cluster: the blocks of one tile add their accumulators through
+// the leader's shared memory)
+__device__ __forceinline__ void tc_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t tc_leader_smem(uint32_t addr) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(0u));
+  return r;
+}
+__device__ __forceinline__ void tc_st_cluster(uint32_t addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t tc_ld_shared(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+  return v;
+}
+
 // HILO: the activations arrive as two bf16 operands, x = hi + lo (lo = the rounding error of hi), both
 // multiplied into the same accumulator: the product carries the activations to about 16 mantissa bits,
 // which is what keeps few-sequence decode on the tensor cores as accurate as the fp32-activation path.
@@ -128,6 +147,11 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
   const int per_z = (nk_total + gridDim.z - 1) / gridDim.z;
   const int kb0 = blockIdx.z * per_z;
   const int nk = max(0, min(per_z, nk_total - kb0));
+  // Split-K without a trip through global memory (few tiles, fused epilogue): the gridDim.z blocks of a tile
+  // form one cluster along z; block z accumulates its K range, the others hand their accumulators to block 0
+  // through its shared memory, and block 0 runs the epilogue.  (With a.partial the planes go to global memory.)
+  const uint32_t cs = (!a.partial && gridDim.z > 1) ? gridDim.z : 1u;
+  const uint32_t crank = cs > 1 ? blockIdx.z : 0u;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -143,6 +167,11 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
         tma_load_2d(dst + kABytes, &map_x, (kb0 + kb) * kBK, a.x_row0 + m0, full_bar(s));
         if (HILO) tma_load_2d(dst + kABytes + kBBytes, &map_xlo, (kb0 + kb) * kBK, a.x_row0 + m0, full_bar(s));
       }
+    }
+    __syncwarp();
+    if (cs > 1) {                                    // the two cluster barriers of the epilogue warps
+      tc_cluster_sync();
+      tc_cluster_sync();
     }
   } else if (warp == 1) {
     if (lane == 0) {
@@ -164,6 +193,11 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
         tc_commit(empty_bar(s));                   // frees the stage once these MMAs have read it
       }
       tc_commit(acc_bar);                          // accumulator complete
+    }
+    __syncwarp();
+    if (cs > 1) {
+      tc_cluster_sync();
+      tc_cluster_sync();
     }
   } else {
     const int quad = warp & 3;                     // TMEM lanes this warp may read
@@ -213,17 +247,8 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
     const bool ok = nk > 0 && mbar_wait(acc_bar, 0);
     if (!ok && nk > 0) atomicOr(&failed, 1u);
     tc_fence_after();
-    if (ok || (nk == 0 && a.partial)) {
-#pragma unroll
-      for (int cc = 0; cc < kChunks; ++cc) {
+    auto do_chunk = [&](int cc, uint32_t (&r)[32]) {
         const int c0 = cc * 32;
-        uint32_t r[32];
-        if (ok) {
-          tmem_ld32(tmem_acc + (static_cast<uint32_t>(quad * 32) << 16) + c0, r);
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = 0u;      // an empty K range contributes zeros
-        }
         if (dec) {
           const int pos = dpos;
           const bool any_rot = __any_sync(0xffffffffu, rotary);
@@ -274,7 +299,7 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
                 pool[page * page_stride] = __float2bfloat16_rn(__uint_as_float(r[i]));
             }
           }
-          continue;
+          return;
         }
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
@@ -315,6 +340,57 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
             a.out[static_cast<size_t>(m) * a.ld_out + n] = v + bias;
           }
         }
+    };
+    if (cs > 1) {
+      // every block of the cluster: accumulator -> registers; blocks 1.. -> block 0's shared memory; block 0
+      // adds them in block order and finishes the tile.  The first barrier says "all accumulators are
+      // complete", i.e. no block's operand ring is in use any more: block 0's ring is the landing zone,
+      // laid out [source block - 1][token column][weight row] so that a warp's stores are conflict-free.
+      static_assert(BN > 64 || 3u * BN * kBM * 4u <= STAGES * kStageBytes, "landing zone exceeds the operand ring");
+      uint32_t racc[kChunks][32];
+#pragma unroll
+      for (int cc = 0; cc < kChunks; ++cc) {
+        if (ok) {
+          tmem_ld32(tmem_acc + (static_cast<uint32_t>(quad * 32) << 16) + cc * 32, racc[cc]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) racc[cc][i] = 0u;   // an empty K range (or a failed wait) adds nothing
+        }
+      }
+      const uint32_t row4 = static_cast<uint32_t>(quad * 32 + lane) * 4u;
+      tc_cluster_sync();
+      if (crank != 0) {
+        const uint32_t dst = tc_leader_smem(smem_base) + (crank - 1u) * (BN * kBM * 4u) + row4;
+#pragma unroll
+        for (int cc = 0; cc < kChunks; ++cc)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) tc_st_cluster(dst + static_cast<uint32_t>(cc * 32 + i) * (kBM * 4u), racc[cc][i]);
+      }
+      tc_cluster_sync();
+      if (crank == 0) {
+        for (uint32_t p = 0; p + 1 < cs; ++p) {
+          const uint32_t src = smem_base + p * (BN * kBM * 4u) + row4;
+#pragma unroll
+          for (int cc = 0; cc < kChunks; ++cc)
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              racc[cc][i] = __float_as_uint(__uint_as_float(racc[cc][i]) +
+                                            __uint_as_float(tc_ld_shared(src + static_cast<uint32_t>(cc * 32 + i) * (kBM * 4u))));
+        }
+#pragma unroll
+        for (int cc = 0; cc < kChunks; ++cc) do_chunk(cc, racc[cc]);
+      }
+    } else if (ok || (nk == 0 && a.partial)) {
+#pragma unroll
+      for (int cc = 0; cc < kChunks; ++cc) {
+        uint32_t r[32];
+        if (ok) {
+          tmem_ld32(tmem_acc + (static_cast<uint32_t>(quad * 32) << 16) + cc * 32, r);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = 0u;      // an empty K range contributes zeros
+        }
+        do_chunk(cc, r);
       }
     }
   }
@@ -685,15 +761,28 @@ cudaError_t launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const GemmTc
     if (e != cudaSuccess) return e;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((a.M + BN - 1) / BN, (a.N + kBM - 1) / kBM, a.partial ? a.ksplit : 1);
+  // cluster split-K (no global partial planes): 2 or 4 blocks per tile, token tiles of at most 64 rows
+  const int ck = (!a.partial && BN <= 64 && (a.cluster_k == 2 || a.cluster_k == 4)) ? a.cluster_k : 1;
+  cfg.gridDim = dim3((a.M + BN - 1) / BN, (a.N + kBM - 1) / kBM, a.partial ? a.ksplit : ck);
   cfg.blockDim = dim3(kTcThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = s;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (pdl) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  if (ck > 1) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = 1;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = ck;
+    ++na;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = pdl ? 1 : 0;
+  cfg.numAttrs = na;
   return cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, STAGES, EPI, HILO>, mw, mx, mxlo ? *mxlo : mx, a);
 }
 
@@ -718,6 +807,17 @@ cudaError_t launch_tc_persist(const CUtensorMap& mw, const CUtensorMap& mx, cons
 }  // namespace
 
 int gemm_tc_token_tile() { return 128; }
+// Batched decode streams each weight tile once, and a block keeps only its TMA ring in flight: with fewer tiles
+// than the GPU holds blocks (two per SM), K is split over a cluster of 2 or 4 blocks per tile so that the
+// bytes in flight -- and with them the HBM rate -- do not fall with the tile count (tensor-parallel slices).
+int gemm_tc_decode_cluster_k(int weight_rows, int M, int K) {
+  if (M > 64) return 1;
+  const int tiles = (weight_rows + kBM - 1) / kBM;      // one token tile
+  int ck = 1;
+  while (ck < 4 && tiles * ck * 2 <= 296 && K / kBK >= ck * 2 * 2) ck *= 2;
+  return ck;
+}
+
 int gemm_tc_token_tile_for(int M) { return M <= 32 ? 32 : (M <= 64 ? 64 : 128); }
 int gemm_tc_wide_token_tile() { return kPBN; }
 

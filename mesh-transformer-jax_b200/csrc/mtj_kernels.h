@@ -205,11 +205,15 @@ struct GemmTcArgs {
   int ld_out;
   float* partial;              // split-K: [ksplit, M, N] raw partial sums (out-proj / logits epilogues), or null
   int ksplit;
+  int cluster_k;               // 2 or 4 (token tiles of at most 64 rows, partial == null): split K over a cluster of
+                               // blocks that add their accumulators in shared memory before the fused epilogue
   uint32_t* dev_err;
 };
 int gemm_tc_token_tile();                 // widest token tile of launch_gemm_tc (128)
 // Token tile launch_gemm_tc uses for M rows (32, 64 or 128): map_x must have been made with this box_rows.
 int gemm_tc_token_tile_for(int M);
+// Cluster split-K factor (1, 2 or 4) launch_gemm_tc should be given for a decode-size GEMM (GemmTcArgs.cluster_k).
+int gemm_tc_decode_cluster_k(int weight_rows, int M, int K);
 cudaError_t launch_splitk_reduce(const float* partial, int ksplit, int M, int N, const float* bias,
                                  const float* residual, float* out, int ld_out, const uint32_t* slot_sel,
                                  size_t slot_stride, cudaStream_t s, bool pdl = false);

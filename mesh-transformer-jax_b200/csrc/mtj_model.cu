@@ -112,6 +112,7 @@ struct mtj_handle {
   bool tp_push = true;              // batched decode at mp > 1: push all-reduce fused with split-K reduction and
                                     // LayerNorm, greedy token without gathering the logits (MTJ_NO_TP_PUSH=1: off)
   bool xn_ready = false;            // the bf16 operand of the next projection has already been written
+  bool tc_cluster_k = true;         // batched decode: split K over block clusters when tiles are few (MTJ_NO_CLUSTER_K=1: off)
   float* uniforms = nullptr;        // [max_batch, V] sampler inputs of the current step
   float* top_p = nullptr;           // [max_batch]
   float* temp = nullptr;            // [max_batch]
@@ -556,6 +557,7 @@ int32_t run_layer_tc(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, c
   a.act_lo = hilo ? h->act_lo : nullptr;
   a.kv = h->kv(layer);
   a.dev_err = h->dev_err;
+  a.cluster_k = (decode && h->tc_cluster_k) ? mtj::gemm_tc_decode_cluster_k(a.N, M, a.K) : 1;
   h->prof_begin(MTJ_FAMILY_INPROJ, s);
   const bool wide = use_tc_wide(h, M) && !decode;
   if (wide)
@@ -691,6 +693,7 @@ int32_t run_logits_tc(mtj_handle* h, int M, int row0, float* out, cudaStream_t s
   a.out = out;
   a.ld_out = h->Vl;
   a.dev_err = h->dev_err;
+  a.cluster_k = (decode && h->tc_cluster_k) ? mtj::gemm_tc_decode_cluster_k(a.N, M, a.K) : 1;
   h->prof_begin(MTJ_FAMILY_LOGITS, s);
   if (use_tc_wide(h, M))
     MTJ_CUDA(mtj::launch_gemm_tc_wide(mtj::kEpiLogits, &h->map_proj, &h->map_xn_wide, a, s));
@@ -951,6 +954,8 @@ int32_t mtj_create(const mtj_config* c, mtj_handle** out) {
   h->mega_push = !(e && e[0] == '1');
   e = getenv("MTJ_NO_TP_PUSH");
   h->tp_push = !(e && e[0] == '1');
+  e = getenv("MTJ_NO_CLUSTER_K");
+  h->tc_cluster_k = !(e && e[0] == '1');
   e = getenv("MTJ_NO_FORK");
   h->fork_attn = !(e && e[0] == '1');
   e = getenv("MTJ_FORK_PDL");

@@ -172,7 +172,7 @@ def test_load_ckpt_skips_optimizer_state_leaves(cuda_device, tmp_path):
     write_ckpt({"opt_state": opt, "params": params, "step": np.array(7)}, path, 0)
     net = _net(cfg, spec.make_params(cfg, seed=46), cuda_device)
     net.load_ckpt(path)
-    assert int(np.asarray(net.state["step"])) == 7
+    assert int(np.asarray(net.state["step"]).reshape(-1)[0]) == 7
     ctx = spec.left_pad(spec.token_ids(3, 1, 25, 512), 64)
     got = net.generate(ctx, [25], 8, GREEDY(1))[1][0]
     assert np.array_equal(got, go.CausalTransformer(cfg, params).generate(ctx, [25], 8)[1][0])
