@@ -308,9 +308,12 @@ int32_t mtj_k_all_reduce(mtj_handle* h, void* const* bufs_host, int32_t rank, in
  * (mtj_k_decode_attn_scratch_bytes) exceeds that size are rejected with
  * MTJ_ERR_INVALID.  The first call on each device looks the array's device
  * address up (with that device current) and should therefore be made before
- * any stream capture begins.  All calls on a device share the one array: two
- * calls whose kernels can overlap on the GPU (different streams) race; calls
- * on one stream are safe, each call re-initialising what it needs. */
+ * any stream capture begins; the looked-up address is kept until the process
+ * exits, so a host that destroys the device's context (cudaDeviceReset) must not
+ * use this entry point on that device afterwards.  All calls on a device share
+ * the one array: two calls whose kernels can overlap on the GPU (different
+ * streams) race; calls on one stream are safe, each call re-initialising what
+ * it needs. */
 #define MTJ_NOALLOC_SCRATCH_BYTES (4 * 1024 * 1024)
 int32_t mtj_k_decode_attn_noalloc(const float* q_dev, const void* kpool_dev, const void* vpool_dev,
                                   const int32_t* page_table_dev, const int32_t* pad_dev,

@@ -109,8 +109,11 @@ struct mtj_handle {
   size_t p2p_push_off = 0;          // receive area of the per-layer push all-reduce [2][mp][p2p_rows][d] floats
   size_t p2p_pflag_off = 0;         // its row flags [mp][p2p_rows]
   size_t p2p_amax_off = 0;          // greedy-token packets [2][mp][p2p_rows][2] uint2
-  bool tp_push = true;              // batched decode at mp > 1: push all-reduce fused with split-K reduction and
-                                    // LayerNorm, greedy token without gathering the logits (MTJ_NO_TP_PUSH=1: off)
+  bool tp_token = true;             // decode at mp > 1: the greedy token is agreed on by pushing each rank's local
+                                    // arg-max to all ranks instead of gathering the logits (MTJ_NO_TP_TOKEN=1: off)
+  bool tp_push = false;             // batched decode at mp > 1: push all-reduce fused with the split-K reduction and
+                                    // the LayerNorm (MTJ_TP_PUSH=1: on; measured slower than the three-kernel chain
+                                    // at 2 GPUs, kept for comparison at larger shard counts)
   bool xn_ready = false;            // the bf16 operand of the next projection has already been written
   bool tc_cluster_k = true;         // batched decode: split K over block clusters when tiles are few (MTJ_NO_CLUSTER_K=1: off)
   float* uniforms = nullptr;        // [max_batch, V] sampler inputs of the current step
@@ -952,8 +955,10 @@ int32_t mtj_create(const mtj_config* c, mtj_handle** out) {
   h->tc_pdl = !(e && e[0] == '1');
   e = getenv("MTJ_NO_MEGA_PUSH");
   h->mega_push = !(e && e[0] == '1');
-  e = getenv("MTJ_NO_TP_PUSH");
-  h->tp_push = !(e && e[0] == '1');
+  e = getenv("MTJ_TP_PUSH");
+  h->tp_push = e && e[0] == '1';
+  e = getenv("MTJ_NO_TP_TOKEN");
+  h->tp_token = !(e && e[0] == '1');
   e = getenv("MTJ_NO_CLUSTER_K");
   h->tc_cluster_k = !(e && e[0] == '1');
   e = getenv("MTJ_NO_FORK");
@@ -1410,7 +1415,7 @@ int32_t mtj_decode_step(mtj_handle* h, const uint32_t* tokens_in, const float* t
     }
     // greedy and nobody asked for the logits: every rank pushes the arg-max of its vocabulary slice to all ranks
     // and all pick the same winner; the gather of the logits (layers.py:565-567) is not needed for the token
-    const bool token_only = greedy && !logits_out && use_push(h, B);
+    const bool token_only = greedy && !logits_out && h->tp_token && h->mp > 1 && use_p2p(h, B);
     if (token_only) {
       mtj::TpArgmaxArgs am = {};
       am.logits = h->logits;

@@ -29,7 +29,10 @@ void* g_scratch_ptr[kMaxDevices] = {};
 
 // In host code `g_noalloc_scratch` is only a stand-in for the device array; the
 // address a kernel may use has to be asked for, per device, with that device
-// current.  Done once per device on the first call.
+// current.  Done once per device on the first call.  The address is kept for the
+// life of the process: a host that calls cudaDeviceReset() destroys the context
+// the address belongs to, and must not call this entry point on that device
+// afterwards (the kept address would be stale).
 int32_t scratch_for_current_device(char** out, std::string* err) {
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);

@@ -29,7 +29,7 @@
 namespace mtj {
 namespace {
 
-constexpr int kPushThreads = 256;
+constexpr int kPushThreads = 1024;        // one 16-byte column group per thread at d_model 4096: every load in flight at once
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   uint32_t v;
@@ -77,9 +77,16 @@ __global__ void __launch_bounds__(kPushThreads) tp_push_reduce_kernel(const TpRe
   const size_t plane = static_cast<size_t>(M) * d;
   for (int i = threadIdx.x * 4; i < d; i += kPushThreads * 4) {
     float4 acc = a.bias ? *reinterpret_cast<const float4*>(a.bias + i) : make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int z = 0; z < a.ksplit; ++z) {
-      const float4 v = __ldcg(reinterpret_cast<const float4*>(a.partial + z * plane + static_cast<size_t>(row) * d + i));
-      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    const float4* pz = reinterpret_cast<const float4*>(a.partial + static_cast<size_t>(row) * d + i);
+    float4 v[8];
+#pragma unroll
+    for (int z = 0; z < 8; ++z)                        // the planes' loads are independent: issue them together
+      v[z] = z < a.ksplit ? __ldcg(pz + z * (plane >> 2)) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int z = 0; z < 8; ++z) { acc.x += v[z].x; acc.y += v[z].y; acc.z += v[z].z; acc.w += v[z].w; }
+    for (int z = 8; z < a.ksplit; ++z) {
+      const float4 w = __ldcg(pz + z * (plane >> 2));
+      acc.x += w.x; acc.y += w.y; acc.z += w.z; acc.w += w.w;
     }
     *reinterpret_cast<float4*>(own + i) = acc;
     for (int r = 0; r < a.world; ++r)

@@ -31,26 +31,26 @@ LAYER_MODULES = {
 PROJECTION_MODULES = {"linear": "lm_head", "replicated_layer_norm": "transformer.ln_f"}
 
 
+LEAF_KINDS = {"w": "weight", "scale": "weight", "b": "bias", "offset": "bias"}
+_LAYER = re.compile(r"layer_(\d+)$")
+
+
 def leaf_to_hf_id(module: str, leaf: str) -> str:
-    """'causal_transformer_shard/~/layer_3/~/linear_4', 'b' -> 'transformer.h.3.mlp.fc_in.bias'
-    (to_hf_weights.py:176-225)."""
-    m = re.fullmatch(re.escape(PREFIX) + r"(?P<top>[^/]+)/~/(?P<inner>[^/]+)", module)
-    if not m:
-        raise NotImplementedError(f"Unknown leaf name: {module}/{leaf}")
-    if leaf in ("w", "scale"):
-        kind = "weight"
-    elif leaf in ("b", "offset"):
-        kind = "bias"
-    else:
-        raise NotImplementedError(f"unknown weight/bias identifier \"{leaf}\" at end of: '{module}/{leaf}'")
-    top, inner = m["top"], m["inner"]
-    if top == "embedding_shard":
-        return f"transformer.wte.{kind}"
-    if top.startswith("layer"):
-        return f"transformer.h.{int(top.split('_')[-1])}.{LAYER_MODULES[inner]}.{kind}"
-    if top == "projection_shard":
-        return f"{PROJECTION_MODULES[inner]}.{kind}"
-    raise NotImplementedError(f"unknown leaf module type \"{top}\" in: '{module}/{leaf}'")
+    """'causal_transformer_shard/~/layer_3/~/linear_4', 'b' -> 'transformer.h.3.mlp.fc_in.bias': a lookup in the
+    two tables above (the reference walks the same names in to_hf_weights.py:176-225).  Anything the tables do
+    not hold (optimizer state, other module trees) raises NotImplementedError."""
+    parts = module[len(PREFIX):].split("/~/") if module.startswith(PREFIX) else []
+    kind = LEAF_KINDS.get(leaf)
+    if len(parts) == 2 and kind is not None:
+        top, inner = parts
+        layer = _LAYER.match(top)
+        if top == "embedding_shard" and inner == "linear":
+            return f"transformer.wte.{kind}"
+        if layer and inner in LAYER_MODULES:
+            return f"transformer.h.{int(layer.group(1))}.{LAYER_MODULES[inner]}.{kind}"
+        if top == "projection_shard" and inner in PROJECTION_MODULES:
+            return f"{PROJECTION_MODULES[inner]}.{kind}"
+    raise NotImplementedError(f"no Hugging Face GPT-J name for parameter '{module}/{leaf}'")
 
 
 def _as_tensor(x):

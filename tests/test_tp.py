@@ -34,10 +34,13 @@ def test_a_rank_that_leaves_between_calls_is_noticed_on_the_host():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("mp,chunk_pipeline", [(2, "0"), (2, "1"), (4, "0"), (8, "0")])
-def test_tensor_parallel_generate_matches_oracle(mp, chunk_pipeline):
-    """chunk_pipeline = "1": prefill / eval run as chunk pairs whose all-reduce overlaps the other chunk's layer."""
+@pytest.mark.parametrize("mp,chunk_pipeline,push_reduce", [(2, "0", "0"), (2, "1", "0"), (2, "0", "1"), (4, "0", "0"),
+                                                            (8, "0", "0"), (8, "0", "1")])
+def test_tensor_parallel_generate_matches_oracle(mp, chunk_pipeline, push_reduce):
+    """chunk_pipeline = "1": prefill / eval run as chunk pairs whose all-reduce overlaps the other chunk's layer.
+    push_reduce = "1": the batched decode step's all-reduce is the push kernel fused with the split-K reduction
+    and the LayerNorm instead of the three-kernel chain."""
     import torch
     if torch.cuda.device_count() < mp:
         pytest.skip(f"needs {mp} GPUs")
-    _run(mp, {"NCCL_DEBUG": "WARN", "MTJ_TP_PIPE": chunk_pipeline}, 240)
+    _run(mp, {"NCCL_DEBUG": "WARN", "MTJ_TP_PIPE": chunk_pipeline, "MTJ_TP_PUSH": push_reduce}, 240)

@@ -66,3 +66,28 @@ def test_no_alloc_entry_point_rejects_shapes_beyond_its_array(cuda_device):
                                        torch.cuda.current_stream().cuda_stream)
     assert rc != 0
     assert b"built-in array holds" in lib.mtj_last_error()
+
+
+def test_no_alloc_entry_point_on_a_second_device():
+    """The built-in array and the kernels' shared-memory attribute exist per GPU: a process that drives two
+    GPUs gets correct results on the second one too (d_head 256 needs the raised shared-memory limit)."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    from mesh_transformer._lib import check, lib
+    d_head, heads, batch, window, cur, pads, split = 256, 4, 2, 300, 310, [0, 250], 64
+    ld = heads * d_head
+    for index in (0, 1):
+        dev = torch.device("cuda", index)
+        with torch.cuda.device(dev):
+            c = _case(dev, 7 + index, d_head, heads, batch, window, cur, pads, split)
+            got = torch.zeros((batch, ld), dtype=torch.float32, device=dev)
+            check(lib.mtj_k_decode_attn_noalloc(ptr(c["q_d"]), ptr(c["k_d"]), ptr(c["v_d"]), ptr(c["tab_d"]),
+                                                ptr(c["pad_d"]), ptr(c["cur_d"]), batch, heads, d_head, window,
+                                                c["ring"], split, ptr(got), ld,
+                                                torch.cuda.current_stream(dev).cuda_stream))
+            torch.cuda.synchronize(dev)
+            g = got.cpu().numpy()
+            for b in range(batch):
+                ref = attention_reference(c["q"][b], c["keys"][b], c["vals"][b], d_head).reshape(-1)
+                assert np.abs(g[b] - ref).max() <= 2e-3 * max(1.0, np.abs(ref).max())
