@@ -581,6 +581,8 @@ def run_mtj(args):
                       "launch in a separate pass (no graph replay, so launch gaps are included)")},
         "parity": dict({"greedy_first16": greedy16, "greedy_first16_sha": _sha(np.array(greedy16 or [], np.int64)),
                         "generate_first16": [int(v) for v in gen_tokens[0, :16, 0]],
+                        "decode_loop_equals_generate": (greedy16 == [int(v) for v in gen_tokens[0, :16, 0]]
+                                                        if greedy16 is not None and K >= 16 else None),
                         "note": "every N runs the same seeded model (full leaves drawn from one seed, sliced per "
                                 "rank) on the same ids: these values agree across N up to summation order"},
                        **parity_eval),

@@ -104,6 +104,17 @@ __device__ __forceinline__ void mega_all_reduce(const MegaArgs& a, uint32_t k, u
         break;
       }
     }
+  } else if (threadIdx.x == a.rank) {
+    // this rank's own partial sums are read below like a peer's: a peer's flag says nothing about them, so
+    // wait until every block of THIS rank has arrived as well (the flag towards the peers is sent by the last)
+    int spins = 0;
+    while (ld_acquire_gpu(c_local) < target) {
+      if (++spins > a.wait_limit) {
+        if (a.dev_err) atomicOr(a.dev_err, kDevErrTimeout);
+        break;
+      }
+    }
+    __threadfence();
   }
   __syncthreads();
   const size_t slot = static_cast<size_t>(k & 1u) * a.slot_elems;

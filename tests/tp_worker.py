@@ -50,6 +50,9 @@ def gpu_checks(rank, world):
     # one sequence takes the whole-step kernel with its in-kernel exchange, without the logits read-back
     _, one = net.generate(ctx[:1], lens[:1], 32, {"top_p": np.zeros(1), "temp": np.ones(1)})
     _, two = net.generate(ctx, lens, 32, {"top_p": np.zeros(2), "temp": np.ones(2)})
+    for _ in range(3):                              # the same call gives the same tokens every time
+        again = net.generate(ctx[:1], lens[:1], 32, {"top_p": np.zeros(1), "temp": np.ones(1)})[1][0]
+        assert np.array_equal(again, one[0]), "the single-sequence decode is not reproducible"
     # nucleus sampling on gathered logits with supplied uniforms
     un = np.random.default_rng(3).random((6, 2, 512), dtype=np.float32).clip(so.TINY, None)
     opts = {"top_p": np.array([0.9, 0.6]), "temp": np.array([1.0, 0.8])}
