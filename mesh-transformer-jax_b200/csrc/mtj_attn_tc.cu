@@ -11,8 +11,13 @@
 //     S[128, 64]   = Q[128, 256] . K^T          16 MMAs (K-major operands)
 //     P            = exp2(S*c - m)              4 softmax warps, one row per thread
 //     O[128, 256] += P[128, 64] . V[64, 256]    4 MMAs (V is MN-major: no transpose)
-// Warp 0 feeds TMA, warp 1 issues the MMAs, warps 2-5 do the softmax and the
-// epilogue.  S is double buffered in tensor memory and issued two key blocks
+// Warp 0 feeds TMA, warp 1 issues the MMAs, warps 2-9 do the softmax and the
+// epilogue: a query row is shared by two threads (warps w and w + 4 read the
+// same tensor-memory lanes), each taking 32 of the block's 64 key columns and
+// half of the 256 output columns; the pair exchanges its row maxima through
+// shared memory behind a 64-thread named barrier.  Two softmax warps per
+// scheduler hide each other's latencies (tensor-memory loads, exp2), which a
+// single warp per scheduler could not.  S is double buffered in tensor memory and issued two key blocks
 // ahead (K and V travel through separate two-slot rings: a K slot is free as
 // soon as its S product is done), so the tensor core computes S[j+2] and
 // P.V[j] while the softmax warps work on block j+1.  Key blocks that every row
@@ -33,7 +38,7 @@ namespace {
 constexpr int kQT = 128;                 // queries per block
 constexpr int kKB = 64;                  // keys per block (one cache page)
 constexpr int kDH = 256;
-constexpr int kThreadsTc = 192;
+constexpr int kThreadsTc = 320;                 // TMA warp, MMA warp, 8 softmax warps
 constexpr uint32_t kQBytes = kQT * kDH * 2;          // 64 KB
 constexpr uint32_t kKBytes = kKB * kDH * 2;          // 32 KB
 constexpr uint32_t kStage = 2 * kKBytes;             // K + V of one key block
@@ -102,7 +107,7 @@ __device__ __forceinline__ void tm_st32(uint32_t taddr, const uint32_t* r) {
       : "memory");
 }
 
-__global__ void __launch_bounds__(kThreadsTc) prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q,
+__global__ void __launch_bounds__(kThreadsTc, 1) prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                      const __grid_constant__ CUtensorMap map_k,
                                                                      const __grid_constant__ CUtensorMap map_v,
                                                                      const PrefillAttnTcArgs a) {
@@ -113,6 +118,8 @@ __global__ void __launch_bounds__(kThreadsTc) prefill_attn_tc_kernel(const __gri
   __shared__ __align__(8) uint64_t bars[13];
   __shared__ uint32_t tmem_slot;
   __shared__ uint32_t failed;
+  __shared__ float xmax[2][2][kQT];      // [iteration parity][column half][row]: the pair's row maxima
+  __shared__ float xl[2][kQT];           // [column half][row]: the pair's softmax denominators
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t bar0 = smem_u32(bars);
@@ -121,7 +128,7 @@ __global__ void __launch_bounds__(kThreadsTc) prefill_attn_tc_kernel(const __gri
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < 13; ++i) mbar_init(bar0 + 8u * i, 1);
-    mbar_init(p_full, 128);
+    mbar_init(p_full, 256);
     mbar_fence_init();
     failed = 0;
   }
@@ -239,42 +246,54 @@ __global__ void __launch_bounds__(kThreadsTc) prefill_attn_tc_kernel(const __gri
       if (!ok) atomicOr(&failed, 1u);
     }
   } else {
-    const int quad = warp & 3;
+    const int quad = warp & 3;                                 // the TMEM lane quadrant this warp may access
+    const int half = (warp - 2) >> 2;                          // 0: key columns [0, 32) / O columns [0, 128); 1: the rest
     const int r = quad * 32 + lane;                            // query row within the tile = TMEM lane
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    const uint32_t pair_bar = 1u + static_cast<uint32_t>(quad);   // named barrier of the two warps sharing these rows
+    auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory"); };
+    const float c2 = 0.0625f * 1.4426950408889634f;            // 1/sqrt(256) * log2(e)
     const bool row_ok = r < q_rows;
     const int qpos = pos0 + tile * kQT + r;
-    const float c2 = 0.0625f * 1.4426950408889634f;            // 1/sqrt(256) * log2(e)
     float m_ref = -INFINITY, l = 0.f;
     const bool warp_rows_ok = quad * 32 + 31 < q_rows;
     const int warp_qpos0 = pos0 + tile * kQT + quad * 32;       // smallest query position of this warp
     bool ok = nb > 0;
-    for (int j = 0; ok && j < nb; ++j) {
-      ok = mbar_wait(s_full0 + 8 * (j & 1), (j >> 1) & 1);
-      if (!ok) break;
+    for (int j = 0; j < nb; ++j) {
+      const int g = j;
+      // a wait that runs out is remembered, but the thread keeps meeting its partner at the pair barrier
+      if (ok) ok = mbar_wait(s_full0 + 8 * (g & 1), (g >> 1) & 1);
       fence_after();
-      uint32_t sr[64];
-      const uint32_t s_addr = tmem + lane_addr + kColS + (j & 1) * kKB;
-      tm_ld32(s_addr, sr);
-      tm_ld32(s_addr + 32, sr + 32);
-      const int kbase = (first_blk + j) * kKB;
-      // every row of this warp sees the whole key block: no mask arithmetic
-      const bool full_blk = warp_rows_ok && kbase >= pad && kbase + kKB - 1 <= min(warp_qpos0, limit);
+      uint32_t sr[32];
+      const uint32_t s_addr = tmem + lane_addr + kColS + (g & 1) * kKB + half * 32;
+      if (ok) {
+        tm_ld32(s_addr, sr);
+      } else {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) sr[c] = 0xff800000u;      // -inf
+      }
+      const int kbase = (first_blk + j) * kKB + half * 32;
+      // every row of this warp sees all of its 32 keys: no mask arithmetic
+      const bool full_blk = ok && warp_rows_ok && kbase >= pad && kbase + 31 <= min(warp_qpos0, limit);
       float mx = -INFINITY;
       if (full_blk) {
 #pragma unroll
-        for (int c = 0; c < 64; ++c) mx = fmaxf(mx, __uint_as_float(sr[c]));
+        for (int c = 0; c < 32; ++c) mx = fmaxf(mx, __uint_as_float(sr[c]));
         mx *= c2;
       } else {
 #pragma unroll
-        for (int c = 0; c < 64; ++c) {
+        for (int c = 0; c < 32; ++c) {
           const int key = kbase + c;
-          const bool vis = row_ok && key >= pad && key <= qpos && key <= limit;
+          const bool vis = ok && row_ok && key >= pad && key <= qpos && key <= limit;
           const float v = vis ? __uint_as_float(sr[c]) : -INFINITY;
           sr[c] = __float_as_uint(v);
           mx = fmaxf(mx, v * c2);
         }
       }
+      // the row's maximum over all 64 keys: the partner thread holds the other half
+      xmax[j & 1][half][r] = mx;
+      pair_sync();
+      mx = fmaxf(mx, xmax[j & 1][half ^ 1][r]);
       float m_new = m_ref;
       if (mx > m_ref + 8.0f || (m_ref == -INFINITY && mx > -INFINITY)) m_new = mx;
       const float corr = (m_new == m_ref || m_ref == -INFINITY) ? 1.0f : exp2f(m_ref - m_new);
@@ -282,23 +301,22 @@ __global__ void __launch_bounds__(kThreadsTc) prefill_attn_tc_kernel(const __gri
       // takes a finite stand-in so that -inf - (-inf) does not appear
       const float neg_m = m_new == -INFINITY ? 0.f : -m_new;
       float psum = 0.f;
-      uint32_t pk[32];
+      uint32_t pk[16];
 #pragma unroll
-      for (int c = 0; c < 64; c += 2) {
+      for (int c = 0; c < 32; c += 2) {
         const float p0 = ex2_fast(fmaf(__uint_as_float(sr[c]), c2, neg_m));
         const float p1 = ex2_fast(fmaf(__uint_as_float(sr[c + 1]), c2, neg_m));
         psum += p0 + p1;
         const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
         pk[c >> 1] = *reinterpret_cast<const uint32_t*>(&pb);
       }
-      l = l * corr + psum;
+      l = l * corr + psum;                                     // this thread's half of the denominator
       if (j > 0) {
-        ok = mbar_wait(o_done, (j - 1) & 1);                   // P buffer and O are free again
-        if (!ok) break;
+        if (ok) ok = mbar_wait(o_done, (g - 1) & 1);           // P buffer and O are free again
         fence_after();
-        if (__any_sync(0xffffffffu, corr != 1.0f)) {
+        if (ok && __any_sync(0xffffffffu, corr != 1.0f)) {     // both warps of a pair see the same corr per row
 #pragma unroll 1
-          for (int c0 = 0; c0 < kDH; c0 += 32) {
+          for (int c0 = half * (kDH / 2); c0 < (half + 1) * (kDH / 2); c0 += 32) {
             uint32_t o[32];
             tm_ld32(tmem + lane_addr + kColO + c0, o);
 #pragma unroll
@@ -308,11 +326,11 @@ __global__ void __launch_bounds__(kThreadsTc) prefill_attn_tc_kernel(const __gri
           asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         }
       }
-      // P row -> shared memory in the 128-byte-swizzled K-major layout the MMA reads
+      // this thread's 32 columns of the P row -> shared memory in the 128-byte-swizzled K-major layout
       unsigned char* prow = base_ptr + (sP - base) + r * 128;
 #pragma unroll
-      for (int ch = 0; ch < 8; ++ch)
-        *reinterpret_cast<uint4*>(prow + ((ch ^ (r & 7)) << 4)) =
+      for (int ch = 0; ch < 4; ++ch)
+        *reinterpret_cast<uint4*>(prow + (((half * 4 + ch) ^ (r & 7)) << 4)) =
             make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       fence_before();
@@ -322,13 +340,16 @@ __global__ void __launch_bounds__(kThreadsTc) prefill_attn_tc_kernel(const __gri
     if (nb > 0 && ok) ok = mbar_wait(o_done, (nb - 1) & 1);
     if (nb > 0 && !ok) atomicOr(&failed, 1u);
     fence_after();
+    xl[half][r] = l;
+    pair_sync();
+    l += xl[half ^ 1][r];
     {
       // the TMEM loads are warp-wide: every lane takes part, only the stores are per row
       __nv_bfloat16* dst = a.out_bf16 + static_cast<size_t>(row0 + (row_ok ? r : 0)) * a.ld_out + head * kDH;
       const bool have = nb > 0 && ok;
       const float inv = (have && l > 0.f) ? 1.0f / l : 0.f;
 #pragma unroll 1
-      for (int c0 = 0; c0 < kDH; c0 += 32) {
+      for (int c0 = half * (kDH / 2); c0 < (half + 1) * (kDH / 2); c0 += 32) {
         uint32_t o[32];
         if (have) {
           tm_ld32(tmem + lane_addr + kColO + c0, o);
@@ -361,6 +382,10 @@ __global__ void __launch_bounds__(kThreadsTc) prefill_attn_tc_kernel(const __gri
 
 }  // namespace
 
+// Blocks are issued longest query tile first, which the hardware's dynamic block scheduling turns into a
+// near-even finish (longest-processing-time order).  Pairing a long and a short tile inside one block, to get
+// one even wave of blocks, was measured slower (2.35 ms against 2.01 ms per GPT-J-6B prefill): the pipeline
+// drains and refills between a block's two tiles.
 cudaError_t launch_prefill_attn_tc(const void* map_q, const void* map_k, const void* map_v,
                                    const PrefillAttnTcArgs& a, cudaStream_t s) {
   if (a.M <= 0 || a.rows.Tc <= 0 || a.M % a.rows.Tc != 0 || a.d_head != kDH) return cudaErrorInvalidValue;

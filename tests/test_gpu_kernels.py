@@ -72,6 +72,9 @@ def test_tensor_core_gemm_matches_fp32_matmul(cuda_device, M, N, K):
     (2, 2, 200, 0, [0, 37], None),                    # two query tiles, the second partial; left padding
     (3, 1, 128, 64, [10], [150]),                     # a later chunk: keys from the cache before pos0, key limit
     (16, 1, 300, 0, [0], None),                       # the GPT-J-6B head count
+    # more blocks than SMs: a block takes a long and a short query tile (odd tile count: the middle one alone)
+    (16, 1, 1300, 0, [5], None),
+    (8, 3, 900, 0, [0, 100, 899], [2000, 450, 2000]),  # paired tiles with left padding, empty tiles, a key limit
 ])
 def test_tensor_core_prefill_attention_unit(cuda_device, heads, batch, T, pos0, pads, limits):
     """mtj_k_prefill_attn (d_head 256) against fp32 softmax attention over the same bf16 values."""
@@ -102,7 +105,7 @@ def test_tensor_core_prefill_attention_unit(cuda_device, heads, batch, T, pos0, 
     assert float(np.abs(got[:, heads * d_head:]).max()) == 0.0
     got = got[:, :heads * d_head].reshape(batch, T, heads, d_head)
     for b in range(batch):
-        for t in range(0, T, 7):
+        for t in list(range(0, T, 7 if T < 512 else 29)) + [T - 1]:
             last = min(pos0 + t, limits[b] if limits is not None else 1 << 30)
             n = last - pads[b] + 1                                       # keys[b][i] sits at position pads[b] + i
             if n <= 0:
