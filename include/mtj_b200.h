@@ -130,13 +130,35 @@ int32_t mtj_prefill(mtj_handle* h, const uint32_t* ctx_dev, const uint32_t* ctx_
 /* One step of the generate scan (transformer_shard.py:198-210): generate_once
  * then the sampler.  tokens_in_dev may be NULL (use the previous step's
  * sample / the held-back last prompt token).  top_p/temp: [batch] f32 device;
- * uniforms_dev: [batch, n_vocab] f32 or NULL when every top_p == 0 (greedy).
+ * uniforms_dev: [batch, n_vocab] f32, or NULL (greedy, or sampling with the
+ * device generator of mtj_set_seed).
  * Outputs: tokens_out_dev [batch] uint32 (may be NULL),
  * logits_out_dev [batch, n_vocab] f32 (may be NULL). */
 int32_t mtj_decode_step(mtj_handle* h, const uint32_t* tokens_in_dev,
                         const float* top_p_dev, const float* temp_dev,
                         const float* uniforms_dev, int32_t greedy,
                         uint32_t* tokens_out_dev, float* logits_out_dev, mtj_stream s);
+
+/* The PRNG key of the generate scan (transformer_shard.py:327,335:
+ * hk.PRNGSequence(random.randint(0, 2**60)), split once per step at :200).
+ * When mtj_decode_step / mtj_generate sample (greedy == 0) without supplied
+ * uniforms, the uniforms come from a counter-based generator on the device
+ * (Philox4x32-10) keyed by this seed and indexed by (decode position,
+ * sequence, vocabulary entry): the same seed gives the same tokens, and every
+ * shard of a tensor-parallel group must be given the same seed.  Synchronises
+ * the stream. */
+int32_t mtj_set_seed(mtj_handle* h, uint64_t seed, mtj_stream s);
+
+/* The whole scan of generate (transformer_shard.py:198-212) from one call:
+ * gen_length decode steps (generate_once + sampler) enqueued back to back on
+ * the stream as replays of the captured step, no host round trip in between.
+ * tokens_out_dev [gen_length, batch] uint32 (may be NULL), logits_out_dev
+ * [gen_length, batch, n_vocab] f32 or NULL, uniforms_dev [gen_length, batch,
+ * n_vocab] f32 or NULL (device generator, see mtj_set_seed); top_p/temp as in
+ * mtj_decode_step. */
+int32_t mtj_generate(mtj_handle* h, int32_t gen_length, int32_t greedy, const float* top_p_dev,
+                     const float* temp_dev, const float* uniforms_dev, uint32_t* tokens_out_dev,
+                     float* logits_out_dev, mtj_stream s);
 
 /* CausalTransformerShard.loss (transformer_shard.py:47-72, :123-132):
  * obs/target [batch, T] uint32 device, ctx_length_host [batch];
@@ -252,6 +274,12 @@ int32_t mtj_k_ln_gemv(const void* w_dev, const float* x_dev, const float* stats_
  * fp32 accumulation in tensor memory, out_dev f32 [M, N].  K % 64 == 0. */
 int32_t mtj_k_gemm_tc(const void* w_dev, const void* x_dev, const float* bias_dev, int32_t M, int32_t N,
                       int32_t K, float* out_dev, mtj_stream s);
+
+/* The uniforms the device generator yields for (seed, decode position): out_dev
+ * [rows, vocab] f32 in [tiny, 1).  The decode position of step t of a generate
+ * call is seq - 1 + t.  For tests that replay a sampled step on the host. */
+int32_t mtj_k_rng_uniforms(uint64_t seed, int32_t position, int32_t rows, int32_t vocab, float* out_dev,
+                           mtj_stream s);
 
 /* nucleaus_filter (sampling.py:10-38 with top_k = None) on its own:
  * filtered_out_dev[r, i] = logits[r, i] - 1e10 * removed[r, i], where an entry

@@ -232,7 +232,8 @@ cudaError_t launch_ln_rows(const float* x, const float* scale, const float* offs
 
 struct SampleArgs {
   const float* logits;         // [rows, V]
-  const float* uniforms;       // [rows, V] in [tiny, 1)
+  const float* uniforms;       // [rows, V] in [tiny, 1), or null with rng_seed set
+  const uint32_t* rng_seed;    // device, 2 words: key of the counter-based generator (indexed by *cur_dev, row, column)
   const float* top_p;          // [rows]
   const float* temp;           // [rows]
   int rows, V;
@@ -244,6 +245,8 @@ struct SampleArgs {
   float* filtered;             // optional [rows, V]: logits - 1e10 * removed (nucleaus_filter's return value)
 };
 int64_t sample_scratch_bytes(int rows, int vocab);
+// the uniforms that generator yields for (seed, decode position): [rows, V]
+cudaError_t launch_rng_uniforms(uint64_t seed, int position, int rows, int V, float* out, cudaStream_t s);
 cudaError_t launch_nucleus_filter(const float* logits, const float* top_p, int rows, int V, float* filtered,
                                   cudaStream_t s);
 cudaError_t launch_sample_top_p(const SampleArgs& a, cudaStream_t s, bool pdl);

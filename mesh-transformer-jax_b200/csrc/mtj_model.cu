@@ -151,6 +151,7 @@ struct mtj_handle {
   int32_t* page_table = nullptr;    // [max_batch, ring_pages]
   int32_t* row_select = nullptr;    // [max_rows]
   uint32_t* dev_err = nullptr;
+  uint32_t* rng_seed = nullptr;     // [2] key of the device generator that draws the sampler's uniforms
   __nv_bfloat16* kpool = nullptr;   // [L][n_pages][heads][kPageTokens][dh]
   __nv_bfloat16* vpool = nullptr;
   int64_t pool_layer_elems = 0;
@@ -291,6 +292,7 @@ struct mtj_handle {
     page_table = c.take<int32_t>(static_cast<int64_t>(max_batch) * ring_pages);
     row_select = c.take<int32_t>(R);
     dev_err = c.take<uint32_t>(4);
+    rng_seed = c.take<uint32_t>(4);
     pool_layer_elems = static_cast<int64_t>(n_pages) * heads * mtj::kPageTokens * dh;
     kpool = c.take<__nv_bfloat16>(pool_layer_elems * L);
     vpool = c.take<__nv_bfloat16>(pool_layer_elems * L);
@@ -1040,6 +1042,7 @@ int32_t mtj_bind_arenas(mtj_handle* h, void* wdev, int64_t wbytes, void* sdev, i
   MTJ_CUDA(cudaMemsetAsync(h->counters, 0, sizeof(uint32_t) * h->max_batch * h->heads, s));
   MTJ_CUDA(cudaMemsetAsync(h->gemv_counters, 0, sizeof(uint32_t) * h->max_rows, s));
   MTJ_CUDA(cudaMemsetAsync(h->dev_err, 0, sizeof(uint32_t) * 4, s));
+  MTJ_CUDA(cudaMemsetAsync(h->rng_seed, 0, sizeof(uint32_t) * 4, s));
   // The tensor-core attention multiplies masked keys' V rows by exactly zero: slots that were
   // never written must hold finite values, so the pools (and the bf16 operand buffers) start at zero.
   MTJ_CUDA(cudaMemsetAsync(h->kpool, 0, sizeof(__nv_bfloat16) * h->pool_layer_elems * h->L, s));
@@ -1359,10 +1362,11 @@ int32_t mtj_decode_step(mtj_handle* h, const uint32_t* tokens_in, const float* t
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int B = h->batch;
   if (!greedy) {
-    if (!top_p || !temp || !uniforms) return fail(MTJ_ERR_INVALID, "sampling needs top_p, temp and uniforms");
+    if (!top_p || !temp) return fail(MTJ_ERR_INVALID, "sampling needs top_p and temp");
     MTJ_CUDA(cudaMemcpyAsync(h->top_p, top_p, sizeof(float) * B, cudaMemcpyDeviceToDevice, s));
     MTJ_CUDA(cudaMemcpyAsync(h->temp, temp, sizeof(float) * B, cudaMemcpyDeviceToDevice, s));
-    MTJ_CUDA(cudaMemcpyAsync(h->uniforms, uniforms, sizeof(float) * B * h->V, cudaMemcpyDeviceToDevice, s));
+    if (uniforms)      // otherwise the device generator keyed by mtj_set_seed draws them
+      MTJ_CUDA(cudaMemcpyAsync(h->uniforms, uniforms, sizeof(float) * B * h->V, cudaMemcpyDeviceToDevice, s));
   }
   if (tokens_in)
     MTJ_CUDA(cudaMemcpyAsync(h->tokens, tokens_in, sizeof(uint32_t) * B, cudaMemcpyDeviceToDevice, s));
@@ -1455,7 +1459,8 @@ int32_t mtj_decode_step(mtj_handle* h, const uint32_t* tokens_in, const float* t
     } else {
       mtj::SampleArgs sa = {};
       sa.logits = h->logits_all;
-      sa.uniforms = h->uniforms;
+      sa.uniforms = uniforms ? h->uniforms : nullptr;
+      sa.rng_seed = h->rng_seed;
       sa.top_p = h->top_p;
       sa.temp = h->temp;
       sa.rows = B;
@@ -1469,7 +1474,7 @@ int32_t mtj_decode_step(mtj_handle* h, const uint32_t* tokens_in, const float* t
     return MTJ_OK;
   };
   if (h->use_graph && !h->profile && (h->mp == 1 || h->steps_done > 0)) {
-    const int graph_kind = (greedy ? 1 : 0) | (logits_out ? 2 : 0);
+    const int graph_kind = (greedy ? 1 : 0) | (logits_out ? 2 : 0) | ((!greedy && !uniforms) ? 4 : 0);
     if (h->graph_exec == nullptr || h->graph_batch != B || h->graph_greedy != graph_kind) {
       if (h->graph_exec) {
         cudaGraphExecDestroy(h->graph_exec);
@@ -1606,6 +1611,29 @@ int32_t mtj_eval_loss(mtj_handle* h, const uint32_t* obs, const uint32_t* target
     return MTJ_OK;
   });
   return rc;
+}
+
+int32_t mtj_set_seed(mtj_handle* h, uint64_t seed, mtj_stream stream) {
+  if (!h || !h->bound) return fail(MTJ_ERR_STATE, "not bound");
+  const uint32_t words[2] = {static_cast<uint32_t>(seed), static_cast<uint32_t>(seed >> 32)};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  MTJ_CUDA(cudaMemcpyAsync(h->rng_seed, words, sizeof(words), cudaMemcpyHostToDevice, s));
+  MTJ_CUDA(cudaStreamSynchronize(s));      // `words` lives on this stack frame
+  return MTJ_OK;
+}
+
+int32_t mtj_generate(mtj_handle* h, int32_t gen_length, int32_t greedy, const float* top_p, const float* temp,
+                     const float* uniforms, uint32_t* tokens_out, float* logits_out, mtj_stream stream) {
+  if (!h) return fail(MTJ_ERR_INVALID, "null handle");
+  if (gen_length <= 0) return fail(MTJ_ERR_INVALID, "gen_length must be positive");
+  const size_t B = static_cast<size_t>(h->batch), V = static_cast<size_t>(h->V);
+  for (int t = 0; t < gen_length; ++t) {
+    const int32_t rc = mtj_decode_step(h, nullptr, top_p, temp, uniforms ? uniforms + t * B * V : nullptr, greedy,
+                                       tokens_out ? tokens_out + t * B : nullptr,
+                                       logits_out ? logits_out + t * B * V : nullptr, stream);
+    if (rc) return rc;
+  }
+  return MTJ_OK;
 }
 
 int64_t mtj_sample_scratch_bytes(int32_t rows, int32_t vocab) {

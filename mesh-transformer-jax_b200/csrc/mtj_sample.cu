@@ -124,6 +124,52 @@ __global__ void __launch_bounds__(256) gumbel_kernel(const float* __restrict__ u
   }
 }
 
+// Counter-based generator for the sampler's uniforms (Philox4x32-10, Salmon et al. 2011): stands in for the
+// jax.random key stream of the generate scan (transformer_shard.py:200,327-335).  One call yields four 32-bit
+// words = the uniforms of four consecutive vocabulary entries of one (position, sequence).
+__device__ __forceinline__ uint4 philox4x32_10(uint4 ctr, uint2 key) {
+  constexpr uint32_t kM0 = 0xD2511F53u, kM1 = 0xCD9E8D57u, kW0 = 0x9E3779B9u, kW1 = 0xBB67AE85u;
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const uint32_t hi0 = __umulhi(kM0, ctr.x), lo0 = kM0 * ctr.x;
+    const uint32_t hi1 = __umulhi(kM1, ctr.z), lo1 = kM1 * ctr.z;
+    ctr = make_uint4(hi1 ^ ctr.y ^ key.x, lo1, hi0 ^ ctr.w ^ key.y, lo0);
+    key.x += kW0;
+    key.y += kW1;
+  }
+  return ctr;
+}
+// 24 random bits -> [tiny, 1): jax.random.gumbel draws its uniforms with minval = tiny
+__device__ __forceinline__ float rng_uniform(uint32_t w) {
+  return fmaxf(static_cast<float>(w >> 8) * 5.9604644775390625e-08f, 1.17549435e-38f);
+}
+
+// uniforms (out_u) or their Gumbel noise (out_g) for rows x V entries at decode position *pos_dev (or pos_host)
+__global__ void __launch_bounds__(256) rng_kernel(const uint32_t* __restrict__ seed, uint32_t seed_lo, uint32_t seed_hi,
+                                                  const int32_t* pos_dev, int pos_host, float* out_u, float* out_g,
+                                                  int rows, int V) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const uint2 key = seed ? make_uint2(seed[0], seed[1]) : make_uint2(seed_lo, seed_hi);
+  const uint32_t pos = static_cast<uint32_t>(pos_dev ? *pos_dev : pos_host);
+  const int groups = (V + 3) >> 2;
+  for (size_t t = static_cast<size_t>(blockIdx.x) * 256 + threadIdx.x; t < static_cast<size_t>(rows) * groups;
+       t += static_cast<size_t>(gridDim.x) * 256) {
+    const uint32_t row = static_cast<uint32_t>(t / groups), grp = static_cast<uint32_t>(t % groups);
+    const uint4 w = philox4x32_10(make_uint4(grp, row, pos, 0x4d544au), key);
+    const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int col = static_cast<int>(grp) * 4 + e;
+      if (col >= V) break;
+      const float u = rng_uniform(ws[e]);
+      const size_t i = static_cast<size_t>(row) * V + col;
+      if (out_u) out_u[i] = u;
+      if (out_g) out_g[i] = -log_pinned(-log_pinned(u));
+    }
+  }
+}
+
 constexpr int kBins = 256;
 constexpr int kMaxCluster = 8;
 
@@ -462,6 +508,15 @@ cudaError_t launch_selection(const SampleArgs& b, cudaStream_t s) {
 }
 }  // namespace
 
+cudaError_t launch_rng_uniforms(uint64_t seed, int position, int rows, int V, float* out, cudaStream_t s) {
+  if (rows <= 0 || V <= 0 || !out) return cudaErrorInvalidValue;
+  const size_t n = static_cast<size_t>(rows) * ((V + 3) / 4);
+  const unsigned grid = static_cast<unsigned>(std::min<size_t>((n + 255) / 256, 148 * 8));
+  rng_kernel<<<grid, 256, 0, s>>>(nullptr, static_cast<uint32_t>(seed), static_cast<uint32_t>(seed >> 32), nullptr,
+                                  position, out, nullptr, rows, V);
+  return cudaGetLastError();
+}
+
 // nucleaus_filter alone (sampling.py:10-38): filtered[r, i] = logits[r, i] - 1e10 * removed[r, i]
 cudaError_t launch_nucleus_filter(const float* logits, const float* top_p, int rows, int V, float* filtered,
                                   cudaStream_t s) {
@@ -496,7 +551,16 @@ cudaError_t launch_sample_top_p(const SampleArgs& a, cudaStream_t s, bool pdl) {
   cfg.attrs = attr;
   cfg.numAttrs = pdl ? 1 : 0;
   float* g = static_cast<float*>(a.scratch);
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gumbel_kernel, a.uniforms, g, n);
+  cudaError_t e;
+  if (a.uniforms) {
+    e = cudaLaunchKernelEx(&cfg, gumbel_kernel, a.uniforms, g, n);
+  } else if (a.rng_seed) {                                 // no uniforms supplied: the device generator draws them
+    cfg.gridDim = dim3(static_cast<unsigned>(std::min<size_t>((n / 4 + 255) / 256, 148 * 8)));
+    e = cudaLaunchKernelEx(&cfg, rng_kernel, a.rng_seed, 0u, 0u, static_cast<const int32_t*>(a.cur_dev), 0,
+                           static_cast<float*>(nullptr), g, a.rows, a.V);
+  } else {
+    return cudaErrorInvalidValue;
+  }
   if (e != cudaSuccess) return e;
   SampleArgs b = a;
   b.gumbel = g;

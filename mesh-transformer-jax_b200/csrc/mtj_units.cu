@@ -152,6 +152,13 @@ int32_t mtj_k_gemm_tc(const void* w, const void* x, const float* bias, int32_t M
 }
 
 
+int32_t mtj_k_rng_uniforms(uint64_t seed, int32_t position, int32_t rows, int32_t vocab, float* out, mtj_stream s) {
+  if (!out || rows <= 0 || vocab <= 0 || position < 0) return mtj_set_error(MTJ_ERR_INVALID, "bad argument");
+  cudaError_t e = mtj::launch_rng_uniforms(seed, position, rows, vocab, out, static_cast<cudaStream_t>(s));
+  if (e != cudaSuccess) return mtj_set_error(MTJ_ERR_CUDA, cudaGetErrorString(e));
+  return MTJ_OK;
+}
+
 int32_t mtj_nucleus_filter(const float* logits, const float* top_p, int32_t rows, int32_t vocab,
                            float* filtered_out, mtj_stream s) {
   if (!logits || !top_p || !filtered_out) return mtj_set_error(MTJ_ERR_INVALID, "null argument");

@@ -66,6 +66,9 @@ def _load():
         "mtj_k_ln_gemv": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp]),
         "mtj_k_gemm_tc": (i32, [vp, vp, vp, i32, i32, i32, vp, vp]),
         "mtj_k_decode_attn_noalloc": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, i32, vp]),
+        "mtj_set_seed": (i32, [vp, ctypes.c_uint64, vp]),
+        "mtj_generate": (i32, [vp, i32, i32, vp, vp, vp, vp, vp, vp]),
+        "mtj_k_rng_uniforms": (i32, [ctypes.c_uint64, i32, i32, i32, vp, vp]),
         "mtj_nucleus_filter": (i32, [vp, vp, i32, i32, vp, vp]),
         "mtj_k_prefill_attn": (i32, [vp, vp, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, i32, vp, vp]),
         "mtj_k_all_reduce_buffer_bytes": (i64, [vp, i32]),

@@ -196,6 +196,18 @@ class ShardRuntime:
         check(lib.mtj_decode_step(self._h, p(tokens_in), p(top_p), p(temp), p(uniforms),
                                   1 if greedy else 0, p(tokens_out), p(logits_out), self.stream))
 
+    def set_seed(self, seed: int) -> None:
+        """Key of the device generator that draws the sampler's uniforms when none are supplied."""
+        check(lib.mtj_set_seed(self._h, int(seed) & ((1 << 64) - 1), self.stream))
+
+    def generate_steps(self, gen_length: int, tokens_out=None, logits_out=None, greedy=True, top_p=None, temp=None,
+                       uniforms=None) -> None:
+        """The whole scan from one call: ``gen_length`` decode steps enqueued back to back.
+        tokens_out [gen, batch] int32, logits_out [gen, batch, n_vocab], uniforms [gen, batch, n_vocab] or None."""
+        p = lambda t: None if t is None else t.data_ptr()
+        check(lib.mtj_generate(self._h, gen_length, 1 if greedy else 0, p(top_p), p(temp), p(uniforms),
+                               p(tokens_out), p(logits_out), self.stream))
+
     def forward_logits(self, obs_dev: torch.Tensor, ctx_length, n_last: int) -> torch.Tensor:
         B, T = obs_dev.shape
         out = torch.empty((B, n_last, self.vocab_local), dtype=torch.float32, device=self.device)

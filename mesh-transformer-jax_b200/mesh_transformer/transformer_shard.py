@@ -16,7 +16,6 @@ import numpy as np
 import torch
 
 from ._runtime import PREFIX, ShardRuntime, param_shapes, validate_config
-from .sampling import draw_uniforms
 from .util import head_print, to_bf16
 
 
@@ -48,6 +47,11 @@ class CausalTransformerShard:
         """One decode step over all layers plus the sampler
         (transformer_shard.py:97-115,198-210)."""
         self.runtime.decode_step(new_tok_dev, tokens_out, logits_out, **sampler)
+
+    def generate_scan(self, gen_length, tokens_out=None, logits_out=None, **sampler):
+        """The ``lax.scan`` over generate_once + sampler (transformer_shard.py:198-212): all steps are enqueued
+        by one library call, the sampled token feeding the next step on the device."""
+        self.runtime.generate_steps(gen_length, tokens_out, logits_out, **sampler)
 
 
 class CausalTransformer:
@@ -231,8 +235,9 @@ class CausalTransformer:
         ``(final_state, (tokens[batch, gen, 1] uint32, None[, logits]))`` like
         the reference's scan output.  ``uniforms`` ([gen, batch, n_vocab] in
         [tiny, 1)) replaces the PRNG key stream for reproducible sampling; when
-        omitted they are drawn on the device from a seed taken from Python's
-        ``random`` like the reference's key (:327)."""
+        omitted they are drawn on the device by a counter-based generator keyed
+        by a seed taken from Python's ``random`` like the reference's key (:327).
+        ``self.last_seed`` keeps that key."""
         sampler_options = sampler_options or {}
         ctx = np.ascontiguousarray(np.asarray(ctx), dtype=np.uint32)
         batch = ctx.shape[0]
@@ -250,6 +255,7 @@ class CausalTransformer:
                               device=self.device if dist.get_backend() == "nccl" else "cpu")
             dist.broadcast(kt, src=0)
             key = int(kt.item())
+        self.last_seed = key
         sampler = self.config.get("sampler")
         name = getattr(sampler, "__name__", None)
         if sampler is not None and name not in ("nucleaus_sample", "softmax_sample"):
@@ -273,26 +279,21 @@ class CausalTransformer:
                 logits = torch.empty((gen_length, batch, self.config["n_vocab"]), dtype=torch.float32,
                                      device=self.device)
             samp = {"greedy": True}
-            gen = None
             if not greedy:
                 samp = {"greedy": False,
                         "top_p": torch.from_numpy(top_p).to(self.device),
                         "temp": torch.from_numpy(temp).to(self.device)}
                 if uniforms is not None:
-                    uniforms = torch.as_tensor(np.asarray(uniforms, dtype=np.float32)).to(self.device)
+                    uniforms = torch.as_tensor(np.asarray(uniforms, dtype=np.float32)).to(self.device).contiguous()
                     assert tuple(uniforms.shape) == (gen_length, batch, self.config["n_vocab"])
+                    samp["uniforms"] = uniforms
                 else:
-                    gen = torch.Generator(device=self.device)
-                    gen.manual_seed(key)
+                    rt.set_seed(key)           # the scan's PRNG key: the uniforms are drawn on the device
             shard = CausalTransformerShard(self.config, runtime=rt)
             shard.generate_initial(ctx_dev, lengths)
             torch.cuda.current_stream(self.device).synchronize()
             t_prefilled = time.perf_counter()
-            for t in range(gen_length):
-                if not greedy:
-                    samp["uniforms"] = uniforms[t].contiguous() if uniforms is not None else \
-                        draw_uniforms(gen, (batch, self.config["n_vocab"]), self.device)
-                shard.generate_once(None, toks[t], None if logits is None else logits[t], **samp)
+            shard.generate_scan(gen_length, toks, logits, **samp)
             out_tokens = toks.cpu().numpy().view(np.uint32).T[:, :, None]
             rt.check_device_status()       # a bounded device-side wait that ran out must not pass as a result
             # wall-clock split of this call, like the timing prints of the reference's callers

@@ -152,3 +152,43 @@ def test_nucleaus_filter_returns_the_oracle_filter(cuda_device, vocab, scale):
     want = row.copy()
     want[0, [0, 1, 11]] -= np.float32(1e10)
     assert np.array_equal(nucleaus_filter(row).cpu().numpy(), want)
+
+
+def test_generate_scan_with_the_device_generator(cuda_device):
+    """generate() without supplied uniforms: one library call runs the whole scan, the uniforms come from the
+    counter-based device generator keyed like the reference's PRNG key (transformer_shard.py:327).  Every sampled
+    id equals the oracle sampler's on the step's own logits and on the uniforms that generator yields for
+    (seed, position); the same key reproduces the tokens, another key does not."""
+    import ctypes
+    import random
+    import torch
+    torch.cuda.set_device(cuda_device)
+    from mesh_transformer._lib import check, lib
+    from mesh_transformer.sampling import nucleaus_sample
+    from mesh_transformer.transformer_shard import CausalTransformer
+    cfg = spec.tiny_config(1, seq=64)
+    params = spec.make_params(cfg, seed=51, stress=True)
+    net = CausalTransformer(dict(cfg, sampler=nucleaus_sample), init_weights=False)
+    net.state = {"params": params, "step": np.array(0)}
+    ctx = spec.left_pad(spec.token_ids(3, 3, 20, 512), 64)
+    opts = {"top_p": np.array([0.9, 0.5, 1.0]), "temp": np.array([1.0, 0.7, 1.5])}
+    random.seed(1234)
+    _, out = net.generate(ctx, [20] * 3, 10, opts, return_logits=True)
+    seed = net.last_seed
+    u = torch.empty((3, 512), dtype=torch.float32, device=cuda_device)
+    means = []
+    for t in range(10):
+        check(lib.mtj_k_rng_uniforms(ctypes.c_uint64(seed), 63 + t, 3, 512, u.data_ptr(),
+                                     torch.cuda.current_stream().cuda_stream))
+        un = u.cpu().numpy()
+        assert un.min() >= so.TINY and un.max() < 1.0
+        means.append(un.mean())
+        want = so.nucleaus_sample(un, out[2][:, t, 0], opts["top_p"].astype(np.float32), opts["temp"].astype(np.float32))
+        assert np.array_equal(out[0][:, t, 0], want), f"step {t}"
+    assert abs(np.mean(means) - 0.5) < 0.02
+    random.seed(1234)
+    again = net.generate(ctx, [20] * 3, 10, opts)[1][0]
+    assert np.array_equal(again, out[0])
+    other = net.generate(ctx, [20] * 3, 10, opts)[1][0]           # the next key of Python's generator
+    assert not np.array_equal(other, out[0])
+    net.close()
