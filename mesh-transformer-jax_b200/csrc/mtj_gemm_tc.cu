@@ -675,6 +675,42 @@ __global__ void __launch_bounds__(kPThreads, 1) gemm_tc_persist_kernel(const __g
               }
             }
           }
+        } else if (EPI == kEpiLogitsCE) {
+          // Cross-entropy without the logits.  The accumulator arrives with lane = vocabulary entry and q = token
+          // row; a reduction over the vocabulary would cross lanes, so the warp's 32 x 32 block is turned through
+          // shared memory (XOR-swizzled, conflict-free both ways): afterwards lane = token row, and the 32 logits
+          // of the group are walked in registers -- max, then sum of exp(l - max), and the target's logit if its
+          // id falls into the group (layers.py:575-585 per group; ce_combine_kernel merges the groups).
+          if (valid > 0) {
+            float* tsm = reinterpret_cast<float*>(tc_smem_raw + (smem_base - smem_u32(tc_smem_raw)) +
+                                                  kPStages * kStageBytes) + (warp - 2) * 1024;
+#pragma unroll
+            for (int q = 0; q < 32; ++q) tsm[q * 32 + (lane ^ q)] = n_ok ? __uint_as_float(r[q]) + bias : -INFINITY;
+            __syncwarp();
+            const float* mine = tsm + lane * 32;
+            float mx = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, mine[i ^ lane]);
+            float sum = 0.f;
+            if (mx > -INFINITY) {                                  // -inf only for a group past the end of the vocabulary
+#pragma unroll
+              for (int i = 0; i < 32; ++i) sum += __expf(mine[i ^ lane] - mx);
+            }
+            if (lane < valid) {
+              const int crow = a.x_row0 + mc + lane;               // chunk row of this lane's token
+              const int sq = a.rows.b0 + crow / Tc, tp = a.rows.pos0_host + crow % Tc;
+              const uint32_t tgt = a.ce_targets[static_cast<size_t>(sq) * a.ce_T + tp];
+              const uint32_t off = tgt - static_cast<uint32_t>(a.ce_vocab_start + n0 + quad * 32);
+              if (off < 32u && n0 + quad * 32 + static_cast<int>(off) < a.N) {
+                a.ce_tlogit[mc + lane] = mine[off ^ lane];
+                a.ce_hit[mc + lane] = 1;
+              }
+              const size_t g = (static_cast<size_t>(t / m_tiles) * 4 + quad) * a.ce_ld + mc + lane;
+              a.ce_gmax[g] = mx;
+              a.ce_gsum[g] = sum;
+            }
+            __syncwarp();                                          // the next chunk overwrites the block
+          }
         } else if (n_ok && valid > 0) {
           const size_t ldo = EPI == kEpiOut ? static_cast<size_t>(a.N) : static_cast<size_t>(a.ld_out);
           float* dst = a.out + static_cast<size_t>(mc) * ldo + n;
@@ -788,19 +824,21 @@ cudaError_t launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const GemmTc
 
 template <int EPI>
 cudaError_t launch_tc_persist(const CUtensorMap& mw, const CUtensorMap& mx, const GemmTcArgs& a, cudaStream_t s) {
-  constexpr int smem = kPStages * (kBM * kBK * 2 + kPBN * kBK * 2) + 1024;
-  static int sms = 0;
-  if (!sms) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_persist_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         smem);
-    if (e != cudaSuccess) return e;
-    int dev = 0, n = 0;
-    if ((e = cudaGetDevice(&dev)) != cudaSuccess) return e;
-    if ((e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
-    sms = n;
-  }
+  // the cross-entropy epilogue turns each epilogue warp's 32 x 32 block through 4 KB of shared memory
+  constexpr int smem = kPStages * (kBM * kBK * 2 + kPBN * kBK * 2) + 1024 + (EPI == kEpiLogitsCE ? kPEpiWarps * 4096 : 0);
+  static DeviceOnce once;
+  static int sms_of[64] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  e = once.run([&] {
+    cudaError_t e2 = cudaFuncSetAttribute(gemm_tc_persist_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e2 != cudaSuccess) return e2;
+    return cudaDeviceGetAttribute(&sms_of[dev], cudaDevAttrMultiProcessorCount, dev);
+  });
+  if (e != cudaSuccess) return e;
   const int total = ((a.M + kPBN - 1) / kPBN) * ((a.N + kBM - 1) / kBM);
-  gemm_tc_persist_kernel<EPI><<<std::min(total, sms), kPThreads, smem, s>>>(mw, mx, a);
+  gemm_tc_persist_kernel<EPI><<<std::min(total, sms_of[dev]), kPThreads, smem, s>>>(mw, mx, a);
   return cudaGetLastError();
 }
 
@@ -829,6 +867,9 @@ cudaError_t launch_gemm_tc_wide(GemvEpilogue epi, const void* map_w, const void*
   switch (epi) {
     case kEpiInProj: return launch_tc_persist<kEpiInProj>(mw, mx, a, s);
     case kEpiOut: return launch_tc_persist<kEpiOut>(mw, mx, a, s);
+    case kEpiLogitsCE:
+      if (!a.ce_gmax || !a.ce_gsum || !a.ce_tlogit || !a.ce_hit || !a.ce_targets || a.ce_ld < a.M) return cudaErrorInvalidValue;
+      return launch_tc_persist<kEpiLogitsCE>(mw, mx, a, s);
     default: return launch_tc_persist<kEpiLogits>(mw, mx, a, s);
   }
 }

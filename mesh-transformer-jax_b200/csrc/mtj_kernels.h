@@ -25,7 +25,9 @@ struct KvCache {
   const int32_t* pad;          // [batch] first valid absolute position
 };
 
-enum GemvEpilogue { kEpiInProj = 0, kEpiOut = 1, kEpiLogits = 2 };
+enum GemvEpilogue { kEpiInProj = 0, kEpiOut = 1, kEpiLogits = 2,
+                    kEpiLogitsCE = 3 };   // logits that are never stored: per (128-entry vocabulary group, token) max and
+                                          // sum of exp instead, plus the target's logit (persistent GEMM only)
 
 struct GemvArgs {
   // y[m, n] = sum_k W[n, k] * act(x[m, k]);  W is bf16 [N, K] (K contiguous).
@@ -205,6 +207,14 @@ struct GemmTcArgs {
   int ld_out;
   float* partial;              // split-K: [ksplit, M, N] raw partial sums (out-proj / logits epilogues), or null
   int ksplit;
+  // kEpiLogitsCE (ProjectionShard.loss, layers.py:569-593): token row m of this launch is chunk row x_row0 + m
+  float* ce_gmax;              // [4 * ceil(N / 128)][ce_ld] max over the group's 32 logits, per token row
+  float* ce_gsum;              // same shape: sum of exp(logit - that max)
+  int ce_ld;                   // row stride of the two arrays (>= M)
+  float* ce_tlogit;            // [M] the target's logit where the target id falls into [ce_vocab_start, + N)
+  uint8_t* ce_hit;             // [M] 1 where it does (both zeroed by the caller before the launch)
+  const uint32_t* ce_targets;  // [batch, ce_T] target ids; row -> (sequence, position) through `rows`
+  int ce_T, ce_vocab_start;
   int cluster_k;               // 2 or 4 (token tiles of at most 64 rows, partial == null): split K over a cluster of
                                // blocks that add their accumulators in shared memory before the fused epilogue
   uint32_t* dev_err;
@@ -265,6 +275,10 @@ struct CeArgs {
   uint8_t* correct_out;        // [batch, T]
 };
 cudaError_t launch_ce_partial(const CeArgs& a, int rows, cudaStream_t s);
+// the same three per-row results from the per-group partials of the fused logits epilogue
+// (gmax / gsum [n_groups][ld], tlogit / ghit [rows]) for chunk rows [a.row0, a.row0 + rows)
+cudaError_t launch_ce_combine(const CeArgs& a, const float* gmax, const float* gsum, int n_groups, int ld,
+                              const float* tlogit, const uint8_t* ghit, int rows, cudaStream_t s);
 cudaError_t launch_ce_rescale(const CeArgs& a, const float* lmax, int n, cudaStream_t s);
 cudaError_t launch_ce_finalize(const CeArgs& a, int n, cudaStream_t s);
 

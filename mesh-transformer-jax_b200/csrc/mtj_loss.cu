@@ -52,6 +52,45 @@ __global__ void __launch_bounds__(kThreads) ce_partial_kernel(const CeArgs a) {
   }
 }
 
+// Combines the per-group (max, sum of exp) pairs that the fused logits epilogue leaves (one group = 32
+// vocabulary entries) into this shard's per-row local max and sum: the same three results ce_partial gives.
+// Block = 32 token rows x 8 warps; the warps split the groups, lanes are rows (coalesced loads).
+__global__ void __launch_bounds__(256) ce_combine_kernel(const CeArgs a, const float* __restrict__ gmax,
+                                                         const float* __restrict__ gsum, int n_groups, int ld,
+                                                         const float* __restrict__ tlogit,
+                                                         const uint8_t* __restrict__ ghit, int rows) {
+  __shared__ float sm[8][32], ss[8][32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int r = blockIdx.x * 32 + lane;
+  float m = -INFINITY, s = 0.f;
+  if (r < rows) {
+    for (int g = warp; g < n_groups; g += 8) {
+      const float gm = gmax[static_cast<size_t>(g) * ld + r], gs = gsum[static_cast<size_t>(g) * ld + r];
+      if (gm == -INFINITY) continue;                       // a group beyond the end of the vocabulary slice
+      const float nm = fmaxf(m, gm);
+      s = s * expf(m - nm) + gs * expf(gm - nm);          // m = -inf only while s = 0: exp(-inf) = 0
+      m = nm;
+    }
+  }
+  sm[warp][lane] = m;
+  ss[warp][lane] = s;
+  __syncthreads();
+  if (warp == 0 && r < rows) {
+    float M = sm[0][lane];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) M = fmaxf(M, sm[w][lane]);
+    float S = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) S += sm[w][lane] == -INFINITY ? 0.f : ss[w][lane] * expf(sm[w][lane] - M);
+    const int mrow = a.row0 + r;
+    const bool hit = ghit[r] != 0;
+    a.pmax[mrow] = M;
+    a.psum[2 * mrow] = S;
+    a.psum[2 * mrow + 1] = hit ? tlogit[r] : 0.f;
+    a.hit[mrow] = hit ? 1 : 0;
+  }
+}
+
 __global__ void ce_rescale_kernel(const CeArgs a, const float* __restrict__ lmax, int n) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
@@ -73,6 +112,11 @@ __global__ void ce_finalize_kernel(const CeArgs a, int n) {
 
 cudaError_t launch_ce_partial(const CeArgs& a, int rows, cudaStream_t s) {
   ce_partial_kernel<<<rows, kThreads, 0, s>>>(a);
+  return cudaGetLastError();
+}
+cudaError_t launch_ce_combine(const CeArgs& a, const float* gmax, const float* gsum, int n_groups, int ld,
+                              const float* tlogit, const uint8_t* ghit, int rows, cudaStream_t s) {
+  ce_combine_kernel<<<(rows + 31) / 32, 256, 0, s>>>(a, gmax, gsum, n_groups, ld, tlogit, ghit, rows);
   return cudaGetLastError();
 }
 cudaError_t launch_ce_rescale(const CeArgs& a, const float* lmax, int n, cudaStream_t s) {

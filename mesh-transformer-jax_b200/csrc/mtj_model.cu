@@ -140,6 +140,16 @@ struct mtj_handle {
   float* tc_partial = nullptr;        // [kTcSplitMax, kTcSplitRows, d] split-K partial sums of small-M out-projections
   int eval_rows = 0;                // rows of logits materialised at a time by the loss path
   float* eval_logits = nullptr;     // [eval_rows, Vl]
+  // loss path on the persistent GEMM: the logits are never stored, its epilogue leaves per (32-entry vocabulary
+  // group, row) the max and the sum of exp, plus the target's logit
+  int ce_groups = 0;
+  int ce_rows = 0;                  // rows per launch of that GEMM: several 256-row token tiles, so that a block's
+                                    // epilogues overlap its next tiles instead of ending the launch
+  float* ce_gmax = nullptr;         // [ce_groups, ce_rows]
+  float* ce_gsum = nullptr;
+  float* ce_tlogit = nullptr;       // [ce_rows]
+  uint8_t* ce_ghit = nullptr;       // [ce_rows]
+  bool fused_ce = true;             // MTJ_NO_FUSED_CE=1: materialise the logits slice and run ce_partial instead
   float* ce_max = nullptr;          // [max_rows] local max, then global max
   float* ce_lmax = nullptr;         // [max_rows] copy of the local max (mp > 1)
   float* ce_sum = nullptr;          // [max_rows, 2]
@@ -278,6 +288,12 @@ struct mtj_handle {
     act_lo = c.take<__nv_bfloat16>(std::min<int64_t>(R, kHiLoRows) * (dl + ffl));
     eval_rows = static_cast<int>(std::min<int64_t>(R, 256));
     eval_logits = c.take<float>(static_cast<int64_t>(eval_rows) * Vl);
+    ce_groups = 4 * ((Vl + 127) / 128);
+    ce_rows = static_cast<int>(std::min<int64_t>(R, 1024));
+    ce_gmax = c.take<float>(static_cast<int64_t>(ce_groups) * ce_rows);
+    ce_gsum = c.take<float>(static_cast<int64_t>(ce_groups) * ce_rows);
+    ce_tlogit = c.take<float>(ce_rows);
+    ce_ghit = c.take<uint8_t>(ce_rows);
     ce_max = c.take<float>(R);
     ce_lmax = c.take<float>(R);
     ce_sum = c.take<float>(R * 2);
@@ -710,6 +726,40 @@ int32_t run_logits_tc(mtj_handle* h, int M, int row0, float* out, cudaStream_t s
   return MTJ_OK;
 }
 
+// ProjectionShard.loss, local part (layers.py:569-585), for rows [row0, row0 + n) of the chunk in h->x: final
+// LayerNorm, then the logits GEMM whose epilogue reduces every 32-entry vocabulary group to (max, sum of exp)
+// instead of storing logits, then the per-row combination.  Leaves ce.pmax / psum / hit like ce_partial.
+int32_t run_loss_rows_fused(mtj_handle* h, int n, int row0, const mtj::CeArgs& ce, cudaStream_t s) {
+  MTJ_CUDA(mtj::launch_ln_rows(h->x + static_cast<size_t>(row0) * h->d, h->lnf_scale, h->lnf_offset,
+                               h->xn_bf16 + static_cast<size_t>(row0) * h->d, n, h->d, s, false, nullptr));
+  MTJ_CUDA(cudaMemsetAsync(h->ce_tlogit, 0, sizeof(float) * n, s));
+  MTJ_CUDA(cudaMemsetAsync(h->ce_ghit, 0, n, s));
+  mtj::GemmTcArgs a = {};
+  a.M = n;
+  a.N = h->Vl;
+  a.K = h->d;
+  a.x_row0 = row0;
+  a.rows = ce.rows;
+  a.bias = h->proj_b;
+  a.ce_gmax = h->ce_gmax;
+  a.ce_gsum = h->ce_gsum;
+  a.ce_ld = h->ce_rows;
+  a.ce_tlogit = h->ce_tlogit;
+  a.ce_hit = h->ce_ghit;
+  a.ce_targets = ce.targets;
+  a.ce_T = ce.T;
+  a.ce_vocab_start = ce.vocab_start;
+  a.dev_err = h->dev_err;
+  h->prof_begin(MTJ_FAMILY_LOGITS, s);
+  MTJ_CUDA(mtj::launch_gemm_tc_wide(mtj::kEpiLogitsCE, &h->map_proj, &h->map_xn_wide, a, s));
+  h->prof_end(s);
+  mtj::CeArgs c2 = ce;
+  c2.row0 = row0;
+  MTJ_CUDA(mtj::launch_ce_combine(c2, h->ce_gmax, h->ce_gsum, h->ce_groups, h->ce_rows, h->ce_tlogit, h->ce_ghit, n, s));
+  h->launches += 3;
+  return MTJ_OK;
+}
+
 bool use_tc(const mtj_handle* h, int M) { return h->tc_ok && M >= 32; }
 // decode: from this many sequences on, one tensor-core pass over the weights beats ceil(B/4) GEMV passes
 bool use_tc_decode(const mtj_handle* h, int B) { return h->tc_ok && B >= h->tc_decode_min_b; }
@@ -963,6 +1013,8 @@ int32_t mtj_create(const mtj_config* c, mtj_handle** out) {
   h->tp_token = !(e && e[0] == '1');
   e = getenv("MTJ_NO_CLUSTER_K");
   h->tc_cluster_k = !(e && e[0] == '1');
+  e = getenv("MTJ_NO_FUSED_CE");
+  h->fused_ce = !(e && e[0] == '1');
   e = getenv("MTJ_NO_FORK");
   h->fork_attn = !(e && e[0] == '1');
   e = getenv("MTJ_FORK_PDL");
@@ -1585,8 +1637,15 @@ int32_t mtj_eval_loss(mtj_handle* h, const uint32_t* obs, const uint32_t* target
     ce.hit = h->ce_hit;
     ce.loss_out = all_loss;
     ce.correct_out = correct;
-    for (int m0 = 0; m0 < M; m0 += h->eval_rows) {
-      const int n = std::min(h->eval_rows, M - m0);
+    const bool fused = h->fused_ce && use_tc(h, M);
+    const int step = fused ? h->ce_rows : h->eval_rows;
+    for (int m0 = 0; m0 < M; m0 += step) {
+      const int n = std::min(step, M - m0);
+      if (fused && use_tc_wide(h, n)) {
+        int32_t r3 = run_loss_rows_fused(h, n, m0, ce, s);
+        if (r3) return r3;
+        continue;
+      }
       int32_t r2 = use_tc(h, M) ? run_logits_tc(h, n, m0, h->eval_logits, s)
                                 : run_logits(h, n, nullptr, h->eval_logits, false, s, m0);
       if (r2) return r2;
@@ -1788,8 +1847,15 @@ int32_t mtj_k_projection_loss(mtj_handle* h, const float* x_in, const uint32_t* 
   ce.hit = h->ce_hit;
   ce.loss_out = loss_out;
   ce.correct_out = correct_out;
-  for (int m0 = 0; m0 < rows; m0 += h->eval_rows) {
-    const int n = std::min(h->eval_rows, rows - m0);
+  const bool fused = h->fused_ce && use_tc(h, rows);
+  const int step = fused ? h->ce_rows : h->eval_rows;
+  for (int m0 = 0; m0 < rows; m0 += step) {
+    const int n = std::min(step, rows - m0);
+    if (fused && use_tc_wide(h, n)) {
+      rc = run_loss_rows_fused(h, n, m0, ce, s);
+      if (rc) return rc;
+      continue;
+    }
     rc = use_tc(h, rows) ? run_logits_tc(h, n, m0, h->eval_logits, s)
                          : run_logits(h, n, nullptr, h->eval_logits, false, s, m0);
     if (rc) return rc;

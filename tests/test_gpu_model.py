@@ -329,3 +329,27 @@ def test_whole_step_kernel_with_several_sequences(cuda_device, monkeypatch, batc
     assert _rel(out[2], ref[2]) <= LOGIT_TOL
     assert np.array_equal(out[0], ref[0])
     net._rt.check_device_status()
+
+
+@pytest.mark.gpu
+def test_fused_cross_entropy_epilogue_equals_the_materialised_logits_path(cuda_device, monkeypatch):
+    """eval over more than 192 rows takes the persistent GEMM whose epilogue reduces the logits to per-group
+    (max, sum of exp) pairs without storing them; MTJ_NO_FUSED_CE=1 materialises the logits slice and runs
+    ce_partial.  Both must give the same per-token loss and `correct` (layers.py:569-593), with a key mask and
+    a vocabulary whose last 128-row tile is partly empty."""
+    cfg = dict(spec.tiny_config(1, seq=160), n_vocab=1000)
+    params = spec.make_params(cfg, seed=61, stress=True)
+    ids = spec.token_ids(62, 3, 161, 1000)
+    sample = {"obs": ids[:, :-1], "target": ids[:, 1:], "ctx_length": np.array([160, 33, 160])}
+    net = _net(cfg, params, cuda_device)
+    fused = net.eval(sample)
+    net.close()
+    monkeypatch.setenv("MTJ_NO_FUSED_CE", "1")
+    net2 = _net(cfg, params, cuda_device)
+    plain = net2.eval(sample)
+    net2.close()
+    assert np.abs(fused["all_loss"] - plain["all_loss"]).max() <= 1e-4
+    assert np.array_equal(fused["correct"], plain["correct"])
+    ref = go.CausalTransformer(cfg, params).eval(sample)
+    assert np.abs(fused["all_loss"] - ref["all_loss"]).max() <= 2e-2
+    assert np.abs(fused["loss"] - ref["loss"]).max() <= 1e-3
