@@ -127,6 +127,23 @@ int32_t mtj_p2p_import(mtj_handle* h, const uint8_t* ipc_handles_all_ranks);
 int32_t mtj_prefill(mtj_handle* h, const uint32_t* ctx_dev, const uint32_t* ctx_length_host,
                     int32_t batch, mtj_stream s);
 
+/* Continuous batching -- the reference's serving loop (device_serve.py:138-194)
+ * runs fixed batches: every request waits for a whole generate call.  These two
+ * calls let a sequence join a batch that is already decoding.
+ * mtj_start_batch opens a running batch of `batch` idle slots (the state
+ * mtj_prefill leaves, without any context).  mtj_admit puts a prompt into one
+ * slot between two decode steps: its first len - 1 tokens are prefilled at the
+ * positions right before the batch's current decode position and its last token
+ * becomes the slot's next input -- generate_initial (transformer_shard.py:74-95)
+ * in a frame shifted by the steps the batch has taken, which changes nothing
+ * because cached keys are rotated at absolute positions and attention depends
+ * on distances only.  The slot's earlier contents fall out of its window.
+ * prompt_dev: [len] uint32 device, 1 <= len <= seq.  A slot whose sequence has
+ * finished simply keeps stepping until the next mtj_admit; the batch can take
+ * max_gen steps in total. */
+int32_t mtj_start_batch(mtj_handle* h, int32_t batch, mtj_stream s);
+int32_t mtj_admit(mtj_handle* h, int32_t slot, const uint32_t* prompt_dev, int32_t len, mtj_stream s);
+
 /* One step of the generate scan (transformer_shard.py:198-210): generate_once
  * then the sampler.  tokens_in_dev may be NULL (use the previous step's
  * sample / the held-back last prompt token).  top_p/temp: [batch] f32 device;

@@ -1404,6 +1404,53 @@ int32_t mtj_prefill(mtj_handle* h, const uint32_t* ctx, const uint32_t* ctx_len,
   return MTJ_OK;
 }
 
+int32_t mtj_start_batch(mtj_handle* h, int32_t batch, mtj_stream stream) {
+  int32_t rc = check_ready(h);
+  if (rc) return rc;
+  if (h->mp > 1 && !h->comm) return fail(MTJ_ERR_STATE, "cores_per_replica > 1 needs mtj_comm_init first");
+  if (batch <= 0 || batch > h->max_batch) return fail(MTJ_ERR_INVALID, "bad batch");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // every slot idles on a one-key window of its own (zeroed) cache until a sequence is admitted into it
+  std::vector<int32_t> pad(batch, h->W), limit(batch, 0x7fffffff);
+  rc = setup_sequences(h, pad, limit, h->W, s);
+  if (rc) return rc;
+  MTJ_CUDA(cudaMemsetAsync(h->tokens, 0, sizeof(uint32_t) * batch, s));
+  h->batch = batch;
+  h->prefilled = true;
+  h->steps_done = 0;
+  return MTJ_OK;
+}
+
+int32_t mtj_admit(mtj_handle* h, int32_t slot, const uint32_t* prompt, int32_t len, mtj_stream stream) {
+  int32_t rc = check_ready(h);
+  if (rc) return rc;
+  if (!h->prefilled) return fail(MTJ_ERR_STATE, "no running batch (mtj_start_batch or mtj_prefill first)");
+  if (!prompt || slot < 0 || slot >= h->batch) return fail(MTJ_ERR_INVALID, "bad slot");
+  if (len < 1 || len > h->seq) return fail(MTJ_ERR_INVALID, "prompt length must be in [1, seq]");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // The batch's next decode position; the prompt's first len - 1 tokens are placed right before it and the last
+  // one becomes the slot's next input, exactly what generate_initial does with a left-padded context
+  // (transformer_shard.py:76-77) -- in a frame shifted by the steps the batch has already taken.  Keys are
+  // cached rotated at absolute positions and attention depends on distances only, so the shift changes nothing.
+  const int cur = h->W + h->steps_done;
+  const int n = len - 1, pos0 = cur - n;
+  if (cur + 1 >= h->max_pos) return fail(MTJ_ERR_STATE, "the batch has used up its positions (max_gen)");
+  const int32_t padv = pos0, lim = 0x7fffffff;
+  MTJ_CUDA(cudaMemcpyAsync(h->pad + slot, &padv, sizeof(int32_t), cudaMemcpyHostToDevice, s));
+  MTJ_CUDA(cudaMemcpyAsync(h->key_limit + slot, &lim, sizeof(int32_t), cudaMemcpyHostToDevice, s));
+  MTJ_CUDA(cudaMemcpyAsync(h->tokens + slot, prompt + n, sizeof(uint32_t), cudaMemcpyDeviceToDevice, s));
+  h->xn_ready = false;
+  for (int t0 = 0; t0 < n && !rc; t0 += h->max_rows) {
+    const int M = std::min(h->max_rows, n - t0);
+    const mtj::RowMap ids_rows = {0, M, 0, nullptr};                  // the prompt is a flat id array
+    const mtj::RowMap rows = {slot, M, pos0 + t0, nullptr};
+    rc = run_embed(h, prompt + t0, 0, M, ids_rows, false, s);
+    for (int l = 0; l < h->L && !rc; ++l)
+      rc = use_tc(h, M) ? run_layer_tc(h, l, M, rows, nullptr, s) : run_layer(h, l, M, rows, false, nullptr, s);
+  }
+  return rc;
+}
+
 int32_t mtj_decode_step(mtj_handle* h, const uint32_t* tokens_in, const float* top_p, const float* temp,
                         const float* uniforms, int32_t greedy, uint32_t* tokens_out, float* logits_out,
                         mtj_stream stream) {

@@ -48,6 +48,8 @@ def _load():
         "mtj_p2p_export": (i32, [vp, vp]),
         "mtj_p2p_import": (i32, [vp, vp]),
         "mtj_prefill": (i32, [vp, vp, ctypes.POINTER(ctypes.c_uint32), i32, vp]),
+        "mtj_start_batch": (i32, [vp, i32, vp]),
+        "mtj_admit": (i32, [vp, i32, vp, i32, vp]),
         "mtj_decode_step": (i32, [vp, vp, vp, vp, vp, i32, vp, vp, vp]),
         "mtj_eval_loss": (i32, [vp, vp, vp, ctypes.POINTER(ctypes.c_uint32), i32, i32, vp, vp, vp]),
         "mtj_forward_logits": (i32, [vp, vp, ctypes.POINTER(ctypes.c_uint32), i32, i32, i32, vp, vp]),

@@ -190,6 +190,16 @@ class ShardRuntime:
         lens = _lib.u32_array(list(ctx_length))
         check(lib.mtj_prefill(self._h, ctx_dev.data_ptr(), lens, ctx_dev.shape[0], self.stream))
 
+    def start_batch(self, batch: int) -> None:
+        """Opens a running decode batch of ``batch`` idle slots (continuous batching)."""
+        check(lib.mtj_start_batch(self._h, batch, self.stream))
+
+    def admit(self, slot: int, prompt_dev: torch.Tensor) -> None:
+        """Puts a prompt ([len] int32 on the device, 1 <= len <= seq) into one slot of the running batch."""
+        prompt_dev = prompt_dev.contiguous()
+        check(lib.mtj_admit(self._h, slot, prompt_dev.data_ptr(), prompt_dev.numel(), self.stream))
+        torch.cuda.current_stream(self.device).synchronize()       # the caller may drop ``prompt_dev``
+
     def decode_step(self, tokens_in=None, tokens_out=None, logits_out=None, greedy=True,
                     top_p=None, temp=None, uniforms=None) -> None:
         p = lambda t: None if t is None else t.data_ptr()

@@ -95,3 +95,88 @@ class CompletionService:
 
     def stop(self):
         self._stop.set()
+
+
+class ContinuousBatchingService:
+    """The same ``/complete`` contract with continuous batching over the paged KV cache: a request joins the
+    running decode batch at the next step (its prompt is prefilled into a free slot) and is answered as soon as
+    ITS ``gen_length`` tokens exist, instead of waiting for a whole fixed batch to be gathered, padded with filler
+    prompts and generated to the end (device_serve.py:143-160,183-192).  Needs the CUDA network (it drives the
+    per-GPU runtime: ``start_batch`` / ``admit`` / ``decode_step``); sampling uses the device generator.
+
+    A running batch can take ``epoch_steps`` decode steps (its position budget); the loop stops admitting when a
+    new request could not finish inside the budget and opens a new batch once the active ones have drained."""
+
+    def __init__(self, network, tokenizer, seq, slots, gen_length=256, epoch_steps=4096, seed=0):
+        self.network, self.tokenizer = network, tokenizer
+        self.seq, self.slots, self.gen_length = seq, slots, gen_length
+        self.epoch_steps = max(epoch_steps, gen_length + 1)
+        self.seed = seed
+        self.requests_queue: Queue = Queue()
+        self._stop = threading.Event()
+        self.steps_taken = 0            # decode steps over the service's life (for tests / monitoring)
+        self.admitted = 0
+
+    def complete(self, content: dict) -> dict:
+        if self.requests_queue.qsize() > MAX_PENDING:
+            return {"error": "queue full, try again later"}
+        response_queue: Queue = Queue()
+        self.requests_queue.put(({"context": content["context"], "top_p": float(content["top_p"]),
+                                  "temp": float(content["temp"])}, response_queue))
+        return {"completion": response_queue.get()}
+
+    def serve_forever(self, poll_s=0.002):
+        import torch
+        rt = self.network._runtime(self.slots, self.epoch_steps)
+        dev = rt.device
+        with torch.cuda.device(dev):
+            top_p = torch.ones((self.slots,), dtype=torch.float32, device=dev)
+            temp = torch.ones((self.slots,), dtype=torch.float32, device=dev)
+            tok = torch.empty((self.slots,), dtype=torch.int32, device=dev)
+            active = {}                  # slot -> [response queue, produced ids]
+            epoch_left = 0
+            while not self._stop.is_set():
+                if epoch_left <= 0 and not active:
+                    rt.set_seed(self.seed + self.steps_taken)
+                    rt.start_batch(self.slots)
+                    epoch_left = self.epoch_steps
+                # admit waiting requests into free slots while the batch can still finish them
+                while len(active) < self.slots and epoch_left > self.gen_length:
+                    try:
+                        req, q = self.requests_queue.get(block=False)
+                    except Empty:
+                        break
+                    try:
+                        ids = list(self.tokenizer.encode(req["context"]))[-self.seq:]
+                    except Exception:                             # device_serve.py:178-179
+                        print("oops exception")
+                        ids = []
+                    if not ids:
+                        ids = [0]
+                    slot = next(i for i in range(self.slots) if i not in active)
+                    prompt = torch.tensor(ids, dtype=torch.int32, device=dev)
+                    rt.admit(slot, prompt)
+                    top_p[slot] = req["top_p"]
+                    temp[slot] = req["temp"]
+                    active[slot] = [q, []]
+                    self.admitted += 1
+                if not active:
+                    if epoch_left <= self.gen_length:
+                        epoch_left = 0                            # nothing left to drain: open a new batch
+                        continue
+                    time.sleep(poll_s)
+                    continue
+                rt.decode_step(None, tok, None, greedy=False, top_p=top_p, temp=temp, uniforms=None)
+                epoch_left -= 1
+                self.steps_taken += 1
+                new = tok.cpu().numpy().view(np.uint32)
+                for slot in list(active):
+                    q, out = active[slot]
+                    out.append(int(new[slot]))
+                    if len(out) == self.gen_length:
+                        q.put(self.tokenizer.decode(np.asarray(out, np.uint32)))
+                        del active[slot]
+            rt.check_device_status()
+
+    def stop(self):
+        self._stop.set()

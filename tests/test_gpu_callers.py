@@ -127,3 +127,54 @@ def test_hf_state_dict_through_the_cuda_path_matches_transformers(cuda_device):
         hf = model.generate(seq_ids, max_new_tokens=8, do_sample=False, pad_token_id=0)[0, 40:].numpy()
     assert np.array_equal(toks, hf.astype(np.uint32))
     net.close()
+
+
+def test_continuous_batching_service(cuda_device):
+    """Requests join a running decode batch at step granularity (mtj_start_batch / mtj_admit): three slots, eight
+    requests arriving while others are being decoded, a position budget small enough to force a second batch.
+    Every greedy completion equals the oracle's greedy generate of the same left-padded prompt -- a sequence
+    admitted in mid-flight sits at shifted absolute positions, which changes nothing (rotary attention depends on
+    distances only)."""
+    import time
+    import serve
+    from mesh_transformer.sampling import nucleaus_sample
+    cfg = spec.tiny_config(1, seq=64)
+    params = spec.make_params(cfg, seed=13, stress=True)
+    net = _net(dict(cfg, sampler=nucleaus_sample), params, cuda_device)
+    tok = ByteTokenizer()
+    gen = 8
+    svc = serve.ContinuousBatchingService(net, tok, seq=64, slots=3, gen_length=gen, epoch_steps=30)
+    texts = ["hello world", "abc", "the quick brown fox jumps over the lazy dog " * 3, "x", "tensor parallel",
+             "paged key value cache", "boom", "zz top"]
+    reqs = [{"context": c, "top_p": 0.0, "temp": 1.0} for c in texts]
+    reqs[3] = {"context": "x", "top_p": 0.9, "temp": 0.8}                 # one sampled request among the greedy ones
+    answers = [None] * len(reqs)
+
+    def client(i):
+        time.sleep(0.01 * i)                                              # arrivals spread over the decode steps
+        answers[i] = svc.complete(reqs[i])
+
+    worker = threading.Thread(target=svc.serve_forever, daemon=True)
+    clients = [threading.Thread(target=client, args=(i,)) for i in range(len(reqs))]
+    worker.start()
+    for c in clients:
+        c.start()
+    for c in clients:
+        c.join(timeout=120)
+    svc.stop()
+    worker.join(timeout=30)
+    assert all(a is not None and "completion" in a for a in answers)
+    assert svc.admitted == len(reqs)
+    # fixed batches of three would take 3 x 8 steps only if all requests were there at the start and no batch
+    # had to be padded; here nothing waits for a batch to fill and no slot decodes a filler prompt to the end
+    assert svc.steps_taken <= len(reqs) * gen
+    ref = go.CausalTransformer(cfg, params)
+    for i, r in enumerate(reqs):
+        if r["top_p"] != 0.0:
+            assert len(answers[i]["completion"].split()) == gen
+            continue
+        ids = tok.encode(r["context"]) if r["context"] != "boom" else [0]
+        padded, n = serve.pad_context(ids, 64)
+        out = ref.generate(padded[None], np.array([min(n, 64)]), gen)
+        assert answers[i]["completion"] == tok.decode(out[1][0][0, :, 0]), r["context"]
+    net.close()
