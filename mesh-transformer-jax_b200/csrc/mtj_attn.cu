@@ -239,12 +239,14 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attn_kernel(const DecodeA
   if (threadIdx.x == 0) a.counters[b * a.heads + head] = 0u;
 }
 
-// The same decode attention for many sequences: one block walks kStreamPages consecutive pages of one
+// The same decode attention for many sequences: one block walks a.stream_pages (1-4) consecutive pages of one
 // (sequence, head) as half-page tiles (32 keys: 16 KB of K + 16 KB of V) through a 3-stage ring fed by a
 // producer warp, so the block's loads stay in flight while its eight consumer warps work, and the
 // per-block costs (launch, warp merge, partial write, ticket) are spread over up to 256 keys.  Each
 // consumer warp keeps its own running (max, sum, weighted V) over the 4 keys it takes from every tile.
-constexpr int kStreamPages = 4;
+// The launcher picks the pages per block so that the grid fills whole waves of resident blocks: with few
+// heads per GPU (tensor-parallel shards) four pages per block leave the last wave mostly empty.
+constexpr int kStreamPages = 4;                            // most pages a block walks
 constexpr int kStreamStages = 3;
 constexpr int kTileTokens = 32;
 constexpr int kStreamThreads = kAttnThreads + 32;
@@ -269,9 +271,10 @@ __global__ void __launch_bounds__(kStreamThreads) decode_attn_stream_kernel(cons
   const int end = cur + 1;
   const int first_page = start / kPageTokens;
   const int n_pages = cur / kPageTokens - first_page + 1;
-  const int nsplit = (n_pages + kStreamPages - 1) / kStreamPages;
-  const int page0 = first_page + split * kStreamPages;     // first page of this block
-  const int my_pages = min(kStreamPages, first_page + n_pages - page0);
+  const int ppb = a.stream_pages;                          // pages per block
+  const int nsplit = (n_pages + ppb - 1) / ppb;
+  const int page0 = first_page + split * ppb;              // first page of this block
+  const int my_pages = min(ppb, first_page + n_pages - page0);
   const int n_tiles = 2 * max(my_pages, 0);
   const uint32_t bar0 = smem_u32(bars);
   auto full_bar = [&](int st) { return bar0 + 8u * st; };
@@ -585,7 +588,25 @@ cudaError_t launch_decode_stream_dh(const DecodeAttnArgs& a, cudaStream_t s, boo
     if (e != cudaSuccess) return e;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((a.grid_splits + kStreamPages - 1) / kStreamPages, a.heads, a.B);
+  // Pages per block: the grid should be whole waves of resident blocks.  est_pages is the number of pages the
+  // sequences hold now (the grid must cover grid_splits, but blocks past a sequence's last page leave at once).
+  int sms = 148, dev = 0, per_sm = 1;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_attn_stream_kernel<DH>, kStreamThreads, smem);
+  const int resident = sms * (per_sm < 1 ? 1 : per_sm);
+  const int pages = a.est_pages > 0 ? (a.est_pages < a.grid_splits ? a.est_pages : a.grid_splits) : a.grid_splits;
+  DecodeAttnArgs b = a;
+  float best = 0.f;
+  for (int p = kStreamPages; p >= 1; --p) {
+    const long blocks = static_cast<long>((pages + p - 1) / p) * a.heads * a.B;
+    const float cost = static_cast<float>((blocks + resident - 1) / resident) * (p + 0.3f);   // 0.3: per-block overhead in page times
+    if (p == kStreamPages || cost < best * 0.97f) {
+      best = cost;
+      b.stream_pages = p;
+    }
+  }
+  if ((a.grid_splits + b.stream_pages - 1) / b.stream_pages > 64) b.stream_pages = kStreamPages;   // merge buffer: 64 splits
+  cfg.gridDim = dim3((a.grid_splits + b.stream_pages - 1) / b.stream_pages, a.heads, a.B);
   cfg.blockDim = dim3(kStreamThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = s;
@@ -594,7 +615,7 @@ cudaError_t launch_decode_stream_dh(const DecodeAttnArgs& a, cudaStream_t s, boo
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl ? 1 : 0;
-  return cudaLaunchKernelEx(&cfg, decode_attn_stream_kernel<DH>, a);
+  return cudaLaunchKernelEx(&cfg, decode_attn_stream_kernel<DH>, b);
 }
 
 // Splits of the visible window: one per 64-token page it can touch.

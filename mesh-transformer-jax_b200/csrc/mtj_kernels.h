@@ -89,6 +89,8 @@ struct DecodeAttnArgs {
   const int32_t* cur_dev;      // absolute position of the query token
   int max_splits;              // stride of the partial buffers
   int grid_splits;             // blocks per (sequence, head) = decode_attn_splits(window)
+  int est_pages;               // optional: pages the sequences hold now (sizes the streaming kernel's blocks), 0 = unknown
+  int stream_pages;            // set by the launcher: pages one block of the streaming kernel walks
   float* part_o;               // [B, heads, max_splits, d_head]
   float* part_ml;              // [B, heads, max_splits, 2]
   uint32_t* counters;          // [B*heads] zero-initialised, self-resetting

@@ -112,8 +112,7 @@ struct mtj_handle {
   bool tp_token = true;             // decode at mp > 1: the greedy token is agreed on by pushing each rank's local
                                     // arg-max to all ranks instead of gathering the logits (MTJ_NO_TP_TOKEN=1: off)
   bool tp_push = false;             // batched decode at mp > 1: push all-reduce fused with the split-K reduction and
-                                    // the LayerNorm (MTJ_TP_PUSH=1: on; measured slower than the three-kernel chain
-                                    // at 2 GPUs, kept for comparison at larger shard counts)
+                                    // the LayerNorm; default: from 4 shards on (MTJ_TP_PUSH=0 / 1 overrides)
   bool xn_ready = false;            // the bf16 operand of the next projection has already been written
   bool tc_cluster_k = true;         // batched decode: split K over block clusters when tiles are few (MTJ_NO_CLUSTER_K=1: off)
   float* uniforms = nullptr;        // [max_batch, V] sampler inputs of the current step
@@ -168,6 +167,13 @@ struct mtj_handle {
   bool bound = false;
 
   // decode state
+  int min_pad = 0;                  // smallest first-visible position over the running sequences
+  // pages a sequence of the running batch holds at most right now (its window start to the decode position)
+  int est_pages() const {
+    const int cur = W + steps_done;
+    const int start = std::max(min_pad, cur - W + 1);
+    return cur / mtj::kPageTokens - start / mtj::kPageTokens + 1;
+  }
   int batch = 0;
   bool prefilled = false;
   int steps_done = 0;
@@ -199,7 +205,8 @@ struct mtj_handle {
   int view_rows[2] = {0, 0};
   cudaStream_t comm_stream = nullptr;
   cudaEvent_t ev_layer[2] = {nullptr, nullptr}, ev_reduced[2] = {nullptr, nullptr};
-  bool tp_pipe = false;             // MTJ_TP_PIPE=1: overlap the all-reduce of one chunk with the layer of the next
+  bool tp_pipe = false;             // overlap the all-reduce of one chunk with the layer of the next; default: from 4
+                                    // shards on (MTJ_TP_PIPE=0 / 1 overrides)
   void save_view(int i) {
     ActView& v = views[i];
     v.x = x; v.stats = stats; v.part = part; v.q = q; v.xn_bf16 = xn_bf16; v.act_bf16 = act_bf16; v.q_bf16 = q_bf16;
@@ -478,6 +485,7 @@ int32_t run_layer(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, bool
     d.cur_dev = h->cur;
     d.max_splits = h->max_splits;
     d.grid_splits = std::min(mtj::decode_attn_splits(h->W), h->ring_pages);
+    d.est_pages = h->est_pages();
     d.dev_err = h->dev_err;
     d.part_o = h->part_o;
     d.part_ml = h->part_ml;
@@ -600,6 +608,7 @@ int32_t run_layer_tc(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, c
     d.cur_dev = h->cur;
     d.max_splits = h->max_splits;
     d.grid_splits = std::min(mtj::decode_attn_splits(h->W), h->ring_pages);
+    d.est_pages = h->est_pages();
     d.dev_err = h->dev_err;
     d.part_o = h->part_o;
     d.part_ml = h->part_ml;
@@ -1007,8 +1016,11 @@ int32_t mtj_create(const mtj_config* c, mtj_handle** out) {
   h->tc_pdl = !(e && e[0] == '1');
   e = getenv("MTJ_NO_MEGA_PUSH");
   h->mega_push = !(e && e[0] == '1');
+  // measured on one box: the fused push exchange loses 6 % of a 32-sequence step at 2 shards and wins 12 % at 4
+  // (the pull all-reduce reads every peer's slot, which grows with the shard count; the push does not)
+  h->tp_push = mp >= 4;
   e = getenv("MTJ_TP_PUSH");
-  h->tp_push = e && e[0] == '1';
+  if (e) h->tp_push = e[0] == '1';
   e = getenv("MTJ_NO_TP_TOKEN");
   h->tp_token = !(e && e[0] == '1');
   e = getenv("MTJ_NO_CLUSTER_K");
@@ -1184,8 +1196,12 @@ int32_t mtj_bind_arenas(mtj_handle* h, void* wdev, int64_t wbytes, void* sdev, i
     h->views_ok = ok;
     h->view_rows[0] = static_cast<int>(r0);
     h->view_rows[1] = static_cast<int>(r1);
+    // measured: overlapping one chunk's all-reduce with the other chunk's layer costs 7 % of a 2047-token prefill
+    // at 2 shards (the halves quantise worse over the GEMM's blocks) and gains 10 % at 4, where the all-reduce
+    // is a larger share
+    h->tp_pipe = h->mp >= 4;
     const char* np = getenv("MTJ_TP_PIPE");
-    h->tp_pipe = np && np[0] == '1';
+    if (np) h->tp_pipe = np[0] == '1';
   }
   h->bound = true;
   h->leaf_loaded.assign(static_cast<size_t>(h->expected), 0);
@@ -1391,6 +1407,7 @@ int32_t mtj_prefill(mtj_handle* h, const uint32_t* ctx, const uint32_t* ctx_len,
   }
   rc = setup_sequences(h, pad, limit, h->W, s);
   if (rc) return rc;
+  h->min_pad = *std::min_element(pad.begin(), pad.end());
   // held-back last token drives the first decode step (transformer_shard.py:76-77)
   MTJ_CUDA(cudaMemcpy2DAsync(h->tokens, sizeof(uint32_t), ctx + (h->seq - 1), sizeof(uint32_t) * h->seq,
                              sizeof(uint32_t), batch, cudaMemcpyDeviceToDevice, s));
@@ -1415,6 +1432,7 @@ int32_t mtj_start_batch(mtj_handle* h, int32_t batch, mtj_stream stream) {
   rc = setup_sequences(h, pad, limit, h->W, s);
   if (rc) return rc;
   MTJ_CUDA(cudaMemsetAsync(h->tokens, 0, sizeof(uint32_t) * batch, s));
+  h->min_pad = h->W;
   h->batch = batch;
   h->prefilled = true;
   h->steps_done = 0;
@@ -1436,6 +1454,7 @@ int32_t mtj_admit(mtj_handle* h, int32_t slot, const uint32_t* prompt, int32_t l
   const int n = len - 1, pos0 = cur - n;
   if (cur + 1 >= h->max_pos) return fail(MTJ_ERR_STATE, "the batch has used up its positions (max_gen)");
   const int32_t padv = pos0, lim = 0x7fffffff;
+  h->min_pad = std::min(h->min_pad, pos0);
   MTJ_CUDA(cudaMemcpyAsync(h->pad + slot, &padv, sizeof(int32_t), cudaMemcpyHostToDevice, s));
   MTJ_CUDA(cudaMemcpyAsync(h->key_limit + slot, &lim, sizeof(int32_t), cudaMemcpyHostToDevice, s));
   MTJ_CUDA(cudaMemcpyAsync(h->tokens + slot, prompt + n, sizeof(uint32_t), cudaMemcpyDeviceToDevice, s));

@@ -35,7 +35,7 @@ def test_a_rank_that_leaves_between_calls_is_noticed_on_the_host():
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("mp,chunk_pipeline,push_reduce", [(2, "0", "0"), (2, "1", "0"), (2, "0", "1"), (4, "0", "0"),
-                                                            (8, "0", "0"), (8, "0", "1")])
+                                                            (4, "1", "1"), (8, "0", "0"), (8, "1", "1")])
 def test_tensor_parallel_generate_matches_oracle(mp, chunk_pipeline, push_reduce):
     """chunk_pipeline = "1": prefill / eval run as chunk pairs whose all-reduce overlaps the other chunk's layer.
     push_reduce = "1": the batched decode step's all-reduce is the push kernel fused with the split-K reduction
