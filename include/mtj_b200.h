@@ -166,6 +166,11 @@ int32_t mtj_decode_step(mtj_handle* h, const uint32_t* tokens_in_dev,
  * the stream. */
 int32_t mtj_set_seed(mtj_handle* h, uint64_t seed, mtj_stream s);
 
+/* The sampler's top_k option (sampling.py:41 nucleaus_sample(..., top_k)) for
+ * the sampled steps of mtj_decode_step / mtj_generate that follow:
+ * top_k_dev [batch] int32 is copied; NULL returns to top_k = None. */
+int32_t mtj_set_top_k(mtj_handle* h, const int32_t* top_k_dev, int32_t batch, mtj_stream s);
+
 /* The whole scan of generate (transformer_shard.py:198-212) from one call:
  * gen_length decode steps (generate_once + sampler) enqueued back to back on
  * the stream as replays of the captured step, no host round trip in between.
@@ -191,11 +196,14 @@ int32_t mtj_forward_logits(mtj_handle* h, const uint32_t* obs_dev, const uint32_
                            float* logits_out_dev, mtj_stream s);
 
 /* nucleaus_sample (sampling.py:10-44): logits [rows, vocab] f32, uniforms
- * [rows, vocab] f32 in (0,1), top_p/temp [rows]; scratch from
- * mtj_sample_scratch_bytes(rows, vocab). */
+ * [rows, vocab] f32 in (0,1), top_p/temp [rows], top_k [rows] int32 or NULL
+ * (the reference's top_k = None); scratch from
+ * mtj_sample_scratch_bytes(rows, vocab).  An entry whose rank in the
+ * descending order is >= top_k[r] loses 1e10 * (its own index), as
+ * sampling.py:15-26 computes it. */
 int64_t mtj_sample_scratch_bytes(int32_t rows, int32_t vocab);
 int32_t mtj_sample_top_p(const float* logits_dev, const float* uniforms_dev,
-                         const float* top_p_dev, const float* temp_dev,
+                         const float* top_p_dev, const int32_t* top_k_dev, const float* temp_dev,
                          int32_t rows, int32_t vocab, void* scratch_dev, int64_t scratch_bytes,
                          uint32_t* tokens_out_dev, mtj_stream s);
 
@@ -298,11 +306,12 @@ int32_t mtj_k_gemm_tc(const void* w_dev, const void* x_dev, const float* bias_de
 int32_t mtj_k_rng_uniforms(uint64_t seed, int32_t position, int32_t rows, int32_t vocab, float* out_dev,
                            mtj_stream s);
 
-/* nucleaus_filter (sampling.py:10-38 with top_k = None) on its own:
+/* nucleaus_filter (sampling.py:10-38; top_k_dev [rows] int32 or NULL) on its own:
  * filtered_out_dev[r, i] = logits[r, i] - 1e10 * removed[r, i], where an entry
  * is removed when the softmax mass of the entries sorted before it (descending,
  * higher index first among equals) exceeds top_p[r]; the first entry stays. */
-int32_t mtj_nucleus_filter(const float* logits_dev, const float* top_p_dev, int32_t rows, int32_t vocab,
+int32_t mtj_nucleus_filter(const float* logits_dev, const float* top_p_dev, const int32_t* top_k_dev,
+                           int32_t rows, int32_t vocab,
                            float* filtered_out_dev, mtj_stream s);
 
 /* The attention of self_attn before the output projection (layers.py:275-283)

@@ -247,6 +247,7 @@ struct SampleArgs {
   const float* uniforms;       // [rows, V] in [tiny, 1), or null with rng_seed set
   const uint32_t* rng_seed;    // device, 2 words: key of the counter-based generator (indexed by *cur_dev, row, column)
   const float* top_p;          // [rows]
+  const int32_t* top_k;        // [rows] or null (the reference's top_k = None)
   const float* temp;           // [rows]
   int rows, V;
   void* scratch;               // sample_scratch_bytes(rows, V): receives the Gumbel noise of the uniforms
@@ -259,8 +260,8 @@ struct SampleArgs {
 int64_t sample_scratch_bytes(int rows, int vocab);
 // the uniforms that generator yields for (seed, decode position): [rows, V]
 cudaError_t launch_rng_uniforms(uint64_t seed, int position, int rows, int V, float* out, cudaStream_t s);
-cudaError_t launch_nucleus_filter(const float* logits, const float* top_p, int rows, int V, float* filtered,
-                                  cudaStream_t s);
+cudaError_t launch_nucleus_filter(const float* logits, const float* top_p, const int32_t* top_k, int rows, int V,
+                                  float* filtered, cudaStream_t s);
 cudaError_t launch_sample_top_p(const SampleArgs& a, cudaStream_t s, bool pdl);
 
 struct CeArgs {

@@ -161,6 +161,8 @@ struct mtj_handle {
   int32_t* row_select = nullptr;    // [max_rows]
   uint32_t* dev_err = nullptr;
   uint32_t* rng_seed = nullptr;     // [2] key of the device generator that draws the sampler's uniforms
+  int32_t* top_k = nullptr;         // [max_batch] the sampler's top_k, used while has_top_k
+  bool has_top_k = false;
   __nv_bfloat16* kpool = nullptr;   // [L][n_pages][heads][kPageTokens][dh]
   __nv_bfloat16* vpool = nullptr;
   int64_t pool_layer_elems = 0;
@@ -316,6 +318,7 @@ struct mtj_handle {
     row_select = c.take<int32_t>(R);
     dev_err = c.take<uint32_t>(4);
     rng_seed = c.take<uint32_t>(4);
+    top_k = c.take<int32_t>(max_batch);
     pool_layer_elems = static_cast<int64_t>(n_pages) * heads * mtj::kPageTokens * dh;
     kpool = c.take<__nv_bfloat16>(pool_layer_elems * L);
     vpool = c.take<__nv_bfloat16>(pool_layer_elems * L);
@@ -956,7 +959,7 @@ extern "C" {
 
 const char* mtj_last_error(void) { return g_last_error.c_str(); }
 int32_t mtj_set_error(int32_t code, const char* msg) { return fail(code, msg ? msg : ""); }
-int32_t mtj_version(void) { return 2; }
+int32_t mtj_version(void) { return 3; }
 
 int32_t mtj_create(const mtj_config* c, mtj_handle** out) {
   if (!c || !out) return fail(MTJ_ERR_INVALID, "null argument");
@@ -1580,6 +1583,7 @@ int32_t mtj_decode_step(mtj_handle* h, const uint32_t* tokens_in, const float* t
       sa.uniforms = uniforms ? h->uniforms : nullptr;
       sa.rng_seed = h->rng_seed;
       sa.top_p = h->top_p;
+      sa.top_k = h->has_top_k ? h->top_k : nullptr;
       sa.temp = h->temp;
       sa.rows = B;
       sa.V = h->V;
@@ -1592,7 +1596,8 @@ int32_t mtj_decode_step(mtj_handle* h, const uint32_t* tokens_in, const float* t
     return MTJ_OK;
   };
   if (h->use_graph && !h->profile && (h->mp == 1 || h->steps_done > 0)) {
-    const int graph_kind = (greedy ? 1 : 0) | (logits_out ? 2 : 0) | ((!greedy && !uniforms) ? 4 : 0);
+    const int graph_kind = (greedy ? 1 : 0) | (logits_out ? 2 : 0) | ((!greedy && !uniforms) ? 4 : 0) |
+                           ((!greedy && h->has_top_k) ? 8 : 0);
     if (h->graph_exec == nullptr || h->graph_batch != B || h->graph_greedy != graph_kind) {
       if (h->graph_exec) {
         cudaGraphExecDestroy(h->graph_exec);
@@ -1766,8 +1771,21 @@ int64_t mtj_sample_scratch_bytes(int32_t rows, int32_t vocab) {
   return mtj::sample_scratch_bytes(rows, vocab);
 }
 
-int32_t mtj_sample_top_p(const float* logits, const float* uniforms, const float* top_p, const float* temp,
-                         int32_t rows, int32_t vocab, void* scratch, int64_t scratch_bytes,
+int32_t mtj_set_top_k(mtj_handle* h, const int32_t* top_k, int32_t batch, mtj_stream stream) {
+  if (!h || !h->bound) return fail(MTJ_ERR_STATE, "not bound");
+  if (!top_k) {
+    h->has_top_k = false;
+    return MTJ_OK;
+  }
+  if (batch < 1 || batch > h->max_batch) return fail(MTJ_ERR_INVALID, "batch outside [1, max_batch]");
+  MTJ_CUDA(cudaMemcpyAsync(h->top_k, top_k, sizeof(int32_t) * batch, cudaMemcpyDeviceToDevice,
+                           static_cast<cudaStream_t>(stream)));
+  h->has_top_k = true;
+  return MTJ_OK;
+}
+
+int32_t mtj_sample_top_p(const float* logits, const float* uniforms, const float* top_p, const int32_t* top_k,
+                         const float* temp, int32_t rows, int32_t vocab, void* scratch, int64_t scratch_bytes,
                          uint32_t* tokens_out, mtj_stream stream) {
   if (!logits || !uniforms || !top_p || !temp || !scratch || !tokens_out)
     return fail(MTJ_ERR_INVALID, "null argument");
@@ -1777,6 +1795,7 @@ int32_t mtj_sample_top_p(const float* logits, const float* uniforms, const float
   sa.logits = logits;
   sa.uniforms = uniforms;
   sa.top_p = top_p;
+  sa.top_k = top_k;
   sa.temp = temp;
   sa.rows = rows;
   sa.V = vocab;

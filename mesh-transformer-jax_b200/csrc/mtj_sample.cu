@@ -20,6 +20,13 @@
 // such a group.  exp and log are fixed polynomials of individually rounded
 // fp32 operations (no FMA contraction), so a CPU restatement reproduces the
 // token ids bit for bit.
+//
+// top_k (sampling.py:15-26) is a second selection, by COUNT instead of weight:
+// the key of the entry with sorted rank top_k - 1 and, among entries with that
+// key, the index below which they fall outside the first top_k.  Such an entry
+// i loses 1e10 * i (the reference scatters the token INDEX, not a flag, into
+// its mask, so token 0 is never masked by this branch); the cumulative
+// probabilities of the top-p rule still come from the unmasked logits.
 #include <math.h>
 
 #include <algorithm>
@@ -219,6 +226,7 @@ __global__ void __launch_bounds__(kSampThreads, 1) sample_top_p_kernel(const Sam
   __shared__ uint32_t sel_digit, sel_none;
   __shared__ unsigned long long sel_before, sel_sum, sel_T;
   __shared__ uint32_t x_max, x_ties, x_best_v, x_best_i;      // read by the other blocks of the cluster
+  __shared__ uint32_t x_kties, x_kidx;
 
   const uint32_t C = cluster_size(), crank = cluster_rank();
   const int row = blockIdx.x / C, t = threadIdx.x, V = a.V;
@@ -406,6 +414,115 @@ __global__ void __launch_bounds__(kSampThreads, 1) sample_top_p_kernel(const Sam
     __syncthreads();
   }
 
+  // ---- top_k: key kk of the entry of sorted rank top_k - 1; equal keys below index kidx are beyond it ----
+  uint32_t kk = 0xFFFFFFFFu;
+  int kidx = 0;                                            // defaults: no entry is beyond the first top_k
+  if (a.top_k) {                                           // uniform over the grid
+    const int k = a.top_k[row];
+    if (k <= 0) {
+      kk = 0u;
+      kidx = V;                                            // every entry is beyond the first top_k
+    } else if (k < V) {                                    // uniform over the cluster
+      uint32_t* cnt = reinterpret_cast<uint32_t*>(hist);
+      const unsigned long long R = static_cast<unsigned long long>(k - 1);
+      uint32_t kprefix = 0;
+      unsigned long long kbefore = 0, kgroup = 0;
+      cluster_sync();                                      // the bin sums of the last top-p level have been read
+      for (int level = 0; level < 4; ++level) {
+        const int shift = 24 - 8 * level;
+        unsigned long long* lbins = bins + (level & 1) * kBins;
+        if (t < kBins) cnt[t] = 0u;
+        __syncthreads();
+        for (int i = i_begin + t; i < i_end; i += kSampThreads) {
+          const uint32_t key = sort_key(logits[i]);
+          if (level == 0 || (key >> (shift + 8)) == kprefix) atomicAdd(cnt + ((key >> shift) & 255u), 1u);
+        }
+        __syncthreads();
+        if (t < kBins) lbins[t] = cnt[t];
+        cluster_sync();
+        if (t < kBins) {
+          unsigned long long sum = 0ull;
+          for (uint32_t c = 0; c < C; ++c) sum += ld_peer_u64(lbins + t, c);
+          gbins[t] = sum;
+        }
+        __syncthreads();
+        if (warp == 0) {
+          unsigned long long b[8], local = 0ull;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            b[j] = gbins[lane * 8 + j];
+            local += b[j];
+          }
+          unsigned long long inc = local;
+#pragma unroll
+          for (int off = 1; off < 32; off <<= 1) {
+            const unsigned long long y = __shfl_up_sync(0xffffffffu, inc, off);
+            if (lane >= off) inc += y;
+          }
+          unsigned long long run = kbefore + inc - local;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            if (R >= run && R - run < b[j]) {
+              sel_digit = static_cast<uint32_t>(lane * 8 + j);
+              sel_before = run;
+              sel_sum = b[j];
+            }
+            run += b[j];
+          }
+        }
+        __syncthreads();
+        kprefix = (kprefix << 8) | sel_digit;
+        kbefore = sel_before;
+        kgroup = sel_sum;
+        __syncthreads();
+      }
+      kk = kprefix;
+      const unsigned long long n_keep = R - kbefore + 1;   // entries with key kk inside the first top_k: 1..kgroup
+      if (n_keep < kgroup) {                               // uniform over the cluster
+        // the n_keep-th highest index among the entries with key kk; same ownership as the tie pass above
+        const int n_own = i_end - i_begin;
+        const int per = (n_own + kSampThreads - 1) / kSampThreads;
+        const int hi_i = i_end - 1 - t * per, lo_i = max(i_begin - 1, hi_i - per);
+        uint32_t mine = 0;
+        for (int i = hi_i; i > lo_i; --i) mine += sort_key(logits[i]) == kk ? 1u : 0u;
+        uint32_t inc = mine;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+          const uint32_t y = __shfl_up_sync(0xffffffffu, inc, off);
+          if (lane >= off) inc += y;
+        }
+        if (t == 0) x_kidx = 0xFFFFFFFFu;
+        __syncthreads();                                   // also: the tie pass above is done with wsum
+        if (lane == 31) wsum[warp] = inc;
+        __syncthreads();
+        if (warp == 0) {
+          const uint32_t w = wsum[lane];
+          uint32_t winc = w;
+#pragma unroll
+          for (int off = 1; off < 32; off <<= 1) {
+            const uint32_t y = __shfl_up_sync(0xffffffffu, winc, off);
+            if (lane >= off) winc += y;
+          }
+          wsum[lane] = winc - w;
+          if (lane == 31) x_kties = winc;
+        }
+        cluster_sync();
+        unsigned long long rank = wsum[warp] + inc - mine;
+        for (uint32_t c = crank + 1; c < C; ++c) rank += ld_peer_u32(&x_kties, c);
+        for (int i = hi_i; i > lo_i; --i) {
+          if (sort_key(logits[i]) == kk) {
+            if (rank + 1 == n_keep) x_kidx = static_cast<uint32_t>(i);       // exactly one entry of the row
+            ++rank;
+          }
+        }
+        cluster_sync();
+        uint32_t found = 0xFFFFFFFFu;
+        for (uint32_t c = 0; c < C; ++c) found = min(found, ld_peer_u32(&x_kidx, c));
+        kidx = static_cast<int>(found);
+      }
+    }
+  }
+
   // ---- Gumbel-max over the filtered, tempered logits ----
   float best = -INFINITY;
   int best_i = 0x7fffffff;
@@ -414,7 +531,9 @@ __global__ void __launch_bounds__(kSampThreads, 1) sample_top_p_kernel(const Sam
     const uint32_t key = sort_key(lg);
     const int j = i - i_begin;
     const bool removed = cut && (key > k0 || (tie_cut && key == k0 && ((bitmap[j >> 5] >> (j & 31)) & 1u)));
-    const float lm = __fsub_rn(lg, removed ? 1e10f : 0.0f);
+    const bool beyond_k = key > kk || (key == kk && i < kidx);
+    const float lk = beyond_k ? __fsub_rn(lg, __fmul_rn(1e10f, static_cast<float>(i))) : lg;
+    const float lm = __fsub_rn(lk, removed ? 1e10f : 0.0f);
     if (a.filtered) a.filtered[static_cast<size_t>(row) * V + i] = lm;       // nucleaus_filter's return value
     const float score = __fadd_rn(__fdiv_rn(lm, temp), gum ? gum[i] : 0.0f);
     if (score > best) {                                    // ascending i: the first maximum stays
@@ -518,14 +637,15 @@ cudaError_t launch_rng_uniforms(uint64_t seed, int position, int rows, int V, fl
 }
 
 // nucleaus_filter alone (sampling.py:10-38): filtered[r, i] = logits[r, i] - 1e10 * removed[r, i]
-cudaError_t launch_nucleus_filter(const float* logits, const float* top_p, int rows, int V, float* filtered,
-                                  cudaStream_t s) {
+cudaError_t launch_nucleus_filter(const float* logits, const float* top_p, const int32_t* top_k, int rows, int V,
+                                  float* filtered, cudaStream_t s) {
   if (rows <= 0 || V <= 0 || sample_smem_bytes(V, sample_cluster(rows)) > 220 * 1024) return cudaErrorInvalidValue;
   cudaError_t e = configure_sampler();
   if (e != cudaSuccess) return e;
   SampleArgs b = {};
   b.logits = logits;
   b.top_p = top_p;
+  b.top_k = top_k;
   b.rows = rows;
   b.V = V;
   b.filtered = filtered;

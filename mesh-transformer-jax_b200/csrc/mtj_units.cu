@@ -159,11 +159,11 @@ int32_t mtj_k_rng_uniforms(uint64_t seed, int32_t position, int32_t rows, int32_
   return MTJ_OK;
 }
 
-int32_t mtj_nucleus_filter(const float* logits, const float* top_p, int32_t rows, int32_t vocab,
+int32_t mtj_nucleus_filter(const float* logits, const float* top_p, const int32_t* top_k, int32_t rows, int32_t vocab,
                            float* filtered_out, mtj_stream s) {
   if (!logits || !top_p || !filtered_out) return mtj_set_error(MTJ_ERR_INVALID, "null argument");
   if (rows <= 0 || vocab <= 0) return mtj_set_error(MTJ_ERR_INVALID, "rows and vocab must be positive");
-  cudaError_t e = mtj::launch_nucleus_filter(logits, top_p, rows, vocab, filtered_out, static_cast<cudaStream_t>(s));
+  cudaError_t e = mtj::launch_nucleus_filter(logits, top_p, top_k, rows, vocab, filtered_out, static_cast<cudaStream_t>(s));
   if (e != cudaSuccess) return mtj_set_error(MTJ_ERR_CUDA, cudaGetErrorString(e));
   return MTJ_OK;
 }

@@ -54,7 +54,7 @@ def _load():
         "mtj_eval_loss": (i32, [vp, vp, vp, ctypes.POINTER(ctypes.c_uint32), i32, i32, vp, vp, vp]),
         "mtj_forward_logits": (i32, [vp, vp, ctypes.POINTER(ctypes.c_uint32), i32, i32, i32, vp, vp]),
         "mtj_sample_scratch_bytes": (i64, [i32, i32]),
-        "mtj_sample_top_p": (i32, [vp, vp, vp, vp, i32, i32, vp, i64, vp, vp]),
+        "mtj_sample_top_p": (i32, [vp, vp, vp, vp, vp, i32, i32, vp, i64, vp, vp]),
         "mtj_launch_count": (i64, [vp]),
         "mtj_check_device_status": (i32, [vp, vp]),
         "mtj_mega_trace": (i32, [vp, i32, ctypes.POINTER(ctypes.c_uint64), i32, vp]),
@@ -69,9 +69,10 @@ def _load():
         "mtj_k_gemm_tc": (i32, [vp, vp, vp, i32, i32, i32, vp, vp]),
         "mtj_k_decode_attn_noalloc": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, i32, vp]),
         "mtj_set_seed": (i32, [vp, ctypes.c_uint64, vp]),
+        "mtj_set_top_k": (i32, [vp, vp, i32, vp]),
         "mtj_generate": (i32, [vp, i32, i32, vp, vp, vp, vp, vp, vp]),
         "mtj_k_rng_uniforms": (i32, [ctypes.c_uint64, i32, i32, i32, vp, vp]),
-        "mtj_nucleus_filter": (i32, [vp, vp, i32, i32, vp, vp]),
+        "mtj_nucleus_filter": (i32, [vp, vp, vp, i32, i32, vp, vp]),
         "mtj_k_prefill_attn": (i32, [vp, vp, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, i32, vp, vp]),
         "mtj_k_all_reduce_buffer_bytes": (i64, [vp, i32]),
         "mtj_k_all_reduce": (i32, [vp, ctypes.POINTER(vp), i32, i32, i32, i32, vp, vp, vp, i32, vp]),

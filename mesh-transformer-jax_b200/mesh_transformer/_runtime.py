@@ -210,6 +210,13 @@ class ShardRuntime:
         """Key of the device generator that draws the sampler's uniforms when none are supplied."""
         check(lib.mtj_set_seed(self._h, int(seed) & ((1 << 64) - 1), self.stream))
 
+    def set_top_k(self, top_k=None) -> None:
+        """The sampler's top_k for the sampled steps that follow: an int32 device tensor [batch], or None."""
+        if top_k is None:
+            check(lib.mtj_set_top_k(self._h, None, 0, self.stream))
+        else:
+            check(lib.mtj_set_top_k(self._h, top_k.data_ptr(), int(top_k.numel()), self.stream))
+
     def generate_steps(self, gen_length: int, tokens_out=None, logits_out=None, greedy=True, top_p=None, temp=None,
                        uniforms=None) -> None:
         """The whole scan from one call: ``gen_length`` decode steps enqueued back to back.

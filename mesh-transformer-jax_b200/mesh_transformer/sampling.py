@@ -39,10 +39,18 @@ def _per_row(value, rows, device):
     return t.to(device).contiguous()
 
 
+def _per_row_int(value, rows, device):
+    """None stays None (the reference's top_k = None); a scalar or [rows] becomes an int32 device tensor."""
+    if value is None:
+        return None
+    t = torch.as_tensor(np.asarray(value, dtype=np.int64).clip(-2**31, 2**31 - 1).astype(np.int32)).reshape(-1)
+    if t.numel() == 1:
+        t = t.expand(rows)
+    return t.to(device).contiguous()
+
+
 def nucleaus_sample(key, logits, _=None, top_p=0.9, temp=1, top_k=None):
     """logits [rows, vocab] (CUDA tensor or array) -> (uint32 token ids [rows], None)."""
-    if top_k is not None:
-        raise NotImplementedError("the reference's top_k branch is outside this path")
     if not isinstance(logits, torch.Tensor):
         logits = torch.as_tensor(np.asarray(logits, dtype=np.float32))
     if not logits.is_cuda:
@@ -52,11 +60,12 @@ def nucleaus_sample(key, logits, _=None, top_p=0.9, temp=1, top_k=None):
     dev = logits.device
     with torch.cuda.device(dev):
         u = draw_uniforms(key, (rows, vocab), dev)
-        tp, tt = _per_row(top_p, rows, dev), _per_row(temp, rows, dev)
+        tp, tt, tk = _per_row(top_p, rows, dev), _per_row(temp, rows, dev), _per_row_int(top_k, rows, dev)
         nbytes = lib.mtj_sample_scratch_bytes(rows, vocab)
         scratch = torch.empty((nbytes,), dtype=torch.uint8, device=dev)
         out = torch.empty((rows,), dtype=torch.int32, device=dev)
-        check(lib.mtj_sample_top_p(logits.data_ptr(), u.data_ptr(), tp.data_ptr(), tt.data_ptr(), rows, vocab,
+        check(lib.mtj_sample_top_p(logits.data_ptr(), u.data_ptr(), tp.data_ptr(),
+                                   tk.data_ptr() if tk is not None else None, tt.data_ptr(), rows, vocab,
                                    scratch.data_ptr(), nbytes, out.data_ptr(),
                                    torch.cuda.current_stream(dev).cuda_stream))
         return out.cpu().numpy().view(np.uint32), None
@@ -68,9 +77,8 @@ def softmax_sample(key, logits, _=None, temp=1):
 
 
 def nucleaus_filter(logits, top_p=0.9, top_k=None):
-    """sampling.py:10-38 (top_k = None): ``logits - 1e10 * removed`` as a CUDA tensor [rows, vocab]."""
-    if top_k is not None:
-        raise NotImplementedError("the reference's top_k branch is outside this path")
+    """sampling.py:10-38: ``logits - 1e10 * removed`` as a CUDA tensor [rows, vocab]; with ``top_k`` also
+    ``- 1e10 * index`` for the entries of sorted rank >= top_k (:15-26)."""
     if not isinstance(logits, torch.Tensor):
         logits = torch.as_tensor(np.asarray(logits, dtype=np.float32))
     if not logits.is_cuda:
@@ -80,7 +88,8 @@ def nucleaus_filter(logits, top_p=0.9, top_k=None):
     dev = logits.device
     with torch.cuda.device(dev):
         out = torch.empty_like(logits)
-        tp = _per_row(top_p, rows, dev)
-        check(lib.mtj_nucleus_filter(logits.data_ptr(), tp.data_ptr(), rows, vocab, out.data_ptr(),
+        tp, tk = _per_row(top_p, rows, dev), _per_row_int(top_k, rows, dev)
+        check(lib.mtj_nucleus_filter(logits.data_ptr(), tp.data_ptr(), tk.data_ptr() if tk is not None else None,
+                                     rows, vocab, out.data_ptr(),
                                      torch.cuda.current_stream(dev).cuda_stream))
         return out

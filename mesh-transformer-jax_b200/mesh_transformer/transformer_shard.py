@@ -265,11 +265,15 @@ class CausalTransformer:
         # the arg-max shortcut below is taken only for an explicit top_p == 0 on every row
         top_p = np.asarray(sampler_options.get("top_p", np.full(batch, 0.9)), dtype=np.float32).reshape(batch)
         temp = np.asarray(sampler_options.get("temp", np.ones(batch)), dtype=np.float32).reshape(batch)
-        if "top_k" in sampler_options and sampler_options["top_k"] is not None:
-            raise NotImplementedError("the reference's top_k branch is outside this path")
+        top_k = sampler_options.get("top_k")
+        if top_k is not None:
+            if name == "softmax_sample":
+                raise TypeError("softmax_sample() got an unexpected keyword argument 'top_k'")   # sampling.py:6
+            top_k = np.broadcast_to(np.asarray(top_k, dtype=np.int64).clip(-2**31, 2**31 - 1).astype(np.int32).reshape(-1),
+                                    (batch,)).copy()
         if name == "softmax_sample":
             top_p = np.full(batch, np.inf, np.float32)
-        greedy = bool(np.all(top_p == 0.0))
+        greedy = bool(np.all(top_p == 0.0)) and top_k is None
         with torch.cuda.device(self.device):
             t_start = time.perf_counter()
             ctx_dev = torch.from_numpy(ctx.view(np.int32)).pin_memory().to(self.device, non_blocking=True)
@@ -289,6 +293,7 @@ class CausalTransformer:
                     samp["uniforms"] = uniforms
                 else:
                     rt.set_seed(key)           # the scan's PRNG key: the uniforms are drawn on the device
+            rt.set_top_k(None if top_k is None or greedy else torch.from_numpy(top_k).to(self.device))
             shard = CausalTransformerShard(self.config, runtime=rt)
             shard.generate_initial(ctx_dev, lengths)
             torch.cuda.current_stream(self.device).synchronize()

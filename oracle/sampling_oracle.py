@@ -51,8 +51,19 @@ def _sorted_desc(logits):
     return logits[order], order
 
 
-def nucleaus_filter_plain(logits, top_p=0.9):
-    """sampling.py:10-38 with top_k=None; logits [rows, V] float32."""
+def top_k_mask(order, top_k):
+    """sampling.py:15-26: every token whose rank in the descending order is >= top_k gets the mask
+    1e10 * (its own index) -- ``where(range >= top_k, sorted_indices, 0)`` scattered back to token order --
+    so token 0 is never masked by this branch.  Returns the fp32 mask [V]."""
+    v = order.shape[0]
+    idx = np.zeros(v, np.int64)
+    idx[order] = np.where(np.arange(v) >= int(top_k), order, 0)
+    return (F32(1e10) * idx.astype(F32)).astype(F32)
+
+
+def nucleaus_filter_plain(logits, top_p=0.9, top_k=None):
+    """sampling.py:10-38; logits [rows, V] float32.  The cumulative probabilities come from the unmasked logits
+    also when top_k is given (:13 precedes :15)."""
     logits = np.asarray(logits, F32)
     out = logits.copy()
     for r in range(logits.shape[0]):
@@ -63,7 +74,10 @@ def nucleaus_filter_plain(logits, top_p=0.9):
         remove_sorted = np.concatenate(([False], remove_sorted))[:-1]
         remove = np.zeros(logits.shape[1], bool)
         remove[order] = remove_sorted                      # sort_key_val(sorted_indices, ...) scatters back
-        out[r] = logits[r] - F32(1e10) * remove
+        row = logits[r]
+        if top_k is not None:
+            row = (row - top_k_mask(order, np.asarray(top_k).reshape(-1)[r % np.asarray(top_k).size])).astype(F32)
+        out[r] = row - F32(1e10) * remove
     return out
 
 
@@ -71,9 +85,9 @@ def gumbel_plain(u):
     return -np.log(-np.log(np.asarray(u, F32)))
 
 
-def nucleaus_sample_plain(uniforms, logits, top_p=0.9, temp=1.0):
+def nucleaus_sample_plain(uniforms, logits, top_p=0.9, temp=1.0, top_k=None):
     """sampling.py:41-44 + :6-7; categorical = argmax(logits/temp + Gumbel)."""
-    filt = nucleaus_filter_plain(logits, top_p)
+    filt = nucleaus_filter_plain(logits, top_p, top_k)
     score = (filt / F32(temp)).astype(F32) + gumbel_plain(uniforms)
     return np.argmax(score, axis=-1).astype(np.uint32)
 
@@ -190,8 +204,9 @@ def weight_threshold(top_p, total):
     return fr.numerator // fr.denominator
 
 
-def nucleaus_filter(logits, top_p=0.9):
-    """sampling.py:10-38 (top_k=None) with pinned arithmetic; returns (filtered, removed)."""
+def nucleaus_filter(logits, top_p=0.9, top_k=None):
+    """sampling.py:10-38 with pinned arithmetic; returns (filtered, removed by the top-p rule).  ``top_k`` (None,
+    a scalar or one value per row) adds the reference's top-k mask, which needs no arithmetic to be pinned."""
     logits = np.asarray(logits, F32)
     out = logits.copy()
     removed = np.zeros(logits.shape, bool)
@@ -205,7 +220,10 @@ def nucleaus_filter(logits, top_p=0.9):
         else:
             remove_sorted = before > np.uint64(thr)          # the head (before == 0) always stays
         removed[r, order] = remove_sorted
-        out[r] = (logits[r] - F32(1e10) * removed[r].astype(F32)).astype(F32)
+        row = logits[r]
+        if top_k is not None:
+            row = (row - top_k_mask(order, np.asarray(top_k).reshape(-1)[r % np.asarray(top_k).size])).astype(F32)
+        out[r] = (row - F32(1e10) * removed[r].astype(F32)).astype(F32)
     return out, removed
 
 
@@ -215,7 +233,7 @@ def gumbel(u):
     return (-log_f32(t)).astype(F32)
 
 
-def nucleaus_sample(uniforms, logits, top_p=0.9, temp=1.0):
+def nucleaus_sample(uniforms, logits, top_p=0.9, temp=1.0, top_k=None):
     """Token ids [rows] uint32: argmax(filtered / temp + Gumbel(uniforms)), first index on ties."""
     logits = np.asarray(logits, F32)
     uniforms = np.asarray(uniforms, F32)
@@ -223,7 +241,8 @@ def nucleaus_sample(uniforms, logits, top_p=0.9, temp=1.0):
     temp = np.broadcast_to(np.asarray(temp, F32), (logits.shape[0],))
     toks = np.zeros(logits.shape[0], np.uint32)
     for r in range(logits.shape[0]):
-        filt, _ = nucleaus_filter(logits[r:r + 1], top_p[r])
+        k_r = None if top_k is None else np.asarray(top_k).reshape(-1)[r % np.asarray(top_k).size]
+        filt, _ = nucleaus_filter(logits[r:r + 1], top_p[r], k_r)
         score = ((filt[0] / temp[r]).astype(F32) + gumbel(uniforms[r])).astype(F32)
         toks[r] = np.argmax(score)
     return toks

@@ -192,3 +192,60 @@ def test_generate_scan_with_the_device_generator(cuda_device):
     other = net.generate(ctx, [20] * 3, 10, opts)[1][0]           # the next key of Python's generator
     assert not np.array_equal(other, out[0])
     net.close()
+
+
+@pytest.mark.parametrize("vocab,scale", [(50400, 3.0), (512, 1.0), (12, 1.0)])
+def test_top_k_branch_matches_the_oracle(cuda_device, vocab, scale):
+    """sampling.py:15-26: entries of sorted rank >= top_k lose 1e10 * (their own index); the top-p rule still works
+    on the unmasked logits.  Filter output and sampled ids equal the oracle's, for top_k inside a group of equal
+    logits, top_k = 1, top_k >= vocab (no entry is masked), top_k <= 0 (every entry but token 0 is)."""
+    import torch
+    torch.cuda.set_device(cuda_device)
+    from mesh_transformer.sampling import nucleaus_filter, nucleaus_sample
+    rng = np.random.default_rng(vocab + 5)
+    rows = 7
+    lg = (rng.standard_normal((rows, vocab)) * scale).astype(np.float32)
+    lg[1] = np.round(lg[1])                                              # rank top_k falls among equal logits
+    lg[2] = np.round(lg[2] * 0.5)
+    top_k = np.array([min(40, vocab - 1), 5, max(1, vocab // 3), 1, vocab, vocab + 9, 0], np.int32)
+    top_p = np.array([0.9, 0.8, 1.0, 0.9, 0.5, 0.95, 0.9], np.float32)
+    temp = np.array([1.0, 0.7, 1.3, 1.0, 2.0, 0.9, 1.0], np.float32)
+    got = nucleaus_filter(torch.from_numpy(lg).to(cuda_device), top_p, top_k).cpu().numpy()
+    for r in range(rows):
+        want, _ = so.nucleaus_filter(lg[r:r + 1], top_p[r], top_k[r])
+        assert np.array_equal(got[r], want[0]), f"row {r}"
+        if r not in (1, 2):                          # (inside a group of equal logits the cut may move by the group)
+            plain = so.nucleaus_filter_plain(lg[r:r + 1], top_p[r], top_k[r:r + 1])
+            assert (plain[0] != want[0]).sum() <= 16                     # the pinned cut moves a few entries at most
+    u = rng.uniform(so.TINY, 1.0, size=(rows, vocab)).astype(np.float32)
+    toks, _ = nucleaus_sample(torch.from_numpy(u).to(cuda_device), torch.from_numpy(lg).to(cuda_device), None,
+                              top_p=top_p, temp=temp, top_k=top_k)
+    assert np.array_equal(toks, so.nucleaus_sample(u, lg, top_p, temp, top_k))
+    one = nucleaus_filter(torch.from_numpy(lg[:2]).to(cuda_device), 0.9, 3).cpu().numpy()        # scalar options
+    assert np.array_equal(one, so.nucleaus_filter(lg[:2], 0.9, 3)[0])
+
+
+def test_generate_with_top_k(cuda_device):
+    """generate() hands sampler_options["top_k"] to the device sampler: every id equals the oracle sampler's on the
+    step's own logits and the supplied uniforms."""
+    import torch
+    torch.cuda.set_device(cuda_device)
+    from mesh_transformer.sampling import nucleaus_sample
+    from mesh_transformer.transformer_shard import CausalTransformer
+    cfg = spec.tiny_config(1, seq=64)
+    params = spec.make_params(cfg, seed=52, stress=True)
+    net = CausalTransformer(dict(cfg, sampler=nucleaus_sample), init_weights=False)
+    net.state = {"params": params, "step": np.array(0)}
+    ctx = spec.left_pad(spec.token_ids(4, 2, 20, 512), 64)
+    rng = np.random.default_rng(9)
+    u = rng.uniform(so.TINY, 1.0, size=(6, 2, 512)).astype(np.float32)
+    opts = {"top_p": np.array([0.95, 1.0]), "temp": np.array([1.0, 1.2]), "top_k": np.array([4, 50])}
+    _, out = net.generate(ctx, [20] * 2, 6, opts, return_logits=True, uniforms=u)
+    for t in range(6):
+        want = so.nucleaus_sample(u[t], out[2][:, t, 0], opts["top_p"].astype(np.float32),
+                                  opts["temp"].astype(np.float32), opts["top_k"])
+        assert np.array_equal(out[0][:, t, 0], want), f"step {t}"
+    _, no_k = net.generate(ctx, [20] * 2, 6, {"top_p": opts["top_p"], "temp": opts["temp"]}, return_logits=True,
+                           uniforms=u)
+    assert not np.array_equal(no_k[0], out[0])                           # top_k = 4 changes what is sampled
+    net.close()

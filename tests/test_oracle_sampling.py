@@ -92,3 +92,25 @@ def test_pinned_cut_against_plain_fp32_and_exact_cuts_over_ten_thousand_rows():
     assert rows >= 10000
     assert mism_exact <= rows // 1000
     assert worst_entries <= 32 and worst_mass <= 5e-4
+
+
+def test_top_k_mask_follows_the_reference_arithmetic():
+    """sampling.py:15-26 by hand on the reference's own demo row (:49): with top_k = 3 the entries 0.8, 0.7, 0.6
+    (indices 3, 10, 9) stay; every other entry i loses 1e10 * i -- so index 0 loses nothing to this branch --
+    and the top-p rule (computed from the unmasked row) then removes indices 0, 1 and 11 as without top_k."""
+    row = np.array([[-2, -1, 0, 0.8, 0, 0.1, 0.3, 0.4, 0.5, 0.6, 0.7, -3]], np.float32)
+    want = row.copy()
+    for i in (1, 2, 4, 5, 6, 7, 8, 11):
+        want[0, i] = np.float32(want[0, i] - np.float32(1e10) * np.float32(i))
+    for i in (0, 1, 11):
+        want[0, i] = np.float32(want[0, i] - np.float32(1e10))
+    for f in (lambda r: so.nucleaus_filter(r, 0.9, 3)[0], lambda r: so.nucleaus_filter_plain(r, 0.9, 3)):
+        assert np.array_equal(f(row), want)
+    # equal logits: the higher index sorts first (argsort()[::-1]), so with top_k = 2 of three equal heads the
+    # lowest index of the three is the one beyond the first two
+    tie = np.array([[0.0, 1.0, 1.0, 1.0]], np.float32)
+    got = so.nucleaus_filter(tie, 1.0, 2)[0]
+    assert np.array_equal(got, np.array([[0.0, np.float32(1.0 - 1e10), 1.0, 1.0]], np.float32))   # index 0 loses 0
+    assert np.array_equal(so.nucleaus_filter(tie, 1.0, 4)[0], tie)        # top_k >= vocab masks nothing
+    u = np.full((1, 4), 0.5, np.float32)
+    assert so.nucleaus_sample(u, tie, 1.0, 1.0, 1)[0] == 3                # only the highest index of the tie is left
