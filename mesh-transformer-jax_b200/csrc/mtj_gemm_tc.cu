@@ -76,6 +76,44 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// ---- two-SM forms (cta_group::2): the two blocks of a cluster of 2 work on ONE tile of 256 weight rows.  Each
+// block holds its own 128 weight rows (A) and half of the token rows (B); the tensor cores of both SMs read both
+// halves, so a block stages 32 KB per k-step instead of 48 KB.  The MMA is issued by the cluster's block 0.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int c0, int c1,
+                                                 uint32_t bar_cluster) {
+  // bar_cluster: shared::cluster address of block 0's barrier (the peer's copy completes bytes there too)
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {      // arrives on `bar` in both blocks of the pair
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"(static_cast<uint16_t>(3))
+               : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                 uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ uint32_t tc_cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t tc_map_to_rank(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster) : "memory");
+}
+
 // thread-block cluster helpers (split-K over a cluster: the blocks of one tile add their accumulators through
 // the leader's shared memory)
 __device__ __forceinline__ void tc_cluster_sync() {
@@ -412,10 +450,26 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
 // core works on tile i + 1.  Warp 0 = TMA producer, warp 1 = MMA issuer, warps 2-9 = epilogue
 // (lane quadrant = warp % 4, column half = (warp - 2) / 4).  Token tiles vary fastest in the tile
 // list, so the blocks that run together share weight tiles through L2.
+//
+// PAIR: the blocks come as clusters of 2 and a tile is 256 weight rows x 256 token rows, computed by
+// tcgen05.mma.cta_group::2 (UMMA 256 x 256 x 16).  Block r of the pair holds weight rows [128 r, 128 r + 128) and
+// token rows [128 r, 128 r + 128) of the tile in its shared memory and the accumulator of its own 128 weight
+// rows in its tensor memory, so the epilogue is the same as without PAIR.  Both producers complete their bytes
+// on block 0's "full" barrier; block 0 issues the MMAs and its commits arrive on the "empty" and "accumulator
+// full" barriers of both blocks; the epilogue warps of both blocks arrive on block 0's "accumulator empty".
 constexpr int kPBN = 256;
 constexpr int kPStages = 4;
 constexpr int kPEpiWarps = 8;
 constexpr int kPThreads = 64 + 32 * kPEpiWarps;
+constexpr int kPMaxStages = 6;
+template <int EPI, bool PAIR>
+struct PersistCfg {
+  static constexpr int kStages = PAIR ? (EPI == kEpiLogitsCE ? 5 : 6) : kPStages;
+  static constexpr uint32_t kABytes = kBM * kBK * 2;
+  static constexpr uint32_t kBBytes = (PAIR ? kPBN / 2 : kPBN) * kBK * 2;     // per block
+  static constexpr uint32_t kStageBytes = kABytes + kBBytes;
+  static constexpr int kSmem = kStages * kStageBytes + 1024 + (EPI == kEpiLogitsCE ? kPEpiWarps * 4096 : 0);
+};
 
 __device__ __forceinline__ void mbar_arrive_cta(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
@@ -426,42 +480,55 @@ __device__ __forceinline__ float gelu_tanh_fast(float x) {
   return __fdividef(x, 1.0f + __expf(-u2));
 }
 
-template <int EPI>
+template <int EPI, bool PAIR>
 __global__ void __launch_bounds__(kPThreads, 1) gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                        const __grid_constant__ CUtensorMap map_x,
                                                                        const GemmTcArgs a) {
-  constexpr uint32_t kABytes = kBM * kBK * 2, kBBytes = kPBN * kBK * 2, kStageBytes = kABytes + kBBytes;
+  using Cfg = PersistCfg<EPI, PAIR>;
+  constexpr int kStages = Cfg::kStages;
+  constexpr uint32_t kABytes = Cfg::kABytes, kStageBytes = Cfg::kStageBytes;
+  constexpr int kTileN = PAIR ? 2 * kBM : kBM;       // weight rows per tile (of the pair)
   constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kPBN >> 3) << 17) |
-                              (static_cast<uint32_t>(kBM >> 4) << 24);
+                              (static_cast<uint32_t>(kTileN >> 4) << 24);
   extern __shared__ unsigned char tc_smem_raw[];
   const uint32_t smem_base = (smem_u32(tc_smem_raw) + 1023u) & ~1023u;
-  __shared__ __align__(8) uint64_t bars[2 * kPStages + 4];
+  __shared__ __align__(8) uint64_t bars[2 * kPMaxStages + 4];
   __shared__ uint32_t tmem_slot;
   __shared__ uint32_t failed;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t crank = PAIR ? tc_cluster_rank() : 0u;              // block of the pair
   const uint32_t bar0 = smem_u32(bars);
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
-  auto empty_bar = [&](int s) { return bar0 + 8u * (kPStages + s); };
-  auto acc_full = [&](int b) { return bar0 + 8u * (2 * kPStages + b); };
-  auto acc_empty = [&](int b) { return bar0 + 8u * (2 * kPStages + 2 + b); };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (kStages + s); };
+  auto acc_full = [&](int b) { return bar0 + 8u * (2 * kStages + b); };
+  auto acc_empty = [&](int b) { return bar0 + 8u * (2 * kStages + 2 + b); };
   volatile uint32_t* failed_v = &failed;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < 2 * kPStages + 2; ++s) mbar_init(bar0 + 8u * s, 1);
-    mbar_init(acc_empty(0), kPEpiWarps);
-    mbar_init(acc_empty(1), kPEpiWarps);
+    for (int s = 0; s < 2 * kStages + 2; ++s) mbar_init(bar0 + 8u * s, 1);
+    mbar_init(acc_empty(0), PAIR ? 2 * kPEpiWarps : kPEpiWarps);      // PAIR: the epilogue warps of both blocks
+    mbar_init(acc_empty(1), PAIR ? 2 * kPEpiWarps : kPEpiWarps);
     mbar_fence_init();
     failed = 0;
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
-                 "r"(512u)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (PAIR) {
+      // the same warp of both blocks takes part; the columns are allocated in both
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
+                   "r"(512u)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
+                   "r"(512u)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   tc_fence_before();
-  __syncthreads();
+  if (PAIR) tc_cluster_sync();                       // both blocks' barriers exist before either is signalled
+  else __syncthreads();
   tc_fence_after();
   const uint32_t tmem_acc = tmem_slot;
 
@@ -469,36 +536,47 @@ __global__ void __launch_bounds__(kPThreads, 1) gemm_tc_persist_kernel(const __g
   pdl_launch_dependents();
 
   const int m_tiles = (a.M + kPBN - 1) / kPBN;
-  const int n_tiles = (a.N + kBM - 1) / kBM;
+  const int n_tiles = (a.N + kTileN - 1) / kTileN;
   const int total = m_tiles * n_tiles;
   const int nk = a.K / kBK;
+  const int tile_first = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  const int tile_step = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
 
   if (warp == 0) {
     if (lane == 0) {
       uint32_t it = 0;
       bool alive = true;
-      for (int t = blockIdx.x; t < total && alive; t += gridDim.x) {
-        const int n0 = (t / m_tiles) * kBM, m0 = (t % m_tiles) * kPBN;
+      for (int t = tile_first; t < total && alive; t += tile_step) {
+        const int n0 = (t / m_tiles) * kTileN + static_cast<int>(crank) * kBM, m0 = (t % m_tiles) * kPBN;
         for (int kb = 0; kb < nk; ++kb, ++it) {
-          const int s = it % kPStages;
-          if (it >= kPStages && !mbar_wait(empty_bar(s), ((it / kPStages) - 1) & 1)) {
+          const int s = it % kStages;
+          if (it >= kStages && !mbar_wait(empty_bar(s), ((it / kStages) - 1) & 1)) {
             atomicOr(&failed, 1u);
             alive = false;
             break;
           }
-          mbar_expect_tx(full_bar(s), kStageBytes);
           const uint32_t dst = smem_base + s * kStageBytes;
-          tma_load_2d(dst, &map_w, kb * kBK, n0, full_bar(s));
-          tma_load_2d(dst + kABytes, &map_x, kb * kBK, a.x_row0 + m0, full_bar(s));
+          if (PAIR) {
+            // block 0's barrier counts the bytes of both blocks; the activation box has 128 token rows
+            if (crank == 0) mbar_expect_tx(full_bar(s), 2 * kStageBytes);
+            const uint32_t fb = tc_map_to_rank(full_bar(s), 0);
+            tma_load_2d_pair(dst, &map_w, kb * kBK, n0, fb);
+            tma_load_2d_pair(dst + kABytes, &map_x, kb * kBK, a.x_row0 + m0 + static_cast<int>(crank) * (kPBN / 2), fb);
+          } else {
+            mbar_expect_tx(full_bar(s), kStageBytes);
+            tma_load_2d(dst, &map_w, kb * kBK, n0, full_bar(s));
+            tma_load_2d(dst + kABytes, &map_x, kb * kBK, a.x_row0 + m0, full_bar(s));
+            tma_load_2d(dst + kABytes + (kPBN / 2) * kBK * 2, &map_x, kb * kBK, a.x_row0 + m0 + kPBN / 2, full_bar(s));
+          }
         }
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    if (lane == 0 && crank == 0) {
       uint32_t it = 0;
       bool alive = true;
       int i = 0;
-      for (int t = blockIdx.x; t < total && alive; t += gridDim.x, ++i) {
+      for (int t = tile_first; t < total && alive; t += tile_step, ++i) {
         const int b = i & 1;
         if (i >= 2 && !mbar_wait(acc_empty(b), ((i >> 1) - 1) & 1)) {
           atomicOr(&failed, 1u);
@@ -507,8 +585,8 @@ __global__ void __launch_bounds__(kPThreads, 1) gemm_tc_persist_kernel(const __g
         tc_fence_after();
         const uint32_t d = tmem_acc + static_cast<uint32_t>(b * kPBN);
         for (int kb = 0; kb < nk; ++kb, ++it) {
-          const int s = it % kPStages;
-          if (!mbar_wait(full_bar(s), (it / kPStages) & 1)) {
+          const int s = it % kStages;
+          if (!mbar_wait(full_bar(s), (it / kStages) & 1)) {
             atomicOr(&failed, 1u);
             alive = false;
             break;
@@ -517,11 +595,17 @@ __global__ void __launch_bounds__(kPThreads, 1) gemm_tc_persist_kernel(const __g
           const uint32_t sa = smem_base + s * kStageBytes;
           const uint64_t adesc = smem_desc_sw128(sa), bdesc = smem_desc_sw128(sa + kABytes);
 #pragma unroll
-          for (int k4 = 0; k4 < kBK / 16; ++k4)
-            tc_mma_bf16(d, adesc + 2 * k4, bdesc + 2 * k4, kIdesc, (kb > 0 || k4 > 0) ? 1u : 0u);
-          tc_commit(empty_bar(s));
+          for (int k4 = 0; k4 < kBK / 16; ++k4) {
+            if (PAIR) tc_mma_bf16_pair(d, adesc + 2 * k4, bdesc + 2 * k4, kIdesc, (kb > 0 || k4 > 0) ? 1u : 0u);
+            else tc_mma_bf16(d, adesc + 2 * k4, bdesc + 2 * k4, kIdesc, (kb > 0 || k4 > 0) ? 1u : 0u);
+          }
+          if (PAIR) tc_commit_pair(empty_bar(s));
+          else tc_commit(empty_bar(s));
         }
-        if (alive) tc_commit(acc_full(b));
+        if (alive) {
+          if (PAIR) tc_commit_pair(acc_full(b));
+          else tc_commit(acc_full(b));
+        }
       }
     }
   } else {
@@ -531,14 +615,15 @@ __global__ void __launch_bounds__(kPThreads, 1) gemm_tc_persist_kernel(const __g
     int pos0 = 0;
     if (EPI == kEpiInProj) pos0 = a.rows.pos0_dev ? *a.rows.pos0_dev : a.rows.pos0_host;
     int i = 0;
-    for (int t = blockIdx.x; t < total; t += gridDim.x, ++i) {
+    for (int t = tile_first; t < total; t += tile_step, ++i) {
       const int b = i & 1;
       if (*failed_v || !mbar_wait(acc_full(b), (i >> 1) & 1)) {
         atomicOr(&failed, 1u);
         break;
       }
       tc_fence_after();
-      const int n0 = (t / m_tiles) * kBM, m0 = (t % m_tiles) * kPBN + half * (kPBN / 2);
+      const int n0 = (t / m_tiles) * kTileN + static_cast<int>(crank) * kBM,
+                m0 = (t % m_tiles) * kPBN + half * (kPBN / 2);
       const int n = n0 + quad * 32 + lane;
       const bool n_ok = n < a.N;
       int region = 0, nn = 0, head = 0, j = 0;
@@ -580,7 +665,10 @@ __global__ void __launch_bounds__(kPThreads, 1) gemm_tc_persist_kernel(const __g
           // this warp has read its part of the accumulator: hand the buffer back to the MMA warp
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive_cta(acc_empty(b));
+          if (lane == 0) {
+            if (PAIR) mbar_arrive_cluster(tc_map_to_rank(acc_empty(b), 0));
+            else mbar_arrive_cta(acc_empty(b));
+          }
         }
         const int mc = m0 + c0;                          // first token row of the chunk
         const int valid = min(32, a.M - mc);             // rows of the chunk that exist
@@ -683,7 +771,7 @@ __global__ void __launch_bounds__(kPThreads, 1) gemm_tc_persist_kernel(const __g
           // id falls into the group (layers.py:575-585 per group; ce_combine_kernel merges the groups).
           if (valid > 0) {
             float* tsm = reinterpret_cast<float*>(tc_smem_raw + (smem_base - smem_u32(tc_smem_raw)) +
-                                                  kPStages * kStageBytes) + (warp - 2) * 1024;
+                                                  kStages * kStageBytes) + (warp - 2) * 1024;
 #pragma unroll
             for (int q = 0; q < 32; ++q) tsm[q * 32 + (lane ^ q)] = n_ok ? __uint_as_float(r[q]) + bias : -INFINITY;
             __syncwarp();
@@ -705,7 +793,7 @@ __global__ void __launch_bounds__(kPThreads, 1) gemm_tc_persist_kernel(const __g
                 a.ce_tlogit[mc + lane] = mine[off ^ lane];
                 a.ce_hit[mc + lane] = 1;
               }
-              const size_t g = (static_cast<size_t>(t / m_tiles) * 4 + quad) * a.ce_ld + mc + lane;
+              const size_t g = (static_cast<size_t>(n0 / kBM) * 4 + quad) * a.ce_ld + mc + lane;
               a.ce_gmax[g] = mx;
               a.ce_gsum[g] = sum;
             }
@@ -729,10 +817,14 @@ __global__ void __launch_bounds__(kPThreads, 1) gemm_tc_persist_kernel(const __g
     }
   }
   tc_fence_before();
-  __syncthreads();
+  if (PAIR) tc_cluster_sync();                       // neither block leaves, or frees, while the other may still signal it
+  else __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(512u) : "memory");
+    if (PAIR)
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(512u) : "memory");
+    else
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(512u) : "memory");
   }
   if (threadIdx.x == 0 && failed && a.dev_err) atomicOr(a.dev_err, kDevErrTimeout);
 }
@@ -825,20 +917,40 @@ cudaError_t launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const GemmTc
 template <int EPI>
 cudaError_t launch_tc_persist(const CUtensorMap& mw, const CUtensorMap& mx, const GemmTcArgs& a, cudaStream_t s) {
   // the cross-entropy epilogue turns each epilogue warp's 32 x 32 block through 4 KB of shared memory
-  constexpr int smem = kPStages * (kBM * kBK * 2 + kPBN * kBK * 2) + 1024 + (EPI == kEpiLogitsCE ? kPEpiWarps * 4096 : 0);
+  constexpr int smem = PersistCfg<EPI, false>::kSmem, smem_pair = PersistCfg<EPI, true>::kSmem;
   static DeviceOnce once;
   static int sms_of[64] = {};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess || dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
   e = once.run([&] {
-    cudaError_t e2 = cudaFuncSetAttribute(gemm_tc_persist_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e2 = cudaFuncSetAttribute(gemm_tc_persist_kernel<EPI, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e2 != cudaSuccess) return e2;
+    e2 = cudaFuncSetAttribute(gemm_tc_persist_kernel<EPI, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_pair);
     if (e2 != cudaSuccess) return e2;
     return cudaDeviceGetAttribute(&sms_of[dev], cudaDevAttrMultiProcessorCount, dev);
   });
   if (e != cudaSuccess) return e;
-  const int total = ((a.M + kPBN - 1) / kPBN) * ((a.N + kBM - 1) / kBM);
-  gemm_tc_persist_kernel<EPI><<<std::min(total, sms_of[dev]), kPThreads, smem, s>>>(mw, mx, a);
+  const int m_tiles = (a.M + kPBN - 1) / kPBN;
+  if (a.pair && a.N >= 2 * kBM && sms_of[dev] >= 2) {
+    // clusters of 2 blocks, one 256 x 256 tile per pair at a time
+    const int total = m_tiles * ((a.N + 2 * kBM - 1) / (2 * kBM));
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(2 * std::min(total, sms_of[dev] / 2)));
+    cfg.blockDim = dim3(kPThreads);
+    cfg.dynamicSmemBytes = smem_pair;
+    cfg.stream = s;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, gemm_tc_persist_kernel<EPI, true>, mw, mx, a);
+  }
+  const int total = m_tiles * ((a.N + kBM - 1) / kBM);
+  gemm_tc_persist_kernel<EPI, false><<<std::min(total, sms_of[dev]), kPThreads, smem, s>>>(mw, mx, a);
   return cudaGetLastError();
 }
 
@@ -857,7 +969,7 @@ int gemm_tc_decode_cluster_k(int weight_rows, int M, int K) {
 }
 
 int gemm_tc_token_tile_for(int M) { return M <= 32 ? 32 : (M <= 64 ? 64 : 128); }
-int gemm_tc_wide_token_tile() { return kPBN; }
+int gemm_tc_wide_token_tile() { return kPBN / 2; }     // rows of the activation box: a tile takes two of them
 
 cudaError_t launch_gemm_tc_wide(GemvEpilogue epi, const void* map_w, const void* map_x, const GemmTcArgs& a,
                                 cudaStream_t s) {

@@ -219,6 +219,7 @@ struct GemmTcArgs {
   int ce_T, ce_vocab_start;
   int cluster_k;               // 2 or 4 (token tiles of at most 64 rows, partial == null): split K over a cluster of
                                // blocks that add their accumulators in shared memory before the fused epilogue
+  int pair;                    // wide kernel only: 1 = clusters of 2 blocks on 256 x 256 tiles (tcgen05 cta_group::2)
   uint32_t* dev_err;
 };
 int gemm_tc_token_tile();                 // widest token tile of launch_gemm_tc (128)
@@ -234,8 +235,8 @@ cudaError_t make_tensor_map_bf16(void* map_out_128B, const void* base, int64_t r
 // (x = hi + lo); both are multiplied into the same accumulator.
 cudaError_t launch_gemm_tc(GemvEpilogue epi, const void* map_w, const void* map_x, const GemmTcArgs& a,
                            cudaStream_t s, bool pdl, const void* map_x_lo = nullptr);
-// Persistent 128 x 256 variant for many token rows; map_x must have been made with box_rows =
-// gemm_tc_wide_token_tile().  No split-K.
+// Persistent variant for many token rows (tiles of 128 or, as block pairs, 256 weight rows x 256 token rows);
+// map_x must have been made with box_rows = gemm_tc_wide_token_tile().  No split-K.
 int gemm_tc_wide_token_tile();
 cudaError_t launch_gemm_tc_wide(GemvEpilogue epi, const void* map_w, const void* map_x, const GemmTcArgs& a,
                                 cudaStream_t s);

@@ -135,6 +135,8 @@ struct mtj_handle {
   int tc_hilo_max_b = kHiLoRows;    // up to this many sequences the activations travel as hi + lo (mtj_config.hilo_max_batch)
   int wait_limit = 1 << 22;         // iteration limit of the bounded device-side waits (mtj_config.wait_limit)
   bool tc_wide_ok = false;   // persistent 128 x 256 GEMM for long chunks
+  int tc_pair = 7;           // ... as block pairs on 256 x 256 tiles: bit 0 in-projection, 1 out-projection, 2 logits
+                             // (MTJ_TC_PAIR=<mask> overrides, for measurement)
   bool mega_push = true;     // per-block push exchange inside the persistent decode kernel (MTJ_NO_MEGA_PUSH=1: slot protocol)
   float* tc_partial = nullptr;        // [kTcSplitMax, kTcSplitRows, d] split-K partial sums of small-M out-projections
   int eval_rows = 0;                // rows of logits materialised at a time by the loss path
@@ -592,6 +594,7 @@ int32_t run_layer_tc(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, c
   a.cluster_k = (decode && h->tc_cluster_k) ? mtj::gemm_tc_decode_cluster_k(a.N, M, a.K) : 1;
   h->prof_begin(MTJ_FAMILY_INPROJ, s);
   const bool wide = use_tc_wide(h, M) && !decode;
+  a.pair = h->tc_pair & 1;
   if (wide)
     MTJ_CUDA(mtj::launch_gemm_tc_wide(mtj::kEpiInProj, &lw.map_in, &h->map_xn_wide, a, s));
   else
@@ -689,6 +692,7 @@ int32_t run_layer_tc(mtj_handle* h, int layer, int M, const mtj::RowMap& rows, c
                                        to_slot ? partial_slot_sel(h, M) : nullptr, partial_slot_stride(h), s, pdl));
     h->launches++;
   } else if (wide) {
+    o.pair = (h->tc_pair >> 1) & 1;
     MTJ_CUDA(mtj::launch_gemm_tc_wide(mtj::kEpiOut, &lw.map_out, &h->map_act_wide, o, s));
   } else {
     MTJ_CUDA(mtj::launch_gemm_tc(mtj::kEpiOut, &lw.map_out, &h->map_act[tc_tile_index(M)], o, s, pdl,
@@ -728,6 +732,7 @@ int32_t run_logits_tc(mtj_handle* h, int M, int row0, float* out, cudaStream_t s
   a.dev_err = h->dev_err;
   a.cluster_k = (decode && h->tc_cluster_k) ? mtj::gemm_tc_decode_cluster_k(a.N, M, a.K) : 1;
   h->prof_begin(MTJ_FAMILY_LOGITS, s);
+  a.pair = (h->tc_pair >> 2) & 1;
   if (use_tc_wide(h, M))
     MTJ_CUDA(mtj::launch_gemm_tc_wide(mtj::kEpiLogits, &h->map_proj, &h->map_xn_wide, a, s));
   else
@@ -763,6 +768,7 @@ int32_t run_loss_rows_fused(mtj_handle* h, int n, int row0, const mtj::CeArgs& c
   a.ce_vocab_start = ce.vocab_start;
   a.dev_err = h->dev_err;
   h->prof_begin(MTJ_FAMILY_LOGITS, s);
+  a.pair = (h->tc_pair >> 2) & 1;
   MTJ_CUDA(mtj::launch_gemm_tc_wide(mtj::kEpiLogitsCE, &h->map_proj, &h->map_xn_wide, a, s));
   h->prof_end(s);
   mtj::CeArgs c2 = ce;
@@ -1148,6 +1154,7 @@ int32_t mtj_bind_arenas(mtj_handle* h, void* wdev, int64_t wbytes, void* sdev, i
     ok = ok && mtj::make_tensor_map_bf16(&h->map_xn_wide, h->xn_bf16, h->max_rows, h->d, bw) == cudaSuccess;
     ok = ok && mtj::make_tensor_map_bf16(&h->map_act_wide, h->act_bf16, h->max_rows, h->dl + h->ffl, bw) == cudaSuccess;
     h->tc_wide_ok = ok && !getenv("MTJ_NO_TC_WIDE");
+    if (const char* e = getenv("MTJ_TC_PAIR")) h->tc_pair = atoi(e) & 7;
     {
       const int64_t rl = std::min<int64_t>(h->max_rows, kHiLoRows);
       bool okl = ok;

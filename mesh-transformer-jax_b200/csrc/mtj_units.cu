@@ -2,6 +2,7 @@
 // the parity tests and by callers that drive single kernels.
 #include <cuda_runtime.h>
 
+#include <cstdlib>
 #include <string>
 
 #include "../../include/mtj_b200.h"
@@ -145,6 +146,7 @@ int32_t mtj_k_gemm_tc(const void* w, const void* x, const float* bias, int32_t M
   a.out = out;
   a.ld_out = N;
   a.cluster_k = mtj::gemm_tc_decode_cluster_k(N, M, K);     // the rule the decode step uses (1 for M > 64)
+  a.pair = 1;
   cudaError_t e = wide ? mtj::launch_gemm_tc_wide(mtj::kEpiLogits, &mw, &mx, a, static_cast<cudaStream_t>(s))
                        : mtj::launch_gemm_tc(mtj::kEpiLogits, &mw, &mx, a, static_cast<cudaStream_t>(s), false);
   if (e != cudaSuccess) return mtj_set_error(MTJ_ERR_CUDA, cudaGetErrorString(e));
