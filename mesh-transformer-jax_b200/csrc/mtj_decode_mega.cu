@@ -26,7 +26,10 @@
 namespace mtj {
 namespace {
 
-constexpr int kMT = 256;                 // threads per block
+#ifndef MTJ_MEGA_MT
+#define MTJ_MEGA_MT 256
+#endif
+constexpr int kMT = MTJ_MEGA_MT;         // threads per block
 constexpr int kMW = kMT / 32;            // warps per block
 #ifndef MTJ_MEGA_NC
 #define MTJ_MEGA_NC 4
@@ -405,7 +408,7 @@ __device__ __forceinline__ void warp_stream(const __nv_bfloat16* __restrict__ W,
 }
 
 template <int BT, int DH>
-__global__ void __launch_bounds__(kMT, BT == 1 ? 2 : 1) decode_mega_kernel(const MegaArgs a) {
+__global__ void __launch_bounds__(kMT, (BT == 1 && kMT == 256) ? 2 : 1) decode_mega_kernel(const MegaArgs a) {
   extern __shared__ __align__(128) unsigned char mega_smem[];
   __shared__ float red[kMW];
 
