@@ -35,9 +35,12 @@ def build(force: bool = False, verbose: bool = False) -> str:
     objs = []
     procs = []
     os.makedirs(os.path.join(HERE, "build"), exist_ok=True)
-    for src in sources():
-        obj = os.path.join(HERE, "build", os.path.basename(src)[:-3] + ".o")
-        cmd = [NVCC, *FLAGS, "-c", src, "-o", obj]
+    units = [(src, "", []) for src in sources()]
+    # the whole-step decode kernel a second time with one 512-thread block per SM (see the head of that file)
+    units.append((os.path.join(CSRC, "mtj_decode_mega.cu"), "_mt512", ["-DMTJ_MEGA_MT=512"]))
+    for src, tag, extra in units:
+        obj = os.path.join(HERE, "build", os.path.basename(src)[:-3] + tag + ".o")
+        cmd = [NVCC, *FLAGS, *extra, "-c", src, "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas")
             cmd.insert(2, "-v")

@@ -20,12 +20,17 @@
 // stand-alone kernels (mtj_gemv.cu, mtj_attn.cu).
 #include <math.h>
 
+#include <cstdlib>
+
 #include "mtj_common.cuh"
 #include "mtj_kernels.h"
 
 namespace mtj {
 namespace {
 
+// This file is compiled twice: with 256 threads per block (two blocks per SM), and with MTJ_MEGA_MT=512 (one block
+// of 16 warps per SM) for one sequence on one GPU, where halving the arrivals per grid-wide hand-over is worth
+// 1.2 % of the step; with tensor-parallel slices the wider block loses more in the attention phase than it gains.
 #ifndef MTJ_MEGA_MT
 #define MTJ_MEGA_MT 256
 #endif
@@ -833,6 +838,10 @@ cudaError_t launch_mega_t(const MegaArgs& a, cudaStream_t s, int* grid_out) {
     e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_mega_kernel<BT, DH>, kMT, smem);
     if (e != cudaSuccess) return e;
     if (per_sm < 1) return cudaErrorLaunchOutOfResources;
+    if (const char* lim = getenv("MTJ_MEGA_BLOCKS_PER_SM")) {      // measurement only
+      const int v = atoi(lim);
+      if (v >= 1 && v < per_sm) per_sm = v;
+    }
     blocks_of[dev] = sms * per_sm;
     smem_of[dev] = smem + 1;
   }
@@ -860,10 +869,19 @@ cudaError_t launch_mega_t(const MegaArgs& a, cudaStream_t s, int* grid_out) {
 
 }  // namespace
 
+#if MTJ_MEGA_MT == 512
+cudaError_t launch_decode_mega_wide(const MegaArgs& a, cudaStream_t s, int* grid_out) {
+  if (a.B != 1) return cudaErrorInvalidValue;
+  if (a.dh == 256) return launch_mega_t<1, 256>(a, s, grid_out);
+  if (a.dh == 64) return launch_mega_t<1, 64>(a, s, grid_out);
+  return cudaErrorInvalidValue;
+}
+#else
 cudaError_t launch_decode_mega(const MegaArgs& a, cudaStream_t s, int* grid_out) {
   if (a.world < 1 || a.world > 8 || a.B < 1 || a.B > 4 || (a.d & 255) || a.d > 8192 || (a.dl & 1) || (a.V & 1) || ((3 * a.dl + a.ffl) & 1) ||
       ((a.dl + a.ffl) & 7) || a.max_splits < 1 || (a.dl + a.ffl) * 4 > 200 * 1024)
     return cudaErrorInvalidValue;
+  if (a.world == 1 && a.B == 1 && !getenv("MTJ_MEGA_NARROW")) return launch_decode_mega_wide(a, s, grid_out);
   if (a.dh == 256) {
     if (a.B == 1) return launch_mega_t<1, 256>(a, s, grid_out);
     if (a.B == 2) return launch_mega_t<2, 256>(a, s, grid_out);
@@ -876,5 +894,6 @@ cudaError_t launch_decode_mega(const MegaArgs& a, cudaStream_t s, int* grid_out)
   }
   return cudaErrorInvalidValue;
 }
+#endif
 
 }  // namespace mtj

@@ -179,6 +179,8 @@ struct MegaArgs {
   int wait_limit;              // spins before a wait on a phase counter, flag or packet gives up
 };
 cudaError_t launch_decode_mega(const MegaArgs& a, cudaStream_t s, int* grid_out);
+// the same kernel built with one 512-thread block per SM (one sequence only); launch_decode_mega picks it on one GPU
+cudaError_t launch_decode_mega_wide(const MegaArgs& a, cudaStream_t s, int* grid_out);
 
 struct ArgmaxArgs {
   const float* logits;         // [B, V]
