@@ -422,6 +422,7 @@ __global__ void __launch_bounds__(kMT, (BT == 1 && kMT == 256) ? 2 : 1) decode_m
   __shared__ float wgt[64];
   __shared__ float inv_l;
   __shared__ bool is_last;
+  __shared__ unsigned long long blk_amax[4];         // greedy token: this block's best (logit order key, index) per row
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int G = gridDim.x;
@@ -797,18 +798,40 @@ __global__ void __launch_bounds__(kMT, (BT == 1 && kMT == 256) ? 2 : 1) decode_m
     trace(a.trace, 6 * L + 0);
     phase_wait(c_x + L, target, a.dev_err, a.wait_limit);
     trace(a.trace, 6 * L + 1);
+    if (threadIdx.x < 4) blk_amax[threadIdx.x] = 0ull;             // (the LayerNorm below has block barriers)
     layer_norm_to_smem<BT>(a.x, B, d, a.lnf_scale, a.lnf_offset, xn, red);
     const int nch = (d + 255) >> 8;
+    // The greedy token (nucleaus_sample with top_p -> 0: the arg-max, highest index among equal logits) is picked
+    // on the way: every lane keeps the best logit it has written as (order key << 32 | index); the blocks fold
+    // theirs into a.amax with a 64-bit atomic max and the last block to finish writes the token.
+    unsigned long long best = 0ull;
     warp_stream<BT, true>(a.proj_w, d, nch, gw, GW, nv, xn, nullptr, 0, lane, [&](int u, float val) {
       const int r = lane & 1, bt = lane >> 1;
       const int n = 2 * u + r;
-      if (lane < 2 * BT && bt < B) a.logits[static_cast<size_t>(bt) * a.V + n] = val + a.proj_b[n];
+      if (lane < 2 * BT && bt < B) {
+        float y = val + a.proj_b[n];
+        a.logits[static_cast<size_t>(bt) * a.V + n] = y;
+        if (a.amax) {
+          if (y == 0.0f) y = 0.0f;                                   // -0 and +0 compare equal
+          uint32_t k = __float_as_uint(y);
+          k = (k & 0x80000000u) ? ~k : (k | 0x80000000u);            // ascending integer order == ascending float order
+          const unsigned long long cand = (static_cast<unsigned long long>(k) << 32) | static_cast<uint32_t>(n);
+          best = cand > best ? cand : best;
+        }
+      }
     });
+    if (a.amax) {
+      const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, 1);
+      best = other > best ? other : best;
+      if (lane < 2 * BT && (lane & 1) == 0 && (lane >> 1) < B && best) atomicMax(&blk_amax[lane >> 1], best);
+    }
   }
 
   // ---- the last block to finish resets the arrival counters for the next launch -----------------
   __syncthreads();
   trace(a.trace, 6 * L + 2);
+  if (a.amax && threadIdx.x < B && blk_amax[threadIdx.x]) atomicMax(a.amax + threadIdx.x, blk_amax[threadIdx.x]);
+  __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence();
     const uint32_t ticket = atomicAdd(c_end, 1u);
@@ -818,6 +841,16 @@ __global__ void __launch_bounds__(kMT, (BT == 1 && kMT == 256) ? 2 : 1) decode_m
   if (is_last) {
     for (int i = threadIdx.x; i < 5 * L + 3; i += kMT) a.sync[i] = 0u;
     if (tp && threadIdx.x == 0) *a.seq = seq0 + 1 + L;
+    if (a.amax) {
+      // every block's maxima were published before its ticket: the token of the step, then the position moves on
+      __threadfence();
+      if (threadIdx.x < B) {
+        const unsigned long long win = *reinterpret_cast<volatile unsigned long long*>(a.amax + threadIdx.x);
+        a.tokens_out[threadIdx.x] = static_cast<uint32_t>(win);
+        a.amax[threadIdx.x] = 0ull;
+      }
+      if (threadIdx.x == 0 && a.cur_out) *a.cur_out += 1;
+    }
   }
 }
 

@@ -162,6 +162,11 @@ struct MegaArgs {
   float* part_ml;
   uint32_t* head_counters;     // [B * heads], zero between launches
   float* logits;               // [B, V]
+  // greedy token inside the kernel (one GPU): per-row running maximum (zero between launches), the token buffer
+  // the last block writes (may be the buffer `tokens` points to) and the position counter it advances; or null
+  unsigned long long* amax;    // [4]
+  uint32_t* tokens_out;        // [B]
+  int32_t* cur_out;
   uint32_t* sync;              // [5 L + 3] phase arrival counters, zero between launches
   // tensor parallel (world > 1): the peer exchange buffers of mtj_p2p.cu
   int rank, world, vocab_start;

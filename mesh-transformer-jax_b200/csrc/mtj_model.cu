@@ -186,8 +186,10 @@ struct mtj_handle {
   int ks_inproj = 0, ks_out = 0, ks_logits = 0;   // K-split overrides (tuning; 0 = automatic)
   // decode of 1-4 sequences on one GPU: the whole step as one persistent kernel
   bool use_mega = true;
+  bool mega_token = true;                  // greedy token picked inside the whole-step kernel (MTJ_NO_MEGA_TOKEN=1: separate kernel)
   mtj::MegaLayer* mega_layers = nullptr;   // device copy of the per-layer pointers
-  uint32_t* mega_sync = nullptr;           // [3 L + 2] phase counters
+  uint32_t* mega_sync = nullptr;           // [5 L + 3] phase counters
+  unsigned long long* mega_amax = nullptr; // [4] running maxima of the in-kernel greedy token
   unsigned long long* mega_trace = nullptr;  // [6 L + 3] phase time stamps (profiling read-out)
   bool mega_trace_on = false;
   // decode: attention runs on a side stream next to the FF half of the in-projection
@@ -311,6 +313,7 @@ struct mtj_handle {
     ce_hit = c.take<uint8_t>(R);
     mega_layers = c.take<mtj::MegaLayer>(L);
     mega_sync = c.take<uint32_t>(5 * L + 3);
+    mega_amax = c.take<unsigned long long>(4);
     mega_trace = c.take<unsigned long long>(6 * L + 3);
     tokens = c.take<uint32_t>(max_batch);
     cur = c.take<int32_t>(4);
@@ -1017,6 +1020,7 @@ int32_t mtj_create(const mtj_config* c, mtj_handle** out) {
   h->use_pdl = !(e && e[0] == '1');
   e = getenv("MTJ_NO_MEGA");
   h->use_mega = !(e && e[0] == '1');
+  h->mega_token = !getenv("MTJ_NO_MEGA_TOKEN");
   if (c->mega_max_batch != 0) h->mega_max_b = std::max(0, c->mega_max_batch);
   if (c->tc_decode_min_batch > 0) h->tc_decode_min_b = c->tc_decode_min_batch;
   if (c->hilo_max_batch != 0) h->tc_hilo_max_b = std::max(0, std::min(kHiLoRows, c->hilo_max_batch));
@@ -1132,6 +1136,7 @@ int32_t mtj_bind_arenas(mtj_handle* h, void* wdev, int64_t wbytes, void* sdev, i
     }
     MTJ_CUDA(cudaMemcpyAsync(h->mega_layers, ml.data(), sizeof(mtj::MegaLayer) * h->L, cudaMemcpyHostToDevice, s));
     MTJ_CUDA(cudaMemsetAsync(h->mega_sync, 0, sizeof(uint32_t) * (5 * h->L + 3), s));
+    MTJ_CUDA(cudaMemsetAsync(h->mega_amax, 0, sizeof(unsigned long long) * 4, s));
     MTJ_CUDA(cudaStreamSynchronize(s));   // `ml` goes out of scope
   }
   MTJ_CUDA(cudaStreamSynchronize(s));   // `tab` is about to go out of scope
@@ -1504,6 +1509,8 @@ int32_t mtj_decode_step(mtj_handle* h, const uint32_t* tokens_in, const float* t
     const bool mega = h->use_mega && (h->mp == 1 || use_p2p(h, B)) && B <= h->mega_max_b && !h->profile && (h->d % 256) == 0;
     const bool tc = use_tc_decode(h, B);
     h->xn_ready = false;
+    // one GPU, greedy: the persistent kernel also picks the token and advances the position
+    const bool mega_token = mega && greedy && h->mp == 1 && h->mega_token;
     int32_t r = mega ? MTJ_OK : run_embed(h, h->tokens, 1, B, erows, true, st, tc);
     if (r) return r;
     if (mega) {
@@ -1520,6 +1527,11 @@ int32_t mtj_decode_step(mtj_handle* h, const uint32_t* tokens_in, const float* t
       ma.head_counters = h->counters; ma.logits = h->logits; ma.sync = h->mega_sync; ma.dev_err = h->dev_err;
       ma.trace = h->mega_trace_on ? h->mega_trace : nullptr;
       ma.wait_limit = h->wait_limit;
+      if (mega_token) {
+        ma.amax = h->mega_amax;
+        ma.tokens_out = h->tokens;
+        ma.cur_out = h->cur;
+      }
       ma.rank = h->rank; ma.world = h->mp; ma.vocab_start = h->rank * h->Vl;
       if (h->mp > 1) {
         ma.slot_base = reinterpret_cast<float*>(h->p2p_local);
@@ -1575,6 +1587,7 @@ int32_t mtj_decode_step(mtj_handle* h, const uint32_t* tokens_in, const float* t
       MTJ_CUDA(mtj::launch_gather_rows(h->logits_gather, h->logits_all, h->mp, B, h->Vl, st));
       h->launches += 2;
     }
+    if (mega_token) return MTJ_OK;
     if (greedy) {
       mtj::ArgmaxArgs am = {};
       am.logits = h->logits_all;
