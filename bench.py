@@ -28,7 +28,7 @@ METRIC = "gptj6b_decode_tokens_per_s"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under profiles/
 # (GPT-J-6B layer shapes, batch 1, window 2047); the kernels read every weight byte exactly once.  The whole-step
 # kernel was captured at 4 layers and its traffic scaled by the algorithmic bytes of the 28-layer step.
-NCU_TRAFFIC = {"mega": 12.69e9, "in_proj": None, "ff_in_proj": None, "attention": 33.6e6, "out_proj": 171.4e6, "logits": 416.4e6}
+NCU_TRAFFIC = {"mega": 12.66e9, "in_proj": None, "ff_in_proj": None, "attention": 33.6e6, "out_proj": 171.4e6, "logits": 416.4e6}
 UNIT = "tokens/s"
 
 GPTJ_6B = {
