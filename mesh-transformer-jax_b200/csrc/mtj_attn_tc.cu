@@ -42,9 +42,9 @@ constexpr int kThreadsTc = 320;                 // TMA warp, MMA warp, 8 softmax
 constexpr uint32_t kQBytes = kQT * kDH * 2;          // 64 KB
 constexpr uint32_t kKBytes = kKB * kDH * 2;          // 32 KB
 constexpr uint32_t kStage = 2 * kKBytes;             // K + V of one key block
-constexpr uint32_t kPBytes = kQT * kKB * 2;          // 16 KB
-constexpr uint32_t kSmemTc = kQBytes + 2 * kStage + kPBytes + 1024;
-constexpr uint32_t kColS = 0, kColO = 128, kTmemCols = 512;   // S0 | S1 | O (256 columns)
+constexpr uint32_t kSmemTc = kQBytes + 2 * kStage + 1024;
+// tensor memory: S0 | S1 (64 fp32 columns each) | O (256) | P0 | P1 (64 bf16 keys = 32 columns each)
+constexpr uint32_t kColS = 0, kColO = 128, kColP = 384, kPCols = kKB / 2, kTmemCols = 512;
 
 __device__ __forceinline__ void tma2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
   asm volatile(
@@ -68,6 +68,14 @@ __device__ __forceinline__ void mma_bf16(uint32_t d, uint64_t a, uint64_t b, uin
       : "memory");
 }
 // shared-memory matrix descriptor, 128-byte swizzle; lbo / sbo in bytes
+// the same with the A operand (bf16, K-major, two elements per 32-bit column) in tensor memory
+__device__ __forceinline__ void mma_bf16_ts(uint32_t d, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d), "r"(a_tmem), "l"(b), "r"(idesc), "r"(acc)
+      : "memory");
+}
 __device__ __forceinline__ uint64_t sdesc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
   uint64_t d = 0;
   d |= static_cast<uint64_t>((addr >> 4) & 0x3FFF);
@@ -107,15 +115,23 @@ __device__ __forceinline__ void tm_st32(uint32_t taddr, const uint32_t* r) {
       : "memory");
 }
 
+__device__ __forceinline__ void tm_st16(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+
 __global__ void __launch_bounds__(kThreadsTc, 1) prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                      const __grid_constant__ CUtensorMap map_k,
                                                                      const __grid_constant__ CUtensorMap map_v,
                                                                      const PrefillAttnTcArgs a) {
   extern __shared__ unsigned char att_smem_raw[];
   const uint32_t base = (smem_u32(att_smem_raw) + 1023u) & ~1023u;
-  unsigned char* base_ptr = att_smem_raw + (base - smem_u32(att_smem_raw));
-  const uint32_t sQ = base, sKV = base + kQBytes, sP = base + kQBytes + 2 * kStage;
-  __shared__ __align__(8) uint64_t bars[13];
+  const uint32_t sQ = base, sKV = base + kQBytes;
+  __shared__ __align__(8) uint64_t bars[16];
   __shared__ uint32_t tmem_slot;
   __shared__ uint32_t failed;
   __shared__ float xmax[2][2][kQT];      // [iteration parity][column half][row]: the pair's row maxima
@@ -124,11 +140,13 @@ __global__ void __launch_bounds__(kThreadsTc, 1) prefill_attn_tc_kernel(const __
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t bar0 = smem_u32(bars);
   const uint32_t q_full = bar0, k_full0 = bar0 + 8, k_empty0 = bar0 + 24, v_full0 = bar0 + 40,
-                 v_empty0 = bar0 + 56, s_full0 = bar0 + 72, p_full = bar0 + 88, o_done = bar0 + 96;
+                 v_empty0 = bar0 + 56, s_full0 = bar0 + 72, p_full0 = bar0 + 88, p_empty0 = bar0 + 104,
+                 o_done = bar0 + 120;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 13; ++i) mbar_init(bar0 + 8u * i, 1);
-    mbar_init(p_full, 256);
+    for (int i = 0; i < 16; ++i) mbar_init(bar0 + 8u * i, 1);
+    mbar_init(p_full0, 256);
+    mbar_init(p_full0 + 8, 256);
     mbar_fence_init();
     failed = 0;
   }
@@ -223,19 +241,22 @@ __global__ void __launch_bounds__(kThreadsTc, 1) prefill_attn_tc_kernel(const __
         }
       }
       for (int j = 0; ok && j < nb; ++j) {
-        ok = mbar_wait(p_full, j & 1) && mbar_wait(v_full0 + 8 * (j & 1), (j >> 1) & 1);   // P_j written, S_j consumed
+        // P_j written (and with it S_j consumed), V_j landed
+        ok = mbar_wait(p_full0 + 8 * (j & 1), (j >> 1) & 1) && mbar_wait(v_full0 + 8 * (j & 1), (j >> 1) & 1);
         if (!ok) break;
         fence_after();
-        // O += P . V : V tile is [64 keys][256 dh] -> MN-major B operand, 64-column blocks 8 KB apart
+        // O += P . V : P from tensor memory (16 keys = 8 columns per MMA), V tile is [64 keys][256 dh] ->
+        // MN-major B operand, 64-column blocks 8 KB apart
         const uint32_t dv = sKV + (j & 1) * kStage + kKBytes;
+        const uint32_t pa = tmem + kColP + (j & 1) * kPCols;
 #pragma unroll
         for (int k4 = 0; k4 < 4; ++k4) {
-          const uint64_t ad = sdesc(sP, 16, 1024) + 2 * k4;
           const uint64_t bd = sdesc(dv + k4 * 2048, kKB * 128, 1024);
-          mma_bf16(tmem + kColO, ad, bd, kIdO, (j | k4) ? 1u : 0u);
+          mma_bf16_ts(tmem + kColO, pa + 8 * k4, bd, kIdO, (j | k4) ? 1u : 0u);
         }
         commit(v_empty0 + 8 * (j & 1));
-        commit(o_done);
+        commit(p_empty0 + 8 * (j & 1));                          // P buffer j & 1 is free, O holds key blocks 0 .. j
+        if (j == nb - 1) commit(o_done);
         if (j + 2 < nb) {
           ok = mbar_wait(k_full0 + 8 * (j & 1), ((j + 2) >> 1) & 1);
           if (!ok) break;
@@ -311,10 +332,13 @@ __global__ void __launch_bounds__(kThreadsTc, 1) prefill_attn_tc_kernel(const __
         pk[c >> 1] = *reinterpret_cast<const uint32_t*>(&pb);
       }
       l = l * corr + psum;                                     // this thread's half of the denominator
-      if (j > 0) {
-        if (ok) ok = mbar_wait(o_done, (g - 1) & 1);           // P buffer and O are free again
+      // P is double buffered in tensor memory: buffer j & 1 is free once PV(j - 2) has read it
+      if (j >= 2 && ok) ok = mbar_wait(p_empty0 + 8 * (j & 1), ((j >> 1) - 1) & 1);
+      if (j > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {    // both warps of a pair see the same corr per row
+        // O changes scale: PV(j - 1) must have landed (PV(j) cannot start before this thread has written P_j)
+        if (ok) ok = mbar_wait(p_empty0 + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1);
         fence_after();
-        if (ok && __any_sync(0xffffffffu, corr != 1.0f)) {     // both warps of a pair see the same corr per row
+        if (ok) {
 #pragma unroll 1
           for (int c0 = half * (kDH / 2); c0 < (half + 1) * (kDH / 2); c0 += 32) {
             uint32_t o[32];
@@ -326,18 +350,15 @@ __global__ void __launch_bounds__(kThreadsTc, 1) prefill_attn_tc_kernel(const __
           asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         }
       }
-      // this thread's 32 columns of the P row -> shared memory in the 128-byte-swizzled K-major layout
-      unsigned char* prow = base_ptr + (sP - base) + r * 128;
-#pragma unroll
-      for (int ch = 0; ch < 4; ++ch)
-        *reinterpret_cast<uint4*>(prow + (((half * 4 + ch) ^ (r & 7)) << 4)) =
-            make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      // this thread's 32 keys of the P row -> tensor memory, two bf16 per column: the A operand of P . V
+      fence_after();
+      tm_st16(tmem + lane_addr + kColP + (j & 1) * kPCols + half * 16, pk);
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       fence_before();
-      mbar_arrive(p_full);
+      mbar_arrive(p_full0 + 8 * (j & 1));
       m_ref = m_new;
     }
-    if (nb > 0 && ok) ok = mbar_wait(o_done, (nb - 1) & 1);
+    if (nb > 0 && ok) ok = mbar_wait(o_done, 0);
     if (nb > 0 && !ok) atomicOr(&failed, 1u);
     fence_after();
     xl[half][r] = l;
