@@ -38,7 +38,12 @@ namespace {
 constexpr int kQT = 128;                 // queries per block
 constexpr int kKB = 64;                  // keys per block (one cache page)
 constexpr int kDH = 256;
-constexpr int kThreadsTc = 320;                 // TMA warp, MMA warp, 8 softmax warps
+// threads sharing a query row (each 64 / kParts key columns and 256 / kParts output columns): 2 and 4 measure the
+// same (1.88 / 1.87 ms of attention per GPT-J-6B prefill); 1 was 25 % slower
+constexpr int kParts = 2;
+constexpr int kSoftWarps = 4 * kParts;          // softmax warps: TMEM lane quadrant = warp % 4, part = (warp - 2) / 4
+constexpr int kThreadsTc = 64 + 32 * kSoftWarps;   // TMA warp, MMA warp, softmax warps
+constexpr int kPartKeys = kKB / kParts, kPartCols = kDH / kParts;
 constexpr uint32_t kQBytes = kQT * kDH * 2;          // 64 KB
 constexpr uint32_t kKBytes = kKB * kDH * 2;          // 32 KB
 constexpr uint32_t kStage = 2 * kKBytes;             // K + V of one key block
@@ -115,6 +120,22 @@ __device__ __forceinline__ void tm_st32(uint32_t taddr, const uint32_t* r) {
       : "memory");
 }
 
+__device__ __forceinline__ void tm_ld16(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tm_st8(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+      : "memory");
+}
 __device__ __forceinline__ void tm_st16(uint32_t taddr, const uint32_t* r) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
@@ -134,8 +155,8 @@ __global__ void __launch_bounds__(kThreadsTc, 1) prefill_attn_tc_kernel(const __
   __shared__ __align__(8) uint64_t bars[16];
   __shared__ uint32_t tmem_slot;
   __shared__ uint32_t failed;
-  __shared__ float xmax[2][2][kQT];      // [iteration parity][column half][row]: the pair's row maxima
-  __shared__ float xl[2][kQT];           // [column half][row]: the pair's softmax denominators
+  __shared__ float xmax[2][kParts][kQT];   // [iteration parity][part][row]: the row maxima of the threads sharing a row
+  __shared__ float xl[kParts][kQT];        // [part][row]: their softmax denominators
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t bar0 = smem_u32(bars);
@@ -145,8 +166,8 @@ __global__ void __launch_bounds__(kThreadsTc, 1) prefill_attn_tc_kernel(const __
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < 16; ++i) mbar_init(bar0 + 8u * i, 1);
-    mbar_init(p_full0, 256);
-    mbar_init(p_full0 + 8, 256);
+    mbar_init(p_full0, 32 * kSoftWarps);
+    mbar_init(p_full0 + 8, 32 * kSoftWarps);
     mbar_fence_init();
     failed = 0;
   }
@@ -268,11 +289,11 @@ __global__ void __launch_bounds__(kThreadsTc, 1) prefill_attn_tc_kernel(const __
     }
   } else {
     const int quad = warp & 3;                                 // the TMEM lane quadrant this warp may access
-    const int half = (warp - 2) >> 2;                          // 0: key columns [0, 32) / O columns [0, 128); 1: the rest
+    const int part = (warp - 2) >> 2;                          // key columns [kPartKeys part, +kPartKeys) / O columns [kPartCols part, +kPartCols)
     const int r = quad * 32 + lane;                            // query row within the tile = TMEM lane
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
-    const uint32_t pair_bar = 1u + static_cast<uint32_t>(quad);   // named barrier of the two warps sharing these rows
-    auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory"); };
+    const uint32_t pair_bar = 1u + static_cast<uint32_t>(quad);   // named barrier of the warps sharing these rows
+    auto pair_sync = [&]() { asm volatile("bar.sync %0, %1;" ::"r"(pair_bar), "n"(32 * kParts) : "memory"); };
     const float c2 = 0.0625f * 1.4426950408889634f;            // 1/sqrt(256) * log2(e)
     const bool row_ok = r < q_rows;
     const int qpos = pos0 + tile * kQT + r;
@@ -285,25 +306,30 @@ __global__ void __launch_bounds__(kThreadsTc, 1) prefill_attn_tc_kernel(const __
       // a wait that runs out is remembered, but the thread keeps meeting its partner at the pair barrier
       if (ok) ok = mbar_wait(s_full0 + 8 * (g & 1), (g >> 1) & 1);
       fence_after();
-      uint32_t sr[32];
-      const uint32_t s_addr = tmem + lane_addr + kColS + (g & 1) * kKB + half * 32;
+      uint32_t sr[kPartKeys];
+      const uint32_t s_addr = tmem + lane_addr + kColS + (g & 1) * kKB + part * kPartKeys;
       if (ok) {
-        tm_ld32(s_addr, sr);
+        if (kPartKeys == 32) tm_ld32(s_addr, sr);
+        else tm_ld16(s_addr, sr);
       } else {
 #pragma unroll
-        for (int c = 0; c < 32; ++c) sr[c] = 0xff800000u;      // -inf
+        for (int c = 0; c < kPartKeys; ++c) sr[c] = 0xff800000u;      // -inf
       }
-      const int kbase = (first_blk + j) * kKB + half * 32;
-      // every row of this warp sees all of its 32 keys: no mask arithmetic
-      const bool full_blk = ok && warp_rows_ok && kbase >= pad && kbase + 31 <= min(warp_qpos0, limit);
+      const int kbase = (first_blk + j) * kKB + part * kPartKeys;
+      // every row of this warp sees all of its keys: no mask arithmetic
+      const bool full_blk = ok && warp_rows_ok && kbase >= pad && kbase + kPartKeys - 1 <= min(warp_qpos0, limit);
       float mx = -INFINITY;
       if (full_blk) {
+        float mxa = -INFINITY, mxb = -INFINITY;               // two chains
 #pragma unroll
-        for (int c = 0; c < 32; ++c) mx = fmaxf(mx, __uint_as_float(sr[c]));
-        mx *= c2;
+        for (int c = 0; c < kPartKeys; c += 2) {
+          mxa = fmaxf(mxa, __uint_as_float(sr[c]));
+          mxb = fmaxf(mxb, __uint_as_float(sr[c + 1]));
+        }
+        mx = fmaxf(mxa, mxb) * c2;
       } else {
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
+        for (int c = 0; c < kPartKeys; ++c) {
           const int key = kbase + c;
           const bool vis = ok && row_ok && key >= pad && key <= qpos && key <= limit;
           const float v = vis ? __uint_as_float(sr[c]) : -INFINITY;
@@ -311,36 +337,38 @@ __global__ void __launch_bounds__(kThreadsTc, 1) prefill_attn_tc_kernel(const __
           mx = fmaxf(mx, v * c2);
         }
       }
-      // the row's maximum over all 64 keys: the partner thread holds the other half
-      xmax[j & 1][half][r] = mx;
+      // the row's maximum over all 64 keys: the partner threads hold the other parts
+      xmax[j & 1][part][r] = mx;
       pair_sync();
-      mx = fmaxf(mx, xmax[j & 1][half ^ 1][r]);
+#pragma unroll
+      for (int q = 1; q < kParts; ++q) mx = fmaxf(mx, xmax[j & 1][(part + q) % kParts][r]);
       float m_new = m_ref;
       if (mx > m_ref + 8.0f || (m_ref == -INFINITY && mx > -INFINITY)) m_new = mx;
       const float corr = (m_new == m_ref || m_ref == -INFINITY) ? 1.0f : exp2f(m_ref - m_new);
       // p = 2^(s c - m); a masked score is -inf and gives 0; a row that has seen no key yet (m = -inf)
       // takes a finite stand-in so that -inf - (-inf) does not appear
       const float neg_m = m_new == -INFINITY ? 0.f : -m_new;
-      float psum = 0.f;
-      uint32_t pk[16];
+      float psum0 = 0.f, psum1 = 0.f;
+      uint32_t pk[kPartKeys / 2];
 #pragma unroll
-      for (int c = 0; c < 32; c += 2) {
+      for (int c = 0; c < kPartKeys; c += 2) {
         const float p0 = ex2_fast(fmaf(__uint_as_float(sr[c]), c2, neg_m));
         const float p1 = ex2_fast(fmaf(__uint_as_float(sr[c + 1]), c2, neg_m));
-        psum += p0 + p1;
+        psum0 += p0;
+        psum1 += p1;
         const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
         pk[c >> 1] = *reinterpret_cast<const uint32_t*>(&pb);
       }
-      l = l * corr + psum;                                     // this thread's half of the denominator
+      l = l * corr + (psum0 + psum1);                          // this thread's part of the denominator
       // P is double buffered in tensor memory: buffer j & 1 is free once PV(j - 2) has read it
       if (j >= 2 && ok) ok = mbar_wait(p_empty0 + 8 * (j & 1), ((j >> 1) - 1) & 1);
-      if (j > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {    // both warps of a pair see the same corr per row
+      if (j > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {    // the warps sharing a row see the same corr per row
         // O changes scale: PV(j - 1) must have landed (PV(j) cannot start before this thread has written P_j)
         if (ok) ok = mbar_wait(p_empty0 + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1);
         fence_after();
         if (ok) {
 #pragma unroll 1
-          for (int c0 = half * (kDH / 2); c0 < (half + 1) * (kDH / 2); c0 += 32) {
+          for (int c0 = part * kPartCols; c0 < (part + 1) * kPartCols; c0 += 32) {
             uint32_t o[32];
             tm_ld32(tmem + lane_addr + kColO + c0, o);
 #pragma unroll
@@ -350,9 +378,10 @@ __global__ void __launch_bounds__(kThreadsTc, 1) prefill_attn_tc_kernel(const __
           asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         }
       }
-      // this thread's 32 keys of the P row -> tensor memory, two bf16 per column: the A operand of P . V
+      // this thread's keys of the P row -> tensor memory, two bf16 per column: the A operand of P . V
       fence_after();
-      tm_st16(tmem + lane_addr + kColP + (j & 1) * kPCols + half * 16, pk);
+      if (kPartKeys == 32) tm_st16(tmem + lane_addr + kColP + (j & 1) * kPCols + part * (kPartKeys / 2), pk);
+      else tm_st8(tmem + lane_addr + kColP + (j & 1) * kPCols + part * (kPartKeys / 2), pk);
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       fence_before();
       mbar_arrive(p_full0 + 8 * (j & 1));
@@ -361,16 +390,18 @@ __global__ void __launch_bounds__(kThreadsTc, 1) prefill_attn_tc_kernel(const __
     if (nb > 0 && ok) ok = mbar_wait(o_done, 0);
     if (nb > 0 && !ok) atomicOr(&failed, 1u);
     fence_after();
-    xl[half][r] = l;
+    xl[part][r] = l;
     pair_sync();
-    l += xl[half ^ 1][r];
+    l = 0.f;
+#pragma unroll
+    for (int q = 0; q < kParts; ++q) l += xl[q][r];          // the same order in every thread of the row
     {
       // the TMEM loads are warp-wide: every lane takes part, only the stores are per row
       __nv_bfloat16* dst = a.out_bf16 + static_cast<size_t>(row0 + (row_ok ? r : 0)) * a.ld_out + head * kDH;
       const bool have = nb > 0 && ok;
       const float inv = (have && l > 0.f) ? 1.0f / l : 0.f;
 #pragma unroll 1
-      for (int c0 = half * (kDH / 2); c0 < (half + 1) * (kDH / 2); c0 += 32) {
+      for (int c0 = part * kPartCols; c0 < (part + 1) * kPartCols; c0 += 32) {
         uint32_t o[32];
         if (have) {
           tm_ld32(tmem + lane_addr + kColO + c0, o);
