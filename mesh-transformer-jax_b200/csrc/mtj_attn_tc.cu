@@ -41,13 +41,13 @@ constexpr int kDH = 256;
 // threads sharing a query row (each 64 / kParts key columns and 256 / kParts output columns): 2 and 4 measure the
 // same (1.88 / 1.87 ms of attention per GPT-J-6B prefill); 1 was 25 % slower
 constexpr int kParts = 2;
-constexpr int kSoftWarps = 4 * kParts;          // softmax warps: TMEM lane quadrant = warp % 4, part = (warp - 2) / 4
-constexpr int kThreadsTc = 64 + 32 * kSoftWarps;   // TMA warp, MMA warp, softmax warps
+constexpr int kSoftWarps = 4 * kParts;          // softmax warps: TMEM lane quadrant = warp % 4, part = (warp - 3) / 4
+constexpr int kThreadsTc = 96 + 32 * kSoftWarps;   // TMA warp, two MMA warps (S; P.V), softmax warps
 constexpr int kPartKeys = kKB / kParts, kPartCols = kDH / kParts;
 constexpr uint32_t kQBytes = kQT * kDH * 2;          // 64 KB
 constexpr uint32_t kKBytes = kKB * kDH * 2;          // 32 KB
-constexpr uint32_t kStage = 2 * kKBytes;             // K + V of one key block
-constexpr uint32_t kSmemTc = kQBytes + 2 * kStage + 1024;
+constexpr int kKSlots = 3, kVSlots = 2;              // ring depths: a K slot is wanted again one key block sooner than a V slot
+constexpr uint32_t kSmemTc = kQBytes + (kKSlots + kVSlots) * kKBytes;   // 224 KB: the dynamic buffer is 1024-byte aligned
 // tensor memory: S0 | S1 (64 fp32 columns each) | O (256) | P0 | P1 (64 bf16 keys = 32 columns each)
 constexpr uint32_t kColS = 0, kColO = 128, kColP = 384, kPCols = kKB / 2, kTmemCols = 512;
 
@@ -149,25 +149,30 @@ __global__ void __launch_bounds__(kThreadsTc, 1) prefill_attn_tc_kernel(const __
                                                                      const __grid_constant__ CUtensorMap map_k,
                                                                      const __grid_constant__ CUtensorMap map_v,
                                                                      const PrefillAttnTcArgs a) {
-  extern __shared__ unsigned char att_smem_raw[];
-  const uint32_t base = (smem_u32(att_smem_raw) + 1023u) & ~1023u;
-  const uint32_t sQ = base, sKV = base + kQBytes;
-  __shared__ __align__(8) uint64_t bars[16];
+  extern __shared__ __align__(1024) unsigned char att_smem_raw[];
+  const uint32_t base = smem_u32(att_smem_raw);       // swizzled tiles need 1024-byte alignment
+  const uint32_t sQ = base, sK = base + kQBytes, sV = sK + kKSlots * kKBytes;
+  __shared__ __align__(8) uint64_t bars[20];
   __shared__ uint32_t tmem_slot;
   __shared__ uint32_t failed;
-  __shared__ float xmax[2][kParts][kQT];   // [iteration parity][part][row]: the row maxima of the threads sharing a row
-  __shared__ float xl[kParts][kQT];        // [part][row]: their softmax denominators
+  __shared__ float xmax[kParts][kQT];      // [part][row]: row maxima, at the end denominators, of the threads sharing a row
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t bar0 = smem_u32(bars);
-  const uint32_t q_full = bar0, k_full0 = bar0 + 8, k_empty0 = bar0 + 24, v_full0 = bar0 + 40,
-                 v_empty0 = bar0 + 56, s_full0 = bar0 + 72, p_full0 = bar0 + 88, p_empty0 = bar0 + 104,
-                 o_done = bar0 + 120;
+  const uint32_t q_full = bar0, k_full0 = bar0 + 8, k_empty0 = bar0 + 32, v_full0 = bar0 + 56,
+                 v_empty0 = bar0 + 72, s_full0 = bar0 + 88, p_full0 = bar0 + 104, p_empty0 = bar0 + 120,
+                 o_done = bar0 + 136, s_read0 = bar0 + 144;
 
+  if (base & 1023u) {                                  // cannot happen with the declared alignment; checked, not assumed
+    if (threadIdx.x == 0 && a.dev_err) atomicOr(a.dev_err, kDevErrTimeout);
+    return;
+  }
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 16; ++i) mbar_init(bar0 + 8u * i, 1);
+    for (int i = 0; i < 20; ++i) mbar_init(bar0 + 8u * i, 1);
     mbar_init(p_full0, 32 * kSoftWarps);
     mbar_init(p_full0 + 8, 32 * kSoftWarps);
+    mbar_init(s_read0, 32 * kSoftWarps);
+    mbar_init(s_read0 + 8, 32 * kSoftWarps);
     mbar_fence_init();
     failed = 0;
   }
@@ -204,10 +209,10 @@ __global__ void __launch_bounds__(kThreadsTc, 1) prefill_attn_tc_kernel(const __
       const int32_t* table = a.kv.page_table + static_cast<size_t>(b) * a.kv.ring_pages;
       auto slab_row = [&](int j) { return (table[(first_blk + j) % a.kv.ring_pages] * a.heads + head) * kKB; };
       auto load_k = [&](int j) {
-        const int st = j & 1;
-        if (j >= 2 && !mbar_wait(k_empty0 + 8 * st, ((j >> 1) - 1) & 1)) return false;
+        const int st = j % kKSlots;
+        if (j >= kKSlots && !mbar_wait(k_empty0 + 8 * st, ((j / kKSlots) - 1) & 1)) return false;
         const int row = slab_row(j);
-        const uint32_t dk = sKV + st * kStage;
+        const uint32_t dk = sK + st * kKBytes;
         mbar_expect_tx(k_full0 + 8 * st, kKBytes);
 #pragma unroll
         for (int kb = 0; kb < 4; ++kb) tma2d(dk + kb * (kKB * 128), &map_k, kb * 64, row, k_full0 + 8 * st);
@@ -217,7 +222,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) prefill_attn_tc_kernel(const __
         const int st = j & 1;
         if (j >= 2 && !mbar_wait(v_empty0 + 8 * st, ((j >> 1) - 1) & 1)) return false;
         const int row = slab_row(j);
-        const uint32_t dv = sKV + st * kStage + kKBytes;
+        const uint32_t dv = sV + st * kKBytes;
         mbar_expect_tx(v_full0 + 8 * st, kKBytes);
 #pragma unroll
         for (int kb = 0; kb < 4; ++kb) tma2d(dv + kb * (kKB * 128), &map_v, kb * 64, row, v_full0 + 8 * st);
@@ -225,71 +230,73 @@ __global__ void __launch_bounds__(kThreadsTc, 1) prefill_attn_tc_kernel(const __
       };
       // the waits follow the tensor core's order: S0 S1 | PV0 S2 | PV1 S3 | ...
       bool okp = load_k(0);
-      if (okp && nb > 1) okp = load_k(1);
+      for (int j = 1; okp && j < kKSlots && j < nb; ++j) okp = load_k(j);
       for (int j = 0; okp && j < nb; ++j) {
         okp = load_v(j);
-        if (okp && j + 2 < nb) okp = load_k(j + 2);
+        if (okp && j + kKSlots < nb) okp = load_k(j + kKSlots);   // its slot is free once S_j is done
       }
       if (!okp) atomicOr(&failed, 1u);
     }
   } else if (warp == 1) {
+    // S = Q . K^T, issued two key blocks ahead.  The products of a block are issued by two warps (this one and the
+    // next): a single thread building descriptors and issuing all 20 MMAs of a block was the longest chain of
+    // the kernel.
     if (lane == 0 && nb > 0) {
-      // instruction descriptors: fp32 accumulate, bf16 operands
       constexpr uint32_t kIdS = (1u << 4) | (1u << 7) | (1u << 10) | ((kKB >> 3) << 17) | ((kQT >> 4) << 24);
-      constexpr uint32_t kIdO = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((kDH >> 3) << 17) | ((kQT >> 4) << 24);
+      uint64_t qd[4];
+#pragma unroll
+      for (int kb = 0; kb < 4; ++kb) qd[kb] = sdesc(sQ + kb * (kQT * 128), 16, 1024);
       auto issue_s = [&](int j) {
-        const uint32_t dk = sKV + (j & 1) * kStage;
+        const uint32_t dk = sK + (j % kKSlots) * kKBytes;
         const uint32_t ds = tmem + kColS + (j & 1) * kKB;
+        const uint64_t kd = sdesc(dk, 16, 1024);
 #pragma unroll
         for (int kb = 0; kb < 4; ++kb) {
-          const uint64_t ad = sdesc(sQ + kb * (kQT * 128), 16, 1024), bd = sdesc(dk + kb * (kKB * 128), 16, 1024);
+          const uint64_t bd = kd + static_cast<uint64_t>((kb * (kKB * 128)) >> 4);
 #pragma unroll
-          for (int k4 = 0; k4 < 4; ++k4) mma_bf16(ds, ad + 2 * k4, bd + 2 * k4, kIdS, (kb | k4) ? 1u : 0u);
+          for (int k4 = 0; k4 < 4; ++k4) mma_bf16(ds, qd[kb] + 2 * k4, bd + 2 * k4, kIdS, (kb | k4) ? 1u : 0u);
         }
         commit(s_full0 + 8 * (j & 1));
-        commit(k_empty0 + 8 * (j & 1));                        // the K slot is free once S_j is done
+        commit(k_empty0 + 8 * (j % kKSlots));                  // the K slot is free once S_j is done
       };
-      bool ok = mbar_wait(q_full, 0) && mbar_wait(k_full0, 0);
-      if (ok) {
-        fence_after();
-        issue_s(0);
-      }
-      if (ok && nb > 1) {
-        ok = mbar_wait(k_full0 + 8, 0);
-        if (ok) {
-          fence_after();
-          issue_s(1);
-        }
-      }
+      bool ok = mbar_wait(q_full, 0);
       for (int j = 0; ok && j < nb; ++j) {
-        // P_j written (and with it S_j consumed), V_j landed
+        // S_j goes into the buffer of S_{j-2} as soon as the softmax warps have READ S_{j-2} into registers: it
+        // does not wait for P_{j-2}, so the scores are ready before the softmax warps ask for them
+        if (j >= 2) ok = mbar_wait(s_read0 + 8 * (j & 1), ((j - 2) >> 1) & 1);
+        if (ok) ok = mbar_wait(k_full0 + 8 * (j % kKSlots), (j / kKSlots) & 1);
+        if (!ok) break;
+        fence_after();
+        issue_s(j);
+      }
+      if (!ok) atomicOr(&failed, 1u);
+    }
+  } else if (warp == 2) {
+    // O += P . V
+    if (lane == 0 && nb > 0) {
+      constexpr uint32_t kIdO = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((kDH >> 3) << 17) | ((kQT >> 4) << 24);
+      bool ok = true;
+      for (int j = 0; ok && j < nb; ++j) {
+        // P_j written, V_j landed
         ok = mbar_wait(p_full0 + 8 * (j & 1), (j >> 1) & 1) && mbar_wait(v_full0 + 8 * (j & 1), (j >> 1) & 1);
         if (!ok) break;
         fence_after();
-        // O += P . V : P from tensor memory (16 keys = 8 columns per MMA), V tile is [64 keys][256 dh] ->
-        // MN-major B operand, 64-column blocks 8 KB apart
-        const uint32_t dv = sKV + (j & 1) * kStage + kKBytes;
+        // P from tensor memory (16 keys = 8 columns per MMA), V tile is [64 keys][256 dh] -> MN-major B operand,
+        // 64-column blocks 8 KB apart
+        const uint64_t vd = sdesc(sV + (j & 1) * kKBytes, kKB * 128, 1024);
         const uint32_t pa = tmem + kColP + (j & 1) * kPCols;
 #pragma unroll
-        for (int k4 = 0; k4 < 4; ++k4) {
-          const uint64_t bd = sdesc(dv + k4 * 2048, kKB * 128, 1024);
-          mma_bf16_ts(tmem + kColO, pa + 8 * k4, bd, kIdO, (j | k4) ? 1u : 0u);
-        }
+        for (int k4 = 0; k4 < 4; ++k4)
+          mma_bf16_ts(tmem + kColO, pa + 8 * k4, vd + static_cast<uint64_t>((k4 * 2048) >> 4), kIdO, (j | k4) ? 1u : 0u);
         commit(v_empty0 + 8 * (j & 1));
         commit(p_empty0 + 8 * (j & 1));                          // P buffer j & 1 is free, O holds key blocks 0 .. j
         if (j == nb - 1) commit(o_done);
-        if (j + 2 < nb) {
-          ok = mbar_wait(k_full0 + 8 * (j & 1), ((j + 2) >> 1) & 1);
-          if (!ok) break;
-          fence_after();
-          issue_s(j + 2);                                      // into the S buffer that P_j was made from
-        }
       }
       if (!ok) atomicOr(&failed, 1u);
     }
   } else {
     const int quad = warp & 3;                                 // the TMEM lane quadrant this warp may access
-    const int part = (warp - 2) >> 2;                          // key columns [kPartKeys part, +kPartKeys) / O columns [kPartCols part, +kPartCols)
+    const int part = (warp - 3) >> 2;                          // key columns [kPartKeys part, +kPartKeys) / O columns [kPartCols part, +kPartCols)
     const int r = quad * 32 + lane;                            // query row within the tile = TMEM lane
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     const uint32_t pair_bar = 1u + static_cast<uint32_t>(quad);   // named barrier of the warps sharing these rows
@@ -311,6 +318,8 @@ __global__ void __launch_bounds__(kThreadsTc, 1) prefill_attn_tc_kernel(const __
       if (ok) {
         if (kPartKeys == 32) tm_ld32(s_addr, sr);
         else tm_ld16(s_addr, sr);
+        fence_before();
+        mbar_arrive(s_read0 + 8 * (g & 1));                    // the scores are in registers: the buffer may be refilled
       } else {
 #pragma unroll
         for (int c = 0; c < kPartKeys; ++c) sr[c] = 0xff800000u;      // -inf
@@ -338,10 +347,11 @@ __global__ void __launch_bounds__(kThreadsTc, 1) prefill_attn_tc_kernel(const __
         }
       }
       // the row's maximum over all 64 keys: the partner threads hold the other parts
-      xmax[j & 1][part][r] = mx;
+      xmax[part][r] = mx;
       pair_sync();
 #pragma unroll
-      for (int q = 1; q < kParts; ++q) mx = fmaxf(mx, xmax[j & 1][(part + q) % kParts][r]);
+      for (int q = 1; q < kParts; ++q) mx = fmaxf(mx, xmax[(part + q) % kParts][r]);
+      pair_sync();                                             // all have read: the next block may overwrite
       float m_new = m_ref;
       if (mx > m_ref + 8.0f || (m_ref == -INFINITY && mx > -INFINITY)) m_new = mx;
       const float corr = (m_new == m_ref || m_ref == -INFINITY) ? 1.0f : exp2f(m_ref - m_new);
@@ -390,11 +400,11 @@ __global__ void __launch_bounds__(kThreadsTc, 1) prefill_attn_tc_kernel(const __
     if (nb > 0 && ok) ok = mbar_wait(o_done, 0);
     if (nb > 0 && !ok) atomicOr(&failed, 1u);
     fence_after();
-    xl[part][r] = l;
+    xmax[part][r] = l;
     pair_sync();
     l = 0.f;
 #pragma unroll
-    for (int q = 0; q < kParts; ++q) l += xl[q][r];          // the same order in every thread of the row
+    for (int q = 0; q < kParts; ++q) l += xmax[q][r];        // the same order in every thread of the row
     {
       // the TMEM loads are warp-wide: every lane takes part, only the stores are per row
       __nv_bfloat16* dst = a.out_bf16 + static_cast<size_t>(row0 + (row_ok ? r : 0)) * a.ld_out + head * kDH;
