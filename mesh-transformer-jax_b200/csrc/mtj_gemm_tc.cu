@@ -769,7 +769,8 @@ __global__ void __launch_bounds__(kPThreads, 1) gemm_tc_persist_kernel(const __g
           // shared memory (XOR-swizzled, conflict-free both ways): afterwards lane = token row, and the 32 logits
           // of the group are walked in registers -- max, then sum of exp(l - max), and the target's logit if its
           // id falls into the group (layers.py:575-585 per group; ce_combine_kernel merges the groups).
-          if (valid > 0) {
+          // (a pair's second block may hold a tile that lies entirely beyond the last weight row: no groups there)
+          if (valid > 0 && n0 < a.N) {
             float* tsm = reinterpret_cast<float*>(tc_smem_raw + (smem_base - smem_u32(tc_smem_raw)) +
                                                   kStages * kStageBytes) + (warp - 2) * 1024;
 #pragma unroll

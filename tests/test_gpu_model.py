@@ -332,14 +332,16 @@ def test_whole_step_kernel_with_several_sequences(cuda_device, monkeypatch, batc
 
 
 @pytest.mark.gpu
-def test_fused_cross_entropy_epilogue_equals_the_materialised_logits_path(cuda_device, monkeypatch):
+@pytest.mark.parametrize("n_vocab", [1000, 840])
+def test_fused_cross_entropy_epilogue_equals_the_materialised_logits_path(cuda_device, monkeypatch, n_vocab):
     """eval over more than 192 rows takes the persistent GEMM whose epilogue reduces the logits to per-group
     (max, sum of exp) pairs without storing them; MTJ_NO_FUSED_CE=1 materialises the logits slice and runs
     ce_partial.  Both must give the same per-token loss and `correct` (layers.py:569-593), with a key mask and
-    a vocabulary whose last 128-row tile is partly empty."""
-    cfg = dict(spec.tiny_config(1, seq=160), n_vocab=1000)
+    a vocabulary whose last 128-row tile is partly empty (1000) or whose last 256-row tile of a block pair has
+    its second half entirely beyond the vocabulary (840 = 3 x 256 + 72)."""
+    cfg = dict(spec.tiny_config(1, seq=160), n_vocab=n_vocab)
     params = spec.make_params(cfg, seed=61, stress=True)
-    ids = spec.token_ids(62, 3, 161, 1000)
+    ids = spec.token_ids(62, 3, 161, n_vocab)
     sample = {"obs": ids[:, :-1], "target": ids[:, 1:], "ctx_length": np.array([160, 33, 160])}
     net = _net(cfg, params, cuda_device)
     fused = net.eval(sample)
