@@ -52,7 +52,9 @@ def test_decode_attention_matches_reference(cuda_device, d_head, heads, batch, w
                                    # few weight tiles and at most 64 token rows: K is split over a cluster of 2 or 4 blocks
                                    (16, 2048, 512), (50, 640, 2048), (8, 18000, 4096), (33, 200, 6144),
                                    # the GPT-J-6B in-projection slice of one of 8 / one of 2 shards at 32 sequences
-                                   (32, 3584, 4096), (32, 14336, 4096)])
+                                   (32, 3584, 4096), (32, 14336, 4096),
+                                   # block pairs on 256-row tiles: the last pair's second block lies entirely beyond N
+                                   (300, 840, 128), (1000, 1288, 256)])
 def test_tensor_core_gemm_matches_fp32_matmul(cuda_device, M, N, K):
     """tcgen05 GEMM against a plain fp32 matmul of the same bf16 values."""
     import torch
