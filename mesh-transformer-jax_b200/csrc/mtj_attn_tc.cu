@@ -308,7 +308,6 @@ __global__ void __launch_bounds__(kThreadsTc, 1) prefill_attn_tc_kernel(const __
     const bool row_ok = r < q_rows;
     const int qpos = pos0 + tile * kQT + r;
     float m_ref = -INFINITY, l = 0.f;
-    const bool warp_rows_ok = quad * 32 + 31 < q_rows;
     const int warp_qpos0 = pos0 + tile * kQT + quad * 32;       // smallest query position of this warp
     bool ok = nb > 0;
     for (int j = 0; j < nb; ++j) {
@@ -328,8 +327,10 @@ __global__ void __launch_bounds__(kThreadsTc, 1) prefill_attn_tc_kernel(const __
         for (int c = 0; c < kPartKeys; ++c) sr[c] = 0xff800000u;      // -inf
       }
       const int kbase = (first_blk + j) * kKB + part * kPartKeys;
-      // every row of this warp sees all of its keys: no mask arithmetic
-      const bool full_blk = ok && warp_rows_ok && kbase >= pad && kbase + kPartKeys - 1 <= min(warp_qpos0, limit);
+      // every row of this warp sees all of its keys: no mask arithmetic.  Rows past the end of a partial query tile
+      // do not exist and are never stored, so they do not force the masked path (with 2047 rows they would, in
+      // one warp pair of the LONGEST tile, which paces the whole kernel: the masked pass costs 800 cycles a block).
+      const bool full_blk = ok && kbase >= pad && kbase + kPartKeys - 1 <= min(warp_qpos0, limit);
       float mx = -INFINITY;
       if (full_blk) {
         float mxa = -INFINITY, mxb = -INFINITY;               // two chains

@@ -106,6 +106,18 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 // Bounded wait: returns false (instead of spinning forever) if the phase does
 // not complete; the caller records kDevErrTimeout and carries on.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  {
+    // a phase that is already complete is seen without the (possibly suspending) try_wait
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
   for (int i = 0; i < (1 << 18); ++i) {
     uint32_t ok;
     asm volatile(
