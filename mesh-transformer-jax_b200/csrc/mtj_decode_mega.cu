@@ -530,7 +530,17 @@ __global__ void __launch_bounds__(kMT, (BT == 1 && kMT == 256) ? 2 : 1) decode_m
     phase_arrive(c_qkv + l);
     // FF-in rows: continue the round-robin where the Q/K/V units stopped, so the load stays even
     const int ff_first = nq + ((gw - nq % GW) + GW) % GW;
-    warp_stream<BT, true>(lw.w_in, d, nch, ff_first, GW, n1, xn, nullptr, 0, lane, in_epi);
+    // The units of the last, partial round do not go to the first warps of the grid but to the last ones: with more
+    // warps than out-projection row pairs those belong to blocks that have no out-projection rows, so being late
+    // here delays nothing, whereas a block that is late into attention is late out of the out-projection, and the
+    // next layer waits for it.
+    const int n_full = (n1 / GW) * GW;
+    const bool tail_swap = n_full >= nq && (d >> 1) <= GW - (n1 - n_full);
+    warp_stream<BT, true>(lw.w_in, d, nch, ff_first, GW, tail_swap ? n_full : n1, xn, nullptr, 0, lane, in_epi);
+    if (tail_swap && gw >= GW - (n1 - n_full)) {
+      const int u = n_full + (GW - 1 - gw);
+      warp_stream<BT, true>(lw.w_in, d, nch, u, GW, u + 1, xn, nullptr, 0, lane, in_epi);
+    }
     phase_arrive(c_ff + l);
 
     // ---- attention: one unit = (sequence, head, contiguous range of up to a.split_tokens keys) ------
@@ -545,6 +555,51 @@ __global__ void __launch_bounds__(kMT, (BT == 1 && kMT == 256) ? 2 : 1) decode_m
       constexpr float scale = DH == 256 ? 0.0625f : 0.125f;
       const int splits = a.grid_splits;
       const int units = B * a.heads * splits;
+      // The merge of a (sequence, head)'s splits takes 4-5 us.  Left to whichever block finishes a head last, it
+      // makes that block late into the out-projection, late out of it, and the next layer waits for it.  With more
+      // blocks than the out-projection has rows for, the merges go to blocks that have no out-projection rows:
+      // block first_idle + (sequence, head) waits (bounded) for that head's splits and merges them.
+      const int first_idle = ((d >> 1) + kMW - 1) / kMW;
+      const bool dedicated = G - first_idle >= B * a.heads;
+      auto merge_head = [&](int b, int head, int nsplit) {   // all threads of the block
+        const size_t pbase = (static_cast<size_t>(b) * a.heads + head) * a.max_splits;
+        __threadfence();
+        if (warp == 0) {
+          float ms[2], ls[2];
+#pragma unroll
+          for (int h2 = 0; h2 < 2; ++h2) {
+            const int sidx = lane + 32 * h2;
+            ms[h2] = sidx < nsplit ? __ldcg(a.part_ml + (pbase + sidx) * 2) : -INFINITY;
+            ls[h2] = sidx < nsplit ? __ldcg(a.part_ml + (pbase + sidx) * 2 + 1) : 0.f;
+          }
+          const float M = warp_max(fmaxf(ms[0], ms[1]));
+          float lt = 0.f;
+#pragma unroll
+          for (int h2 = 0; h2 < 2; ++h2) {
+            const float f = ms[h2] == -INFINITY ? 0.f : __expf(ms[h2] - M);
+            wgt[lane + 32 * h2] = f;
+            lt = fmaf(ls[h2], f, lt);
+          }
+          lt = warp_sum(lt);
+          if (lane == 0) inv_l = 1.0f / lt;
+        }
+        __syncthreads();
+        if (threadIdx.x < DH) {
+          const float* po = a.part_o + pbase * DH + threadIdx.x;
+          float O = 0.f;
+          int sidx = 0;
+          for (; sidx + 8 <= nsplit; sidx += 8) {
+            float v[8];
+#pragma unroll
+            for (int t = 0; t < 8; ++t) v[t] = __ldcg(po + static_cast<size_t>(sidx + t) * DH);
+#pragma unroll
+            for (int t = 0; t < 8; ++t) O = fmaf(v[t], wgt[sidx + t], O);
+          }
+          for (; sidx < nsplit; ++sidx) O = fmaf(__ldcg(po + static_cast<size_t>(sidx) * DH), wgt[sidx], O);
+          a.act2[static_cast<size_t>(b) * (dl + ffl) + head * DH + threadIdx.x] = O * inv_l;
+        }
+        if (threadIdx.x == 0) a.head_counters[b * a.heads + head] = 0u;
+      };
       for (int unit = blockIdx.x; unit < units; unit += G) {
         const int split = unit % splits, head = (unit / splits) % a.heads, b = unit / (splits * a.heads);
         const int start = max(a.pad[b], cur - a.window + 1);
@@ -646,48 +701,30 @@ __global__ void __launch_bounds__(kMT, (BT == 1 && kMT == 256) ? 2 : 1) decode_m
         __syncthreads();
         if (threadIdx.x == 0) {
           const uint32_t ticket = atomicAdd(a.head_counters + b * a.heads + head, 1u);
-          is_last = (ticket == static_cast<uint32_t>(nsplit - 1));
+          is_last = !dedicated && (ticket == static_cast<uint32_t>(nsplit - 1));
         }
         __syncthreads();
-        if (is_last) {                                  // uniform: merge the splits of this (sequence, head)
-          __threadfence();
-          if (warp == 0) {
-            float ms[2], ls[2];
-#pragma unroll
-            for (int h2 = 0; h2 < 2; ++h2) {
-              const int sidx = lane + 32 * h2;
-              ms[h2] = sidx < nsplit ? __ldcg(a.part_ml + (pbase + sidx) * 2) : -INFINITY;
-              ls[h2] = sidx < nsplit ? __ldcg(a.part_ml + (pbase + sidx) * 2 + 1) : 0.f;
-            }
-            const float M = warp_max(fmaxf(ms[0], ms[1]));
-            float lt = 0.f;
-#pragma unroll
-            for (int h2 = 0; h2 < 2; ++h2) {
-              const float f = ms[h2] == -INFINITY ? 0.f : __expf(ms[h2] - M);
-              wgt[lane + 32 * h2] = f;
-              lt = fmaf(ls[h2], f, lt);
-            }
-            lt = warp_sum(lt);
-            if (lane == 0) inv_l = 1.0f / lt;
-          }
-          __syncthreads();
-          if (threadIdx.x < DH) {
-            const float* po = a.part_o + pbase * DH + threadIdx.x;
-            float O = 0.f;
-            int sidx = 0;
-            for (; sidx + 8 <= nsplit; sidx += 8) {
-              float v[8];
-#pragma unroll
-              for (int t = 0; t < 8; ++t) v[t] = __ldcg(po + static_cast<size_t>(sidx + t) * DH);
-#pragma unroll
-              for (int t = 0; t < 8; ++t) O = fmaf(v[t], wgt[sidx + t], O);
-            }
-            for (; sidx < nsplit; ++sidx) O = fmaf(__ldcg(po + static_cast<size_t>(sidx) * DH), wgt[sidx], O);
-            a.act2[static_cast<size_t>(b) * (dl + ffl) + head * DH + threadIdx.x] = O * inv_l;
-          }
-          if (threadIdx.x == 0) a.head_counters[b * a.heads + head] = 0u;
-        }
+        if (is_last) merge_head(b, head, nsplit);       // uniform
         __syncthreads();                                // shared buffers are free for the next unit
+      }
+      if (dedicated && static_cast<int>(blockIdx.x) >= first_idle &&
+          static_cast<int>(blockIdx.x) - first_idle < B * a.heads) {
+        const int hb = static_cast<int>(blockIdx.x) - first_idle;
+        const int b = hb / a.heads, head = hb % a.heads;
+        const int start = max(a.pad[b], cur - a.window + 1);
+        const int nsplit = (cur + 1 - start + a.split_tokens - 1) / a.split_tokens;
+        if (threadIdx.x == 0) {
+          int spins = 0;
+          while (ld_acquire_gpu(a.head_counters + hb) < static_cast<uint32_t>(nsplit)) {
+            if (++spins > a.wait_limit) {
+              if (a.dev_err) atomicOr(a.dev_err, kDevErrTimeout);
+              break;
+            }
+          }
+        }
+        __syncthreads();
+        merge_head(b, head, nsplit);
+        __syncthreads();
       }
     }
     // prefetch this block's first out-projection rows, then wait for attention + FF-in everywhere
