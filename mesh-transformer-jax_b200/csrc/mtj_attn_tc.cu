@@ -341,14 +341,21 @@ __global__ void __launch_bounds__(kThreadsTc, 1) prefill_attn_tc_kernel(const __
         }
         mx = fmaxf(mxa, mxb) * c2;
       } else {
+        // the visible columns of this row are one range [lo_c, hi_c] of the block (empty for a row that does not
+        // exist): two compares against constants per score instead of the full predicate
+        const int lo_c = pad - kbase;
+        const int hi_c = (ok && row_ok) ? min(qpos, limit) - kbase : -1;
+        float mxa = -INFINITY, mxb = -INFINITY;
 #pragma unroll
-        for (int c = 0; c < kPartKeys; ++c) {
-          const int key = kbase + c;
-          const bool vis = ok && row_ok && key >= pad && key <= qpos && key <= limit;
-          const float v = vis ? __uint_as_float(sr[c]) : -INFINITY;
-          sr[c] = __float_as_uint(v);
-          mx = fmaxf(mx, v * c2);
+        for (int c = 0; c < kPartKeys; c += 2) {
+          const float v0 = (c >= lo_c && c <= hi_c) ? __uint_as_float(sr[c]) : -INFINITY;
+          const float v1 = (c + 1 >= lo_c && c + 1 <= hi_c) ? __uint_as_float(sr[c + 1]) : -INFINITY;
+          sr[c] = __float_as_uint(v0);
+          sr[c + 1] = __float_as_uint(v1);
+          mxa = fmaxf(mxa, v0);
+          mxb = fmaxf(mxb, v1);
         }
+        mx = fmaxf(mxa, mxb) * c2;                             // c2 > 0; (-inf) * c2 stays -inf
       }
       // the row's maximum over all 64 keys: the partner threads hold the other parts
       xmax[part][r] = mx;
