@@ -412,6 +412,72 @@ __device__ __forceinline__ void warp_stream(const __nv_bfloat16* __restrict__ W,
   }
 }
 
+#if MTJ_MEGA_MT == 256
+// The same pipeline for units of ONE row of W (2 * NC chunks of the row per stage): rows r = r_first, r_first +
+// r_step, ... (< r_end); epi(r, acc) gets the BT sums of the row in every lane.  Used for the FF-in rows of
+// tensor-parallel slices, where whole row pairs leave the warps too unevenly loaded.
+template <int BT, typename Epi>
+__device__ __forceinline__ void warp_stream1(const __nv_bfloat16* __restrict__ W, int K, int nch, int r_first,
+                                             int r_step, int r_end, const float4* xn, int lane, Epi epi) {
+  constexpr int NC = 2 * MTJ_MEGA_NC;
+  if (r_first >= r_end) return;
+  const int spu = (nch + NC - 1) / NC;       // stages per row
+  const uint4 z4 = make_uint4(0u, 0u, 0u, 0u);
+  auto load = [&](uint4 (&buf)[NC], int r, int st) {
+    const __nv_bfloat16* wl = W + static_cast<size_t>(r) * K + lane * 8;
+#pragma unroll
+    for (int i = 0; i < NC; ++i) {
+      const int cc = st * NC + i;
+      const bool ok = cc < nch && cc * 256 + lane * 8 < K;
+      buf[i] = ok ? ld_stream16(wl + static_cast<size_t>(cc) * 256) : z4;
+    }
+  };
+  float acc[BT];
+#pragma unroll
+  for (int bt = 0; bt < BT; ++bt) acc[bt] = 0.f;
+  uint4 nxt[NC];
+  int r = r_first, st = 0;
+  load(nxt, r, st);
+  while (r < r_end) {
+    uint4 cur[NC];
+#pragma unroll
+    for (int i = 0; i < NC; ++i) cur[i] = nxt[i];
+    int rn = r, sn = st + 1;
+    if (sn == spu) {
+      sn = 0;
+      rn = r + r_step;
+    }
+    if (rn < r_end) load(nxt, rn, sn);
+#pragma unroll
+    for (int i = 0; i < NC; ++i) {
+      const int cc = st * NC + i;
+      if (cc >= nch) break;
+      const bool in_k = cc * 256 + lane * 8 < K;
+      float w0[8];
+      unpack8(cur[i], w0);
+#pragma unroll
+      for (int bt = 0; bt < BT; ++bt) {
+        const float4* lo = xn + static_cast<size_t>(bt) * 2 * (K >> 3);
+        const float4 xa = in_k ? lo[cc * 32 + lane] : make_float4(0.f, 0.f, 0.f, 0.f);
+        const float4 xb = in_k ? lo[(K >> 3) + cc * 32 + lane] : make_float4(0.f, 0.f, 0.f, 0.f);
+        const float xv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[bt] = fmaf(w0[e], xv[e], acc[bt]);
+      }
+    }
+    if (st == spu - 1) {
+#pragma unroll
+      for (int bt = 0; bt < BT; ++bt) acc[bt] = warp_sum(acc[bt]);
+      epi(r, acc);
+#pragma unroll
+      for (int bt = 0; bt < BT; ++bt) acc[bt] = 0.f;
+    }
+    r = rn;
+    st = sn;
+  }
+}
+#endif
+
 template <int BT, int DH>
 __global__ void __launch_bounds__(kMT, (BT == 1 && kMT == 256) ? 2 : 1) decode_mega_kernel(const MegaArgs a) {
   extern __shared__ __align__(128) unsigned char mega_smem[];
@@ -528,6 +594,28 @@ __global__ void __launch_bounds__(kMT, (BT == 1 && kMT == 256) ? 2 : 1) decode_m
     // Q/K/V rows first; once this block's share is behind it the attention phase may count on it
     warp_stream<BT, true>(lw.w_in, d, nch, gw, GW, nq, xn, nullptr, 0, lane, in_epi);
     phase_arrive(c_qkv + l);
+#if MTJ_MEGA_MT == 256
+    if (a.ff_row_units) {
+      // Tensor-parallel slices have too few row pairs per warp for pairs to spread evenly (a quarter of GPT-J-6B:
+      // 3584 pairs on 2368 warps, i.e. two pairs for half of the warps and one for the rest).  The warps that are a
+      // Q/K/V pair short take one FF pair first; the remaining FF rows then go round ONE row at a time.
+      const int q_rem = nq % GW, ffu = ffl >> 1;
+      const int lvl = q_rem > 0 ? min(ffu, GW - q_rem) : 0;
+      if (q_rem > 0 && gw >= q_rem && gw - q_rem < lvl) {
+        const int u = nq + (gw - q_rem);
+        warp_stream<BT, true>(lw.w_in, d, nch, u, GW, u + 1, xn, nullptr, 0, lane, in_epi);
+      }
+      warp_stream1<BT>(lw.w_in + static_cast<size_t>(3 * dl) * d, d, nch, 2 * lvl + gw, GW, ffl, xn, lane,
+                       [&](int f, const float (&acc)[BT]) {
+                         float val = 0.f;
+#pragma unroll
+                         for (int bt = 0; bt < BT; ++bt)
+                           if (lane == bt) val = acc[bt];
+                         if (lane < BT && lane < B)
+                           a.act2[static_cast<size_t>(lane) * (dl + ffl) + dl + f] = gelu_tanh(val + lw.b_ff[f]);
+                       });
+    } else {
+#endif
     // FF-in rows: continue the round-robin where the Q/K/V units stopped, so the load stays even
     const int ff_first = nq + ((gw - nq % GW) + GW) % GW;
     // The units of the last, partial round do not go to the first warps of the grid but to the last ones: with more
@@ -541,6 +629,9 @@ __global__ void __launch_bounds__(kMT, (BT == 1 && kMT == 256) ? 2 : 1) decode_m
       const int u = n_full + (GW - 1 - gw);
       warp_stream<BT, true>(lw.w_in, d, nch, u, GW, u + 1, xn, nullptr, 0, lane, in_epi);
     }
+#if MTJ_MEGA_MT == 256
+    }
+#endif
     phase_arrive(c_ff + l);
 
     // ---- attention: one unit = (sequence, head, contiguous range of up to a.split_tokens keys) ------

@@ -164,6 +164,7 @@ struct MegaArgs {
   float* logits;               // [B, V]
   // greedy token inside the kernel (one GPU): per-row running maximum (zero between launches), the token buffer
   // the last block writes (may be the buffer `tokens` points to) and the position counter it advances; or null
+  int ff_row_units;            // 256-thread build: FF-in rows one at a time behind a levelling pair (tensor-parallel slices)
   unsigned long long* amax;    // [4]
   uint32_t* tokens_out;        // [B]
   int32_t* cur_out;

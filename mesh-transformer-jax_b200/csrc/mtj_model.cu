@@ -1527,6 +1527,8 @@ int32_t mtj_decode_step(mtj_handle* h, const uint32_t* tokens_in, const float* t
       ma.head_counters = h->counters; ma.logits = h->logits; ma.sync = h->mega_sync; ma.dev_err = h->dev_err;
       ma.trace = h->mega_trace_on ? h->mega_trace : nullptr;
       ma.wait_limit = h->wait_limit;
+      // FF-in rows one at a time from 4 shards on (measured: +4.3 % at 4, -1 % at 2; MTJ_*_ROW_UNITS for measurements)
+      ma.ff_row_units = (h->mp >= 4 && !getenv("MTJ_NO_MEGA_ROW_UNITS")) || getenv("MTJ_MEGA_ROW_UNITS") ? 1 : 0;
       if (mega_token) {
         ma.amax = h->mega_amax;
         ma.tokens_out = h->tokens;
