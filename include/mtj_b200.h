@@ -77,6 +77,8 @@ typedef struct mtj_config {
 } mtj_config;
 
 const char* mtj_last_error(void);
+/* ABI revision: 3 (2: mtj_config with the tuning fields, mtj_generate, mtj_start_batch / mtj_admit;
+ * 3: top_k in mtj_sample_top_p / mtj_nucleus_filter, mtj_set_top_k). */
 int32_t mtj_version(void);
 
 /* CausalTransformerShard.__init__ (transformer_shard.py:21-45): validates the
